@@ -1,0 +1,162 @@
+/*
+ * klas_b200.h -- C ABI of the B200-native Klas matrix-multiply library.
+ *
+ * Every function here has C linkage, takes plain pointers and sizes, and
+ * returns a klas_status (0 = success).  Unless the name ends in `_host`, all
+ * data pointers are DEVICE pointers on the current CUDA device, the call is
+ * asynchronous on `stream` (a cudaStream_t passed as void*, NULL = the legacy
+ * default stream) and allocates nothing.
+ *
+ * Each entry point names the reference interface (FStarLang/kuiper, paths
+ * relative to that project) whose work it takes over.  The reference's own
+ * C++-linkage names (dist/Klas_*.h) are thin wrappers over these functions:
+ * see include/klas/Klas_*.h.
+ */
+#ifndef KLAS_B200_H
+#define KLAS_B200_H 1
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum klas_status_e {
+    KLAS_OK = 0,
+    KLAS_ERR_INVALID = 1,      /* bad argument (null pointer, bad enum, misaligned) */
+    KLAS_ERR_UNSUPPORTED = 2,  /* legal request this kernel cannot serve (e.g. K % 8 != 0 on the tensor-core path) */
+    KLAS_ERR_CUDA = 3,         /* a CUDA runtime/driver call failed; see klas_b200_last_error() */
+    KLAS_ERR_TIMEOUT = 4,      /* a bounded device-side wait gave up; output is undefined, context still usable */
+    KLAS_ERR_TOO_LARGE = 5     /* size beyond a documented fixed limit */
+} klas_status;
+
+typedef enum klas_dtype_e {
+    KLAS_F32 = 0,
+    KLAS_F64 = 1,
+    KLAS_U32 = 2,
+    KLAS_U64 = 3,
+    KLAS_BF16 = 4,
+    KLAS_F16 = 5
+} klas_dtype;
+
+/* Storage order of the three matrices of a CUDA-core GEMM. */
+typedef enum klas_layout_e {
+    KLAS_RRR = 0,  /* A, B, C row-major */
+    KLAS_CCC = 1   /* A, B, C column-major */
+} klas_layout;
+
+/* Storage order of the B operand of a tensor-core GEMM (A and C/D are row-major). */
+typedef enum klas_b_major_e {
+    KLAS_B_ROW_MAJOR = 0,  /* B is shared x cols, cols contiguous (the reference's layout) */
+    KLAS_B_COL_MAJOR = 1   /* B is stored as cols x shared, shared contiguous ("TN" GEMM) */
+} klas_b_major;
+
+/* Last error message of the calling thread ("" if none). Never NULL. */
+const char *klas_b200_last_error(void);
+
+/* Library ABI version (major * 1000 + minor). */
+int klas_b200_version(void);
+
+/* Number of streaming multiprocessors of the current device (grid sizing aid). */
+int klas_b200_sm_count(void);
+
+/*
+ * CUDA-core GEMM on f32 / f64 / u32 / u64 (bf16 accepted: f32 accumulate, one
+ * rounding at the end).  Integers wrap mod 2^32 / 2^64.
+ *
+ *   alpha == NULL && beta == NULL :  C = A.B            (C is never read)
+ *   otherwise (both non-NULL)     :  C = beta*C + alpha*(A.B)   (C read even if beta == 0)
+ *
+ * alpha/beta point to HOST scalars of type `dtype`.  A is m x k, B is k x n,
+ * C is m x n in `layout`; with batch > 1 the matrices are contiguous pages
+ * [batch][m][k], [batch][k][n], [batch][m][n].  Any m, n, k >= 0 is legal.
+ *
+ * Replaces: Klas_GEMM_SHMem_g_{matmul,gemm}_* (dist/Klas_GEMM_SHMem.h:8-187),
+ * Klas_GEMM_Tiled_* (dist/Klas_GEMM_Tiled.h), Klas_GEMM_BlockTiling1D_*
+ * (dist/Klas_GEMM_BlockTiling1D.h:8-131), Klas_GEMM_BlockTiling2D_g_gemm_*
+ * (dist/Klas_GEMM_BlockTiling2D.h:8-1376), Klas_GEMM_Naive{1,2}_*
+ * (dist/Klas_GEMM_Naive1.h:8-65) and Klas_GEMM_Naive3_* (dist/Klas_GEMM_Naive3.h:8-41).
+ */
+int klas_b200_gemm(int dtype, int layout, uint32_t batch,
+                   uint64_t m, uint64_t n, uint64_t k,
+                   const void *alpha, const void *beta,
+                   const void *A, const void *B, void *C, void *stream);
+
+/*
+ * Tensor-core GEMM (tcgen05 UMMA, fp32 accumulation in tensor memory):
+ *
+ *   D = out_dtype( alpha * (A.B) + beta * C )      if C != NULL
+ *   D = out_dtype( A.B )                           if C == NULL (alpha, beta ignored)
+ *
+ * A: rows x shared row-major, in_dtype (KLAS_BF16 or KLAS_F16).
+ * B: shared x cols, in_dtype, storage order `b_major`.
+ * C: rows x cols row-major, out_dtype, may alias D (in-place accumulate).
+ * D: rows x cols row-major, out_dtype (KLAS_F32, KLAS_F16 or KLAS_BF16).
+ * batch > 1: contiguous pages of A, B, C, D.
+ * Requires shared % 8 == 0, cols % 8 == 0 and 16-byte aligned A, B, C, D.
+ * `status_word`: optional device int (may be NULL) that receives a non-zero
+ * code when a bounded device-side wait gives up.
+ *
+ * Replaces: Klas_GEMM_TensorCore2D_g_gemm_{bf16_f32,f16_f16}_* (dist/Klas_GEMM_TensorCore2D.h:8-1220),
+ * Klas_GEMM_TensorCore2D_To_g_gemm_bf16_f32_bf16_* (dist/Klas_GEMM_TensorCore2D_To.h),
+ * Klas_GEMM_TensorCore_g_gemm_f16_{f16,f32}_* (dist/Klas_GEMM_TensorCore.h:8-85).
+ */
+int klas_b200_gemm_tc(int in_dtype, int out_dtype, int b_major, uint32_t batch,
+                      uint64_t rows, uint64_t shared, uint64_t cols,
+                      const void *A, const void *B, const void *C, void *D,
+                      float alpha, float beta, int *status_word, void *stream);
+
+/*
+ * Reads (and then clears) the current device's tensor-core status word.
+ * Returns KLAS_OK and *site = 0 when no bounded wait has given up since the
+ * last call; otherwise KLAS_ERR_TIMEOUT and *site = the code of the first wait
+ * that gave up.  Synchronises with the default stream; `site` may be NULL.
+ * While the word is non-zero every later klas_b200_gemm_tc launch on that
+ * device drains immediately, so call this after a suspicious result.
+ * No counterpart in the reference (its kernels have no waits that can fail).
+ */
+int klas_b200_gemm_tc_status(int *site);
+
+/*
+ * CSR x dense:  C[rows x cols] = CSR(A)[rows x shared] . B[shared x cols],
+ * B and C row-major, dtype KLAS_F32 or KLAS_U32 (wrapping).  Each row's
+ * products are summed in CSR order starting from 0.  Every row of C is
+ * overwritten (all-zero rows included).  `row_indices` (a permutation of
+ * 0..rows-1 giving the order in which rows are scheduled) may be NULL.
+ * CSR: row_off[0] == 0, monotone, row_off[rows] == nnz, columns < shared.
+ *
+ * Replaces: Klas_SPMM_spmm_{f32,u32}, Klas_SPMM_g_spmm_f32_* (dist/Klas_SPMM.h:15-673).
+ */
+int klas_b200_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32_t nnz,
+                   const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
+                   const uint32_t *row_indices, const void *B, void *C, void *stream);
+
+/*
+ * Host-buffer variants: same semantics, but every data pointer is a HOST
+ * pointer (pinned memory makes the copies asynchronous and faster).  The call
+ * stages inputs into a per-device workspace that grows on demand and is kept
+ * until klas_b200_release_workspace(), runs the kernel, copies the result
+ * back and returns after the result is in host memory.
+ */
+int klas_b200_gemm_host(int dtype, int layout, uint32_t batch,
+                        uint64_t m, uint64_t n, uint64_t k,
+                        const void *alpha, const void *beta,
+                        const void *A, const void *B, void *C);
+
+int klas_b200_gemm_tc_host(int in_dtype, int out_dtype, int b_major, uint32_t batch,
+                           uint64_t rows, uint64_t shared, uint64_t cols,
+                           const void *A, const void *B, const void *C, void *D,
+                           float alpha, float beta);
+
+int klas_b200_spmm_host(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32_t nnz,
+                        const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
+                        const uint32_t *row_indices, const void *B, void *C);
+
+/* Frees the calling device's host-variant workspace. */
+int klas_b200_release_workspace(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KLAS_B200_H */

@@ -1,0 +1,64 @@
+"""ctypes binding of libklas_b200.so.  There is no fallback: if the library is
+missing or does not export a symbol of include/klas_b200.h, importing fails."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libklas_b200.so"
+
+# klas_status / klas_dtype / klas_layout / klas_b_major of include/klas_b200.h
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE = range(6)
+F32, F64, U32, U64, BF16, F16 = range(6)
+RRR, CCC = 0, 1
+B_ROW_MAJOR, B_COL_MAJOR = 0, 1
+
+_u32, _u64, _vp, _int, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int, C.c_float
+
+# name -> (restype, argtypes): every function declared in include/klas_b200.h
+SIGNATURES = {
+    "klas_b200_last_error": (C.c_char_p, []),
+    "klas_b200_version": (_int, []),
+    "klas_b200_sm_count": (_int, []),
+    "klas_b200_gemm": (_int, [_int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "klas_b200_gemm_tc": (_int, [_int, _int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp,
+                                  _f32, _f32, _vp, _vp]),
+    "klas_b200_gemm_tc_status": (_int, [C.POINTER(_int)]),
+    "klas_b200_spmm": (_int, [_int, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "klas_b200_gemm_host": (_int, [_int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _vp]),
+    "klas_b200_gemm_tc_host": (_int, [_int, _int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp,
+                                       _f32, _f32]),
+    "klas_b200_spmm_host": (_int, [_int, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "klas_b200_release_workspace": (_int, []),
+}
+
+_lib = None
+
+
+class KlasError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__("klas status %d: %s" % (status, message))
+        self.status = status
+
+
+def load() -> C.CDLL:
+    """Loads the shared library once and types every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            "%s not found: build it with `python -m kuiper_b200.build` (needs nvcc); "
+            "there is no CPU or PyTorch fallback" % LIB_PATH)
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is missing
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise KlasError(status, load().klas_b200_last_error().decode())

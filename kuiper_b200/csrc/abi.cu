@@ -1,0 +1,224 @@
+// extern "C" entry points of libklas_b200.so (declared in include/klas_b200.h),
+// plus the small amount of per-thread / per-device state behind them.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "klas_internal.h"
+
+namespace klas {
+
+static thread_local char tls_error[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tls_error, sizeof tls_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+void clear_error() { tls_error[0] = '\0'; }
+
+constexpr int MAX_DEVICES = 64;
+static std::mutex g_mutex;
+static DeviceInfo g_info[MAX_DEVICES];
+
+int device_info(DeviceInfo *out) {
+    int dev = 0;
+    KLAS_TRY_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return fail(KLAS_ERR_INVALID, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceInfo &d = g_info[dev];
+    if (d.device != dev) {
+        KLAS_TRY_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        KLAS_TRY_CUDA(cudaDeviceGetAttribute(&d.l2_bytes, cudaDevAttrL2CacheSize, dev));
+        KLAS_TRY_CUDA(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        KLAS_TRY_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+        KLAS_TRY_CUDA(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+        d.device = dev;
+    }
+    *out = d;
+    return KLAS_OK;
+}
+
+// ------------------------------------------------------------------ workspace
+constexpr int WS_SLOTS = 8;
+struct Workspace {
+    void *ptr[WS_SLOTS] = {};
+    size_t cap[WS_SLOTS] = {};
+};
+static Workspace g_ws[MAX_DEVICES];
+
+int workspace_reserve(int slot, size_t bytes, void **ptr) {
+    int dev = 0;
+    KLAS_TRY_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES || slot < 0 || slot >= WS_SLOTS)
+        return fail(KLAS_ERR_INVALID, "workspace: bad device or slot");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Workspace &w = g_ws[dev];
+    if (bytes == 0) bytes = 16;
+    if (w.cap[slot] < bytes) {
+        if (w.ptr[slot]) KLAS_TRY_CUDA(cudaFree(w.ptr[slot]));
+        w.ptr[slot] = nullptr;
+        w.cap[slot] = 0;
+        KLAS_TRY_CUDA(cudaMalloc(&w.ptr[slot], bytes));
+        w.cap[slot] = bytes;
+    }
+    *ptr = w.ptr[slot];
+    return KLAS_OK;
+}
+
+int workspace_release() {
+    int dev = 0;
+    KLAS_TRY_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return fail(KLAS_ERR_INVALID, "workspace: bad device");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Workspace &w = g_ws[dev];
+    for (int s = 0; s < WS_SLOTS; ++s) {
+        if (w.ptr[s]) KLAS_TRY_CUDA(cudaFree(w.ptr[s]));
+        w.ptr[s] = nullptr;
+        w.cap[s] = 0;
+    }
+    return KLAS_OK;
+}
+
+int umma_read_status(int *value);
+int umma_clear_status();
+
+// Stages `bytes` from host pointer `src` into workspace slot `slot`.
+static int stage_in(int slot, const void *src, size_t bytes, cudaStream_t s, void **dptr) {
+    if (int rc = workspace_reserve(slot, bytes, dptr)) return rc;
+    if (bytes && src) KLAS_TRY_CUDA(cudaMemcpyAsync(*dptr, src, bytes, cudaMemcpyHostToDevice, s));
+    return KLAS_OK;
+}
+
+}  // namespace klas
+
+using namespace klas;
+
+extern "C" {
+
+const char *klas_b200_last_error(void) { return tls_error; }
+
+int klas_b200_version(void) { return 1000; }
+
+int klas_b200_sm_count(void) {
+    DeviceInfo info;
+    if (device_info(&info)) return 0;
+    return info.sm_count;
+}
+
+int klas_b200_gemm(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t n, uint64_t k,
+                   const void *alpha, const void *beta, const void *A, const void *B, void *C,
+                   void *stream) {
+    clear_error();
+    return launch_gemm_simt(dtype, layout, batch, m, n, k, alpha, beta, A, B, C,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int klas_b200_gemm_tc(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                      uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
+                      void *D, float alpha, float beta, int *status_word, void *stream) {
+    clear_error();
+    return launch_gemm_umma(in_dtype, out_dtype, b_major, batch, rows, shared, cols, A, B, C, D,
+                            alpha, beta, status_word, static_cast<cudaStream_t>(stream));
+}
+
+int klas_b200_gemm_tc_status(int *site) {
+    clear_error();
+    int v = 0;
+    if (int rc = umma_read_status(&v)) return rc;
+    if (site) *site = v;
+    if (v == 0) return KLAS_OK;
+    if (int rc = umma_clear_status()) return rc;
+    return fail(KLAS_ERR_TIMEOUT, "gemm_tc: a device-side wait gave up at site 0x%x", v);
+}
+
+int klas_b200_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32_t nnz,
+                   const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
+                   const uint32_t *row_indices, const void *B, void *C, void *stream) {
+    clear_error();
+    return launch_spmm(dtype, rows, shared, cols, nnz, elems, col_ind, row_off, row_indices, B, C,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int klas_b200_gemm_host(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t n, uint64_t k,
+                        const void *alpha, const void *beta, const void *A, const void *B,
+                        void *C) {
+    clear_error();
+    const size_t es = dtype_size(dtype);
+    if (es == 0) return fail(KLAS_ERR_INVALID, "gemm_host: bad dtype");
+    const size_t a_bytes = size_t(batch) * m * k * es, b_bytes = size_t(batch) * k * n * es,
+                 c_bytes = size_t(batch) * m * n * es;
+    if (c_bytes == 0) return KLAS_OK;
+    if (!C) return fail(KLAS_ERR_INVALID, "gemm_host: null C");
+    cudaStream_t s = nullptr;
+    void *dA, *dB, *dC;
+    if (int rc = stage_in(0, A, a_bytes, s, &dA)) return rc;
+    if (int rc = stage_in(1, B, b_bytes, s, &dB)) return rc;
+    if (int rc = stage_in(2, alpha ? C : nullptr, c_bytes, s, &dC)) return rc;
+    if (int rc = launch_gemm_simt(dtype, layout, batch, m, n, k, alpha, beta, dA, dB, dC, s)) return rc;
+    KLAS_TRY_CUDA(cudaMemcpyAsync(C, dC, c_bytes, cudaMemcpyDeviceToHost, s));
+    KLAS_TRY_CUDA(cudaStreamSynchronize(s));
+    return KLAS_OK;
+}
+
+int klas_b200_gemm_tc_host(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                           uint64_t shared, uint64_t cols, const void *A, const void *B,
+                           const void *C, void *D, float alpha, float beta) {
+    clear_error();
+    const size_t is = dtype_size(in_dtype), os = dtype_size(out_dtype);
+    if (is == 0 || os == 0) return fail(KLAS_ERR_INVALID, "gemm_tc_host: bad dtype");
+    const size_t a_bytes = size_t(batch) * rows * shared * is,
+                 b_bytes = size_t(batch) * shared * cols * is,
+                 d_bytes = size_t(batch) * rows * cols * os;
+    if (d_bytes == 0) return KLAS_OK;
+    if (!D) return fail(KLAS_ERR_INVALID, "gemm_tc_host: null D");
+    cudaStream_t s = nullptr;
+    void *dA, *dB, *dC = nullptr, *dD;
+    if (int rc = stage_in(0, A, a_bytes, s, &dA)) return rc;
+    if (int rc = stage_in(1, B, b_bytes, s, &dB)) return rc;
+    if (C)
+        if (int rc = stage_in(2, C, d_bytes, s, &dC)) return rc;
+    if (int rc = workspace_reserve(3, d_bytes, &dD)) return rc;
+    if (int rc = launch_gemm_umma(in_dtype, out_dtype, b_major, batch, rows, shared, cols, dA, dB,
+                                  dC, dD, alpha, beta, nullptr, s))
+        return rc;
+    KLAS_TRY_CUDA(cudaMemcpyAsync(D, dD, d_bytes, cudaMemcpyDeviceToHost, s));
+    KLAS_TRY_CUDA(cudaStreamSynchronize(s));
+    return klas_b200_gemm_tc_status(nullptr);
+}
+
+int klas_b200_spmm_host(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32_t nnz,
+                        const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
+                        const uint32_t *row_indices, const void *B, void *C) {
+    clear_error();
+    if (dtype != KLAS_F32 && dtype != KLAS_U32) return fail(KLAS_ERR_INVALID, "spmm_host: bad dtype");
+    const size_t c_bytes = size_t(rows) * cols * 4;
+    if (c_bytes == 0) return KLAS_OK;
+    if (!C || !row_off) return fail(KLAS_ERR_INVALID, "spmm_host: null C or row_off");
+    cudaStream_t s = nullptr;
+    void *dE, *dCi, *dRo, *dRi = nullptr, *dB, *dC;
+    if (int rc = stage_in(0, elems, size_t(nnz) * 4, s, &dE)) return rc;
+    if (int rc = stage_in(1, col_ind, size_t(nnz) * 4, s, &dCi)) return rc;
+    if (int rc = stage_in(2, row_off, (size_t(rows) + 1) * 4, s, &dRo)) return rc;
+    if (row_indices)
+        if (int rc = stage_in(3, row_indices, size_t(rows) * 4, s, &dRi)) return rc;
+    if (int rc = stage_in(4, B, size_t(shared) * cols * 4, s, &dB)) return rc;
+    if (int rc = workspace_reserve(5, c_bytes, &dC)) return rc;
+    if (int rc = launch_spmm(dtype, rows, shared, cols, nnz, dE, static_cast<uint32_t *>(dCi),
+                             static_cast<uint32_t *>(dRo), static_cast<uint32_t *>(dRi), dB, dC, s))
+        return rc;
+    KLAS_TRY_CUDA(cudaMemcpyAsync(C, dC, c_bytes, cudaMemcpyDeviceToHost, s));
+    KLAS_TRY_CUDA(cudaStreamSynchronize(s));
+    return KLAS_OK;
+}
+
+int klas_b200_release_workspace(void) {
+    clear_error();
+    return workspace_release();
+}
+
+}  // extern "C"

@@ -1,0 +1,335 @@
+// CUDA-core GEMM for f32 / f64 / u32 / u64 (and bf16 storage with f32 math):
+//   C = A.B            or            C = beta*C + alpha*(A.B)
+// B200 has no tensor-core path for fp64 or for wrapping 32/64-bit integers, so
+// these run as a register-blocked, shared-memory-staged kernel:
+//   * a CTA of 256 threads owns a BM x BN tile of C and walks K in BK steps;
+//   * global -> register -> shared staging is double buffered (the loads of
+//     step i+1 are in flight while step i is multiplied);
+//   * A is stored transposed in shared memory, and each thread's TM x TN
+//     register tile is split into 16-byte groups that are BM/ (TM/VEC) apart,
+//     so every shared read is a conflict-free 128-bit access;
+//   * each output element is accumulated strictly in ascending k, starting
+//     from 0 (the order of the reference's exact spec,
+//     src/lib/kernel/gemm/Kuiper.Kernel.GEMM.BlockTiling2D.fsti:18-28);
+//   * integer types wrap mod 2^32 / 2^64 (src/lib/kuiper/types/Kuiper.Scalars.fst:30-47).
+// A "fast" instantiation (sizes multiples of the tile, 16-byte aligned rows)
+// uses unpredicated vector loads; every other shape takes the predicated one.
+//
+// Takes over the work of dist/Klas_GEMM_SHMem.cu:9-72, dist/Klas_GEMM_Tiled.cu:8-54,
+// dist/Klas_GEMM_BlockTiling1D.cu:8-69, dist/Klas_GEMM_BlockTiling2D.cu:9-214 and
+// dist/Klas_GEMM_Naive{1,2,3}.cu.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "klas_internal.h"
+
+namespace klas {
+namespace simt {
+
+constexpr int THREADS = 256;
+constexpr int TX = 16;  // threads along N
+constexpr int TY = 16;  // threads along M
+
+template <typename S, typename T>
+struct Conv {
+    static __device__ __forceinline__ T load(S v) { return static_cast<T>(v); }
+    static __device__ __forceinline__ S store(T v) { return static_cast<S>(v); }
+};
+template <>
+struct Conv<__nv_bfloat16, float> {
+    static __device__ __forceinline__ float load(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 store(float v) {
+        return __float2bfloat16_rn(v);
+    }
+};
+
+template <typename T>
+struct Args {
+    const void *A;
+    const void *B;
+    void *C;
+    uint64_t M, N, K;
+    uint64_t tiles_m, tiles_n;
+    T alpha, beta;
+    int scaled;  // 0: C = A.B   1: C = beta*C + alpha*A.B
+};
+
+template <typename T, int N>
+struct alignas(16) Vec {
+    T v[N];
+};
+
+// S = storage type in global memory, T = arithmetic type.
+template <typename S, typename T, int BM, int BN, int BK, bool FAST>
+__global__ void __launch_bounds__(THREADS, 2) gemm_simt_kernel(const Args<T> a) {
+    constexpr int VEC = 16 / sizeof(T);
+    constexpr int TM = BM / TY;
+    constexpr int TN = BN / TX;
+    static_assert(TM % VEC == 0 && TN % VEC == 0, "thread tile must be whole 16-byte groups");
+    constexpr int GM = TM / VEC;  // 16-byte groups per thread along M
+    constexpr int GN = TN / VEC;
+    constexpr int PAD = VEC;      // keeps rows 16-byte aligned
+    constexpr int A_VECS = BM * BK / VEC;
+    constexpr int B_VECS = BK * BN / VEC;
+    constexpr int A_PER_THREAD = (A_VECS + THREADS - 1) / THREADS;
+    constexpr int B_PER_THREAD = (B_VECS + THREADS - 1) / THREADS;
+    static_assert(BK % VEC == 0 && BN % VEC == 0, "tile not vectorisable");
+
+    __shared__ __align__(16) T As[2][BK][BM + PAD];  // transposed: [k][m]
+    __shared__ __align__(16) T Bs[2][BK][BN + PAD];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % TX;
+    const int ty = tid / TX;
+
+    const uint64_t per_batch = a.tiles_m * a.tiles_n;
+    const uint64_t bidx = blockIdx.x / per_batch;
+    const uint64_t rem = blockIdx.x - bidx * per_batch;
+    const uint64_t m0 = (rem / a.tiles_n) * BM;
+    const uint64_t n0 = (rem % a.tiles_n) * BN;
+
+    const S *__restrict__ A = static_cast<const S *>(a.A) + bidx * a.M * a.K;
+    const S *__restrict__ B = static_cast<const S *>(a.B) + bidx * a.K * a.N;
+    S *C = static_cast<S *>(a.C) + bidx * a.M * a.N;
+
+    T acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = T(0);
+
+    Vec<T, VEC> ra[A_PER_THREAD], rb[B_PER_THREAD];
+
+    auto load_global = [&](uint64_t k0) {
+#pragma unroll
+        for (int i = 0; i < A_PER_THREAD; ++i) {
+            const int idx = tid + i * THREADS;
+            if (A_VECS % THREADS == 0 || idx < A_VECS) {
+                const int r = idx / (BK / VEC);
+                const int kv = (idx % (BK / VEC)) * VEC;
+                if constexpr (FAST) {
+                    ra[i] = *reinterpret_cast<const Vec<T, VEC> *>(
+                        reinterpret_cast<const T *>(A) + (m0 + r) * a.K + k0 + kv);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) {
+                        const uint64_t gr = m0 + r, gk = k0 + kv + e;
+                        ra[i].v[e] = (gr < a.M && gk < a.K) ? Conv<S, T>::load(A[gr * a.K + gk]) : T(0);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER_THREAD; ++i) {
+            const int idx = tid + i * THREADS;
+            if (B_VECS % THREADS == 0 || idx < B_VECS) {
+                const int kr = idx / (BN / VEC);
+                const int nv = (idx % (BN / VEC)) * VEC;
+                if constexpr (FAST) {
+                    rb[i] = *reinterpret_cast<const Vec<T, VEC> *>(
+                        reinterpret_cast<const T *>(B) + (k0 + kr) * a.N + n0 + nv);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) {
+                        const uint64_t gk = k0 + kr, gc = n0 + nv + e;
+                        rb[i].v[e] = (gk < a.K && gc < a.N) ? Conv<S, T>::load(B[gk * a.N + gc]) : T(0);
+                    }
+                }
+            }
+        }
+    };
+
+    auto store_shared = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < A_PER_THREAD; ++i) {
+            const int idx = tid + i * THREADS;
+            if (A_VECS % THREADS == 0 || idx < A_VECS) {
+                const int r = idx / (BK / VEC);
+                const int kv = (idx % (BK / VEC)) * VEC;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) As[buf][kv + e][r] = ra[i].v[e];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER_THREAD; ++i) {
+            const int idx = tid + i * THREADS;
+            if (B_VECS % THREADS == 0 || idx < B_VECS) {
+                const int kr = idx / (BN / VEC);
+                const int nv = (idx % (BN / VEC)) * VEC;
+                *reinterpret_cast<Vec<T, VEC> *>(&Bs[buf][kr][nv]) = rb[i];
+            }
+        }
+    };
+
+    const uint64_t num_kb = (a.K + BK - 1) / BK;
+    if (num_kb > 0) {
+        load_global(0);
+        store_shared(0);
+    }
+    __syncthreads();
+
+    for (uint64_t kb = 0; kb < num_kb; ++kb) {
+        const int buf = int(kb & 1);
+        const bool more = kb + 1 < num_kb;
+        if (more) load_global((kb + 1) * BK);
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            Vec<T, VEC> av[GM], bv[GN];
+#pragma unroll
+            for (int g = 0; g < GM; ++g)
+                av[g] = *reinterpret_cast<const Vec<T, VEC> *>(&As[buf][k][g * (BM / GM) + ty * VEC]);
+#pragma unroll
+            for (int g = 0; g < GN; ++g)
+                bv[g] = *reinterpret_cast<const Vec<T, VEC> *>(&Bs[buf][k][g * (BN / GN) + tx * VEC]);
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j)
+                    acc[i][j] += av[i / VEC].v[i % VEC] * bv[j / VEC].v[j % VEC];
+        }
+        if (more) store_shared(buf ^ 1);
+        __syncthreads();
+    }
+
+    // Epilogue: thread-tile row i lives at m0 + (i/VEC)*(BM/GM) + ty*VEC + i%VEC.
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const uint64_t r = m0 + (i / VEC) * (BM / GM) + ty * VEC + (i % VEC);
+#pragma unroll
+        for (int g = 0; g < GN; ++g) {
+            const uint64_t c = n0 + g * (BN / GN) + tx * VEC;
+            if constexpr (FAST) {
+                Vec<T, VEC> out;
+                T *cp = reinterpret_cast<T *>(C) + r * a.N + c;
+                if (a.scaled) {
+                    const Vec<T, VEC> old = *reinterpret_cast<const Vec<T, VEC> *>(cp);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e)
+                        out.v[e] = a.beta * old.v[e] + a.alpha * acc[i][g * VEC + e];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) out.v[e] = acc[i][g * VEC + e];
+                }
+                *reinterpret_cast<Vec<T, VEC> *>(cp) = out;
+            } else {
+                if (r < a.M) {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) {
+                        if (c + e < a.N) {
+                            S *cp = C + r * a.N + c + e;
+                            T val = acc[i][g * VEC + e];
+                            if (a.scaled) val = a.beta * Conv<S, T>::load(*cp) + a.alpha * val;
+                            *cp = Conv<S, T>::store(val);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <typename S, typename T, int BM, int BN, int BK>
+static int launch_cfg(uint32_t batch, uint64_t m, uint64_t n, uint64_t k, T alpha, T beta,
+                      int scaled, const void *A, const void *B, void *C, cudaStream_t stream) {
+    Args<T> a;
+    a.A = A;
+    a.B = B;
+    a.C = C;
+    a.M = m;
+    a.N = n;
+    a.K = k;
+    a.tiles_m = (m + BM - 1) / BM;
+    a.tiles_n = (n + BN - 1) / BN;
+    a.alpha = alpha;
+    a.beta = beta;
+    a.scaled = scaled;
+    const uint64_t blocks = a.tiles_m * a.tiles_n * batch;
+    if (blocks > 0x7fffffffull) return fail(KLAS_ERR_TOO_LARGE, "gemm: too many tiles for one grid");
+    constexpr int VEC = 16 / sizeof(T);
+    const bool same_storage = sizeof(S) == sizeof(T);
+    const bool fast = same_storage && m % BM == 0 && n % BN == 0 && k % BK == 0 && k > 0 &&
+                      n % VEC == 0 && k % VEC == 0 &&
+                      ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+                        reinterpret_cast<uintptr_t>(C)) & 15u) == 0;
+    if constexpr (sizeof(S) == sizeof(T)) {
+        if (fast) {
+            gemm_simt_kernel<S, T, BM, BN, BK, true><<<unsigned(blocks), THREADS, 0, stream>>>(a);
+            return check_cuda(cudaGetLastError(), "gemm_simt_kernel launch");
+        }
+    }
+    gemm_simt_kernel<S, T, BM, BN, BK, false><<<unsigned(blocks), THREADS, 0, stream>>>(a);
+    return check_cuda(cudaGetLastError(), "gemm_simt_kernel launch");
+}
+
+template <typename S, typename T>
+static int launch_type(uint32_t batch, uint64_t m, uint64_t n, uint64_t k, T alpha, T beta,
+                       int scaled, const void *A, const void *B, void *C, int sm_count,
+                       cudaStream_t stream) {
+    if constexpr (sizeof(T) == 4) {
+        // Large tiles once they fill the machine; small ones otherwise.
+        const uint64_t big_tiles = ((m + 127) / 128) * ((n + 127) / 128) * batch;
+        if (big_tiles >= uint64_t(sm_count))
+            return launch_cfg<S, T, 128, 128, 16>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
+        return launch_cfg<S, T, 64, 64, 16>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
+    } else {
+        const uint64_t big_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
+        if (big_tiles >= uint64_t(sm_count))
+            return launch_cfg<S, T, 128, 64, 8>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
+        return launch_cfg<S, T, 64, 32, 8>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
+    }
+}
+
+}  // namespace simt
+
+int launch_gemm_simt(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t n, uint64_t k,
+                     const void *alpha, const void *beta, const void *A, const void *B, void *C,
+                     cudaStream_t stream) {
+    if (layout != KLAS_RRR && layout != KLAS_CCC) return fail(KLAS_ERR_INVALID, "gemm: bad layout");
+    if ((alpha == nullptr) != (beta == nullptr))
+        return fail(KLAS_ERR_INVALID, "gemm: alpha and beta must both be NULL or both be set");
+    if (m == 0 || n == 0 || batch == 0) return KLAS_OK;
+    if (!C || (k > 0 && (!A || !B))) return fail(KLAS_ERR_INVALID, "gemm: null matrix pointer");
+    if (layout == KLAS_CCC) {
+        // Column-major C = A.B is the row-major product C^T = B^T.A^T on the same buffers.
+        const void *t = A;
+        A = B;
+        B = t;
+        const uint64_t tm = m;
+        m = n;
+        n = tm;
+    }
+    DeviceInfo info;
+    if (int rc = device_info(&info)) return rc;
+    const int scaled = alpha != nullptr;
+    switch (dtype) {
+        case KLAS_F32:
+            return simt::launch_type<float, float>(
+                batch, m, n, k, scaled ? *static_cast<const float *>(alpha) : 1.0f,
+                scaled ? *static_cast<const float *>(beta) : 0.0f, scaled, A, B, C, info.sm_count, stream);
+        case KLAS_F64:
+            return simt::launch_type<double, double>(
+                batch, m, n, k, scaled ? *static_cast<const double *>(alpha) : 1.0,
+                scaled ? *static_cast<const double *>(beta) : 0.0, scaled, A, B, C, info.sm_count, stream);
+        case KLAS_U32:
+            return simt::launch_type<uint32_t, uint32_t>(
+                batch, m, n, k, scaled ? *static_cast<const uint32_t *>(alpha) : 1u,
+                scaled ? *static_cast<const uint32_t *>(beta) : 0u, scaled, A, B, C, info.sm_count, stream);
+        case KLAS_U64:
+            return simt::launch_type<uint64_t, uint64_t>(
+                batch, m, n, k, scaled ? *static_cast<const uint64_t *>(alpha) : 1ull,
+                scaled ? *static_cast<const uint64_t *>(beta) : 0ull, scaled, A, B, C, info.sm_count, stream);
+        case KLAS_BF16: {
+            float fa = 1.0f, fb = 0.0f;
+            if (scaled) {
+                fa = __bfloat162float(*static_cast<const __nv_bfloat16 *>(alpha));
+                fb = __bfloat162float(*static_cast<const __nv_bfloat16 *>(beta));
+            }
+            return simt::launch_type<__nv_bfloat16, float>(batch, m, n, k, fa, fb, scaled, A, B, C,
+                                                           info.sm_count, stream);
+        }
+        default:
+            return fail(KLAS_ERR_INVALID, "gemm: dtype must be F32, F64, U32, U64 or BF16");
+    }
+}
+
+}  // namespace klas

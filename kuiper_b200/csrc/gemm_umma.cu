@@ -1,0 +1,502 @@
+// Tensor-core GEMM for sm_100a: D = out( alpha * A.B + beta * C ).
+//
+// One persistent, warp-specialised CTA per SM walks a rasterised list of
+// 128 x 256 output tiles:
+//   warp 0      TMA producer: streams 128x64 A tiles and 256x64 B tiles (bf16/f16,
+//               128-byte swizzle) through a 4-stage shared-memory ring;
+//   warp 1      owns tensor memory and issues tcgen05.mma (M=128, N=256, K=16) from
+//               one thread; the fp32 accumulator lives in TMEM, double-buffered
+//               (2 x 256 columns) so tile i+1's main loop overlaps tile i's epilogue;
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, apply
+//               alpha/beta, convert, and store to global memory.
+// All hand-offs are mbarriers; every wait is bounded in time and a wait that
+// gives up raises a status word and makes all roles drain and return.
+//
+// Takes over the work of the reference's wmma kernels, e.g.
+// dist/Klas_GEMM_TensorCore2D.cu:16797-16936 (bf16 -> f32, 128x128x32 tiles),
+// dist/Klas_GEMM_TensorCore2D_To.cu:9-176 (alpha/beta, bf16 out) and
+// dist/Klas_GEMM_TensorCore.cu:9-115 (C += A.B).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "klas_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace klas {
+namespace umma {
+
+constexpr uint32_t BM = 128;
+constexpr uint32_t BN = 256;
+constexpr uint32_t BK = 64;  // 64 x 2 bytes = one 128-byte swizzle row
+constexpr uint32_t UMMA_K = 16;
+constexpr uint32_t STAGES = 4;
+constexpr uint32_t A_STAGE_BYTES = BM * BK * 2;
+constexpr uint32_t B_STAGE_BYTES = BN * BK * 2;
+constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr uint32_t B_CHUNK_BYTES = 64 * BK * 2;  // one 64-column slab of a row-major B tile
+constexpr uint32_t ACC_STAGES = 2;
+constexpr uint32_t TMEM_COLS = ACC_STAGES * BN;  // 512 = all of tensor memory
+constexpr uint32_t NUM_THREADS = 192;
+constexpr uint32_t NUM_EPI_WARPS = 4;
+constexpr uint32_t BARRIER_BYTES = 256;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;  // + alignment slack
+constexpr uint32_t RASTER_GROUP = 8;  // tile columns swept together for L2 reuse
+constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
+
+// First failing wait of the most recent launches on this device (0 = none).
+__device__ int g_umma_status;
+
+struct Params {
+    const void *C;
+    void *D;
+    uint32_t M, N, K, batch;
+    uint32_t tiles_m, tiles_n, num_tiles, num_kb;
+    float alpha, beta;
+    uint32_t idesc;
+    uint32_t b_row_major;  // 1: B is K x N (N contiguous) -> MN-major operand
+    int *status;           // optional caller-visible copy of the status word
+};
+
+enum WaitSite : int {
+    SITE_PRODUCER_EMPTY = 0x11,
+    SITE_MMA_FULL = 0x21,
+    SITE_MMA_TMEM_EMPTY = 0x22,
+    SITE_EPI_TMEM_FULL = 0x31,
+};
+
+struct Ctl {
+    volatile int *abort_flag;  // shared memory, per CTA
+    int *user_status;
+};
+
+// Spins on an mbarrier phase for at most WAIT_LIMIT_NS.  On give-up records
+// `site` in the status words and returns false; also returns false early when
+// another role of this CTA (or another CTA) has already given up.
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const Ctl &ctl,
+                                             int site) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 0x3F) == 0) {
+            if (*ctl.abort_flag != 0) return false;
+            if (*reinterpret_cast<volatile int *>(&g_umma_status) != 0) {
+                *ctl.abort_flag = 1;
+                return false;
+            }
+            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *ctl.abort_flag = 1;
+                atomicCAS(&g_umma_status, 0, site);
+                if (ctl.user_status) atomicCAS(ctl.user_status, 0, site);
+                __threadfence();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void decode_tile(uint32_t t, const Params &p, uint32_t &b, uint32_t &tm,
+                                            uint32_t &tn) {
+    const uint32_t per_batch = p.tiles_m * p.tiles_n;
+    b = t / per_batch;
+    const uint32_t r = t - b * per_batch;
+    const uint32_t group_tiles = RASTER_GROUP * p.tiles_m;
+    const uint32_t g = r / group_tiles;
+    const uint32_t first_n = g * RASTER_GROUP;
+    const uint32_t width = min(RASTER_GROUP, p.tiles_n - first_n);
+    const uint32_t in = r - g * group_tiles;
+    tm = in / width;
+    tn = first_n + in % width;
+}
+
+template <typename T>
+struct OutTraits;
+template <>
+struct OutTraits<float> {
+    static __device__ __forceinline__ float to_f32(float v) { return v; }
+    static __device__ __forceinline__ float from_f32(float v) { return v; }
+};
+template <>
+struct OutTraits<__half> {
+    static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <>
+struct OutTraits<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) {
+        return __bfloat162float(v);
+    }
+    static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) {
+        return __float2bfloat16_rn(v);
+    }
+};
+
+// Writes 32 consecutive columns of one output row (`acc` = this lane's slice of
+// the accumulator) with 16-byte accesses.  `ncols_left` = columns of the matrix
+// remaining from the first of the 32 (a multiple of 8 by the entry point's contract).
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT *__restrict__ drow,
+                                                const OutT *__restrict__ crow, float alpha,
+                                                float beta, uint32_t ncols_left) {
+    constexpr uint32_t VEC = 16 / sizeof(OutT);  // elements per 16-byte access
+#pragma unroll
+    for (uint32_t v0 = 0; v0 < 32; v0 += VEC) {
+        if (v0 < ncols_left) {
+            union {
+                uint4 raw;
+                OutT e[VEC];
+            } out, cin;
+            if (crow != nullptr) {
+                cin.raw = *reinterpret_cast<const uint4 *>(crow + v0);
+#pragma unroll
+                for (uint32_t j = 0; j < VEC; ++j) {
+                    const float a = __uint_as_float(acc[v0 + j]);
+                    out.e[j] = OutTraits<OutT>::from_f32(
+                        fmaf(alpha, a, beta * OutTraits<OutT>::to_f32(cin.e[j])));
+                }
+            } else {
+#pragma unroll
+                for (uint32_t j = 0; j < VEC; ++j)
+                    out.e[j] = OutTraits<OutT>::from_f32(__uint_as_float(acc[v0 + j]));
+            }
+            *reinterpret_cast<uint4 *>(drow + v0) = out.raw;
+        }
+    }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a,
+                     const __grid_constant__ CUtensorMap tm_b, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzled tiles need 1024-byte aligned bases.
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t *smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+
+    uint8_t *bar_region = smem + STAGES * STAGE_BYTES;
+    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+    // layout: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag
+    auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + ACC_STAGES + a); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_region + 8u * (2 * STAGES + 2 * ACC_STAGES));
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const Ctl ctl{abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (uint32_t a = 0; a < ACC_STAGES; ++a) {
+            ptx::mbar_init(tfull_bar(a), 1);
+            ptx::mbar_init(tempty_bar(a), NUM_EPI_WARPS);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == 0 && lane == 0 && p.num_kb > 0) {
+        ptx::prefetch_tensormap(&tm_a);
+        ptx::prefetch_tensormap(&tm_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+            uint32_t b, tm, tn;
+            decode_tile(t, p, b, tm, tn);
+            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                ok = bounded_wait(empty_bar(stage), phase ^ 1u, ctl, SITE_PRODUCER_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+                    ptx::tma_load_3d(a_dst, &tm_a, full_bar(stage), int32_t(kb * BK),
+                                     int32_t(tm * BM), int32_t(b));
+                    if (p.b_row_major) {
+#pragma unroll
+                        for (uint32_t j = 0; j < BN / 64; ++j)
+                            ptx::tma_load_3d(b_dst + j * B_CHUNK_BYTES, &tm_b, full_bar(stage),
+                                             int32_t(tn * BN + j * 64), int32_t(kb * BK),
+                                             int32_t(b));
+                    } else {
+                        ptx::tma_load_3d(b_dst, &tm_b, full_bar(stage), int32_t(kb * BK),
+                                         int32_t(tn * BN), int32_t(b));
+                    }
+                }
+                __syncwarp();
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        // K-major operand: 8-row groups 1024 bytes apart; a K step of 16 elements = 32 bytes.
+        // MN-major B: 64-column slabs 8192 bytes apart (leading), 8-row K groups 1024 bytes
+        // apart (stride); a K step of 16 rows = 2048 bytes.
+        const uint64_t a_desc_base = ptx::umma_desc_base_sw128(16, 1024);
+        const uint64_t b_desc_base = p.b_row_major ? ptx::umma_desc_base_sw128(B_CHUNK_BYTES, 1024)
+                                                   : ptx::umma_desc_base_sw128(16, 1024);
+        const uint32_t b_kstep = p.b_row_major ? UMMA_K * 128u : UMMA_K * 2u;
+        uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; ok && p.num_kb > 0 && t < p.num_tiles; t += gridDim.x) {
+            ok = bounded_wait(tempty_bar(acc), acc_phase ^ 1u, ctl, SITE_MMA_TMEM_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                ok = bounded_wait(full_bar(stage), phase, ctl, SITE_MMA_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+                    for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t a_desc =
+                            ptx::umma_desc_at(a_desc_base, a_addr + kk * UMMA_K * 2u);
+                        const uint64_t b_desc = ptx::umma_desc_at(b_desc_base, b_addr + kk * b_kstep);
+                        ptx::umma_f16_ss(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    ptx::umma_commit(empty_bar(stage));  // frees the smem stage when the MMAs retire
+                    if (kb + 1 == p.num_kb) ptx::umma_commit(tfull_bar(acc));
+                }
+                __syncwarp();
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (++acc == ACC_STAGES) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+        OutT *const D = static_cast<OutT *>(p.D);
+        const OutT *const C = static_cast<const OutT *>(p.C);
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+            uint32_t b, tm, tn;
+            decode_tile(t, p, b, tm, tn);
+            if (p.num_kb > 0) {
+                ok = bounded_wait(tfull_bar(acc), acc_phase, ctl, SITE_EPI_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+            }
+            const uint32_t row = tm * BM + quad * 32u + lane;
+            const uint32_t col0 = tn * BN;
+            const size_t row_off = (size_t(b) * p.M + row) * size_t(p.N);
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                if (p.num_kb > 0) {
+                    ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + acc * BN + c * 32u, v);
+                    ptx::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j) v[j] = 0u;
+                }
+                const uint32_t col = col0 + c * 32u;
+                if (row < p.M && col < p.N) {
+                    store_row_chunk<OutT>(v, D + row_off + col, C ? C + row_off + col : nullptr,
+                                          p.alpha, p.beta, p.N - col);
+                }
+            }
+            if (p.num_kb > 0) {
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+                if (++acc == ACC_STAGES) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        if (*abort_flag != 0) {
+            // A role gave up: let copies and MMAs already in flight land before the
+            // tensor memory and this CTA's shared memory are handed back.
+            for (int i = 0; i < 256; ++i) __nanosleep(1000);
+        }
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) !=
+                cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return static_cast<EncodeTiledFn>(nullptr);
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// 3-D map over `batch` row-major pages of `outer` x `inner` 16-bit elements,
+// box = box_inner x box_outer x 1, 128-byte swizzle, zero fill outside.
+static int make_map_16bit(CUtensorMap *map, int dtype, const void *base, uint64_t inner,
+                          uint64_t outer, uint64_t batch, uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(KLAS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {inner, outer, batch};
+    const cuuint64_t strides[2] = {inner * 2, inner * outer * 2};
+    const cuuint32_t box[3] = {box_inner, box_outer, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt =
+        dtype == KLAS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult rc = fn(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS)
+        return fail(KLAS_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu outer=%llu batch=%llu)",
+                    int(rc), (unsigned long long)inner, (unsigned long long)outer,
+                    (unsigned long long)batch);
+    return KLAS_OK;
+}
+
+template <typename OutT>
+static int launch_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
+                        cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    KLAS_TRY_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<OutT>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured[dev] = true;
+    } else if (dev >= 64) {
+        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<OutT>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    }
+    gemm_umma_kernel<OutT><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    return check_cuda(cudaGetLastError(), "gemm_umma_kernel launch");
+}
+
+}  // namespace umma
+
+int umma_read_status(int *value) {
+    return check_cuda(cudaMemcpyFromSymbol(value, umma::g_umma_status, sizeof(int)),
+                      "cudaMemcpyFromSymbol(status)");
+}
+
+int umma_clear_status() {
+    const int zero = 0;
+    return check_cuda(cudaMemcpyToSymbol(umma::g_umma_status, &zero, sizeof(int)),
+                      "cudaMemcpyToSymbol(status)");
+}
+
+int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                     uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
+                     void *D, float alpha, float beta, int *status_word, cudaStream_t stream) {
+    using namespace umma;
+    if (in_dtype != KLAS_BF16 && in_dtype != KLAS_F16)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: in_dtype must be KLAS_BF16 or KLAS_F16");
+    if (out_dtype != KLAS_F32 && out_dtype != KLAS_F16 && out_dtype != KLAS_BF16)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: out_dtype must be KLAS_F32, KLAS_F16 or KLAS_BF16");
+    if (b_major != KLAS_B_ROW_MAJOR && b_major != KLAS_B_COL_MAJOR)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: bad b_major");
+    if (rows == 0 || cols == 0 || batch == 0) return KLAS_OK;
+    if (!D || (shared > 0 && (!A || !B)))
+        return fail(KLAS_ERR_INVALID, "gemm_tc: null matrix pointer");
+    if (shared % 8 != 0 || cols % 8 != 0)
+        return fail(KLAS_ERR_UNSUPPORTED,
+                    "gemm_tc: shared (%llu) and cols (%llu) must be multiples of 8",
+                    (unsigned long long)shared, (unsigned long long)cols);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+         reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(D)) & 15u)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: A, B, C, D must be 16-byte aligned");
+    if (rows > 0x7fffffffull || cols > 0x7fffffffull || shared > 0x7fffffffull)
+        return fail(KLAS_ERR_TOO_LARGE, "gemm_tc: dimension beyond 2^31-1");
+
+    DeviceInfo info;
+    if (int rc = device_info(&info)) return rc;
+    if (info.cc_major != 10)
+        return fail(KLAS_ERR_UNSUPPORTED, "gemm_tc needs an sm_100 device (found sm_%d%d)",
+                    info.cc_major, info.cc_minor);
+
+    Params p{};
+    p.C = C;
+    p.D = D;
+    p.M = uint32_t(rows);
+    p.N = uint32_t(cols);
+    p.K = uint32_t(shared);
+    p.batch = batch;
+    p.tiles_m = uint32_t((rows + BM - 1) / BM);
+    p.tiles_n = uint32_t((cols + BN - 1) / BN);
+    const uint64_t num_tiles = uint64_t(p.tiles_m) * p.tiles_n * batch;
+    if (num_tiles > 0xffffffffull) return fail(KLAS_ERR_TOO_LARGE, "gemm_tc: too many tiles");
+    p.num_tiles = uint32_t(num_tiles);
+    p.num_kb = uint32_t((shared + BK - 1) / BK);
+    p.alpha = alpha;
+    p.beta = beta;
+    p.b_row_major = (b_major == KLAS_B_ROW_MAJOR) ? 1u : 0u;
+    p.idesc = ptx::umma_idesc_f16(in_dtype == KLAS_BF16, false, p.b_row_major != 0, BM, BN);
+    p.status = status_word;
+
+    CUtensorMap ta{}, tb{};
+    if (shared > 0) {
+        if (int rc = make_map_16bit(&ta, in_dtype, A, shared, rows, batch, BK, BM)) return rc;
+        if (p.b_row_major) {
+            if (int rc = make_map_16bit(&tb, in_dtype, B, cols, shared, batch, 64, BK)) return rc;
+        } else {
+            if (int rc = make_map_16bit(&tb, in_dtype, B, shared, cols, batch, BK, BN)) return rc;
+        }
+    }
+    const int grid = int(num_tiles < uint64_t(info.sm_count) ? num_tiles : uint64_t(info.sm_count));
+    switch (out_dtype) {
+        case KLAS_F32: return launch_typed<float>(ta, tb, p, grid, stream);
+        case KLAS_F16: return launch_typed<__half>(ta, tb, p, grid, stream);
+        default: return launch_typed<__nv_bfloat16>(ta, tb, p, grid, stream);
+    }
+}
+
+}  // namespace klas

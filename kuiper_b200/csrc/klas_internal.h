@@ -1,0 +1,66 @@
+// Internal helpers shared by the translation units of libklas_b200.so.
+#pragma once
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cuda_runtime.h>
+
+#include "klas_b200.h"
+
+namespace klas {
+
+// Stores a printf-style message for klas_b200_last_error() of this thread and
+// returns `code`, so that error paths read `return fail(KLAS_ERR_X, "...")`.
+int fail(int code, const char *fmt, ...);
+void clear_error();
+
+inline int check_cuda(cudaError_t rc, const char *what) {
+    if (rc == cudaSuccess) return KLAS_OK;
+    return fail(KLAS_ERR_CUDA, "%s: %s", what, cudaGetErrorString(rc));
+}
+
+#define KLAS_TRY_CUDA(expr)                                         \
+    do {                                                            \
+        int _rc = ::klas::check_cuda((expr), #expr);                \
+        if (_rc != KLAS_OK) return _rc;                             \
+    } while (0)
+
+inline size_t dtype_size(int dtype) {
+    switch (dtype) {
+        case KLAS_F32: case KLAS_U32: return 4;
+        case KLAS_F64: case KLAS_U64: return 8;
+        case KLAS_BF16: case KLAS_F16: return 2;
+        default: return 0;
+    }
+}
+
+struct DeviceInfo {
+    int device = -1;
+    int sm_count = 0;
+    int l2_bytes = 0;
+    int max_smem_optin = 0;
+    int cc_major = 0, cc_minor = 0;
+};
+
+// Properties of the current device, cached per device.
+int device_info(DeviceInfo *out);
+
+// Grow-only per-device scratch used by the *_host entry points.
+int workspace_reserve(int slot, size_t bytes, void **ptr);
+int workspace_release();
+
+// Kernel launchers (one per translation unit).
+int launch_gemm_simt(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t n, uint64_t k,
+                     const void *alpha, const void *beta, const void *A, const void *B, void *C,
+                     cudaStream_t stream);
+
+int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                     uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
+                     void *D, float alpha, float beta, int *status_word, cudaStream_t stream);
+
+int launch_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32_t nnz,
+                const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
+                const uint32_t *row_indices, const void *B, void *C, cudaStream_t stream);
+
+}  // namespace klas

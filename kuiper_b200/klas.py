@@ -1,0 +1,325 @@
+"""Host-side mirror of the Klas entry points over the C ABI (include/klas_b200.h).
+
+Two levels:
+
+* `gemm`, `gemm_tc`, `spmm` -- typed wrappers that take CUDA tensors, launch on
+  torch's current stream and return the output tensor;
+* `call(name, *args)` -- the reference's own entry-point names
+  (dist/Klas_GEMM_*.h, dist/Klas_SPMM.h) with the reference's argument order
+  and guards, e.g.
+  `call("Klas_GEMM_SHMem_g_matmul_f32_tile32_rrr", m, n, k, A, B, C)`.
+  A violated guard raises `KlasGuardError` where the reference aborts.
+
+torch is used for device memory and streams only; every flop runs in
+libklas_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import re
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import KlasError, check
+from .synth import Csr
+
+_DTYPES = {
+    torch.float32: _lib.F32, torch.float64: _lib.F64,
+    torch.int32: _lib.U32, torch.int64: _lib.U64,
+    torch.bfloat16: _lib.BF16, torch.float16: _lib.F16,
+}
+for _name, _code in (("uint32", _lib.U32), ("uint64", _lib.U64)):
+    if hasattr(torch, _name):
+        _DTYPES[getattr(torch, _name)] = _code
+
+_CTYPE = {_lib.F32: C.c_float, _lib.F64: C.c_double, _lib.U32: C.c_uint32, _lib.U64: C.c_uint64}
+
+
+class KlasGuardError(ValueError):
+    """A precondition the reference checks with KPR_GUARD (include/kuiper.h:57-66) does not hold."""
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError("unsupported dtype %s" % t.dtype) from None
+
+
+def _dev(t: torch.Tensor, what: str) -> int:
+    if not t.is_cuda:
+        raise ValueError("%s must be a CUDA tensor" % what)
+    if not t.is_contiguous():
+        raise ValueError("%s must be contiguous" % what)
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _scalar(code: int, value):
+    """Host scalar of the matrix dtype, as the C ABI wants alpha/beta."""
+    if code == _lib.BF16:
+        bits = torch.tensor(float(value), dtype=torch.bfloat16).view(torch.int16).item() & 0xFFFF
+        return C.c_uint16(bits)
+    if code in (_lib.U32, _lib.U64):
+        return _CTYPE[code](int(value) & ((1 << (32 if code == _lib.U32 else 64)) - 1))
+    return _CTYPE[code](float(value))
+
+
+def gemm(A: torch.Tensor, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *, alpha=None,
+         beta=None, layout: str = "rrr") -> torch.Tensor:
+    """CUDA-core GEMM.  `A` is [batch,] m x k and `B` [batch,] k x n as seen through `layout`
+    ("rrr": tensors are row-major m x k etc.; "ccc": tensors hold the column-major data, i.e.
+    A.shape == (k, m), B.shape == (n, k), C.shape == (n, m)).  With alpha/beta given computes
+    beta*C + alpha*A.B in place in `C_`, otherwise overwrites / allocates C."""
+    code = _code(A)
+    if B.dtype != A.dtype:
+        raise TypeError("A and B dtypes differ")
+    batch = 1
+    if A.dim() == 3:
+        batch = A.shape[0]
+        a2, b2 = A.shape[1:], B.shape[1:]
+    else:
+        a2, b2 = A.shape, B.shape
+    if layout == "rrr":
+        m, k = a2
+        k2, n = b2
+        cshape = (m, n)
+    elif layout == "ccc":
+        k, m = a2
+        n, k2 = b2
+        cshape = (n, m)
+    else:
+        raise ValueError("layout must be 'rrr' or 'ccc'")
+    if k != k2:
+        raise ValueError("inner dimensions differ: %d vs %d" % (k, k2))
+    if A.dim() == 3:
+        cshape = (batch,) + tuple(cshape)
+    if C_ is None:
+        if alpha is not None:
+            raise ValueError("alpha/beta need an existing C")
+        C_ = torch.empty(cshape, dtype=A.dtype, device=A.device)
+    elif tuple(C_.shape) != tuple(cshape) or C_.dtype != A.dtype:
+        raise ValueError("C has shape %s / dtype %s, expected %s / %s"
+                         % (tuple(C_.shape), C_.dtype, tuple(cshape), A.dtype))
+    pa = pb = None
+    if (alpha is None) != (beta is None):
+        raise ValueError("give both alpha and beta or neither")
+    if alpha is not None:
+        sa, sb = _scalar(code, alpha), _scalar(code, beta)
+        pa, pb = C.addressof(sa), C.addressof(sb)
+    lib = _lib.load()
+    with torch.cuda.device(A.device):
+        check(lib.klas_b200_gemm(code, _lib.RRR if layout == "rrr" else _lib.CCC, batch, m, n, k,
+                                 pa, pb, _dev(A, "A"), _dev(B, "B"), _dev(C_, "C"), _stream()))
+    return C_
+
+
+def gemm_tc(A: torch.Tensor, B: torch.Tensor, *, out_dtype=torch.float32, b_col_major: bool = False,
+            C_: Optional[torch.Tensor] = None, D: Optional[torch.Tensor] = None,
+            alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+    """Tensor-core GEMM D = out_dtype(alpha*A.B + beta*C) (or A.B when C_ is None).
+    A: [batch,] rows x shared; B: [batch,] shared x cols, or [batch,] cols x shared when
+    `b_col_major`.  Returns D (allocated when not given; pass D=C_ to accumulate in place)."""
+    if A.dtype not in (torch.bfloat16, torch.float16) or B.dtype != A.dtype:
+        raise TypeError("A and B must both be bf16 or both be f16")
+    batch = A.shape[0] if A.dim() == 3 else 1
+    rows, shared = A.shape[-2:]
+    if b_col_major:
+        cols, k2 = B.shape[-2:]
+    else:
+        k2, cols = B.shape[-2:]
+    if k2 != shared:
+        raise ValueError("inner dimensions differ: %d vs %d" % (shared, k2))
+    dshape = ((batch,) if A.dim() == 3 else ()) + (rows, cols)
+    if D is None:
+        D = torch.empty(dshape, dtype=out_dtype, device=A.device)
+    if tuple(D.shape) != dshape or D.dtype != out_dtype:
+        raise ValueError("D has the wrong shape or dtype")
+    pc = None
+    if C_ is not None:
+        if tuple(C_.shape) != dshape or C_.dtype != out_dtype:
+            raise ValueError("C has the wrong shape or dtype")
+        pc = _dev(C_, "C")
+    lib = _lib.load()
+    with torch.cuda.device(A.device):
+        check(lib.klas_b200_gemm_tc(_code(A), _DTYPES[out_dtype],
+                                    _lib.B_COL_MAJOR if b_col_major else _lib.B_ROW_MAJOR, batch,
+                                    rows, shared, cols, _dev(A, "A"), _dev(B, "B"), pc, _dev(D, "D"),
+                                    float(alpha), float(beta), None, _stream()))
+    return D
+
+
+def gemm_tc_status() -> int:
+    """Raises KlasError(ERR_TIMEOUT) if a bounded device-side wait of the tensor-core kernel
+    gave up since the last call (synchronises the device); returns 0 otherwise."""
+    site = C.c_int(0)
+    check(_lib.load().klas_b200_gemm_tc_status(C.byref(site)))
+    return site.value
+
+
+def spmm(A: Csr, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
+         use_row_indices: bool = True) -> torch.Tensor:
+    """C = CSR(A) . B for f32 (elems float32) or wrapping u32 (elems int32)."""
+    code = _code(A.elems)
+    if code not in (_lib.F32, _lib.U32) or B.dtype != A.elems.dtype:
+        raise TypeError("spmm needs f32 or 32-bit integer elems and a B of the same dtype")
+    shared, cols = B.shape
+    if shared != A.shared:
+        raise ValueError("B has %d rows, the CSR matrix %d columns" % (shared, A.shared))
+    if C_ is None:
+        C_ = torch.empty((A.rows, cols), dtype=B.dtype, device=B.device)
+    elif tuple(C_.shape) != (A.rows, cols) or C_.dtype != B.dtype:
+        raise ValueError("C has the wrong shape or dtype")
+    ri = _dev(A.row_indices, "row_indices") if use_row_indices and A.row_indices is not None else None
+    lib = _lib.load()
+    with torch.cuda.device(B.device):
+        check(lib.klas_b200_spmm(code, A.rows, shared, cols, A.nnz,
+                                 _dev(A.elems, "elems") if A.nnz else None,
+                                 _dev(A.col_ind, "col_ind") if A.nnz else None,
+                                 _dev(A.row_off, "row_off"), ri, _dev(B, "B"), _dev(C_, "C"),
+                                 _stream()))
+    return C_
+
+
+# --------------------------------------------------------------------------- reference names
+_TORCH_OF = {"f32": torch.float32, "f64": torch.float64, "u32": torch.int32, "u64": torch.int64,
+             "bf16": torch.bfloat16, "f16": torch.float16}
+
+_RE_TILED = re.compile(r"^Klas_GEMM_(SHMem|Tiled|BlockTiling1D)_g_(matmul|gemm)_(f32|f64|u32|u64)"
+                       r"(?:_tile(16|32))?_rrr$")
+_RE_BT2D = re.compile(r"^Klas_GEMM_BlockTiling2D_g_gemm_(f32|bf16)_(\d+)x(\d+)x(\d+)_(\d+)x(\d+)$")
+_RE_NAIVE = re.compile(r"^Klas_GEMM_Naive([123])_g_matmul_(bf16|f32|f64|u32|u64)_(rrr|ccc)$")
+_RE_NAIVE_B = re.compile(r"^Klas_GEMM_Naive([12])_batched_(matmul|gemm)_f32$")
+_RE_TC2D = re.compile(r"^Klas_GEMM_TensorCore2D_g_gemm_(bf16_f32|f16_f16)_(\d+)x(\d+)x(\d+)"
+                      r"_16x16x16_(\d+)x(\d+)$")
+_RE_TC2D_TO = re.compile(r"^Klas_GEMM_TensorCore2D_To_g_gemm_bf16_f32_bf16_(\d+)x(\d+)x(\d+)"
+                         r"_16x16x16_(\d+)x(\d+)$")
+_RE_TC1D = re.compile(r"^Klas_GEMM_TensorCore_g_gemm_f16_(f16|f32)_(\d+)x(\d+)x(\d+)_(\d+)x(\d+)x(\d+)$")
+_RE_SPMM = re.compile(r"^Klas_SPMM_(?:spmm_(f32|u32)|g_spmm_f32_(\d+)x(\d+)x(\d+))$")
+
+
+def _guard(cond: bool, text: str) -> None:
+    if not cond:
+        raise KlasGuardError("Guard failed: " + text)
+
+
+def _view(t: torch.Tensor, dtype, *shape) -> torch.Tensor:
+    if t.dtype != dtype:
+        raise TypeError("expected %s, got %s" % (dtype, t.dtype))
+    n = 1
+    for s in shape:
+        n *= s
+    if t.numel() < n:
+        raise ValueError("buffer of %d elements is too small for %s" % (t.numel(), shape))
+    return t.reshape(-1)[:n].view(*shape)
+
+
+def call(name: str, *args):
+    """Runs the reference entry point `name` with the reference's positional arguments
+    (device tensors where the reference takes device pointers).  Results land in the
+    caller's output tensor, as with the reference; returns None."""
+    m_ = _RE_TILED.match(name)
+    if m_:
+        family, kind, dt, tile = m_.groups()
+        args = list(args)
+        if tile is None:
+            if family == "BlockTiling1D":
+                raise KeyError(name)
+            tile_v = int(args.pop(0))
+            _guard(tile_v > 0, "tile > 0U")
+        else:
+            tile_v = int(tile)
+        alpha = beta = None
+        if kind == "gemm":
+            alpha, beta = args.pop(0), args.pop(0)
+        m, n, k, A, B, Cc = args
+        if family == "BlockTiling1D":
+            for v, nm in ((m, "m"), (k, "k"), (n, "n")):
+                _guard(v % tile_v == 0, "%s %% %dU == 0U" % (nm, tile_v))
+        t = _TORCH_OF[dt]
+        gemm(_view(A, t, m, k), _view(B, t, k, n), _view(Cc, t, m, n), alpha=alpha, beta=beta)
+        return None
+    m_ = _RE_BT2D.match(name)
+    if m_:
+        dt, bm, bn, bk = m_.group(1), int(m_.group(2)), int(m_.group(3)), int(m_.group(4))
+        alpha, beta, m, n, k, A, B, Cc = args
+        _guard(m % bm == 0, "m %% %dU == 0U" % bm)
+        _guard(k % bk == 0, "k %% %dU == 0U" % bk)
+        _guard(n % bn == 0, "n %% %dU == 0U" % bn)
+        t = _TORCH_OF[dt]
+        gemm(_view(A, t, m, k), _view(B, t, k, n), _view(Cc, t, m, n), alpha=alpha, beta=beta)
+        return None
+    m_ = _RE_NAIVE.match(name)
+    if m_:
+        _, dt, lay = m_.groups()
+        m, n, k, A, B, Cc = args
+        t = _TORCH_OF[dt]
+        if lay == "rrr":
+            gemm(_view(A, t, m, k), _view(B, t, k, n), _view(Cc, t, m, n))
+        else:
+            gemm(_view(A, t, k, m), _view(B, t, n, k), _view(Cc, t, n, m), layout="ccc")
+        return None
+    m_ = _RE_NAIVE_B.match(name)
+    if m_:
+        kind = m_.group(2)
+        args = list(args)
+        alpha = beta = None
+        if kind == "gemm":
+            alpha, beta = args.pop(0), args.pop(0)
+        batch, m, n, k, A, B, Cc = args
+        t = torch.float32
+        gemm(_view(A, t, batch, m, k), _view(B, t, batch, k, n), _view(Cc, t, batch, m, n),
+             alpha=alpha, beta=beta)
+        return None
+    m_ = _RE_TC2D.match(name)
+    if m_:
+        dt, bm, bn, bk = m_.group(1), int(m_.group(2)), int(m_.group(3)), int(m_.group(4))
+        rows, shared, cols, A, B, Cc = args
+        _guard(rows % bm == 0, "rows %% %dU == 0U" % bm)
+        _guard(shared % bk == 0, "shared %% %dU == 0U" % bk)
+        _guard(cols % bn == 0, "cols %% %dU == 0U" % bn)
+        tin, tout = (torch.bfloat16, torch.float32) if dt == "bf16_f32" else (torch.float16, torch.float16)
+        gemm_tc(_view(A, tin, rows, shared), _view(B, tin, shared, cols), out_dtype=tout,
+                D=_view(Cc, tout, rows, cols))
+        return None
+    m_ = _RE_TC2D_TO.match(name)
+    if m_:
+        bm, bn, bk = int(m_.group(1)), int(m_.group(2)), int(m_.group(3))
+        rows, shared, cols, A, B, Cc, Dd, alpha, beta = args
+        _guard(rows % bm == 0, "rows %% %dU == 0U" % bm)
+        _guard(shared % bk == 0, "shared %% %dU == 0U" % bk)
+        _guard(cols % bn == 0, "cols %% %dU == 0U" % bn)
+        t = torch.bfloat16
+        gemm_tc(_view(A, t, rows, shared), _view(B, t, shared, cols), out_dtype=t,
+                C_=_view(Cc, t, rows, cols), D=_view(Dd, t, rows, cols), alpha=alpha, beta=beta)
+        return None
+    m_ = _RE_TC1D.match(name)
+    if m_:
+        acc = m_.group(1)
+        bm, bn, bk, tm, tn, tk = (int(v) for v in m_.groups()[1:])
+        if (bm, bn, bk, tm, tn, tk) == (8, 32, 16, 8, 32, 16):
+            # This one name guards on 32 in every dimension: its block tile really is
+            # 32x32x32 (dist/Klas_GEMM_TensorCore.cu:531-535, src/klas/Klas.GEMM.TensorCore.fst:14).
+            bm, bk, bn = 32, 32, 32
+        rows, shared, cols, A, B, Cc = args
+        _guard(rows % bm == 0, "rows %% %dU == 0U" % bm)
+        _guard(shared % bk == 0, "shared %% %dU == 0U" % bk)
+        _guard(cols % bn == 0, "cols %% %dU == 0U" % bn)
+        tout = torch.float16 if acc == "f16" else torch.float32
+        cv = _view(Cc, tout, rows, cols)
+        gemm_tc(_view(A, torch.float16, rows, shared), _view(B, torch.float16, shared, cols),
+                out_dtype=tout, C_=cv, D=cv, alpha=1.0, beta=1.0)
+        return None
+    m_ = _RE_SPMM.match(name)
+    if m_:
+        rows, shared, cols, A, row_indices, B, Cc = args
+        dt = torch.int32 if m_.group(1) == "u32" else torch.float32
+        csr = Csr(rows, shared, A.elems, A.col_ind, A.row_off, row_indices)
+        spmm(csr, _view(B, dt, shared, cols), _view(Cc, dt, rows, cols))
+        return None
+    raise KeyError("unknown Klas entry point: %s" % name)

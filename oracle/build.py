@@ -1,0 +1,113 @@
+"""Builds the checkers: oracle/libklas_oracle.so (the CPU restatement, gcc) and --
+only where the FStarLang/kuiper tree is mounted -- oracle/_ref/: the reference's own
+host loops, GPU kernels and test drivers compiled from where they lie.
+
+    python oracle/build.py [--ref-root /path/to/kuiper] [--no-ref-gpu] [--no-drivers]
+
+Outputs are git-ignored build products; nothing here is part of the product library.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ORACLE_DIR = Path(__file__).resolve().parent
+REPO_DIR = ORACLE_DIR.parent
+ORACLE_LIB = ORACLE_DIR / "libklas_oracle.so"
+REF_DIR = ORACLE_DIR / "_ref"
+DEFAULT_REF_ROOT = Path("/root/reference")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+REF_GPU_UNITS = [
+    "Klas_GEMM_SHMem", "Klas_GEMM_Tiled", "Klas_GEMM_BlockTiling1D", "Klas_GEMM_BlockTiling2D",
+    "Klas_GEMM_Naive1", "Klas_GEMM_Naive2", "Klas_GEMM_Naive3", "Klas_GEMM_TensorCore",
+    "Klas_GEMM_TensorCore2D", "Klas_GEMM_TensorCore2D_To", "Klas_SPMM",
+]
+
+
+def _run(cmd, **kw):
+    r = subprocess.run(list(map(str, cmd)), stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, **kw)
+    if r.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s" % (" ".join(map(str, cmd)), r.stdout))
+    return r.stdout
+
+
+def _newer(target: Path, *deps: Path) -> bool:
+    return target.exists() and all(target.stat().st_mtime >= d.stat().st_mtime for d in deps if d.exists())
+
+
+def build_oracle(force: bool = False) -> Path:
+    src = ORACLE_DIR / "klas_oracle.c"
+    if not force and _newer(ORACLE_LIB, src):
+        return ORACLE_LIB
+    _run(["gcc", "-O3", "-fopenmp", "-ffp-contract=off", "-fPIC", "-shared", "-o", ORACLE_LIB, src, "-lm"])
+    return ORACLE_LIB
+
+
+def build_ref_cpu(ref_root: Path, force: bool = False) -> Path:
+    """The reference's host gold loops (test/matmul_common.c.inc, dist/Kuiper_Example_Sparse_MM.cu)."""
+    out = REF_DIR / "libklas_ref_cpu.so"
+    wrap = ORACLE_DIR / "ref_wrap" / "ref_cpu.cu"
+    if not force and _newer(out, wrap):
+        return out
+    REF_DIR.mkdir(exist_ok=True)
+    _run(["nvcc", "-O3", "-std=c++17", *ARCH, "-Xcompiler", "-fPIC", "-shared",
+          "-I", ref_root / "include", "-I", ref_root / "test", "-I", ref_root / "dist",
+          "-o", out, wrap, ref_root / "dist" / "Kuiper_Example_Sparse_MM.cu"])
+    return out
+
+
+def build_ref_gpu(ref_root: Path, force: bool = False) -> Path:
+    """The reference's extracted kernels (dist/Klas_*.cu) for sm_100a, one shared library,
+    plus symbols.json mapping each entry-point name to its mangled symbol."""
+    out = REF_DIR / "libklas_ref_gpu.so"
+    if not force and out.exists() and (REF_DIR / "symbols.json").exists():
+        return out
+    obj_dir = REF_DIR / "obj"
+    obj_dir.mkdir(parents=True, exist_ok=True)
+
+    def compile_unit(unit):
+        obj = obj_dir / (unit + ".o")
+        if force or not obj.exists():
+            _run(["nvcc", "-O3", *ARCH, "-Xcompiler", "-fPIC", "-I", ref_root / "include",
+                  "-I", ref_root / "dist", "-DKUIPER_CFG_TENSORCORES=1",
+                  "-c", ref_root / "dist" / (unit + ".cu"), "-o", obj])
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+        objs = list(ex.map(compile_unit, REF_GPU_UNITS))
+    _run(["nvcc", "-shared", *ARCH, "-o", out, *objs])
+    names = {}
+    for line in _run(["nm", "-D", "--defined-only", out]).splitlines():
+        parts = line.split()
+        if len(parts) == 3 and parts[1] == "T" and "Klas_" in parts[2]:
+            demangled = _run(["c++filt", parts[2]]).strip()
+            names[demangled.split("(")[0]] = parts[2]
+    (REF_DIR / "symbols.json").write_text(json.dumps(names, indent=0, sort_keys=True))
+    return out
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref-root", type=Path, default=DEFAULT_REF_ROOT)
+    ap.add_argument("--no-ref-gpu", action="store_true")
+    ap.add_argument("--force", action="store_true")
+    a = ap.parse_args(argv)
+    print(build_oracle(a.force))
+    if (a.ref_root / "dist").is_dir():
+        print(build_ref_cpu(a.ref_root, a.force))
+        if not a.no_ref_gpu:
+            print(build_ref_gpu(a.ref_root, a.force))
+    else:
+        print("reference tree not mounted at %s: oracle/_ref not (re)built" % a.ref_root)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,216 @@
+"""numpy-facing binding of the CPU checkers.
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
+CPU-baseline legs of bench.py.  The product package never imports this module.
+
+`Oracle` wraps oracle/libklas_oracle.so (the restatement, always buildable with
+gcc); `RefCpu` wraps oracle/_ref/libklas_ref_cpu.so (the reference's own host
+loops, present only where the reference tree was available at build time).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+ORACLE_DIR = Path(__file__).resolve().parent
+ORACLE_LIB = ORACLE_DIR / "libklas_oracle.so"
+REF_CPU_LIB = ORACLE_DIR / "_ref" / "libklas_ref_cpu.so"
+
+_sz, _vp, _int = C.c_size_t, C.c_void_p, C.c_int
+
+
+def _p(a: np.ndarray) -> int:
+    assert a.flags["C_CONTIGUOUS"], "array must be C-contiguous"
+    return a.ctypes.data
+
+
+def bf16_bits(t) -> np.ndarray:
+    """uint16 bit patterns of a torch bf16/f16 tensor (on the CPU)."""
+    import torch
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+class Oracle:
+    def __init__(self):
+        if not ORACLE_LIB.exists():
+            raise FileNotFoundError("%s missing: run `python oracle/build.py`" % ORACLE_LIB)
+        self.lib = C.CDLL(str(ORACLE_LIB))
+        self.lib.klas_oracle_max_threads.restype = _int
+        for name in ("klas_oracle_sgemm_f32",):
+            getattr(self.lib, name).argtypes = [_sz, _sz, _sz, C.c_float, C.c_float, _vp, _vp, _vp, _vp, _int]
+        self.lib.klas_oracle_gemm_u32.argtypes = [_sz, _sz, _sz, C.c_uint32, C.c_uint32, _int, _vp, _vp, _vp, _int]
+        self.lib.klas_oracle_gemm_u64.argtypes = [_sz, _sz, _sz, C.c_uint64, C.c_uint64, _int, _vp, _vp, _vp, _int]
+        for name in ("klas_oracle_acc_f32", "klas_oracle_acc_f64", "klas_oracle_acc_bf16",
+                     "klas_oracle_acc_f16", "klas_oracle_acc_bf16_bt", "klas_oracle_absacc_f64",
+                     "klas_oracle_gemm_f32", "klas_oracle_gemm_f64", "klas_oracle_gemm_bf16_f32",
+                     "klas_oracle_gemm_f16_f16"):
+            getattr(self.lib, name).argtypes = [_sz, _sz, _sz, _vp, _vp, _vp, _int]
+        self.lib.klas_oracle_batched_f32.argtypes = [_sz, _sz, _sz, _sz, _vp, _vp, _vp]
+        self.lib.klas_oracle_spmm_u32.argtypes = [C.c_uint32, C.c_uint32, _vp, _vp, _vp, _vp, _vp, _int]
+        self.lib.klas_oracle_spmm_f32.argtypes = [C.c_uint32, C.c_uint32, _vp, _vp, _vp, _vp, _vp, _vp, _int]
+        self.lib.klas_oracle_dense_matmul_f32.argtypes = [_sz, _sz, _sz, _vp, _vp, _vp]
+        for name in ("klas_oracle_f64_to_f16_bits", "klas_oracle_f64_to_bf16_bits", "klas_oracle_f16_bits_to_f64"):
+            getattr(self.lib, name).argtypes = [_vp, _vp, _sz]
+
+    @property
+    def max_threads(self) -> int:
+        return self.lib.klas_oracle_max_threads()
+
+    # ---- double accumulators -------------------------------------------------
+    def acc(self, A: np.ndarray, B: np.ndarray, kind: str | None = None, threads: int = 0) -> np.ndarray:
+        """float64 A.B with the drivers' i-k-j double accumulation.  `kind` is 'bf16' or
+        'f16' when A and B hold uint16 bit patterns."""
+        m, k = A.shape
+        k2, n = B.shape
+        assert k == k2
+        out = np.empty((m, n), dtype=np.float64)
+        fn = {("float32", None): "klas_oracle_acc_f32", ("float64", None): "klas_oracle_acc_f64",
+              ("uint16", "bf16"): "klas_oracle_acc_bf16", ("uint16", "f16"): "klas_oracle_acc_f16"}[(A.dtype.name, kind)]
+        assert B.dtype == A.dtype
+        getattr(self.lib, fn)(m, n, k, _p(A), _p(B), _p(out), threads)
+        return out
+
+    def acc_bf16_bt(self, A: np.ndarray, Bt: np.ndarray, threads: int = 0) -> np.ndarray:
+        m, k = A.shape
+        n, k2 = Bt.shape
+        assert k == k2 and A.dtype == np.uint16 and Bt.dtype == np.uint16
+        out = np.empty((m, n), dtype=np.float64)
+        self.lib.klas_oracle_acc_bf16_bt(m, n, k, _p(A), _p(Bt), _p(out), threads)
+        return out
+
+    def absacc(self, A: np.ndarray, B: np.ndarray, threads: int = 0) -> np.ndarray:
+        """|A|.|B| in float64: the component-wise scale of a relative-error bound."""
+        A = np.ascontiguousarray(A, dtype=np.float64)
+        B = np.ascontiguousarray(B, dtype=np.float64)
+        out = np.empty((A.shape[0], B.shape[1]), dtype=np.float64)
+        self.lib.klas_oracle_absacc_f64(A.shape[0], B.shape[1], A.shape[1], _p(A), _p(B), _p(out), threads)
+        return out
+
+    # ---- typed gold ------------------------------------------------------------
+    def gemm(self, A: np.ndarray, B: np.ndarray, kind: str | None = None, threads: int = 0) -> np.ndarray:
+        m, k = A.shape
+        n = B.shape[1]
+        if A.dtype == np.float32:
+            out = np.empty((m, n), np.float32)
+            self.lib.klas_oracle_gemm_f32(m, n, k, _p(A), _p(B), _p(out), threads)
+        elif A.dtype == np.float64:
+            out = np.empty((m, n), np.float64)
+            self.lib.klas_oracle_gemm_f64(m, n, k, _p(A), _p(B), _p(out), threads)
+        elif A.dtype == np.uint16 and kind == "bf16":
+            out = np.empty((m, n), np.float32)
+            self.lib.klas_oracle_gemm_bf16_f32(m, n, k, _p(A), _p(B), _p(out), threads)
+        elif A.dtype == np.uint16 and kind == "f16":
+            out = np.empty((m, n), np.uint16)
+            self.lib.klas_oracle_gemm_f16_f16(m, n, k, _p(A), _p(B), _p(out), threads)
+        else:
+            raise TypeError(A.dtype)
+        return out
+
+    def sgemm_f32(self, alpha, beta, A, B, Cin, threads: int = 0) -> np.ndarray:
+        m, k = A.shape
+        n = B.shape[1]
+        out = np.empty((m, n), np.float32)
+        self.lib.klas_oracle_sgemm_f32(m, n, k, alpha, beta, _p(A), _p(B), _p(Cin), _p(out), threads)
+        return out
+
+    def gemm_int(self, A: np.ndarray, B: np.ndarray, Cin: np.ndarray | None = None, alpha: int = 1,
+                 beta: int = 0, threads: int = 0) -> np.ndarray:
+        """Wrapping u32/u64 product; with Cin computes beta*Cin + alpha*A.B."""
+        m, k = A.shape
+        n = B.shape[1]
+        assert A.dtype in (np.uint32, np.uint64) and B.dtype == A.dtype
+        out = np.zeros((m, n), A.dtype) if Cin is None else np.array(Cin, dtype=A.dtype, order="C")
+        fn = self.lib.klas_oracle_gemm_u32 if A.dtype == np.uint32 else self.lib.klas_oracle_gemm_u64
+        bits = 32 if A.dtype == np.uint32 else 64
+        fn(m, n, k, alpha & ((1 << bits) - 1), beta & ((1 << bits) - 1), 0 if Cin is None else 1,
+           _p(A), _p(B), _p(out), threads)
+        return out
+
+    def batched_f32(self, A: np.ndarray, B: np.ndarray) -> np.ndarray:
+        b, m, k = A.shape
+        n = B.shape[2]
+        out = np.empty((b, m, n), np.float32)
+        self.lib.klas_oracle_batched_f32(b, m, n, k, _p(A), _p(B), _p(out))
+        return out
+
+    # ---- SpMM ------------------------------------------------------------------
+    def spmm_u32(self, rows, cols, elems, col_ind, row_off, B, threads: int = 0) -> np.ndarray:
+        out = np.empty((rows, cols), np.uint32)
+        self.lib.klas_oracle_spmm_u32(rows, cols, _p(elems), _p(col_ind), _p(row_off), _p(B), _p(out), threads)
+        return out
+
+    def spmm_f32(self, rows, cols, elems, col_ind, row_off, B, with_abs: bool = False, threads: int = 0):
+        out = np.empty((rows, cols), np.float64)
+        ab = np.empty((rows, cols), np.float64) if with_abs else None
+        self.lib.klas_oracle_spmm_f32(rows, cols, _p(elems), _p(col_ind), _p(row_off), _p(B), _p(out),
+                                      _p(ab) if with_abs else None, threads)
+        return (out, ab) if with_abs else out
+
+    def dense_matmul_f32(self, A, B) -> np.ndarray:
+        out = np.empty((A.shape[0], B.shape[1]), np.float32)
+        self.lib.klas_oracle_dense_matmul_f32(A.shape[0], A.shape[1], B.shape[1], _p(A), _p(B), _p(out))
+        return out
+
+    # ---- 16-bit conversions ------------------------------------------------------
+    def to_f16_bits(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float64)
+        out = np.empty(x.shape, np.uint16)
+        self.lib.klas_oracle_f64_to_f16_bits(_p(x), _p(out), x.size)
+        return out
+
+    def to_bf16_bits(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float64)
+        out = np.empty(x.shape, np.uint16)
+        self.lib.klas_oracle_f64_to_bf16_bits(_p(x), _p(out), x.size)
+        return out
+
+    def f16_bits_to_f64(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.uint16)
+        out = np.empty(x.shape, np.float64)
+        self.lib.klas_oracle_f16_bits_to_f64(_p(x), _p(out), x.size)
+        return out
+
+
+class RefCpu:
+    """The reference's own gold loops (cpu_mul / cpu_sgemm per element type, the u32 CSR loop)."""
+
+    KINDS = {"f32": (np.float32, np.float32), "f64": (np.float64, np.float64),
+             "u32": (np.uint32, np.uint32), "u64": (np.uint64, np.uint64),
+             "bf16_f32": (np.uint16, np.float32), "f16_f16": (np.uint16, np.uint16)}
+
+    def __init__(self):
+        if not REF_CPU_LIB.exists():
+            raise FileNotFoundError(str(REF_CPU_LIB))
+        self.lib = C.CDLL(str(REF_CPU_LIB))
+
+    @staticmethod
+    def available() -> bool:
+        return REF_CPU_LIB.exists()
+
+    def cpu_mul(self, kind: str, A: np.ndarray, B: np.ndarray) -> np.ndarray:
+        et, cet = self.KINDS[kind]
+        assert A.dtype == et and B.dtype == et
+        out = np.empty((A.shape[0], B.shape[1]), cet)
+        fn = getattr(self.lib, "ref_cpu_mul_" + kind)
+        fn.argtypes = [_sz, _sz, _sz, _vp, _vp, _vp]
+        fn(A.shape[0], A.shape[1], B.shape[1], _p(A), _p(B), _p(out))
+        return out
+
+    def cpu_sgemm(self, kind: str, A, B, Cin, alpha, beta) -> np.ndarray:
+        et, cet = self.KINDS[kind]
+        out = np.empty((A.shape[0], B.shape[1]), cet)
+        al = np.array([alpha], dtype=cet)
+        be = np.array([beta], dtype=cet)
+        fn = getattr(self.lib, "ref_cpu_sgemm_" + kind)
+        fn.argtypes = [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp]
+        fn(A.shape[0], A.shape[1], B.shape[1], _p(A), _p(B), _p(Cin), _p(al), _p(be), _p(out))
+        return out
+
+    def mmsd_u32_rr(self, rows, shared, cols, elems, col_ind, row_off, B) -> np.ndarray:
+        out = np.empty((rows, cols), np.uint32)
+        fn = self.lib.ref_mmsd_u32_rr
+        fn.argtypes = [C.c_uint32] * 4 + [_vp] * 5
+        fn(rows, shared, cols, elems.size, _p(elems), _p(col_ind), _p(row_off), _p(B), _p(out))
+        return out

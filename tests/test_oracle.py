@@ -1,0 +1,162 @@
+"""Pins the CPU oracle (oracle/klas_oracle.c): bit-for-bit against the golden values
+produced by the reference's own host loops (tests/golden/klas_golden.npz) and, where
+oracle/_ref is built, against those loops run live on further inputs."""
+import hashlib
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from driver_inputs import bits16, tc_inputs, tiled_inputs
+from kuiper_b200 import synth
+
+GOLD = np.load(Path(__file__).parent / "golden" / "klas_golden.npz")
+SMALL = (24, 40, 16)
+TC_SMALL = (32, 48, 24)
+BIG = (1024, 1024, 1024)
+STRIDE = 4099
+
+
+def sha(a):
+    return np.frombuffer(hashlib.sha256(np.ascontiguousarray(a).tobytes()).digest(), dtype=np.uint8)
+
+
+@pytest.mark.parametrize("kind,dt", [("f32", np.float32), ("f64", np.float64)])
+def test_float_gold_small_and_driver_size(oracle, kind, dt):
+    m1, m2, m3 = tiled_inputs(dt, *SMALL)
+    assert np.array_equal(oracle.gemm(m1, m2), GOLD["mul_%s_small" % kind])
+    m1, m2, _ = tiled_inputs(dt, *BIG)
+    big = oracle.gemm(m1, m2, threads=0)
+    assert np.array_equal(sha(big), GOLD["mul_%s_big_sha256" % kind])
+    assert np.array_equal(big.reshape(-1)[::STRIDE], GOLD["mul_%s_big_samples" % kind])
+
+
+def test_sgemm_f32_gold(oracle):
+    m1, m2, m3 = tiled_inputs(np.float32, *SMALL)
+    got = oracle.sgemm_f32(0.7, 0.3, m1, m2, m3)
+    assert np.array_equal(got, GOLD["sgemm_f32_small"])
+
+
+@pytest.mark.parametrize("kind,dt", [("u32", np.uint32), ("u64", np.uint64)])
+def test_integer_gold(oracle, kind, dt):
+    m1, m2, _ = tiled_inputs(dt, *SMALL)
+    assert np.array_equal(oracle.gemm_int(m1, m2), GOLD["mul_%s_small" % kind])
+    m1, m2, _ = tiled_inputs(dt, *BIG)
+    big = oracle.gemm_int(m1, m2)
+    if kind == "u64":
+        # every sum of the driver's inputs stays below 2^53, where the reference's
+        # double-accumulating gold loop is exact: bit-for-bit agreement
+        assert np.array_equal(sha(big), GOLD["mul_u64_big_sha256"])
+        assert np.array_equal(big.reshape(-1)[::STRIDE], GOLD["mul_u64_big_samples"])
+    else:
+        # u32 at the driver's size: sums reach ~3.6e9 < 2^32, still exact
+        assert np.array_equal(sha(big), GOLD["mul_u32_big_sha256"])
+
+
+def test_integer_wraparound_matches_python_bigints(oracle):
+    rng = np.random.default_rng(5)
+    for dt, bits in ((np.uint32, 32), (np.uint64, 64)):
+        A = rng.integers(0, 1 << bits, size=(5, 7), dtype=dt)
+        B = rng.integers(0, 1 << bits, size=(7, 3), dtype=dt)
+        Cin = rng.integers(0, 1 << bits, size=(5, 3), dtype=dt)
+        alpha, beta = (1 << bits) - 3, 12345
+        got = oracle.gemm_int(A, B)
+        got2 = oracle.gemm_int(A, B, Cin, alpha, beta)
+        for i in range(5):
+            for j in range(3):
+                s = sum(int(A[i, l]) * int(B[l, j]) for l in range(7))
+                assert int(got[i, j]) == s % (1 << bits)
+                assert int(got2[i, j]) == (beta * int(Cin[i, j]) + alpha * s) % (1 << bits)
+
+
+@pytest.mark.parametrize("kind,tdt", [("bf16_f32", torch.bfloat16), ("f16_f16", torch.float16)])
+def test_tensor_core_driver_gold(oracle, kind, tdt):
+    sub = "bf16" if kind == "bf16_f32" else "f16"
+    A, B = tc_inputs(tdt, *TC_SMALL)
+    assert np.array_equal(oracle.gemm(bits16(A), bits16(B), kind=sub), GOLD["mul_%s_small" % kind])
+    A, B = tc_inputs(tdt, *BIG)
+    big = oracle.gemm(bits16(A), bits16(B), kind=sub)
+    assert np.array_equal(sha(big), GOLD["mul_%s_big_sha256" % kind])
+    if kind == "f16_f16":
+        # fp16 overflow to +inf is part of the drivers' gold
+        assert int((big == 0x7c00).sum()) == int(GOLD["mul_f16_f16_big_inf_count"][0]) > 0
+
+
+def test_f16_conversion_single_rounding(oracle):
+    # every finite half value round-trips; ties go to even; 65520 overflows
+    allbits = np.arange(0, 0x7c00, dtype=np.uint16)
+    vals = oracle.f16_bits_to_f64(allbits)
+    assert np.array_equal(oracle.to_f16_bits(vals), allbits)
+    assert np.array_equal(oracle.to_f16_bits(-vals[1:]), allbits[1:] | 0x8000)
+    assert np.array_equal(vals, torch.tensor(allbits.view(np.int16)).view(torch.float16).double().numpy())
+    mid = (vals[:-1] + vals[1:]) / 2     # exact midpoints: must pick the even neighbour
+    r = oracle.to_f16_bits(mid)
+    assert np.array_equal(r, np.where(allbits[:-1] % 2 == 0, allbits[:-1], allbits[1:]))
+    assert oracle.to_f16_bits(np.array([65519.999, 65520.0, 1e9, -65520.0])).tolist() == [0x7bff, 0x7c00, 0x7c00, 0xfc00]
+    # double rounding trap: 1 + 2^-11 + 2^-30 must round up in one step
+    x = np.array([1.0 + 2.0 ** -11 + 2.0 ** -30])
+    assert oracle.to_f16_bits(x)[0] == 0x3c01
+
+
+def test_bf16_conversion(oracle):
+    x = torch.randn(4096, dtype=torch.float64) * 37.0
+    ref = bits16(x.float().to(torch.bfloat16))   # float -> bf16 is a single rounding of the float
+    got = oracle.to_bf16_bits(x.float().double().numpy())
+    assert np.array_equal(got, ref)
+
+
+def test_spmm_u32_gold(oracle):
+    csr = synth.csr_poisson(11, 96, 80, 6.0, value_kind="u32")
+    Bd = synth.spmm_dense_b(11, 80, 24, value_kind="u32")
+    got = oracle.spmm_u32(96, 24, csr.elems.numpy().view(np.uint32), csr.col_ind.numpy().view(np.uint32),
+                          csr.row_off.numpy().view(np.uint32), Bd.numpy().view(np.uint32))
+    assert np.array_equal(got, GOLD["spmm_u32_small"])
+
+
+def test_spmm_f32_matches_dense_product(oracle):
+    csr = synth.csr_poisson(4, 64, 50, 5.0)
+    Bd = synth.spmm_dense_b(4, 50, 12)
+    dense = np.zeros((64, 50), np.float32)
+    ro = csr.row_off.numpy()
+    for r in range(64):
+        dense[r, csr.col_ind.numpy()[ro[r]:ro[r + 1]]] = csr.elems.numpy()[ro[r]:ro[r + 1]]
+    got, ab = oracle.spmm_f32(64, 12, csr.elems.numpy(), csr.col_ind.numpy().view(np.uint32),
+                              ro.view(np.uint32), Bd.numpy(), with_abs=True)
+    want = dense.astype(np.float64) @ Bd.numpy().astype(np.float64)
+    assert np.allclose(got, want, rtol=0, atol=1e-12)
+    assert np.all(ab >= np.abs(got) - 1e-12)
+    # the drivers' float gold loop agrees within float rounding
+    assert np.allclose(oracle.dense_matmul_f32(dense, Bd.numpy()), want, rtol=1e-5, atol=1e-5)
+
+
+# ------------------------------------------------------------------ live checks against oracle/_ref
+@pytest.mark.parametrize("shape", [(7, 5, 3), (33, 65, 17), (128, 96, 64)])
+def test_live_reference_loops(oracle, refcpu, shape):
+    rng = np.random.default_rng(shape[0])
+    A = rng.uniform(-1, 1, size=shape[:2]).astype(np.float32)
+    B = rng.uniform(-1, 1, size=shape[1:]).astype(np.float32)
+    Cin = rng.uniform(-1, 1, size=(shape[0], shape[2])).astype(np.float32)
+    assert np.array_equal(oracle.gemm(A, B), refcpu.cpu_mul("f32", A, B))
+    assert np.array_equal(oracle.sgemm_f32(0.7, 0.3, A, B, Cin), refcpu.cpu_sgemm("f32", A, B, Cin, 0.7, 0.3))
+    Ad, Bd = A.astype(np.float64), B.astype(np.float64)
+    assert np.array_equal(oracle.gemm(Ad, Bd), refcpu.cpu_mul("f64", Ad, Bd))
+    for dt in (np.uint32, np.uint64):
+        Ai = rng.integers(0, 3000, size=shape[:2]).astype(dt)
+        Bi = rng.integers(0, 3000, size=shape[1:]).astype(dt)
+        assert np.array_equal(oracle.gemm_int(Ai, Bi), refcpu.cpu_mul("u32" if dt == np.uint32 else "u64", Ai, Bi))
+    Ah = torch.tensor(A).to(torch.float16)
+    Bh = (torch.tensor(B) * 300).to(torch.float16)
+    assert np.array_equal(oracle.gemm(bits16(Ah), bits16(Bh), kind="f16"),
+                          refcpu.cpu_mul("f16_f16", bits16(Ah), bits16(Bh)))
+    Ab, Bb = torch.tensor(A).to(torch.bfloat16), torch.tensor(B).to(torch.bfloat16)
+    assert np.array_equal(oracle.gemm(bits16(Ab), bits16(Bb), kind="bf16"),
+                          refcpu.cpu_mul("bf16_f32", bits16(Ab), bits16(Bb)))
+
+
+def test_live_reference_csr_loop(oracle, refcpu):
+    csr = synth.csr_poisson(21, 200, 150, 9.0, value_kind="u32")
+    Bd = synth.spmm_dense_b(21, 150, 33, value_kind="u32")
+    e, c, r, b = (csr.elems.numpy().view(np.uint32), csr.col_ind.numpy().view(np.uint32),
+                  csr.row_off.numpy().view(np.uint32), Bd.numpy().view(np.uint32))
+    assert np.array_equal(oracle.spmm_u32(200, 33, e, c, r, b), refcpu.mmsd_u32_rr(200, 150, 33, e, c, r, b))
