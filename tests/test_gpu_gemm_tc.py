@@ -1,0 +1,162 @@
+"""Parity of the tcgen05 tensor-core GEMM (through the C ABI) with the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from driver_inputs import bits16, tc_inputs
+from gpu_util import rel_err_componentwise, tc_reference
+from kuiper_b200 import klas, synth
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16_F32 = 2e-3   # bf16 x bf16 -> f32, relative to fp64, component-wise scale
+TOL_F16_F16 = 1e-2    # f16 x f16 -> f16
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert klas.gemm_tc_status() == 0
+
+
+SHAPES = [
+    (128, 64, 256),     # one tile, one k-block
+    (128, 256, 256),    # one tile, pipeline wraps (4 k-blocks = ring depth)
+    (256, 512, 512),    # 2x2 tiles, ring wraps twice
+    (64, 16, 64),       # smallest legacy guard multiple: partial tile in M, N and K
+    (192, 80, 328),     # ragged everywhere (multiples of 8 only)
+    (1024, 1024, 1024), # the reference drivers' default size
+    (640, 2048, 1280),  # more tiles than fit one wave of a small grid; deep K
+]
+
+
+@pytest.mark.parametrize("rows,shared,cols", SHAPES)
+@pytest.mark.parametrize("b_col_major", [False, True])
+def test_bf16_f32_matches_oracle(oracle, rows, shared, cols, b_col_major):
+    A, Bm = synth.gemm_bf16(1, rows, cols, shared, b_col_major=b_col_major, device="cuda")
+    D = klas.gemm_tc(A, Bm, out_dtype=torch.float32, b_col_major=b_col_major)
+    torch.cuda.synchronize()
+    acc, scale = tc_reference(oracle, A.cpu(), Bm.cpu(), b_col_major)
+    err = rel_err_componentwise(D.cpu().numpy(), acc, scale)
+    assert err <= TOL_BF16_F32, "relative error %.3e" % err
+    # fp32 accumulation of exact bf16 products: far inside the tolerance
+    assert err <= 1e-5
+
+
+@pytest.mark.parametrize("rows,shared,cols", SHAPES[:6])
+def test_f16_f16_matches_oracle(oracle, rows, shared, cols):
+    A, B = synth.gemm_f16_batched(2, 1, rows, cols, shared, device="cuda")
+    D = klas.gemm_tc(A[0], B[0], out_dtype=torch.float16)
+    torch.cuda.synchronize()
+    acc, scale = tc_reference(oracle, A[0].cpu(), B[0].cpu(), False)
+    err = rel_err_componentwise(D.double().cpu().numpy(), acc, scale)
+    assert err <= TOL_F16_F16, "relative error %.3e" % err
+
+
+def test_f16_driver_inputs_overflow_pattern(oracle):
+    """The six F16_F16 drivers' inputs: ~13 % of the results overflow to +inf in the gold;
+    the kernel must overflow too (never saturate to 65504)."""
+    A, B = tc_inputs(torch.float16, 1024, 1024, 1024)
+    gold = oracle.gemm(bits16(A), bits16(B), kind="f16")
+    D = klas.gemm_tc(A.cuda(), B.cuda(), out_dtype=torch.float16)
+    got = bits16(D.cpu())
+    inf_gold, inf_got = gold == 0x7c00, got == 0x7c00
+    assert inf_gold.sum() > 100000
+    # entries within rounding distance of the 65520 threshold may differ; the driver's own
+    # comparison tolerates up to 9 mismatching cells (test/matmul_common.c.inc:106-112)
+    assert int((inf_gold != inf_got).sum()) <= 9
+    fin = ~inf_gold & ~inf_got
+    g64, d64 = oracle.f16_bits_to_f64(gold[fin]), oracle.f16_bits_to_f64(got[fin])
+    assert np.max(np.abs(g64 - d64) / np.abs(g64)) <= 0.02   # the drivers' TOLERANCE
+
+
+def test_bf16_driver_inputs(oracle):
+    A, B = tc_inputs(torch.bfloat16, 1024, 1024, 1024)
+    gold = oracle.gemm(bits16(A), bits16(B), kind="bf16")
+    D = klas.gemm_tc(A.cuda(), B.cuda(), out_dtype=torch.float32).cpu().numpy()
+    assert np.max(np.abs(D - gold) / np.abs(gold)) <= 1e-5
+
+
+def test_alpha_beta_bf16_out(oracle):
+    """D = bf16(beta*C + alpha*A.B) with distinct C and D (the TensorCore2D_To contract,
+    src/klas/Klas.GEMM.TensorCore2D.To.Inst.fsti:65-66)."""
+    rows, shared, cols = 256, 320, 384
+    A, B = synth.gemm_bf16(7, rows, cols, shared, b_col_major=False, device="cuda")
+    Cin = synth.normal(7, 9, 0, rows * cols, torch.bfloat16, "cuda").view(rows, cols)
+    Cin_copy = Cin.clone()
+    D = klas.gemm_tc(A, B, out_dtype=torch.bfloat16, C_=Cin, alpha=0.7, beta=0.3)
+    acc, scale = tc_reference(oracle, A.cpu(), B.cpu(), False)
+    want = 0.3 * Cin.double().cpu().numpy() + 0.7 * acc
+    bound = 0.3 * np.abs(Cin.double().cpu().numpy()) + 0.7 * scale
+    # one bf16 rounding of the result (2^-9 relative) on top of the accumulation error
+    assert rel_err_componentwise(D.double().cpu().numpy(), want, bound) <= 2 ** -8
+    assert torch.equal(Cin, Cin_copy)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_accumulate_in_place(oracle, out_dtype):
+    """C += A.B (dist/Klas_GEMM_TensorCore.cu:28-33): D aliases C, alpha = beta = 1."""
+    rows, shared, cols = 128, 192, 128
+    A, B = synth.gemm_f16_batched(5, 1, rows, cols, shared, device="cuda")
+    C0 = synth.uniform(5, 7, 0, rows * cols, -1.0, 1.0, out_dtype, "cuda").view(rows, cols)
+    Cio = C0.clone()
+    klas.gemm_tc(A[0], B[0], out_dtype=out_dtype, C_=Cio, D=Cio, alpha=1.0, beta=1.0)
+    acc, scale = tc_reference(oracle, A[0].cpu(), B[0].cpu(), False)
+    want = C0.double().cpu().numpy() + acc
+    tol = 1e-2 if out_dtype == torch.float16 else 1e-5
+    assert rel_err_componentwise(Cio.double().cpu().numpy(), want, scale + np.abs(C0.double().cpu().numpy())) <= tol
+
+
+def test_batched_pages(oracle):
+    batch, m, n, k = 3, 192, 264, 136
+    A, B = synth.gemm_f16_batched(2, batch, m, n, k, device="cuda")
+    D = klas.gemm_tc(A, B, out_dtype=torch.float16)
+    for b in range(batch):
+        acc, scale = tc_reference(oracle, A[b].cpu(), B[b].cpu(), False)
+        assert rel_err_componentwise(D[b].double().cpu().numpy(), acc, scale) <= TOL_F16_F16
+
+
+def test_never_writes_outside_the_output(oracle):
+    """Canary rows around D stay intact for a ragged shape."""
+    rows, shared, cols = 200, 72, 136
+    A, B = synth.gemm_bf16(3, rows, cols, shared, b_col_major=True, device="cuda")
+    buf = torch.full((rows + 16, cols), 12345.0, device="cuda")
+    D = buf[8:8 + rows]
+    klas.gemm_tc(A, B, out_dtype=torch.float32, b_col_major=True, D=D)
+    torch.cuda.synchronize()
+    assert bool((buf[:8] == 12345.0).all()) and bool((buf[8 + rows:] == 12345.0).all())
+
+
+def test_linearity_at_full_size():
+    """Size-independent property at the benchmark's size (8192^3): (A1 + A2).B == A1.B + A2.B
+    when the sums are exact -- rows of small integers keep every product and partial sum
+    exactly representable, so the identity must hold bit for bit."""
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(1)
+    A1 = torch.randint(-3, 4, (n, n), device="cuda", generator=g).to(torch.bfloat16)
+    A2 = torch.randint(-3, 4, (n, n), device="cuda", generator=g).to(torch.bfloat16)
+    Bt = torch.randint(-3, 4, (n, n), device="cuda", generator=g).to(torch.bfloat16)
+    d1 = klas.gemm_tc(A1, Bt, b_col_major=True)
+    d2 = klas.gemm_tc(A2, Bt, b_col_major=True)
+    d12 = klas.gemm_tc((A1 + A2), Bt, b_col_major=True)
+    assert torch.equal(d12, d1 + d2)
+    # and a sampled exact check against an fp64 product of the same small integers
+    rows = torch.tensor([0, 1, 127, 128, 4095, 8191], device="cuda")
+    want = A1[rows].double() @ Bt.double().t()   # exact: every partial sum is a small integer
+    assert torch.equal(d1[rows].double(), want)
+
+
+def test_rejects_unsupported_shapes():
+    A = torch.zeros((64, 60), dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros((60, 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(klas.KlasError) as e:
+        klas.gemm_tc(A, B)
+    assert e.value.status == 2   # KLAS_ERR_UNSUPPORTED: shared % 8 != 0
+
+
+def test_zero_inner_dimension():
+    A = torch.zeros((64, 0), dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros((0, 64), dtype=torch.bfloat16, device="cuda")
+    D = torch.full((64, 64), 7.0, device="cuda")
+    klas.gemm_tc(A, B, D=D)
+    assert bool((D == 0).all())
