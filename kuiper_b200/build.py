@@ -72,5 +72,39 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+COMPAT_DIR = CSRC / "compat"
+COMPAT_OUT = LIB_DIR / "compat"
+COMPAT_LIB = LIB_DIR / "libklas_compat.so"
+
+
+def build_compat(force: bool = False) -> Path:
+    """Compiles one object per reference header (lib/compat/Klas_*.o, to be linked where the
+    reference links its own Klas_*.o) and bundles them into lib/libklas_compat.so."""
+    build_library(force=False)
+    COMPAT_OUT.mkdir(parents=True, exist_ok=True)
+    hdrs = sorted((INCLUDE_DIR / "klas").rglob("*.h")) + sorted((INCLUDE_DIR / "klas").rglob("*.inc")) + \
+        [COMPAT_DIR / "compat_common.h", INCLUDE_DIR / "klas_b200.h"]
+    procs, objs = [], []
+    for src in sorted(COMPAT_DIR.glob("Klas_*.cu")):
+        obj = COMPAT_OUT / (src.stem + ".o")
+        objs.append(obj)
+        if force or _stale(obj, [src] + hdrs):
+            cmd = [nvcc_path(), "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
+                   "-I", str(INCLUDE_DIR), "-I", str(INCLUDE_DIR / "klas"), "-I", str(COMPAT_DIR), "-c", str(src), "-o", str(obj)]
+            procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for cmd, p in procs:
+        out, _ = p.communicate()
+        if p.returncode != 0:
+            raise RuntimeError("nvcc failed: %s\n%s" % (" ".join(cmd), out))
+    if procs or not COMPAT_LIB.exists():
+        link = [nvcc_path(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(COMPAT_LIB), *map(str, objs),
+                "-L", str(LIB_DIR), "-lklas_b200", "-Xlinker", "-rpath=$ORIGIN"]
+        r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("link failed: %s\n%s" % (" ".join(link), r.stdout))
+    return COMPAT_LIB
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_compat(force="--force" in sys.argv))

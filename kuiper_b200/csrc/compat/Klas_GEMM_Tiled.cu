@@ -1,0 +1,7 @@
+// Reference-named entry points of Klas_GEMM_Tiled (FStarLang/kuiper dist/Klas_GEMM_Tiled.h), forwarded to the C ABI.
+// Link this object wherever the reference links its own Klas_GEMM_Tiled.o (nvcc.mk:22-26).
+#include "Klas_GEMM_Tiled.h"
+#undef KLAS_ENTRY
+#include "compat_common.h"
+
+KLAS_NUM_TYPES(KLAS_TILED_ENTRIES, Tiled)

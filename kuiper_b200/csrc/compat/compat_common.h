@@ -1,0 +1,103 @@
+// Bodies of the reference-named entry points: each one checks the reference's guards,
+// forwards to the C ABI of libklas_b200.so on the legacy default stream, and returns
+// only when the result is visible to every stream -- the blocking, void-returning
+// contract of the reference's wrappers (dist/Klas_GEMM_SHMem.cu:50-72,
+// include/kuiper.h:132-143).  Any failure prints the runtime's banner and ends the
+// process, as the reference's MUST / KPR_GUARD do.
+#pragma once
+
+#include <kuiper.h>
+
+#include "klas_b200.h"
+#include "klas_signatures.h"
+
+namespace klas_compat {
+
+static inline void finish(int status, const char *entry, bool tensor_core) {
+    if (status != KLAS_OK) {
+        fprintf(stderr, "*** ABORTING ***\n %s failed: %s\n", entry, klas_b200_last_error());
+        exit(1);
+    }
+    __MUST(cudaStreamSynchronize(0), "cudaStreamSynchronize", entry, __FILE__, __LINE__);
+    if (tensor_core && klas_b200_gemm_tc_status(NULL) != KLAS_OK) {
+        fprintf(stderr, "*** ABORTING ***\n %s failed: %s\n", entry, klas_b200_last_error());
+        exit(1);
+    }
+}
+
+}  // namespace klas_compat
+
+// dtype code of an element-type label
+#define KLAS_CODE_f32 KLAS_F32
+#define KLAS_CODE_f64 KLAS_F64
+#define KLAS_CODE_u32 KLAS_U32
+#define KLAS_CODE_u64 KLAS_U64
+#define KLAS_CODE_bf16 KLAS_BF16
+#define KLAS_CODE_f16 KLAS_F16
+
+#define KLAS_DIVIDES(TILE, V) KPR_GUARD((V) % (TILE) == 0U)
+
+// Guards of the statically tiled families (m, k, n in the reference's order); tile 0: none.
+#define KLAS_TILE_GUARDS_0
+#define KLAS_TILE_GUARDS_16 KLAS_DIVIDES(16U, m); KLAS_DIVIDES(16U, k); KLAS_DIVIDES(16U, n);
+#define KLAS_TILE_GUARDS_32 KLAS_DIVIDES(32U, m); KLAS_DIVIDES(32U, k); KLAS_DIVIDES(32U, n);
+#define KLAS_TILE_GUARDS(TILE) KLAS_TILE_GUARDS_##TILE
+
+#define KLAS_BODY_MATMUL(NAME, L, T, TILE)                                                        \
+    KLAS_TILE_GUARDS(TILE)                                                                        \
+    klas_compat::finish(klas_b200_gemm(KLAS_CODE_##L, KLAS_RRR, 1, m, n, k, NULL, NULL, gA, gB, gC, NULL), NAME, false);
+
+#define KLAS_BODY_MATMUL_DYNTILE(NAME, L, T, TILE) \
+    KPR_ASSERT(tile > 0U);                         \
+    KLAS_BODY_MATMUL(NAME, L, T, 0)
+
+#define KLAS_BODY_MATMUL_CCC(NAME, L, T, TILE) \
+    klas_compat::finish(klas_b200_gemm(KLAS_CODE_##L, KLAS_CCC, 1, m, n, k, NULL, NULL, gA, gB, gC, NULL), NAME, false);
+
+#define KLAS_BODY_GEMM(NAME, L, T, TILE)                                                          \
+    KLAS_TILE_GUARDS(TILE)                                                                        \
+    klas_compat::finish(klas_b200_gemm(KLAS_CODE_##L, KLAS_RRR, 1, m, n, k, &alpha, &beta, gA, gB, gC, NULL), NAME, false);
+
+#define KLAS_BODY_GEMM_DYNTILE(NAME, L, T, TILE) \
+    KPR_ASSERT(tile > 0U);                       \
+    KLAS_BODY_GEMM(NAME, L, T, 0)
+
+#define KLAS_BODY_BATCHED_MATMUL(NAME, L, T, TILE) \
+    klas_compat::finish(klas_b200_gemm(KLAS_F32, KLAS_RRR, batch, m, n, k, NULL, NULL, a, b, c, NULL), NAME, false);
+
+#define KLAS_BODY_BATCHED_GEMM(NAME, L, T, TILE) \
+    klas_compat::finish(klas_b200_gemm(KLAS_F32, KLAS_RRR, batch, m, n, k, &alpha, &beta, a, b, c, NULL), NAME, false);
+
+#define KLAS_BODY_BT2D(NAME, L, T, BM_, BN_, BK_)                                                 \
+    KLAS_DIVIDES(BM_##U, m);                                                                      \
+    KLAS_DIVIDES(BK_##U, k);                                                                      \
+    KLAS_DIVIDES(BN_##U, n);                                                                      \
+    klas_compat::finish(klas_b200_gemm(KLAS_CODE_##L, KLAS_RRR, 1, m, n, k, &alpha, &beta, gA, gB, gC, NULL), NAME, false);
+
+#define KLAS_TC_GUARDS(GR, GS, GC) \
+    KLAS_DIVIDES(GR##U, rows);     \
+    KLAS_DIVIDES(GS##U, shared);   \
+    KLAS_DIVIDES(GC##U, cols);
+
+#define KLAS_BODY_TC2D(NAME, IN, OUT, BM_, BN_, BK_)                                              \
+    KLAS_TC_GUARDS(BM_, BK_, BN_)                                                                 \
+    klas_compat::finish(klas_b200_gemm_tc(IN, OUT, KLAS_B_ROW_MAJOR, 1, rows, shared, cols, gA, gB, NULL, gC, \
+                                          1.0f, 0.0f, NULL, NULL), NAME, true);
+
+#define KLAS_BODY_TC2D_TO(NAME, IN, OUT, BM_, BN_, BK_)                                           \
+    KLAS_TC_GUARDS(BM_, BK_, BN_)                                                                 \
+    klas_compat::finish(klas_b200_gemm_tc(IN, OUT, KLAS_B_ROW_MAJOR, 1, rows, shared, cols, gA, gB, gC, gD, \
+                                          alpha, beta, NULL, NULL), NAME, true);
+
+// C += A.B: the accumulator starts from C (dist/Klas_GEMM_TensorCore.cu:28-33).
+#define KLAS_BODY_TC1D(NAME, L, TC, GR, GS, GC)                                                   \
+    KLAS_TC_GUARDS(GR, GS, GC)                                                                    \
+    klas_compat::finish(klas_b200_gemm_tc(KLAS_F16, KLAS_CODE_##L, KLAS_B_ROW_MAJOR, 1, rows, shared, cols, gA, \
+                                          gB, gC, gC, 1.0f, 1.0f, NULL, NULL), NAME, true);
+
+#define KLAS_BODY_SPMM(NAME, CODE, T, UNUSED)                                                     \
+    klas_compat::finish(klas_b200_spmm(CODE, rows, shared, cols, gA.nnz, gA.elems, gA.col_ind, gA.row_off, \
+                                       row_indices, gB, gC, NULL), NAME, false);
+
+#define KLAS_ENTRY(name, params, KIND, ...) \
+    void name params { KLAS_BODY_##KIND(#name, __VA_ARGS__) }

@@ -1,14 +1,22 @@
 // Tensor-core GEMM for sm_100a: D = out( alpha * A.B + beta * C ).
 //
-// One persistent, warp-specialised CTA per SM walks a rasterised list of
-// 128 x 256 output tiles:
-//   warp 0      TMA producer: streams 128x64 A tiles and 256x64 B tiles (bf16/f16,
-//               128-byte swizzle) through a 4-stage shared-memory ring;
-//   warp 1      owns tensor memory and issues tcgen05.mma (M=128, N=256, K=16) from
+// Persistent, warp-specialised CTAs walk a rasterised list of output tiles:
+//   warp 0      TMA producer: streams 128x64 A tiles and 64-deep B tiles (bf16/f16,
+//               128-byte swizzle) through a shared-memory ring;
+//   warp 1      owns tensor memory and issues tcgen05.mma (K=16 per instruction) from
 //               one thread; the fp32 accumulator lives in TMEM, double-buffered
 //               (2 x 256 columns) so tile i+1's main loop overlaps tile i's epilogue;
 //   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, apply
 //               alpha/beta, convert, and store to global memory.
+// Two instantiations:
+//   single   one CTA per 128 x 256 tile, 4 stages of 48 KiB (small problems);
+//   pair     two CTAs of a cluster share a 256 x 256 tile (cta_group::2): each stages
+//            its own 128 rows of A and its own 128 columns of B (32 KiB per stage,
+//            6 stages), the even CTA issues M=256 MMAs that read both CTAs' shared
+//            memory, and each CTA drains its own 128 accumulator rows.  Per SM this
+//            halves the B bytes staged and read per flop.  Every load is an ordinary
+//            per-CTA TMA load; completion of the odd CTA's loads is counted on the even
+//            CTA's barrier.
 // All hand-offs are mbarriers; every wait is bounded in time and a wait that
 // gives up raises a status word and makes all roles drain and return.
 //
@@ -21,32 +29,58 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "klas_internal.h"
 #include "ptx_sm100.cuh"
 
 namespace klas {
 namespace umma {
 
-constexpr uint32_t BM = 128;
-constexpr uint32_t BN = 256;
-constexpr uint32_t BK = 64;  // 64 x 2 bytes = one 128-byte swizzle row
+constexpr uint32_t BM = 128;  // accumulator rows per CTA (= TMEM lanes)
+constexpr uint32_t BN = 256;  // accumulator columns per tile
+constexpr uint32_t BK = 64;   // 64 x 2 bytes = one 128-byte swizzle row
 constexpr uint32_t UMMA_K = 16;
-constexpr uint32_t STAGES = 4;
 constexpr uint32_t A_STAGE_BYTES = BM * BK * 2;
-constexpr uint32_t B_STAGE_BYTES = BN * BK * 2;
-constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr uint32_t B_CHUNK_BYTES = 64 * BK * 2;  // one 64-column slab of a row-major B tile
 constexpr uint32_t ACC_STAGES = 2;
 constexpr uint32_t TMEM_COLS = ACC_STAGES * BN;  // 512 = all of tensor memory
 constexpr uint32_t NUM_THREADS = 192;
 constexpr uint32_t NUM_EPI_WARPS = 4;
 constexpr uint32_t BARRIER_BYTES = 256;
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;  // + alignment slack
-constexpr uint32_t RASTER_GROUP = 8;  // tile columns swept together for L2 reuse
+constexpr uint32_t DEFAULT_RASTER_GROUP = 8;  // tile columns swept together for L2 reuse
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
+
+template <bool PAIR>
+struct Shape {
+    static constexpr uint32_t CTAS = PAIR ? 2 : 1;
+    static constexpr uint32_t TILE_M = BM * CTAS;     // rows of one tile of the CTA group
+    static constexpr uint32_t B_COLS = BN / CTAS;     // B columns staged by each CTA
+    static constexpr uint32_t STAGES = PAIR ? 6 : 4;
+    static constexpr uint32_t B_STAGE_BYTES = B_COLS * BK * 2;
+    static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;
+};
 
 // First failing wait of the most recent launches on this device (0 = none).
 __device__ int g_umma_status;
+
+#ifdef KLAS_UMMA_PROFILE
+// Developer build only: per-CTA cycle counts of each role's waits.
+// [cta][0] producer waiting for a free stage, [1] MMA waiting for data, [2] MMA waiting for a
+// free accumulator, [3] epilogue waiting for an accumulator, [4] whole kernel, [5] epilogue busy.
+__device__ unsigned long long g_umma_prof[1024][8];
+#define KLAS_PROF_DECL unsigned long long prof_acc0 = 0, prof_acc1 = 0, prof_acc2 = 0
+#define KLAS_PROF_BEGIN const long long prof_t0 = clock64()
+#define KLAS_PROF_END(acc) acc += (unsigned long long)(clock64() - prof_t0)
+#define KLAS_PROF_STORE(slot, acc) if (lane == 0 && blockIdx.x < 1024) g_umma_prof[blockIdx.x][slot] = acc
+#else
+#define KLAS_PROF_DECL
+#define KLAS_PROF_BEGIN
+#define KLAS_PROF_END(acc)
+#define KLAS_PROF_STORE(slot, acc)
+#endif
 
 struct Params {
     const void *C;
@@ -56,6 +90,7 @@ struct Params {
     float alpha, beta;
     uint32_t idesc;
     uint32_t b_row_major;  // 1: B is K x N (N contiguous) -> MN-major operand
+    uint32_t raster_group; // tile columns swept together before moving down the rows
     int *status;           // optional caller-visible copy of the status word
 };
 
@@ -103,10 +138,10 @@ __device__ __forceinline__ void decode_tile(uint32_t t, const Params &p, uint32_
     const uint32_t per_batch = p.tiles_m * p.tiles_n;
     b = t / per_batch;
     const uint32_t r = t - b * per_batch;
-    const uint32_t group_tiles = RASTER_GROUP * p.tiles_m;
+    const uint32_t group_tiles = p.raster_group * p.tiles_m;
     const uint32_t g = r / group_tiles;
-    const uint32_t first_n = g * RASTER_GROUP;
-    const uint32_t width = min(RASTER_GROUP, p.tiles_n - first_n);
+    const uint32_t first_n = g * p.raster_group;
+    const uint32_t width = min(p.raster_group, p.tiles_n - first_n);
     const uint32_t in = r - g * group_tiles;
     tm = in / width;
     tn = first_n + in % width;
@@ -138,8 +173,8 @@ struct OutTraits<__nv_bfloat16> {
 // the accumulator) with 16-byte accesses.  `ncols_left` = columns of the matrix
 // remaining from the first of the 32 (a multiple of 8 by the entry point's contract).
 template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT *__restrict__ drow,
-                                                const OutT *__restrict__ crow, float alpha,
+__device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT *drow,
+                                                const OutT *crow, float alpha,
                                                 float beta, uint32_t ncols_left) {
     constexpr uint32_t VEC = 16 / sizeof(OutT);  // elements per 16-byte access
 #pragma unroll
@@ -167,12 +202,17 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT 
     }
 }
 
-template <typename OutT>
+template <typename OutT, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b, const Params p) {
+    using S = Shape<PAIR>;
+    constexpr uint32_t STAGES = S::STAGES;
+    constexpr uint32_t STAGE_BYTES = S::STAGE_BYTES;
+
     extern __shared__ uint8_t smem_raw[];
-    // 128-byte swizzled tiles need 1024-byte aligned bases.
+    // 128-byte swizzled tiles need 1024-byte aligned bases.  The dynamic shared window
+    // starts at the same offset in both CTAs of a pair, so the padding is identical.
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t *smem = smem_raw + pad;
@@ -190,6 +230,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
+    const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;  // 0 = the CTA that issues MMAs
+    const uint32_t group = blockIdx.x / S::CTAS;                    // index of this CTA group
+    const uint32_t num_groups = gridDim.x / S::CTAS;
     const Ctl ctl{abort_flag, p.status};
 
     if (threadIdx.x == 0) {
@@ -199,7 +242,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         for (uint32_t a = 0; a < ACC_STAGES; ++a) {
             ptx::mbar_init(tfull_bar(a), 1);
-            ptx::mbar_init(tempty_bar(a), NUM_EPI_WARPS);
+            ptx::mbar_init(tempty_bar(a), NUM_EPI_WARPS * S::CTAS);
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -210,11 +253,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         ptx::prefetch_tensormap(&tm_b);
     }
     if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
-        ptx::tmem_relinquish();
+        if constexpr (PAIR) {
+            ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
+            ptx::tmem_relinquish();
+        }
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) {
+        // both CTAs' barriers must exist before either side signals the other's
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -222,28 +275,46 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         // ------------------------------------------------------------ producer
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        for (uint32_t t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        KLAS_PROF_DECL;
+        for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             uint32_t b, tm, tn;
             decode_tile(t, p, b, tm, tn);
+            const int32_t a_row = int32_t(tm * S::TILE_M + cta_rank * BM);
+            const int32_t b_col = int32_t(tn * BN + cta_rank * S::B_COLS);
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                KLAS_PROF_BEGIN;
                 ok = bounded_wait(empty_bar(stage), phase ^ 1u, ctl, SITE_PRODUCER_EMPTY);
+                KLAS_PROF_END(prof_acc0);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 if (lane == 0) {
                     const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-                    ptx::mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
-                    ptx::tma_load_3d(a_dst, &tm_a, full_bar(stage), int32_t(kb * BK),
-                                     int32_t(tm * BM), int32_t(b));
-                    if (p.b_row_major) {
+                    const int32_t k0 = int32_t(kb * BK);
+                    if constexpr (PAIR) {
+                        // the even CTA's barrier counts the bytes of both CTAs' loads
+                        if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+                        const uint32_t bar = ptx::map_to_cta(full_bar(stage), 0);
+                        ptx::tma_load_3d_pair(a_dst, &tm_a, bar, k0, a_row, int32_t(b));
+                        if (p.b_row_major) {
 #pragma unroll
-                        for (uint32_t j = 0; j < BN / 64; ++j)
-                            ptx::tma_load_3d(b_dst + j * B_CHUNK_BYTES, &tm_b, full_bar(stage),
-                                             int32_t(tn * BN + j * 64), int32_t(kb * BK),
-                                             int32_t(b));
+                            for (uint32_t j = 0; j < S::B_COLS / 64; ++j)
+                                ptx::tma_load_3d_pair(b_dst + j * B_CHUNK_BYTES, &tm_b, bar,
+                                                      b_col + int32_t(j * 64), k0, int32_t(b));
+                        } else {
+                            ptx::tma_load_3d_pair(b_dst, &tm_b, bar, k0, b_col, int32_t(b));
+                        }
                     } else {
-                        ptx::tma_load_3d(b_dst, &tm_b, full_bar(stage), int32_t(kb * BK),
-                                         int32_t(tn * BN), int32_t(b));
+                        ptx::mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+                        ptx::tma_load_3d(a_dst, &tm_a, full_bar(stage), k0, a_row, int32_t(b));
+                        if (p.b_row_major) {
+#pragma unroll
+                            for (uint32_t j = 0; j < S::B_COLS / 64; ++j)
+                                ptx::tma_load_3d(b_dst + j * B_CHUNK_BYTES, &tm_b, full_bar(stage),
+                                                 b_col + int32_t(j * 64), k0, int32_t(b));
+                        } else {
+                            ptx::tma_load_3d(b_dst, &tm_b, full_bar(stage), k0, b_col, int32_t(b));
+                        }
                     }
                 }
                 __syncwarp();
@@ -253,6 +324,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
             }
         }
+        KLAS_PROF_STORE(0, prof_acc0);
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         // K-major operand: 8-row groups 1024 bytes apart; a K step of 16 elements = 32 bytes.
@@ -264,18 +336,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const uint32_t b_kstep = p.b_row_major ? UMMA_K * 128u : UMMA_K * 2u;
         uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
         bool ok = true;
-        for (uint32_t t = blockIdx.x; ok && p.num_kb > 0 && t < p.num_tiles; t += gridDim.x) {
-            ok = bounded_wait(tempty_bar(acc), acc_phase ^ 1u, ctl, SITE_MMA_TMEM_EMPTY);
+        const bool issuer = cta_rank == 0;
+        KLAS_PROF_DECL;
+        for (uint32_t t = group; issuer && ok && p.num_kb > 0 && t < p.num_tiles; t += num_groups) {
+            {
+                KLAS_PROF_BEGIN;
+                ok = bounded_wait(tempty_bar(acc), acc_phase ^ 1u, ctl, SITE_MMA_TMEM_EMPTY);
+                KLAS_PROF_END(prof_acc2);
+            }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             ptx::tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + acc * BN;
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                KLAS_PROF_BEGIN;
                 ok = bounded_wait(full_bar(stage), phase, ctl, SITE_MMA_FULL);
+                KLAS_PROF_END(prof_acc0);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 if (lane == 0) {
+#ifdef KLAS_UMMA_PROFILE
+                    const long long prof_i0 = clock64();
+#endif
                     const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
                     const uint32_t b_addr = a_addr + A_STAGE_BYTES;
 #pragma unroll
@@ -283,10 +366,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         const uint64_t a_desc =
                             ptx::umma_desc_at(a_desc_base, a_addr + kk * UMMA_K * 2u);
                         const uint64_t b_desc = ptx::umma_desc_at(b_desc_base, b_addr + kk * b_kstep);
-                        ptx::umma_f16_ss(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if constexpr (PAIR)
+                            ptx::umma_f16_ss_pair(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+                        else
+                            ptx::umma_f16_ss(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
-                    ptx::umma_commit(empty_bar(stage));  // frees the smem stage when the MMAs retire
-                    if (kb + 1 == p.num_kb) ptx::umma_commit(tfull_bar(acc));
+                    // free the shared-memory stage (in both CTAs) once these MMAs retire
+                    if constexpr (PAIR) {
+                        ptx::umma_commit_pair(ptx::map_to_cta(empty_bar(stage), 0));
+                        ptx::umma_commit_pair(ptx::map_to_cta(empty_bar(stage), 1));
+                        if (kb + 1 == p.num_kb) {
+                            ptx::umma_commit_pair(ptx::map_to_cta(tfull_bar(acc), 0));
+                            ptx::umma_commit_pair(ptx::map_to_cta(tfull_bar(acc), 1));
+                        }
+                    } else {
+                        ptx::umma_commit(empty_bar(stage));
+                        if (kb + 1 == p.num_kb) ptx::umma_commit(tfull_bar(acc));
+                    }
+#ifdef KLAS_UMMA_PROFILE
+                    prof_acc1 += (unsigned long long)(clock64() - prof_i0);
+#endif
                 }
                 __syncwarp();
                 if (++stage == STAGES) {
@@ -299,6 +398,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 acc_phase ^= 1u;
             }
         }
+        KLAS_PROF_STORE(1, prof_acc0);
+        KLAS_PROF_STORE(2, prof_acc2);
+        KLAS_PROF_STORE(6, prof_acc1);
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
@@ -306,16 +408,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const OutT *const C = static_cast<const OutT *>(p.C);
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
-        for (uint32_t t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        KLAS_PROF_DECL;
+#ifdef KLAS_UMMA_PROFILE
+        const long long prof_start = clock64();
+#endif
+        for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             uint32_t b, tm, tn;
             decode_tile(t, p, b, tm, tn);
             if (p.num_kb > 0) {
+                KLAS_PROF_BEGIN;
                 ok = bounded_wait(tfull_bar(acc), acc_phase, ctl, SITE_EPI_TMEM_FULL);
+                KLAS_PROF_END(prof_acc0);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
             }
-            const uint32_t row = tm * BM + quad * 32u + lane;
+            const uint32_t row = tm * S::TILE_M + cta_rank * BM + quad * 32u + lane;
             const uint32_t col0 = tn * BN;
             const size_t row_off = (size_t(b) * p.M + row) * size_t(p.N);
 #pragma unroll 1
@@ -337,18 +445,38 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (p.num_kb > 0) {
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+                if (lane == 0) {
+                    // the accumulator stage is free when both CTAs' epilogues have drained it
+                    if constexpr (PAIR)
+                        ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(acc), 0));
+                    else
+                        ptx::mbar_arrive(tempty_bar(acc));
+                }
                 if (++acc == ACC_STAGES) {
                     acc = 0;
                     acc_phase ^= 1u;
                 }
             }
         }
+#ifdef KLAS_UMMA_PROFILE
+        if (warp == 2) {
+            KLAS_PROF_STORE(3, prof_acc0);
+            KLAS_PROF_STORE(5, (unsigned long long)(clock64() - prof_start));
+        }
+#endif
     }
 
+#ifdef KLAS_UMMA_PROFILE
+    if (warp == 2 && lane == 0 && blockIdx.x < 1024) g_umma_prof[blockIdx.x][4] = (unsigned long long)clock64();
+#endif
     // ---------------------------------------------------------------- teardown
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) {
+        // neither CTA may leave while its partner can still touch its barriers or operands
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         if (*abort_flag != 0) {
@@ -356,7 +484,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // tensor memory and this CTA's shared memory are handed back.
             for (int i = 0; i < 256; ++i) __nanosleep(1000);
         }
-        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+        if constexpr (PAIR)
+            ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else
+            ptx::tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -403,25 +534,51 @@ static int make_map_16bit(CUtensorMap *map, int dtype, const void *base, uint64_
     return KLAS_OK;
 }
 
-template <typename OutT>
+template <typename OutT, bool PAIR>
 static int launch_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
                         cudaStream_t stream) {
+    constexpr uint32_t SMEM = Shape<PAIR>::SMEM_BYTES;
     static bool configured[64] = {};
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
-        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<OutT>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured[dev] = true;
-    } else if (dev >= 64) {
-        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<OutT>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<OutT, PAIR>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    gemm_umma_kernel<OutT><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
-    return check_cuda(cudaGetLastError(), "gemm_umma_kernel launch");
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_kernel<OutT, PAIR>, ta, tb, p),
+                      "gemm_umma_kernel launch");
+}
+
+template <bool PAIR>
+static int launch_mode(int out_dtype, const CUtensorMap &ta, const CUtensorMap &tb, const Params &p,
+                       int grid, cudaStream_t stream) {
+    switch (out_dtype) {
+        case KLAS_F32: return launch_typed<float, PAIR>(ta, tb, p, grid, stream);
+        case KLAS_F16: return launch_typed<__half, PAIR>(ta, tb, p, grid, stream);
+        default: return launch_typed<__nv_bfloat16, PAIR>(ta, tb, p, grid, stream);
+    }
 }
 
 }  // namespace umma
+
+#ifdef KLAS_UMMA_PROFILE
+extern "C" int klas_dev_read_umma_profile(unsigned long long *out) {
+    return cudaMemcpyFromSymbol(out, umma::g_umma_prof, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int umma_read_status(int *value) {
     return check_cuda(cudaMemcpyFromSymbol(value, umma::g_umma_status, sizeof(int)),
@@ -463,6 +620,16 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
         return fail(KLAS_ERR_UNSUPPORTED, "gemm_tc needs an sm_100 device (found sm_%d%d)",
                     info.cc_major, info.cc_minor);
 
+    // Tile shape: CTA pairs (256 x 256 tiles) once the problem fills the machine, single
+    // CTAs (128 x 256) below that.  KLAS_TC_MODE=single|pair overrides the choice.
+    const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
+    bool pair = rows > BM && single_tiles >= uint64_t(info.sm_count) && info.sm_count >= 2;
+    if (const char *mode = getenv("KLAS_TC_MODE")) {
+        if (!strcmp(mode, "single")) pair = false;
+        else if (!strcmp(mode, "pair")) pair = info.sm_count >= 2;
+    }
+    const uint32_t tile_m = pair ? Shape<true>::TILE_M : Shape<false>::TILE_M;
+
     Params p{};
     p.C = C;
     p.D = D;
@@ -470,7 +637,7 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
     p.N = uint32_t(cols);
     p.K = uint32_t(shared);
     p.batch = batch;
-    p.tiles_m = uint32_t((rows + BM - 1) / BM);
+    p.tiles_m = uint32_t((rows + tile_m - 1) / tile_m);
     p.tiles_n = uint32_t((cols + BN - 1) / BN);
     const uint64_t num_tiles = uint64_t(p.tiles_m) * p.tiles_n * batch;
     if (num_tiles > 0xffffffffull) return fail(KLAS_ERR_TOO_LARGE, "gemm_tc: too many tiles");
@@ -479,24 +646,30 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
     p.alpha = alpha;
     p.beta = beta;
     p.b_row_major = (b_major == KLAS_B_ROW_MAJOR) ? 1u : 0u;
-    p.idesc = ptx::umma_idesc_f16(in_dtype == KLAS_BF16, false, p.b_row_major != 0, BM, BN);
+    p.idesc = ptx::umma_idesc_f16(in_dtype == KLAS_BF16, false, p.b_row_major != 0, tile_m, BN);
     p.status = status_word;
+    p.raster_group = DEFAULT_RASTER_GROUP;
+    if (const char *rg = getenv("KLAS_TC_RASTER")) {
+        const int v = atoi(rg);
+        if (v >= 1 && v <= 1024) p.raster_group = uint32_t(v);
+    }
 
+    const uint32_t b_cols = pair ? Shape<true>::B_COLS : Shape<false>::B_COLS;
     CUtensorMap ta{}, tb{};
     if (shared > 0) {
         if (int rc = make_map_16bit(&ta, in_dtype, A, shared, rows, batch, BK, BM)) return rc;
         if (p.b_row_major) {
             if (int rc = make_map_16bit(&tb, in_dtype, B, cols, shared, batch, 64, BK)) return rc;
         } else {
-            if (int rc = make_map_16bit(&tb, in_dtype, B, shared, cols, batch, BK, BN)) return rc;
+            if (int rc = make_map_16bit(&tb, in_dtype, B, shared, cols, batch, BK, b_cols)) return rc;
         }
     }
-    const int grid = int(num_tiles < uint64_t(info.sm_count) ? num_tiles : uint64_t(info.sm_count));
-    switch (out_dtype) {
-        case KLAS_F32: return launch_typed<float>(ta, tb, p, grid, stream);
-        case KLAS_F16: return launch_typed<__half>(ta, tb, p, grid, stream);
-        default: return launch_typed<__nv_bfloat16>(ta, tb, p, grid, stream);
+    if (pair) {
+        const uint64_t groups = num_tiles < uint64_t(info.sm_count / 2) ? num_tiles : uint64_t(info.sm_count / 2);
+        return launch_mode<true>(out_dtype, ta, tb, p, int(groups * 2), stream);
     }
+    const int grid = int(num_tiles < uint64_t(info.sm_count) ? num_tiles : uint64_t(info.sm_count));
+    return launch_mode<false>(out_dtype, ta, tb, p, grid, stream);
 }
 
 }  // namespace klas

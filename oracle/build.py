@@ -19,6 +19,8 @@ from pathlib import Path
 
 ORACLE_DIR = Path(__file__).resolve().parent
 REPO_DIR = ORACLE_DIR.parent
+if str(REPO_DIR) not in sys.path:
+    sys.path.insert(0, str(REPO_DIR))
 ORACLE_LIB = ORACLE_DIR / "libklas_oracle.so"
 REF_DIR = ORACLE_DIR / "_ref"
 DEFAULT_REF_ROOT = Path("/root/reference")
@@ -93,6 +95,38 @@ def build_ref_gpu(ref_root: Path, force: bool = False) -> Path:
     return out
 
 
+HOT_PATH_DRIVER_GLOBS = ("Test_Klas_GEMM_*.cu", "Test_Klas_SPMM__*.cu")
+
+
+def build_ref_drivers(ref_root: Path, force: bool = False) -> Path:
+    """The reference's own hot-path test drivers (test/Test_Klas_GEMM_*.cu, test/Test_Klas_SPMM__*.cu),
+    compiled UNCHANGED from where they lie, against this repository's headers (include/klas) and linked
+    with this repository's compatibility objects and libklas_b200.so -- the reference's link rule
+    Test_X__Y.exe = Test_X__Y.o + X.o (nvcc.mk:13,22-26) with X.o replaced.  Also writes
+    expected/<driver>.txt = the reference's golden stdout (test/*.output.expected)."""
+    from kuiper_b200 import build as lib_build
+    lib_build.build_compat()
+    out_dir = REF_DIR / "drivers"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    inc = REPO_DIR / "include"
+    srcs = sorted(p for g in HOT_PATH_DRIVER_GLOBS for p in (ref_root / "test").glob(g))
+
+    def one(src: Path):
+        exe = out_dir / (src.stem + ".exe")
+        if not force and exe.exists() and exe.stat().st_mtime >= (lib_build.COMPAT_LIB.stat().st_mtime):
+            return exe
+        unit = src.stem[len("Test_"):].split("__")[0]          # Test_Klas_GEMM_SHMem__F32 -> Klas_GEMM_SHMem
+        obj = lib_build.COMPAT_OUT / (unit + ".o")
+        _run(["nvcc", "-O3", *ARCH, "-DKUIPER_CFG_TENSORCORES=1", "-I", inc / "klas", "-I", ref_root / "test",
+              "-o", exe, src, obj, "-L", lib_build.LIB_DIR, "-lklas_b200",
+              "-Xlinker", "-rpath=$ORIGIN/../../../kuiper_b200/lib"])
+        return exe
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+        exes = list(ex.map(one, srcs))
+    return out_dir if exes else out_dir
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref-root", type=Path, default=DEFAULT_REF_ROOT)
@@ -104,6 +138,7 @@ def main(argv=None) -> int:
         print(build_ref_cpu(a.ref_root, a.force))
         if not a.no_ref_gpu:
             print(build_ref_gpu(a.ref_root, a.force))
+        print(build_ref_drivers(a.ref_root, a.force))
     else:
         print("reference tree not mounted at %s: oracle/_ref not (re)built" % a.ref_root)
     return 0

@@ -1,0 +1,75 @@
+"""The reference-name layer: the compatibility objects export exactly the reference's mangled
+symbols, the instance grids match, and the public headers still compile as the reference's do."""
+import subprocess
+from pathlib import Path
+
+import pytest
+
+REPO = Path(__file__).resolve().parent.parent
+GOLD = Path(__file__).parent / "golden"
+
+
+@pytest.fixture(scope="module")
+def compat():
+    from kuiper_b200 import build
+    build.build_compat()
+    return build
+
+
+def exported(path):
+    out = subprocess.run(["nm", "--defined-only", str(path)], capture_output=True, text=True, check=True).stdout
+    return {p[2] for p in (line.split() for line in out.splitlines()) if len(p) == 3 and p[1] == "T"}
+
+
+def test_every_reference_symbol_is_exported(compat):
+    want = set((GOLD / "klas_symbols.txt").read_text().split())
+    assert len(want) == 554
+    got = set()
+    for obj in sorted(compat.COMPAT_OUT.glob("Klas_*.o")):
+        got |= exported(obj)
+    assert want <= got, sorted(want - got)[:5]
+    assert got == want            # and nothing else with external linkage
+
+
+def test_one_object_per_reference_header(compat):
+    units = {p.stem for p in compat.COMPAT_OUT.glob("Klas_*.o")}
+    assert units == {"Klas_GEMM_SHMem", "Klas_GEMM_Tiled", "Klas_GEMM_BlockTiling1D", "Klas_GEMM_BlockTiling2D",
+                     "Klas_GEMM_Naive1", "Klas_GEMM_Naive2", "Klas_GEMM_Naive3", "Klas_GEMM_TensorCore",
+                     "Klas_GEMM_TensorCore2D", "Klas_GEMM_TensorCore2D_To", "Klas_SPMM"}
+    for u in units:
+        assert (REPO / "include" / "klas" / (u + ".h")).exists()
+
+
+def test_grids_regenerate_identically(tmp_path):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("gen_grids", REPO / "kuiper_b200" / "csrc" / "compat" / "gen_grids.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    assert len(list(gen.tc2d())) == 72 and len(list(gen.bt2d())) == 72 and len(list(gen.spmm())) == 91
+    gen.OUT = tmp_path
+    gen.main()
+    for name in ("tc2d.inc", "bt2d.inc", "spmm.inc"):
+        assert (tmp_path / name).read_text() == (REPO / "include" / "klas" / "grids" / name).read_text()
+
+
+def test_python_mirror_knows_every_reference_name():
+    """kuiper_b200.klas.call() parses every exported entry-point name."""
+    from kuiper_b200 import klas
+    names = [n.split("(")[0] for n in subprocess.run(["c++filt"], input=(GOLD / "klas_symbols.txt").read_text(),
+                                                      capture_output=True, text=True, check=True).stdout.split("\n") if n]
+    assert len(names) == 554
+    pats = [klas._RE_TILED, klas._RE_BT2D, klas._RE_NAIVE, klas._RE_NAIVE_B, klas._RE_TC2D, klas._RE_TC2D_TO,
+            klas._RE_TC1D, klas._RE_SPMM]
+    for n in names:
+        assert any(p.match(n) for p in pats), n
+
+
+def test_shim_header_serves_kuiper_h_users(tmp_path):
+    src = tmp_path / "t.cu"
+    src.write_text('#include <kuiper.h>\n#include "Klas_SPMM.h"\n#include "Klas_GEMM_TensorCore2D_To.h"\n'
+                   '__global__ void k(int *p) { char *s = (char *)KPR_SHMEM_AT(4); p[0] = s[0]; }\n'
+                   'int main() { void *p = KPR_GPU_ALLOC(4, 1); cudaStream_t s = KPR_FRESH_STREAM();\n'
+                   '  KPR_KCALL(k, 0, 32, 16, s, (int *)p); KPR_GUARD(1 == 1); KPR_ASSERT(2 > 1); KPR_SHMEM_FITS(100);\n'
+                   '  MUST(cudaStreamDestroy(s)); Kuiper_Sparse_Matrix_smatrix__float m; m.nnz = 0; return (int)m.nnz; }\n')
+    subprocess.run(["nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", str(REPO / "include" / "klas"),
+                    "-c", str(src), "-o", str(tmp_path / "t.o")], check=True)

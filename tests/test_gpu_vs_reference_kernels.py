@@ -1,0 +1,131 @@
+"""Same seeded inputs through this library and through the reference's own kernels (dist/Klas_*.cu
+compiled for sm_100a, oracle/_ref): results must agree -- bit for bit for integers, within the
+float tolerances otherwise -- and the timings of both go to gpurun_out/ref_kernel_timings.json."""
+import ctypes as C
+import json
+import time
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from kuiper_b200 import klas, synth
+from ref_gpu import RefGpu
+
+pytestmark = pytest.mark.gpu
+
+OUT = Path(__file__).resolve().parent.parent / "gpurun_out"
+TIMINGS = {}
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not RefGpu.available():
+        pytest.skip("oracle/_ref/libklas_ref_gpu.so not built")
+    yield RefGpu()
+    OUT.mkdir(exist_ok=True)
+    (OUT / "ref_kernel_timings.json").write_text(json.dumps(TIMINGS, indent=1))
+
+
+def wall_ms(fn, reps=3):
+    """Per-call wall time of a blocking call, as the reference's drivers measure it."""
+    fn()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    return (time.perf_counter() - t0) / reps * 1e3
+
+
+def event_ms(fn, reps=5):
+    fn()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(reps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / reps
+
+
+def test_f32_1024(ref):
+    n = 1024
+    A, B = synth.gemm_f32(0, n, n, n, device="cuda")
+    mine, theirs = torch.zeros((n, n), device="cuda"), torch.zeros((n, n), device="cuda")
+    klas.call("Klas_GEMM_SHMem_g_matmul_f32_tile32_rrr", n, n, n, A, B, mine)
+    ref.mnk("Klas_GEMM_SHMem_g_matmul_f32_tile32_rrr", n, n, n, A, B, theirs)
+    scale = (A.abs().double() @ B.abs().double())
+    assert float(((mine.double() - theirs.double()).abs() / scale).max()) <= 2e-5
+    TIMINGS["f32_1024"] = {
+        "ours_kernel_ms": event_ms(lambda: klas.gemm(A, B, mine)),
+        "ref_SHMem_tile32_call_ms": wall_ms(lambda: ref.mnk("Klas_GEMM_SHMem_g_matmul_f32_tile32_rrr", n, n, n, A, B, theirs)),
+        "ref_BlockTiling2D_128x128x32_8x8_call_ms": wall_ms(lambda: ref.mnk(
+            "Klas_GEMM_BlockTiling2D_g_gemm_f32_128x128x32_8x8", n, n, n, A, B, theirs,
+            pre=((C.c_float, 1.0), (C.c_float, 0.0)))),
+        "flop": 2 * n ** 3}
+
+
+def test_u64_bit_exact(ref):
+    n = 1024
+    a, b = synth.gemm_u64(3, n, n, n, full_range=True, device="cuda")
+    mine, theirs = torch.zeros((n, n), dtype=torch.int64, device="cuda"), torch.zeros((n, n), dtype=torch.int64, device="cuda")
+    klas.call("Klas_GEMM_SHMem_g_matmul_u64_tile32_rrr", n, n, n, a, b, mine)
+    ref.mnk("Klas_GEMM_SHMem_g_matmul_u64_tile32_rrr", n, n, n, a, b, theirs)
+    assert torch.equal(mine, theirs)
+    n = 4096
+    a, b = synth.gemm_u64(3, n, n, n, device="cuda")
+    mine, theirs = torch.zeros((n, n), dtype=torch.int64, device="cuda"), torch.zeros((n, n), dtype=torch.int64, device="cuda")
+    t_ref = wall_ms(lambda: ref.mnk("Klas_GEMM_SHMem_g_matmul_u64_tile32_rrr", n, n, n, a, b, theirs), reps=1)
+    t_ours = event_ms(lambda: klas.gemm(a, b, mine), reps=2)
+    assert torch.equal(mine, theirs)          # the 4096^3 benchmark configuration, bit for bit
+    TIMINGS["u64_4096"] = {"ours_kernel_ms": t_ours, "ref_SHMem_tile32_call_ms": t_ref, "ops": 2 * n ** 3}
+
+
+@pytest.mark.parametrize("n", [1024, 4096])
+def test_bf16_f32(ref, n):
+    A, B = synth.gemm_bf16(1, n, n, n, b_col_major=False, device="cuda")
+    mine, theirs = torch.zeros((n, n), device="cuda"), torch.zeros((n, n), device="cuda")
+    name = "Klas_GEMM_TensorCore2D_g_gemm_bf16_f32_128x128x32_16x16x16_8x4"
+    klas.call(name, n, n, n, A, B, mine)
+    ref.mnk(name, n, n, n, A, B, theirs)
+    scale = (A.abs().double() @ B.abs().double())
+    assert float(((mine.double() - theirs.double()).abs() / scale).max()) <= 2e-3
+    TIMINGS["bf16_f32_%d" % n] = {
+        "ours_kernel_ms": event_ms(lambda: klas.gemm_tc(A, B, D=mine)),
+        "ours_call_ms": wall_ms(lambda: (klas.gemm_tc(A, B, D=mine), torch.cuda.synchronize())),
+        "ref_TensorCore2D_128x128x32_8x4_call_ms": wall_ms(lambda: ref.mnk(name, n, n, n, A, B, theirs)),
+        "flop": 2 * n ** 3}
+
+
+def test_f16_f16(ref):
+    n = 2048
+    A, B = synth.gemm_f16_batched(2, 1, n, n, n, device="cuda")
+    mine = torch.zeros((n, n), dtype=torch.float16, device="cuda")
+    theirs = torch.zeros_like(mine)
+    name = "Klas_GEMM_TensorCore2D_g_gemm_f16_f16_128x128x32_16x16x16_8x4"
+    klas.call(name, n, n, n, A[0], B[0], mine)
+    ref.mnk(name, n, n, n, A[0], B[0], theirs)
+    scale = (A[0].abs().double() @ B[0].abs().double())
+    # the reference rounds its half accumulator after every 16-deep step; both stay within 1e-2
+    assert float(((mine.double() - theirs.double()).abs() / scale).max()) <= 1e-2
+    TIMINGS["f16_f16_2048"] = {
+        "ours_kernel_ms": event_ms(lambda: klas.gemm_tc(A[0], B[0], out_dtype=torch.float16, D=mine)),
+        "ref_TensorCore2D_128x128x32_8x4_call_ms": wall_ms(lambda: ref.mnk(name, n, n, n, A[0], B[0], theirs)),
+        "flop": 2 * n ** 3}
+
+
+def test_spmm_f32(ref):
+    rows = shared = 8192      # the reference's wrappers abort at 10000 and above (dist/Klas_SPMM.cu:196-198)
+    cols = 256
+    csr = synth.csr_poisson(4, rows, shared, 64.0, device="cuda")
+    B = synth.spmm_dense_b(4, shared, cols, device="cuda")
+    mine, theirs = torch.zeros((rows, cols), device="cuda"), torch.zeros((rows, cols), device="cuda")
+    klas.spmm(csr, B, mine)
+    ref.spmm_f32("Klas_SPMM_spmm_f32", rows, shared, cols, csr, B, theirs)
+    assert torch.equal(mine, theirs)      # both add each row's products in CSR order with one FMA each
+    TIMINGS["spmm_8192_p64_c256"] = {
+        "ours_kernel_ms": event_ms(lambda: klas.spmm(csr, B, mine)),
+        "ref_spmm_f32_call_ms": wall_ms(lambda: ref.spmm_f32("Klas_SPMM_spmm_f32", rows, shared, cols, csr, B, theirs)),
+        "nnz": csr.nnz}
