@@ -52,12 +52,22 @@ constexpr uint32_t BARRIER_BYTES = 256;
 constexpr uint32_t DEFAULT_RASTER_GROUP = 8;  // tile columns swept together for L2 reuse
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
+#ifndef KLAS_PAIR_STAGES
+#define KLAS_PAIR_STAGES 6
+#endif
+#ifndef KLAS_PAIR_RELEASE
+#define KLAS_PAIR_RELEASE 1
+#endif
+
 template <bool PAIR>
 struct Shape {
     static constexpr uint32_t CTAS = PAIR ? 2 : 1;
     static constexpr uint32_t TILE_M = BM * CTAS;     // rows of one tile of the CTA group
     static constexpr uint32_t B_COLS = BN / CTAS;     // B columns staged by each CTA
-    static constexpr uint32_t STAGES = PAIR ? 6 : 4;
+    static constexpr uint32_t STAGES = PAIR ? KLAS_PAIR_STAGES : 4;
+    // Consecutive stages released by one tcgen05.commit.  A commit costs the issuing thread
+    // about as much as two MMAs, so the pair tiles free their stages two at a time.
+    static constexpr uint32_t RELEASE_GROUP = PAIR ? KLAS_PAIR_RELEASE : 1;
     static constexpr uint32_t B_STAGE_BYTES = B_COLS * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;
@@ -71,7 +81,7 @@ __device__ int g_umma_status;
 // [cta][0] producer waiting for a free stage, [1] MMA waiting for data, [2] MMA waiting for a
 // free accumulator, [3] epilogue waiting for an accumulator, [4] whole kernel, [5] epilogue busy.
 __device__ unsigned long long g_umma_prof[1024][8];
-#define KLAS_PROF_DECL unsigned long long prof_acc0 = 0, prof_acc1 = 0, prof_acc2 = 0
+#define KLAS_PROF_DECL unsigned long long prof_acc0 = 0, prof_acc1 = 0, prof_acc2 = 0, prof_mma0 = 0, prof_mma3 = 0
 #define KLAS_PROF_BEGIN const long long prof_t0 = clock64()
 #define KLAS_PROF_END(acc) acc += (unsigned long long)(clock64() - prof_t0)
 #define KLAS_PROF_STORE(slot, acc) if (lane == 0 && blockIdx.x < 1024) g_umma_prof[blockIdx.x][slot] = acc
@@ -273,8 +283,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
+        // One thread runs the whole loop: no warp-wide votes or re-convergence per stage.
         uint32_t stage = 0, phase = 0;
-        bool ok = true;
+        bool ok = lane == 0;
+        [[maybe_unused]] const uint32_t full_bars_cta0 = PAIR ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);
         KLAS_PROF_DECL;
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             uint32_t b, tm, tn;
@@ -282,19 +294,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const int32_t a_row = int32_t(tm * S::TILE_M + cta_rank * BM);
             const int32_t b_col = int32_t(tn * BN + cta_rank * S::B_COLS);
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-                KLAS_PROF_BEGIN;
-                ok = bounded_wait(empty_bar(stage), phase ^ 1u, ctl, SITE_PRODUCER_EMPTY);
-                KLAS_PROF_END(prof_acc0);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                if (lane == 0) {
+                if (stage % S::RELEASE_GROUP == 0) {
+                    // stages are handed back in groups; the group's last stage carries the barrier
+                    KLAS_PROF_BEGIN;
+                    ok = bounded_wait(empty_bar(stage + S::RELEASE_GROUP - 1), phase ^ 1u, ctl, SITE_PRODUCER_EMPTY);
+                    KLAS_PROF_END(prof_acc0);
+                    if (!ok) break;
+                }
+                {
                     const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_STAGE_BYTES;
                     const int32_t k0 = int32_t(kb * BK);
                     if constexpr (PAIR) {
                         // the even CTA's barrier counts the bytes of both CTAs' loads
                         if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
-                        const uint32_t bar = ptx::map_to_cta(full_bar(stage), 0);
+                        const uint32_t bar = full_bars_cta0 + 8u * stage;
                         ptx::tma_load_3d_pair(a_dst, &tm_a, bar, k0, a_row, int32_t(b));
                         if (p.b_row_major) {
 #pragma unroll
@@ -317,7 +331,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         }
                     }
                 }
-                __syncwarp();
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
@@ -325,6 +338,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
         }
         KLAS_PROF_STORE(0, prof_acc0);
+        __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         // K-major operand: 8-row groups 1024 bytes apart; a K step of 16 elements = 32 bytes.
@@ -335,7 +349,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                                    : ptx::umma_desc_base_sw128(16, 1024);
         const uint32_t b_kstep = p.b_row_major ? UMMA_K * 128u : UMMA_K * 2u;
         uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-        bool ok = true;
+        bool ok = lane == 0;   // one thread runs the whole loop
         const bool issuer = cta_rank == 0;
         KLAS_PROF_DECL;
         for (uint32_t t = group; issuer && ok && p.num_kb > 0 && t < p.num_tiles; t += num_groups) {
@@ -344,18 +358,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 ok = bounded_wait(tempty_bar(acc), acc_phase ^ 1u, ctl, SITE_MMA_TMEM_EMPTY);
                 KLAS_PROF_END(prof_acc2);
             }
-            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            ptx::tc_fence_after_sync();
+            ptx::tc_fence_after_sync();   // orders the epilogue's TMEM reads before these MMAs' writes
             const uint32_t d_tmem = tmem_base + acc * BN;
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 KLAS_PROF_BEGIN;
                 ok = bounded_wait(full_bar(stage), phase, ctl, SITE_MMA_FULL);
                 KLAS_PROF_END(prof_acc0);
-                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                ptx::tc_fence_after_sync();
-                if (lane == 0) {
+                {
 #ifdef KLAS_UMMA_PROFILE
                     const long long prof_i0 = clock64();
 #endif
@@ -370,15 +381,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                             ptx::umma_f16_ss_pair(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
                         else
                             ptx::umma_f16_ss(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+#ifdef KLAS_UMMA_PROFILE
+                        if (kk == 0) prof_mma0 += (unsigned long long)(clock64() - prof_i0);
+                        if (kk == 3) prof_mma3 = prof_mma3 - (unsigned long long)prof_i0 + (unsigned long long)clock64();
+#endif
                     }
                     // free the shared-memory stage (in both CTAs) once these MMAs retire
                     if constexpr (PAIR) {
-                        ptx::umma_commit_pair(ptx::map_to_cta(empty_bar(stage), 0));
-                        ptx::umma_commit_pair(ptx::map_to_cta(empty_bar(stage), 1));
-                        if (kb + 1 == p.num_kb) {
-                            ptx::umma_commit_pair(ptx::map_to_cta(tfull_bar(acc), 0));
-                            ptx::umma_commit_pair(ptx::map_to_cta(tfull_bar(acc), 1));
-                        }
+                        if (stage % S::RELEASE_GROUP == S::RELEASE_GROUP - 1)
+                            ptx::umma_commit_pair_mask(empty_bar(stage), 0x3);
+                        if (kb + 1 == p.num_kb) ptx::umma_commit_pair_mask(tfull_bar(acc), 0x3);
                     } else {
                         ptx::umma_commit(empty_bar(stage));
                         if (kb + 1 == p.num_kb) ptx::umma_commit(tfull_bar(acc));
@@ -387,7 +399,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     prof_acc1 += (unsigned long long)(clock64() - prof_i0);
 #endif
                 }
-                __syncwarp();
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
@@ -398,9 +409,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 acc_phase ^= 1u;
             }
         }
+        __syncwarp();
         KLAS_PROF_STORE(1, prof_acc0);
         KLAS_PROF_STORE(2, prof_acc2);
         KLAS_PROF_STORE(6, prof_acc1);
+        KLAS_PROF_STORE(7, prof_mma0);
+        KLAS_PROF_STORE(4, prof_mma3);
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
@@ -466,9 +480,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #endif
     }
 
-#ifdef KLAS_UMMA_PROFILE
-    if (warp == 2 && lane == 0 && blockIdx.x < 1024) g_umma_prof[blockIdx.x][4] = (unsigned long long)clock64();
-#endif
     // ---------------------------------------------------------------- teardown
     ptx::tc_fence_before_sync();
     __syncthreads();

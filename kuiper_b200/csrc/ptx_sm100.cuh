@@ -238,6 +238,15 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
                  : "memory");
 }
 
+// Same, signalling the barrier at this shared-memory offset in every CTA of `cta_mask`
+// (bit r = CTA rank r of the cluster) with one instruction.
+__device__ __forceinline__ void umma_commit_pair_mask(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"(cta_mask)
+        : "memory");
+}
+
 // ---------------------------------------------------------------- descriptors
 // UMMA shared-memory matrix descriptor for a 128-byte-swizzled operand tile.
 //   bits  0-13  start address >> 4
