@@ -195,8 +195,8 @@ def csr_poisson(seed: int, rows: int, shared: int, mean_nnz: float, row0: int = 
     ridx = torch.arange(row0, row0 + nrows, dtype=torch.int64, device=device)
     if maxc == 0:
         cols_sorted = torch.zeros((nrows, 0), dtype=torch.int64, device=device)
-    elif maxc * 8 >= shared:
-        # dense-ish rows: first cnt entries of a per-row random permutation
+    elif maxc * 8 >= shared or maxc * maxc * 2 >= shared:
+        # rows where repeated draws would collide often: first cnt entries of a per-row random permutation
         keys = splitmix64(_stream_seed(seed, 3),
                           (ridx[:, None] * shared + torch.arange(shared, device=device)[None, :]).reshape(-1))
         perm = torch.argsort(keys.view(nrows, shared), dim=1, stable=True)[:, :maxc]
