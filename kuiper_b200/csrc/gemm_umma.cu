@@ -503,6 +503,272 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 }
 
 // ---------------------------------------------------------------------------
+// "Wide" instantiation for problems that fill the machine: a cluster of two CTAs owns a
+// 512 x 256 tile; each CTA holds 256 rows of A (two M=128 halves) and 128 columns of B,
+// 4 stages of 48 KiB.  Per K step the even CTA issues two M=256 pair-MMAs (one per half),
+// so a barrier round covers 8 MMAs and the B slab staged by a CTA feeds 512 output rows:
+// the L2 -> SM bytes per flop are half those of the single-CTA tile.  Both accumulator
+// halves (2 x 256 columns) fill tensor memory, so the epilogue drains TMEM before the next
+// tile's MMAs start; it is kept short by staging 32 x 128-byte blocks in swizzled shared
+// memory and writing them with TMA stores, and the producer keeps loading during it.
+// ---------------------------------------------------------------------------
+namespace wide {
+constexpr uint32_t STAGES = 4;
+constexpr uint32_t A_ROWS = 256;                       // rows of A staged by each CTA
+constexpr uint32_t B_COLS = 128;                       // columns of B staged by each CTA
+constexpr uint32_t A_BYTES = A_ROWS * BK * 2;
+constexpr uint32_t B_BYTES = B_COLS * BK * 2;
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;    // 48 KiB
+constexpr uint32_t TILE_M = 2 * A_ROWS;                // rows of a cluster tile
+constexpr uint32_t EPI_BUF_BYTES = 32 * 128;           // one staging block: 32 rows x 128 bytes
+constexpr uint32_t EPI_BYTES = NUM_EPI_WARPS * 2 * EPI_BUF_BYTES;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BARRIER_BYTES + 1024;
+}  // namespace wide
+
+enum : int { SITE_WIDE = 0x100 };
+
+template <typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_umma_wide_kernel(const __grid_constant__ CUtensorMap tm_a,
+                          const __grid_constant__ CUtensorMap tm_b,
+                          const __grid_constant__ CUtensorMap tm_d, const Params p) {
+    using namespace wide;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t *smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    const uint32_t epi_base = smem_base + STAGES * STAGE_BYTES;
+    uint8_t *bar_region = smem + STAGES * STAGE_BYTES + EPI_BYTES;
+    const uint32_t bar_base = epi_base + EPI_BYTES;
+    // layout: full[STAGES], empty[STAGES], tmem_full, tmem_empty, tmem slot, abort flag
+    auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+    const uint32_t tfull_bar = bar_base + 8u * (2 * STAGES);
+    const uint32_t tempty_bar = bar_base + 8u * (2 * STAGES + 1);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_region + 8u * (2 * STAGES + 2));
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t cta_rank = ptx::cluster_ctarank();
+    const uint32_t group = blockIdx.x / 2;
+    const uint32_t num_groups = gridDim.x / 2;
+    const Ctl ctl{abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        ptx::mbar_init(tfull_bar, 1);
+        ptx::mbar_init(tempty_bar, NUM_EPI_WARPS * 2);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == 0 && lane == 0) {
+        if (p.num_kb > 0) {
+            ptx::prefetch_tensormap(&tm_a);
+            ptx::prefetch_tensormap(&tm_b);
+        }
+        ptx::prefetch_tensormap(&tm_d);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (one thread)
+        uint32_t stage = 0, phase = 0;
+        bool ok = lane == 0;
+        const uint32_t full_bars_cta0 = ptx::map_to_cta(full_bar(0), 0);
+        for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
+            uint32_t b, tm, tn;
+            decode_tile(t, p, b, tm, tn);
+            const int32_t a_row = int32_t(tm * TILE_M + cta_rank * A_ROWS);
+            const int32_t b_col = int32_t(tn * BN + cta_rank * B_COLS);
+            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                ok = bounded_wait(empty_bar(stage), phase ^ 1u, ctl, SITE_WIDE | SITE_PRODUCER_EMPTY);
+                if (!ok) break;
+                const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+                const uint32_t b_dst = a_dst + A_BYTES;
+                const int32_t k0 = int32_t(kb * BK);
+                // the even CTA's barrier counts the bytes of both CTAs' loads
+                if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+                const uint32_t bar = full_bars_cta0 + 8u * stage;
+                ptx::tma_load_3d_pair(a_dst, &tm_a, bar, k0, a_row, int32_t(b));
+                if (p.b_row_major) {
+#pragma unroll
+                    for (uint32_t j = 0; j < B_COLS / 64; ++j)
+                        ptx::tma_load_3d_pair(b_dst + j * B_CHUNK_BYTES, &tm_b, bar,
+                                              b_col + int32_t(j * 64), k0, int32_t(b));
+                } else {
+                    ptx::tma_load_3d_pair(b_dst, &tm_b, bar, k0, b_col, int32_t(b));
+                }
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (one thread, even CTA)
+        const uint64_t a_desc_base = ptx::umma_desc_base_sw128(16, 1024);
+        const uint64_t b_desc_base = p.b_row_major ? ptx::umma_desc_base_sw128(B_CHUNK_BYTES, 1024)
+                                                   : ptx::umma_desc_base_sw128(16, 1024);
+        const uint32_t b_kstep = p.b_row_major ? UMMA_K * 128u : UMMA_K * 2u;
+        uint32_t stage = 0, phase = 0, tile_phase = 0;
+        bool ok = lane == 0 && cta_rank == 0;
+        for (uint32_t t = group; ok && p.num_kb > 0 && t < p.num_tiles; t += num_groups) {
+            // both CTAs' epilogues must have drained the previous tile's accumulators
+            ok = bounded_wait(tempty_bar, tile_phase ^ 1u, ctl, SITE_WIDE | SITE_MMA_TMEM_EMPTY);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                ok = bounded_wait(full_bar(stage), phase, ctl, SITE_WIDE | SITE_MMA_FULL);
+                if (!ok) break;
+                const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+                const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
+                    const uint64_t b_desc = ptx::umma_desc_at(b_desc_base, b_addr + kk * b_kstep);
+#pragma unroll
+                    for (uint32_t h = 0; h < 2; ++h) {
+                        // half h: rows [128 h, 128 h + 128) of each CTA's A tile -> accumulator columns [256 h, ...)
+                        const uint64_t a_desc = ptx::umma_desc_at(
+                            a_desc_base, a_addr + h * (BM * BK * 2) + kk * UMMA_K * 2u);
+                        ptx::umma_f16_ss_pair(tmem_base + h * BN, a_desc, b_desc, p.idesc,
+                                              (kb | kk) != 0 ? 1u : 0u);
+                    }
+                }
+                ptx::umma_commit_pair_mask(empty_bar(stage), 0x3);
+                if (kb + 1 == p.num_kb) ptx::umma_commit_pair_mask(tfull_bar, 0x3);
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+            tile_phase ^= 1u;
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t quad = warp & 3u;
+        OutT *const D = static_cast<OutT *>(p.D);
+        const OutT *const C = static_cast<const OutT *>(p.C);
+        constexpr uint32_t COLS_PER_BLOCK = 128 / sizeof(OutT);     // columns of one 128-byte staging row
+        constexpr uint32_t CHUNKS_PER_BLOCK = COLS_PER_BLOCK / 32;  // TMEM chunks (32 columns) per block
+        const uint32_t my_bufs = epi_base + (warp - 2) * 2 * EPI_BUF_BYTES;
+        const uint32_t tempty_cta0 = ptx::map_to_cta(tempty_bar, 0);
+        uint32_t tile_phase = 0, block_it = 0;
+        bool ok = true;
+        for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
+            uint32_t b, tm, tn;
+            decode_tile(t, p, b, tm, tn);
+            if (p.num_kb > 0) {
+                ok = bounded_wait(tfull_bar, tile_phase, ctl, SITE_WIDE | SITE_EPI_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+            }
+#pragma unroll 1
+            for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t row0 = tm * TILE_M + cta_rank * A_ROWS + h * BM + quad * 32u;
+                const uint32_t row = row0 + lane;
+                const size_t row_off = (size_t(b) * p.M + row) * size_t(p.N);
+#pragma unroll 1
+                for (uint32_t c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    if (p.num_kb > 0) {
+                        ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + h * BN + c * 32u, v);
+                        ptx::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (uint32_t j = 0; j < 32; ++j) v[j] = 0u;
+                    }
+                    const uint32_t col = tn * BN + c * 32u;
+                    if (C != nullptr) {
+                        // alpha/beta path: C is read with plain loads, D written directly
+                        if (row < p.M && col < p.N)
+                            store_row_chunk<OutT>(v, D + row_off + col, C + row_off + col, p.alpha,
+                                                  p.beta, p.N - col);
+                        continue;
+                    }
+                    // Stage the 32 x 32 block into a 128-byte-swizzled buffer: 16-byte piece j of
+                    // row r lives at piece (j ^ (r & 7)), which is what the TMA store expects
+                    // and makes the 32 lanes' 16-byte stores conflict-free.
+                    const uint32_t sub = c % CHUNKS_PER_BLOCK;          // position inside the staging row
+                    const uint32_t buf = my_bufs + (block_it & 1u) * EPI_BUF_BYTES;
+                    if (sub == 0) {
+                        // the store that last read this buffer (two blocks ago) must have finished reading
+                        if (lane == 0) ptx::tma_store_wait_read<1>();
+                        __syncwarp();
+                    }
+                    constexpr uint32_t PIECES = 32 * sizeof(OutT) / 16;  // 16-byte pieces per chunk per row
+#pragma unroll
+                    for (uint32_t j = 0; j < PIECES; ++j) {
+                        union {
+                            uint4 raw;
+                            OutT e[16 / sizeof(OutT)];
+                        } pk;
+#pragma unroll
+                        for (uint32_t e = 0; e < 16 / sizeof(OutT); ++e)
+                            pk.e[e] = OutTraits<OutT>::from_f32(__uint_as_float(v[j * (16 / sizeof(OutT)) + e]));
+                        const uint32_t piece = (sub * PIECES + j) ^ (lane & 7u);
+                        const uint32_t addr = buf + lane * 128u + piece * 16u;
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.raw.x),
+                                     "r"(pk.raw.y), "r"(pk.raw.z), "r"(pk.raw.w)
+                                     : "memory");
+                    }
+                    if (sub == CHUNKS_PER_BLOCK - 1) {
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        const uint32_t col_blk = col - sub * 32u;
+                        // blocks wholly outside the matrix are not stored (and keep their buffer)
+                        const bool in_range = row0 < p.M && col_blk < p.N;
+                        if (lane == 0 && in_range) {
+                            ptx::tma_store_3d(&tm_d, buf, int32_t(col_blk), int32_t(row0), int32_t(b));
+                            ptx::tma_store_commit();
+                        }
+                        if (in_range) ++block_it;
+                    }
+                }
+            }
+            if (p.num_kb > 0) {
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(tempty_cta0);
+                tile_phase ^= 1u;
+            }
+        }
+        if (lane == 0) ptx::tma_store_wait_all<0>();   // every output block has left shared memory and landed
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        if (*abort_flag != 0) {
+            for (int i = 0; i < 256; ++i) __nanosleep(1000);
+        }
+        ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -523,18 +789,20 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 3-D map over `batch` row-major pages of `outer` x `inner` 16-bit elements,
-// box = box_inner x box_outer x 1, 128-byte swizzle, zero fill outside.
-static int make_map_16bit(CUtensorMap *map, int dtype, const void *base, uint64_t inner,
-                          uint64_t outer, uint64_t batch, uint32_t box_inner, uint32_t box_outer) {
+// 3-D map over `batch` row-major pages of `outer` x `inner` elements of `elt` bytes,
+// box = box_inner x box_outer x 1, 128-byte swizzle, zero fill outside (loads) / clipping (stores).
+static int make_map(CUtensorMap *map, int dtype, const void *base, uint64_t inner, uint64_t outer,
+                    uint64_t batch, uint32_t box_inner, uint32_t box_outer) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(KLAS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const uint64_t elt = dtype_size(dtype);
     const cuuint64_t dims[3] = {inner, outer, batch};
-    const cuuint64_t strides[2] = {inner * 2, inner * outer * 2};
+    const cuuint64_t strides[2] = {inner * elt, inner * outer * elt};
     const cuuint32_t box[3] = {box_inner, box_outer, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUtensorMapDataType dt =
-        dtype == KLAS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapDataType dt = dtype == KLAS_BF16   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                   : dtype == KLAS_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     const CUresult rc = fn(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -543,6 +811,38 @@ static int make_map_16bit(CUtensorMap *map, int dtype, const void *base, uint64_
                     int(rc), (unsigned long long)inner, (unsigned long long)outer,
                     (unsigned long long)batch);
     return KLAS_OK;
+}
+
+static int make_map_16bit(CUtensorMap *map, int dtype, const void *base, uint64_t inner,
+                          uint64_t outer, uint64_t batch, uint32_t box_inner, uint32_t box_outer) {
+    return make_map(map, dtype, base, inner, outer, batch, box_inner, box_outer);
+}
+
+template <typename OutT>
+static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &td,
+                             const Params &p, int grid, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    KLAS_TRY_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_wide_kernel<OutT>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = wide::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_wide_kernel<OutT>, ta, tb, td, p),
+                      "gemm_umma_wide_kernel launch");
 }
 
 template <typename OutT, bool PAIR>
@@ -631,13 +931,59 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
         return fail(KLAS_ERR_UNSUPPORTED, "gemm_tc needs an sm_100 device (found sm_%d%d)",
                     info.cc_major, info.cc_minor);
 
-    // Tile shape: CTA pairs (256 x 256 tiles) once the problem fills the machine, single
-    // CTAs (128 x 256) below that.  KLAS_TC_MODE=single|pair overrides the choice.
+    // Tile shape: "wide" (512 x 256 per CTA pair) once such tiles fill the machine, CTA pairs with
+    // 256 x 256 tiles below that, single CTAs (128 x 256) for small problems.
+    // KLAS_TC_MODE=single|pair|wide overrides the choice.
     const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
-    bool pair = rows > BM && single_tiles >= uint64_t(info.sm_count) && info.sm_count >= 2;
+    const uint64_t wide_tiles = ((rows + wide::TILE_M - 1) / wide::TILE_M) * ((cols + BN - 1) / BN) * batch;
+    const bool can_pair = info.sm_count >= 2;
+    bool pair = can_pair && rows > BM && single_tiles >= uint64_t(info.sm_count);
+    bool use_wide = can_pair && wide_tiles >= uint64_t(info.sm_count / 2);
     if (const char *mode = getenv("KLAS_TC_MODE")) {
-        if (!strcmp(mode, "single")) pair = false;
-        else if (!strcmp(mode, "pair")) pair = info.sm_count >= 2;
+        if (!strcmp(mode, "single")) pair = use_wide = false;
+        else if (!strcmp(mode, "pair")) { pair = can_pair; use_wide = false; }
+        else if (!strcmp(mode, "wide")) use_wide = can_pair;
+    }
+    if (use_wide) {
+        Params p{};
+        p.C = C;
+        p.D = D;
+        p.M = uint32_t(rows);
+        p.N = uint32_t(cols);
+        p.K = uint32_t(shared);
+        p.batch = batch;
+        p.tiles_m = uint32_t((rows + wide::TILE_M - 1) / wide::TILE_M);
+        p.tiles_n = uint32_t((cols + BN - 1) / BN);
+        if (wide_tiles > 0xffffffffull) return fail(KLAS_ERR_TOO_LARGE, "gemm_tc: too many tiles");
+        p.num_tiles = uint32_t(wide_tiles);
+        p.num_kb = uint32_t((shared + BK - 1) / BK);
+        p.alpha = alpha;
+        p.beta = beta;
+        p.b_row_major = (b_major == KLAS_B_ROW_MAJOR) ? 1u : 0u;
+        p.idesc = ptx::umma_idesc_f16(in_dtype == KLAS_BF16, false, p.b_row_major != 0, 256, BN);
+        p.status = status_word;
+        p.raster_group = DEFAULT_RASTER_GROUP;
+        if (const char *rg = getenv("KLAS_TC_RASTER")) {
+            const int v = atoi(rg);
+            if (v >= 1 && v <= 1024) p.raster_group = uint32_t(v);
+        }
+        CUtensorMap ta{}, tb{}, td{};
+        if (shared > 0) {
+            if (int rc = make_map(&ta, in_dtype, A, shared, rows, batch, BK, wide::A_ROWS)) return rc;
+            if (p.b_row_major) {
+                if (int rc = make_map(&tb, in_dtype, B, cols, shared, batch, 64, BK)) return rc;
+            } else {
+                if (int rc = make_map(&tb, in_dtype, B, shared, cols, batch, BK, wide::B_COLS)) return rc;
+            }
+        }
+        const uint32_t out_box = out_dtype == KLAS_F32 ? 32 : 64;   // 128 bytes of output per staging row
+        if (int rc = make_map(&td, out_dtype, D, cols, rows, batch, out_box, 32)) return rc;
+        const uint64_t groups = wide_tiles < uint64_t(info.sm_count / 2) ? wide_tiles : uint64_t(info.sm_count / 2);
+        switch (out_dtype) {
+            case KLAS_F32: return launch_wide_typed<float>(ta, tb, td, p, int(groups * 2), stream);
+            case KLAS_F16: return launch_wide_typed<__half>(ta, tb, td, p, int(groups * 2), stream);
+            default: return launch_wide_typed<__nv_bfloat16>(ta, tb, td, p, int(groups * 2), stream);
+        }
     }
     const uint32_t tile_m = pair ? Shape<true>::TILE_M : Shape<false>::TILE_M;
 

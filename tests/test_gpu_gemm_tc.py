@@ -13,9 +13,9 @@ TOL_BF16_F32 = 2e-3   # bf16 x bf16 -> f32, relative to fp64, component-wise sca
 TOL_F16_F16 = 1e-2    # f16 x f16 -> f16
 
 
-@pytest.fixture(autouse=True, params=["single", "pair", "auto"])
+@pytest.fixture(autouse=True, params=["single", "pair", "wide", "auto"])
 def tc_mode(request, monkeypatch):
-    """Every test runs with the single-CTA tiles, the CTA-pair tiles and the library's own choice."""
+    """Every test runs with the single-CTA tiles, the CTA-pair tiles, the wide pair tiles and the library's own choice."""
     if request.param == "auto":
         monkeypatch.delenv("KLAS_TC_MODE", raising=False)
     else:
