@@ -415,7 +415,7 @@ def cpu_baseline_leg(workload_name):
 
 # --------------------------------------------------------------------------- main
 # DRAM traffic of one launch from an ncu capture of the same kernel (profiles/): bytes read + written.
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {"spmm": 1.141e9, "gemm_u64": 2.163e9, "gemm_f32": 8.4e6}
 
 
 def main():
@@ -498,10 +498,16 @@ def main():
             peak, runit = peaks["hbm_gbs"], "GB/s"
             peak_note = "stream copy, of %s" % peaks["source"]
         else:
-            # CUDA-core GEMMs: issue-bound; reported against the FP32 FMA issue peak at max clock
+            # CUDA-core GEMMs are issue-bound: reported against the nominal issue peak at max clock
             achieved = wl.per_step_units() / (per_launch_ms * 1e-3) / 1e12
-            peak, runit = 2 * 128 * 148 * 1.965e9 / 1e12, "TFLOP/s"
-            peak_note = "2*128 lanes*148 SMs*1965 MHz FP32 issue peak (nominal)"
+            if wl.name == "gemm_u64":
+                # a wrapping u64 multiply-add = one widening 32x32 multiply-add (2 issue slots of the
+                # 64-lane integer-multiply pipe) + two 32-bit ones: 4 slots per MAC, 2 ops per MAC
+                peak, runit = 2 * (64 / 4) * 148 * 1.965e9 / 1e12, "Tops/s"
+                peak_note = "64 integer-multiply lanes/clk/SM, 4 slots per u64 MAC, 148 SMs, 1965 MHz (nominal)"
+            else:
+                peak, runit = 2 * 128 * 148 * 1.965e9 / 1e12, "TFLOP/s"
+                peak_note = "2*128 lanes*148 SMs*1965 MHz FP32 issue peak (nominal)"
         roofline = {"bound": "tensor" if wl.bound == "tensor" else "hbm" if wl.bound == "hbm" else "issue",
                     "achieved": achieved, "peak": peak, "unit": runit, "frac": achieved / peak,
                     "traffic": NCU_TRAFFIC.get(wl.name), "peak_note": peak_note,
