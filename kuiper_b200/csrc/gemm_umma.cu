@@ -509,8 +509,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // so a barrier round covers 8 MMAs and the B slab staged by a CTA feeds 512 output rows:
 // the L2 -> SM bytes per flop are half those of the single-CTA tile.  Both accumulator
 // halves (2 x 256 columns) fill tensor memory, so the epilogue drains TMEM before the next
-// tile's MMAs start; it is kept short by staging 32 x 128-byte blocks in swizzled shared
-// memory and writing them with TMA stores, and the producer keeps loading during it.
+// tile's MMAs start; it is kept short by eight epilogue warps (one group of four per half)
+// that transpose 32 x 128-byte blocks through swizzled shared memory into coalesced global
+// stores, and the producer keeps loading during it.
 // ---------------------------------------------------------------------------
 namespace wide {
 constexpr uint32_t STAGES = 4;
@@ -521,17 +522,18 @@ constexpr uint32_t B_BYTES = B_COLS * BK * 2;
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;    // 48 KiB
 constexpr uint32_t TILE_M = 2 * A_ROWS;                // rows of a cluster tile
 constexpr uint32_t EPI_BUF_BYTES = 32 * 128;           // one staging block: 32 rows x 128 bytes
-constexpr uint32_t EPI_BYTES = NUM_EPI_WARPS * 2 * EPI_BUF_BYTES;
+constexpr uint32_t EPI_WARPS = 8;                     // two groups of four, one per accumulator half
+constexpr uint32_t THREADS = (2 + EPI_WARPS) * 32;
+constexpr uint32_t EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BARRIER_BYTES + 1024;
 }  // namespace wide
 
 enum : int { SITE_WIDE = 0x100 };
 
 template <typename OutT>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(wide::THREADS, 1)
     gemm_umma_wide_kernel(const __grid_constant__ CUtensorMap tm_a,
-                          const __grid_constant__ CUtensorMap tm_b,
-                          const __grid_constant__ CUtensorMap tm_d, const Params p) {
+                          const __grid_constant__ CUtensorMap tm_b, const Params p) {
     using namespace wide;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -562,17 +564,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             ptx::mbar_init(empty_bar(s), 1);
         }
         ptx::mbar_init(tfull_bar, 1);
-        ptx::mbar_init(tempty_bar, NUM_EPI_WARPS * 2);
+        ptx::mbar_init(tempty_bar, EPI_WARPS * 2);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
     }
-    if (warp == 0 && lane == 0) {
-        if (p.num_kb > 0) {
-            ptx::prefetch_tensormap(&tm_a);
-            ptx::prefetch_tensormap(&tm_b);
-        }
-        ptx::prefetch_tensormap(&tm_d);
+    if (warp == 0 && lane == 0 && p.num_kb > 0) {
+        ptx::prefetch_tensormap(&tm_a);
+        ptx::prefetch_tensormap(&tm_b);
     }
     if (warp == 1) {
         ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
@@ -628,13 +627,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const uint32_t b_kstep = p.b_row_major ? UMMA_K * 128u : UMMA_K * 2u;
         uint32_t stage = 0, phase = 0, tile_phase = 0;
         bool ok = lane == 0 && cta_rank == 0;
+        KLAS_PROF_DECL;
+#ifdef KLAS_UMMA_PROFILE
+        const long long prof_start = clock64();
+#endif
         for (uint32_t t = group; ok && p.num_kb > 0 && t < p.num_tiles; t += num_groups) {
             // both CTAs' epilogues must have drained the previous tile's accumulators
-            ok = bounded_wait(tempty_bar, tile_phase ^ 1u, ctl, SITE_WIDE | SITE_MMA_TMEM_EMPTY);
+            {
+                KLAS_PROF_BEGIN;
+                ok = bounded_wait(tempty_bar, tile_phase ^ 1u, ctl, SITE_WIDE | SITE_MMA_TMEM_EMPTY);
+                KLAS_PROF_END(prof_acc2);
+            }
             if (!ok) break;
             ptx::tc_fence_after_sync();
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-                ok = bounded_wait(full_bar(stage), phase, ctl, SITE_WIDE | SITE_MMA_FULL);
+                {
+                    KLAS_PROF_BEGIN;
+                    ok = bounded_wait(full_bar(stage), phase, ctl, SITE_WIDE | SITE_MMA_FULL);
+                    KLAS_PROF_END(prof_acc0);
+                }
                 if (!ok) break;
                 const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
                 const uint32_t b_addr = a_addr + A_BYTES;
@@ -659,99 +670,126 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
             tile_phase ^= 1u;
         }
+#ifdef KLAS_UMMA_PROFILE
+        if (lane == 0 && cta_rank == 0 && blockIdx.x < 1024) {
+            g_umma_prof[blockIdx.x][1] = prof_acc0;
+            g_umma_prof[blockIdx.x][2] = prof_acc2;
+            g_umma_prof[blockIdx.x][5] = (unsigned long long)(clock64() - prof_start);
+        }
+#endif
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ epilogue
+        // ------------------------------------------------------------ epilogue (8 warps)
+        // Warps 2-5 drain accumulator half 0, warps 6-9 half 1; within a group warp w owns the
+        // TMEM lanes of quadrant w & 3.  Each warp walks its 8 chunks of 32 columns with the
+        // next tcgen05.ld in flight while the current chunk is converted and staged, and hands
+        // the accumulator back as soon as its last chunk is in registers.
         const uint32_t quad = warp & 3u;
+        const uint32_t h = (warp - 2) >> 2;
         OutT *const D = static_cast<OutT *>(p.D);
         const OutT *const C = static_cast<const OutT *>(p.C);
         constexpr uint32_t COLS_PER_BLOCK = 128 / sizeof(OutT);     // columns of one 128-byte staging row
         constexpr uint32_t CHUNKS_PER_BLOCK = COLS_PER_BLOCK / 32;  // TMEM chunks (32 columns) per block
-        const uint32_t my_bufs = epi_base + (warp - 2) * 2 * EPI_BUF_BYTES;
+        constexpr uint32_t PIECES = 32 * sizeof(OutT) / 16;         // 16-byte pieces per chunk per row
+        constexpr uint32_t NCHUNK = BN / 32;
+        const uint32_t buf = epi_base + (warp - 2) * EPI_BUF_BYTES;
         const uint32_t tempty_cta0 = ptx::map_to_cta(tempty_bar, 0);
-        uint32_t tile_phase = 0, block_it = 0;
+        const uint32_t taddr0 = tmem_base + ((quad * 32u) << 16) + h * BN;
+        uint32_t tile_phase = 0;
         bool ok = true;
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             uint32_t b, tm, tn;
             decode_tile(t, p, b, tm, tn);
-            if (p.num_kb > 0) {
+            const bool have_acc = p.num_kb > 0;
+            if (have_acc) {
                 ok = bounded_wait(tfull_bar, tile_phase, ctl, SITE_WIDE | SITE_EPI_TMEM_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
             }
-#pragma unroll 1
-            for (uint32_t h = 0; h < 2; ++h) {
-                const uint32_t row0 = tm * TILE_M + cta_rank * A_ROWS + h * BM + quad * 32u;
-                const uint32_t row = row0 + lane;
-                const size_t row_off = (size_t(b) * p.M + row) * size_t(p.N);
-#pragma unroll 1
-                for (uint32_t c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    if (p.num_kb > 0) {
-                        ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + h * BN + c * 32u, v);
-                        ptx::tmem_ld_wait();
-                    } else {
+            const uint32_t row0 = tm * TILE_M + cta_rank * A_ROWS + h * BM + quad * 32u;
+            const uint32_t row = row0 + lane;
+            const size_t row_off = (size_t(b) * p.M + row) * size_t(p.N);
+
+            // Converts one chunk and either stores it directly (alpha/beta path, C read with plain
+            // loads) or transposes it through shared memory so that global stores are coalesced:
+            // lane r (= row r) writes 16-byte piece j of its row to piece (j ^ (r & 7)) of a
+            // 32-row x 128-byte buffer (conflict-free), then the warp reads the buffer back four
+            // rows per instruction -- 8 lanes per row, 128 contiguous bytes -- and stores those.
+            auto emit = [&](const uint32_t (&v)[32], uint32_t c) {
+                const uint32_t col = tn * BN + c * 32u;
+                if (C != nullptr) {
+                    if (row < p.M && col < p.N)
+                        store_row_chunk<OutT>(v, D + row_off + col, C + row_off + col, p.alpha, p.beta,
+                                              p.N - col);
+                    return;
+                }
+                const uint32_t sub = c % CHUNKS_PER_BLOCK;
 #pragma unroll
-                        for (uint32_t j = 0; j < 32; ++j) v[j] = 0u;
-                    }
-                    const uint32_t col = tn * BN + c * 32u;
-                    if (C != nullptr) {
-                        // alpha/beta path: C is read with plain loads, D written directly
-                        if (row < p.M && col < p.N)
-                            store_row_chunk<OutT>(v, D + row_off + col, C + row_off + col, p.alpha,
-                                                  p.beta, p.N - col);
-                        continue;
-                    }
-                    // Stage the 32 x 32 block into a 128-byte-swizzled buffer: 16-byte piece j of
-                    // row r lives at piece (j ^ (r & 7)), which is what the TMA store expects
-                    // and makes the 32 lanes' 16-byte stores conflict-free.
-                    const uint32_t sub = c % CHUNKS_PER_BLOCK;          // position inside the staging row
-                    const uint32_t buf = my_bufs + (block_it & 1u) * EPI_BUF_BYTES;
-                    if (sub == 0) {
-                        // the store that last read this buffer (two blocks ago) must have finished reading
-                        if (lane == 0) ptx::tma_store_wait_read<1>();
-                        __syncwarp();
-                    }
-                    constexpr uint32_t PIECES = 32 * sizeof(OutT) / 16;  // 16-byte pieces per chunk per row
+                for (uint32_t j = 0; j < PIECES; ++j) {
+                    union {
+                        uint4 raw;
+                        OutT e[16 / sizeof(OutT)];
+                    } pk;
 #pragma unroll
-                    for (uint32_t j = 0; j < PIECES; ++j) {
-                        union {
-                            uint4 raw;
-                            OutT e[16 / sizeof(OutT)];
-                        } pk;
+                    for (uint32_t e = 0; e < 16 / sizeof(OutT); ++e)
+                        pk.e[e] = OutTraits<OutT>::from_f32(__uint_as_float(v[j * (16 / sizeof(OutT)) + e]));
+                    const uint32_t piece = (sub * PIECES + j) ^ (lane & 7u);
+                    const uint32_t addr = buf + lane * 128u + piece * 16u;
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.raw.x),
+                                 "r"(pk.raw.y), "r"(pk.raw.z), "r"(pk.raw.w)
+                                 : "memory");
+                }
+                if (sub == CHUNKS_PER_BLOCK - 1) {
+                    __syncwarp();
+                    const uint32_t col_blk = col - sub * 32u;
+                    const uint32_t piece = lane & 7u;
+                    const uint32_t gcol = col_blk + piece * (16 / sizeof(OutT));
 #pragma unroll
-                        for (uint32_t e = 0; e < 16 / sizeof(OutT); ++e)
-                            pk.e[e] = OutTraits<OutT>::from_f32(__uint_as_float(v[j * (16 / sizeof(OutT)) + e]));
-                        const uint32_t piece = (sub * PIECES + j) ^ (lane & 7u);
-                        const uint32_t addr = buf + lane * 128u + piece * 16u;
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.raw.x),
-                                     "r"(pk.raw.y), "r"(pk.raw.z), "r"(pk.raw.w)
+                    for (uint32_t i = 0; i < 8; ++i) {
+                        const uint32_t r = i * 4u + (lane >> 3);
+                        uint4 val;
+                        const uint32_t addr = buf + r * 128u + ((piece ^ (r & 7u)) * 16u);
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                                     : "r"(addr)
                                      : "memory");
+                        if (row0 + r < p.M && gcol < p.N)
+                            *reinterpret_cast<uint4 *>(D + (size_t(b) * p.M + row0 + r) * size_t(p.N) + gcol) = val;
                     }
-                    if (sub == CHUNKS_PER_BLOCK - 1) {
-                        ptx::fence_proxy_async_smem();
+                    __syncwarp();   // the buffer may be overwritten by the next block
+                }
+            };
+
+            uint32_t va[32], vb[32];
+            if (have_acc) {
+                ptx::tmem_ld_32x32b_x32(taddr0, va);
+            } else {
+#pragma unroll
+                for (uint32_t j = 0; j < 32; ++j) va[j] = vb[j] = 0u;
+            }
+#pragma unroll
+            for (uint32_t c = 0; c < NCHUNK; c += 2) {
+                if (have_acc) {
+                    ptx::tmem_ld_wait();
+                    ptx::tmem_ld_32x32b_x32(taddr0 + (c + 1) * 32u, vb);
+                }
+                emit(va, c);
+                if (have_acc) {
+                    ptx::tmem_ld_wait();
+                    if (c + 2 < NCHUNK) {
+                        ptx::tmem_ld_32x32b_x32(taddr0 + (c + 2) * 32u, va);
+                    } else {
+                        // last chunk is in registers: this warp no longer needs the accumulator
+                        ptx::tc_fence_before_sync();
                         __syncwarp();
-                        const uint32_t col_blk = col - sub * 32u;
-                        // blocks wholly outside the matrix are not stored (and keep their buffer)
-                        const bool in_range = row0 < p.M && col_blk < p.N;
-                        if (lane == 0 && in_range) {
-                            ptx::tma_store_3d(&tm_d, buf, int32_t(col_blk), int32_t(row0), int32_t(b));
-                            ptx::tma_store_commit();
-                        }
-                        if (in_range) ++block_it;
+                        if (lane == 0) ptx::mbar_arrive_cluster(tempty_cta0);
                     }
                 }
+                emit(vb, c + 1);
             }
-            if (p.num_kb > 0) {
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive_cluster(tempty_cta0);
-                tile_phase ^= 1u;
-            }
+            if (have_acc) tile_phase ^= 1u;
         }
-        if (lane == 0) ptx::tma_store_wait_all<0>();   // every output block has left shared memory and landed
-        __syncwarp();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -819,8 +857,8 @@ static int make_map_16bit(CUtensorMap *map, int dtype, const void *base, uint64_
 }
 
 template <typename OutT>
-static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &td,
-                             const Params &p, int grid, cudaStream_t stream) {
+static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
+                             cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
@@ -831,7 +869,7 @@ static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(grid), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(wide::THREADS, 1, 1);
     cfg.dynamicSmemBytes = wide::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -841,7 +879,7 @@ static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_wide_kernel<OutT>, ta, tb, td, p),
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_wide_kernel<OutT>, ta, tb, p),
                       "gemm_umma_wide_kernel launch");
 }
 
@@ -967,7 +1005,7 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
             const int v = atoi(rg);
             if (v >= 1 && v <= 1024) p.raster_group = uint32_t(v);
         }
-        CUtensorMap ta{}, tb{}, td{};
+        CUtensorMap ta{}, tb{};
         if (shared > 0) {
             if (int rc = make_map(&ta, in_dtype, A, shared, rows, batch, BK, wide::A_ROWS)) return rc;
             if (p.b_row_major) {
@@ -976,13 +1014,11 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
                 if (int rc = make_map(&tb, in_dtype, B, shared, cols, batch, BK, wide::B_COLS)) return rc;
             }
         }
-        const uint32_t out_box = out_dtype == KLAS_F32 ? 32 : 64;   // 128 bytes of output per staging row
-        if (int rc = make_map(&td, out_dtype, D, cols, rows, batch, out_box, 32)) return rc;
         const uint64_t groups = wide_tiles < uint64_t(info.sm_count / 2) ? wide_tiles : uint64_t(info.sm_count / 2);
         switch (out_dtype) {
-            case KLAS_F32: return launch_wide_typed<float>(ta, tb, td, p, int(groups * 2), stream);
-            case KLAS_F16: return launch_wide_typed<__half>(ta, tb, td, p, int(groups * 2), stream);
-            default: return launch_wide_typed<__nv_bfloat16>(ta, tb, td, p, int(groups * 2), stream);
+            case KLAS_F32: return launch_wide_typed<float>(ta, tb, p, int(groups * 2), stream);
+            case KLAS_F16: return launch_wide_typed<__half>(ta, tb, p, int(groups * 2), stream);
+            default: return launch_wide_typed<__nv_bfloat16>(ta, tb, p, int(groups * 2), stream);
         }
     }
     const uint32_t tile_m = pair ? Shape<true>::TILE_M : Shape<false>::TILE_M;
