@@ -87,6 +87,35 @@ int workspace_release() {
 int umma_read_status(int *value);
 int umma_clear_status();
 
+// Streams and events of the chunked host-buffer calls, one set per device, created on first use.
+struct HostPipe {
+    static constexpr int MAX_CHUNKS = 8;
+    cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
+    cudaEvent_t loaded[MAX_CHUNKS + 1] = {}, computed[MAX_CHUNKS + 1] = {};
+    bool ready = false;
+};
+static HostPipe g_pipes[MAX_DEVICES];
+
+static int host_pipe(HostPipe **out) {
+    int dev = 0;
+    KLAS_TRY_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return fail(KLAS_ERR_INVALID, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    HostPipe &h = g_pipes[dev];
+    if (!h.ready) {
+        KLAS_TRY_CUDA(cudaStreamCreateWithFlags(&h.in, cudaStreamNonBlocking));
+        KLAS_TRY_CUDA(cudaStreamCreateWithFlags(&h.compute, cudaStreamNonBlocking));
+        KLAS_TRY_CUDA(cudaStreamCreateWithFlags(&h.out, cudaStreamNonBlocking));
+        for (int i = 0; i <= HostPipe::MAX_CHUNKS; ++i) {
+            KLAS_TRY_CUDA(cudaEventCreateWithFlags(&h.loaded[i], cudaEventDisableTiming));
+            KLAS_TRY_CUDA(cudaEventCreateWithFlags(&h.computed[i], cudaEventDisableTiming));
+        }
+        h.ready = true;
+    }
+    *out = &h;
+    return KLAS_OK;
+}
+
 // Stages `bytes` from host pointer `src` into workspace slot `slot`.
 static int stage_in(int slot, const void *src, size_t bytes, cudaStream_t s, void **dptr) {
     if (int rc = workspace_reserve(slot, bytes, dptr)) return rc;
@@ -176,18 +205,58 @@ int klas_b200_gemm_tc_host(int in_dtype, int out_dtype, int b_major, uint32_t ba
                  d_bytes = size_t(batch) * rows * cols * os;
     if (d_bytes == 0) return KLAS_OK;
     if (!D) return fail(KLAS_ERR_INVALID, "gemm_tc_host: null D");
-    cudaStream_t s = nullptr;
+    HostPipe *hp = nullptr;
+    if (int rc = host_pipe(&hp)) return rc;
     void *dA, *dB, *dC = nullptr, *dD;
-    if (int rc = stage_in(0, A, a_bytes, s, &dA)) return rc;
-    if (int rc = stage_in(1, B, b_bytes, s, &dB)) return rc;
+    if (int rc = workspace_reserve(0, a_bytes, &dA)) return rc;
+    if (int rc = workspace_reserve(1, b_bytes, &dB)) return rc;
     if (C)
-        if (int rc = stage_in(2, C, d_bytes, s, &dC)) return rc;
+        if (int rc = workspace_reserve(2, d_bytes, &dC)) return rc;
     if (int rc = workspace_reserve(3, d_bytes, &dD)) return rc;
-    if (int rc = launch_gemm_umma(in_dtype, out_dtype, b_major, batch, rows, shared, cols, dA, dB,
-                                  dC, dD, alpha, beta, nullptr, s))
-        return rc;
-    KLAS_TRY_CUDA(cudaMemcpyAsync(D, dD, d_bytes, cudaMemcpyDeviceToHost, s));
-    KLAS_TRY_CUDA(cudaStreamSynchronize(s));
+
+    // The work is cut into chunks -- row blocks of A/C/D for one matrix, groups of pages for a
+    // batch -- that flow through three streams: host->device copies, kernels, device->host
+    // copies.  The two copy directions overlap each other and the kernels, so a call costs
+    // about max(bytes in, bytes out) over PCIe instead of their sum.
+    const bool by_rows = batch == 1;
+    const uint64_t units = by_rows ? rows : batch;
+    uint64_t per_chunk = by_rows ? ((rows + HostPipe::MAX_CHUNKS - 1) / HostPipe::MAX_CHUNKS + 511) / 512 * 512
+                                 : (batch + HostPipe::MAX_CHUNKS - 1) / HostPipe::MAX_CHUNKS;
+    if (per_chunk == 0) per_chunk = 1;
+    const size_t a_unit = (by_rows ? size_t(shared) : size_t(rows) * shared) * is;     // bytes of A per unit
+    const size_t d_unit = (by_rows ? size_t(cols) : size_t(rows) * cols) * os;         // bytes of C/D per unit
+    const size_t b_unit = by_rows ? 0 : size_t(shared) * cols * is;                    // bytes of B per page
+    if (by_rows && b_bytes)
+        KLAS_TRY_CUDA(cudaMemcpyAsync(dB, B, b_bytes, cudaMemcpyHostToDevice, hp->in));
+    int chunk = 0;
+    for (uint64_t u0 = 0; u0 < units; u0 += per_chunk, ++chunk) {
+        const uint64_t n = units - u0 < per_chunk ? units - u0 : per_chunk;
+        char *a_dev = static_cast<char *>(dA) + u0 * a_unit;
+        char *b_dev = static_cast<char *>(dB) + u0 * b_unit;
+        char *c_dev = dC ? static_cast<char *>(dC) + u0 * d_unit : nullptr;
+        char *d_dev = static_cast<char *>(dD) + u0 * d_unit;
+        if (a_unit && shared)
+            KLAS_TRY_CUDA(cudaMemcpyAsync(a_dev, static_cast<const char *>(A) + u0 * a_unit, n * a_unit,
+                                          cudaMemcpyHostToDevice, hp->in));
+        if (!by_rows && b_unit)
+            KLAS_TRY_CUDA(cudaMemcpyAsync(b_dev, static_cast<const char *>(B) + u0 * b_unit, n * b_unit,
+                                          cudaMemcpyHostToDevice, hp->in));
+        if (c_dev)
+            KLAS_TRY_CUDA(cudaMemcpyAsync(c_dev, static_cast<const char *>(C) + u0 * d_unit, n * d_unit,
+                                          cudaMemcpyHostToDevice, hp->in));
+        KLAS_TRY_CUDA(cudaEventRecord(hp->loaded[chunk], hp->in));
+        KLAS_TRY_CUDA(cudaStreamWaitEvent(hp->compute, hp->loaded[chunk], 0));
+        if (int rc = launch_gemm_umma(in_dtype, out_dtype, b_major, by_rows ? 1u : uint32_t(n),
+                                      by_rows ? n : rows, shared, cols, a_dev, by_rows ? dB : b_dev, c_dev,
+                                      d_dev, alpha, beta, nullptr, hp->compute))
+            return rc;
+        KLAS_TRY_CUDA(cudaEventRecord(hp->computed[chunk], hp->compute));
+        KLAS_TRY_CUDA(cudaStreamWaitEvent(hp->out, hp->computed[chunk], 0));
+        KLAS_TRY_CUDA(cudaMemcpyAsync(static_cast<char *>(D) + u0 * d_unit, d_dev, n * d_unit,
+                                      cudaMemcpyDeviceToHost, hp->out));
+    }
+    KLAS_TRY_CUDA(cudaStreamSynchronize(hp->out));
+    KLAS_TRY_CUDA(cudaStreamSynchronize(hp->in));
     return klas_b200_gemm_tc_status(nullptr);
 }
 
