@@ -43,6 +43,34 @@ struct Conv<__nv_bfloat16, float> {
     }
 };
 
+// Blackwell issues fp32 multiply-adds two per instruction (fma.rn.f32x2 on a packed pair);
+// a kernel made of scalar FFMAs is bound by instruction issue at ~60 % of the fp32 rate.  The
+// f32 kernels therefore keep accumulators as packed pairs of neighbouring columns.  Each half
+// is an ordinary IEEE fused multiply-add, so results equal the scalar formulation bit for bit.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
+    unsigned int a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a);
+    hi = __uint_as_float(b);
+}
+__device__ __forceinline__ void ffma2(unsigned long long &acc, unsigned long long a, unsigned long long b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+
+template <typename T>
+struct IsF32 {
+    static constexpr bool value = false;
+};
+template <>
+struct IsF32<float> {
+    static constexpr bool value = true;
+};
+
 template <typename T>
 struct Args {
     const void *A;
@@ -61,7 +89,7 @@ struct alignas(16) Vec {
 
 // S = storage type in global memory, T = arithmetic type.
 template <typename S, typename T, int BM, int BN, int BK, bool FAST>
-__global__ void __launch_bounds__(THREADS, 2) gemm_simt_kernel(const Args<T> a) {
+__global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) ? 3 : 2) gemm_simt_kernel(const Args<T> a) {
     constexpr int VEC = 16 / sizeof(T);
     constexpr int TM = BM / TY;
     constexpr int TN = BN / TX;
@@ -92,11 +120,17 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_simt_kernel(const Args<T> a) 
     const S *__restrict__ B = static_cast<const S *>(a.B) + bidx * a.K * a.N;
     S *C = static_cast<S *>(a.C) + bidx * a.M * a.N;
 
-    T acc[TM][TN];
+    constexpr bool PACKED = IsF32<T>::value;   // f32: accumulate column pairs with fma.rn.f32x2
+    T acc[PACKED ? 1 : TM][PACKED ? 1 : TN];
+    unsigned long long acc2[PACKED ? TM : 1][PACKED ? TN / 2 : 1];
 #pragma unroll
-    for (int i = 0; i < TM; ++i)
+    for (int i = 0; i < (PACKED ? 1 : TM); ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = T(0);
+        for (int j = 0; j < (PACKED ? 1 : TN); ++j) acc[i][j] = T(0);
+#pragma unroll
+    for (int i = 0; i < (PACKED ? TM : 1); ++i)
+#pragma unroll
+        for (int j = 0; j < (PACKED ? TN / 2 : 1); ++j) acc2[i][j] = 0ull;
 
     Vec<T, VEC> ra[A_PER_THREAD], rb[B_PER_THREAD];
 
@@ -181,15 +215,40 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_simt_kernel(const Args<T> a) 
 #pragma unroll
             for (int g = 0; g < GN; ++g)
                 bv[g] = *reinterpret_cast<const Vec<T, VEC> *>(&Bs[buf][k][g * (BN / GN) + tx * VEC]);
+            if constexpr (PACKED) {
+                unsigned long long bp[TN / 2];
 #pragma unroll
-            for (int i = 0; i < TM; ++i)
+                for (int j = 0; j < TN / 2; ++j)
+                    bp[j] = pack2(float(bv[(2 * j) / VEC].v[(2 * j) % VEC]), float(bv[(2 * j + 1) / VEC].v[(2 * j + 1) % VEC]));
 #pragma unroll
-                for (int j = 0; j < TN; ++j)
-                    acc[i][j] += av[i / VEC].v[i % VEC] * bv[j / VEC].v[j % VEC];
+                for (int i = 0; i < TM; ++i) {
+                    const float ai = float(av[i / VEC].v[i % VEC]);
+                    const unsigned long long a2 = pack2(ai, ai);
+#pragma unroll
+                    for (int j = 0; j < TN / 2; ++j) ffma2(acc2[i][j], a2, bp[j]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < TM; ++i)
+#pragma unroll
+                    for (int j = 0; j < TN; ++j)
+                        acc[i][j] += av[i / VEC].v[i % VEC] * bv[j / VEC].v[j % VEC];
+            }
         }
         if (more) store_shared(buf ^ 1);
         __syncthreads();
     }
+
+    // Accumulator (i, j) whichever way it is held.
+    auto acc_at = [&](int i, int j) -> T {
+        if constexpr (PACKED) {
+            float lo, hi;
+            unpack2(acc2[i][j / 2], lo, hi);
+            return T((j & 1) ? hi : lo);
+        } else {
+            return acc[i][j];
+        }
+    };
 
     // Epilogue: thread-tile row i lives at m0 + (i/VEC)*(BM/GM) + ty*VEC + i%VEC.
 #pragma unroll
@@ -205,10 +264,10 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_simt_kernel(const Args<T> a) 
                     const Vec<T, VEC> old = *reinterpret_cast<const Vec<T, VEC> *>(cp);
 #pragma unroll
                     for (int e = 0; e < VEC; ++e)
-                        out.v[e] = a.beta * old.v[e] + a.alpha * acc[i][g * VEC + e];
+                        out.v[e] = a.beta * old.v[e] + a.alpha * acc_at(i, g * VEC + e);
                 } else {
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) out.v[e] = acc[i][g * VEC + e];
+                    for (int e = 0; e < VEC; ++e) out.v[e] = acc_at(i, g * VEC + e);
                 }
                 *reinterpret_cast<Vec<T, VEC> *>(cp) = out;
             } else {
@@ -217,7 +276,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_simt_kernel(const Args<T> a) 
                     for (int e = 0; e < VEC; ++e) {
                         if (c + e < a.N) {
                             S *cp = C + r * a.N + c + e;
-                            T val = acc[i][g * VEC + e];
+                            T val = acc_at(i, g * VEC + e);
                             if (a.scaled) val = a.beta * Conv<S, T>::load(*cp) + a.alpha * val;
                             *cp = Conv<S, T>::store(val);
                         }

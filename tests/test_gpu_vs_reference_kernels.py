@@ -129,3 +129,55 @@ def test_spmm_f32(ref):
         "ours_kernel_ms": event_ms(lambda: klas.spmm(csr, B, mine)),
         "ref_spmm_f32_call_ms": wall_ms(lambda: ref.spmm_f32("Klas_SPMM_spmm_f32", rows, shared, cols, csr, B, theirs)),
         "nnz": csr.nnz}
+
+
+def test_vendor_library_comparison_rows(ref):
+    """cuBLAS (through torch.matmul) and cuSPARSE (through torch.sparse) on the benchmark shapes:
+    recorded for the comparison table only; nothing in the product calls them."""
+    n = 8192
+    A, Bt = synth.gemm_bf16(1, n, n, n, b_col_major=True, device="cuda")
+    D = torch.empty((n, n), device="cuda")
+    TIMINGS["bf16_f32_8192_colmajorB"] = {
+        "ours_kernel_ms": event_ms(lambda: klas.gemm_tc(A, Bt, b_col_major=True, D=D), reps=10),
+        "cublas_bf16_out_bf16_ms": event_ms(lambda: torch.matmul(A, Bt.t()), reps=10),
+        "flop": 2 * n ** 3}
+    Brm = Bt.t().contiguous()
+    TIMINGS["bf16_f32_8192_rowmajorB"] = {
+        "ours_kernel_ms": event_ms(lambda: klas.gemm_tc(A, Brm, D=D), reps=10),
+        "cublas_bf16_out_bf16_ms": event_ms(lambda: torch.matmul(A, Brm), reps=10),
+        "flop": 2 * n ** 3}
+    del A, Bt, Brm, D
+    n = 4096
+    a32, b32 = synth.gemm_f32(0, n, n, n, device="cuda")
+    c32 = torch.empty((n, n), device="cuda")
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        TIMINGS["f32_4096"] = {
+            "ours_kernel_ms": event_ms(lambda: klas.gemm(a32, b32, c32), reps=3),
+            "cublas_sgemm_ms": event_ms(lambda: torch.matmul(a32, b32), reps=3),
+            "ref_BlockTiling2D_128x128x32_8x8_call_ms": wall_ms(lambda: ref.mnk(
+                "Klas_GEMM_BlockTiling2D_g_gemm_f32_128x128x32_8x8", n, n, n, a32, b32, c32,
+                pre=((C.c_float, 1.0), (C.c_float, 0.0))), reps=2),
+            "flop": 2 * n ** 3}
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    a64, b64 = a32[:2048, :2048].double().contiguous(), b32[:2048, :2048].double().contiguous()
+    c64 = torch.empty((2048, 2048), dtype=torch.float64, device="cuda")
+    TIMINGS["f64_2048"] = {
+        "ours_kernel_ms": event_ms(lambda: klas.gemm(a64, b64, c64), reps=3),
+        "cublas_dgemm_ms": event_ms(lambda: torch.matmul(a64, b64), reps=3),
+        "flop": 2 * 2048 ** 3}
+    rows = shared = 131072
+    cols = 256
+    csr = synth.csr_poisson(4, rows, shared, 64.0, device="cuda")
+    Bd = synth.spmm_dense_b(4, shared, cols, device="cuda")
+    Cd = torch.empty((rows, cols), device="cuda")
+    sp = torch.sparse_csr_tensor(csr.row_off.long(), csr.col_ind.long(), csr.elems, size=(rows, shared))
+    got = klas.spmm(csr, Bd, Cd)
+    want = torch.sparse.mm(sp, Bd)
+    assert float((got - want).abs().max()) <= 1e-4
+    TIMINGS["spmm_131072_p64_c256"] = {
+        "ours_kernel_ms": event_ms(lambda: klas.spmm(csr, Bd, Cd), reps=5),
+        "cusparse_csr_spmm_ms": event_ms(lambda: torch.sparse.mm(sp, Bd), reps=5),
+        "nnz": csr.nnz}
