@@ -119,6 +119,17 @@ int klas_b200_gemm_tc(int in_dtype, int out_dtype, int b_major, uint32_t batch,
 int klas_b200_gemm_tc_status(int *site);
 
 /*
+ * Diagnostic: launches one warp that waits, with the same bounded wait the tensor-core
+ * pipeline uses, on a barrier nothing will ever signal.  After `limit_ms` (1..1000) the wait
+ * gives up, the device status word receives site 0x7F, `*gave_up` (optional device int) is set
+ * to 1, and the kernel returns normally: the context stays usable and the next
+ * klas_b200_gemm_tc_status() call reports KLAS_ERR_TIMEOUT once.  Lets a host program (or a
+ * test) exercise its handling of a stalled pipeline without stalling one.
+ * No counterpart in the reference.
+ */
+int klas_b200_debug_wait_probe(uint32_t limit_ms, int *gave_up, void *stream);
+
+/*
  * CSR x dense:  C[rows x cols] = CSR(A)[rows x shared] . B[shared x cols],
  * B and C row-major, dtype KLAS_F32 or KLAS_U32 (wrapping).  Each row's
  * products are summed in CSR order starting from 0.  Every row of C is

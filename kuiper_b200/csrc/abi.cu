@@ -86,6 +86,7 @@ int workspace_release() {
 
 int umma_read_status(int *value);
 int umma_clear_status();
+int umma_wait_probe(uint32_t limit_ms, int *gave_up, cudaStream_t stream);
 
 // Streams and events of the chunked host-buffer calls, one set per device, created on first use.
 struct HostPipe {
@@ -163,6 +164,12 @@ int klas_b200_gemm_tc_status(int *site) {
     if (v == 0) return KLAS_OK;
     if (int rc = umma_clear_status()) return rc;
     return fail(KLAS_ERR_TIMEOUT, "gemm_tc: a device-side wait gave up at site 0x%x", v);
+}
+
+int klas_b200_debug_wait_probe(uint32_t limit_ms, int *gave_up, void *stream) {
+    clear_error();
+    if (limit_ms == 0 || limit_ms > 1000) return fail(KLAS_ERR_INVALID, "wait_probe: limit must be 1..1000 ms");
+    return umma_wait_probe(limit_ms, gave_up, static_cast<cudaStream_t>(stream));
 }
 
 int klas_b200_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32_t nnz,

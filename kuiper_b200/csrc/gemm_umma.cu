@@ -120,7 +120,7 @@ struct Ctl {
 // `site` in the status words and returns false; also returns false early when
 // another role of this CTA (or another CTA) has already given up.
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const Ctl &ctl,
-                                             int site) {
+                                             int site, uint64_t limit_ns = WAIT_LIMIT_NS) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
@@ -132,7 +132,7 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
                 *ctl.abort_flag = 1;
                 return false;
             }
-            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (ptx::globaltimer_ns() - t0 > limit_ns) {
                 *ctl.abort_flag = 1;
                 atomicCAS(&g_umma_status, 0, site);
                 if (ctl.user_status) atomicCAS(ctl.user_status, 0, site);
@@ -806,6 +806,24 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
     }
 }
 
+// Diagnostic kernel: one warp waits, with the pipeline's bounded wait, on a barrier that
+// nothing will ever signal.  After `limit_ns` the wait gives up, records SITE_PROBE in the
+// status word and the kernel returns normally -- the path a stalled pipeline would take.
+enum : int { SITE_PROBE = 0x7F };
+__global__ void wait_probe_kernel(uint64_t limit_ns, int *user_status, int *gave_up) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+    const Ctl ctl{&abort_flag, user_status};
+    const bool ok = bounded_wait(ptx::smem_u32(&bar), 0, ctl, SITE_PROBE, limit_ns);
+    if (threadIdx.x == 0 && gave_up) *gave_up = ok ? 0 : 1;
+}
+
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
@@ -928,6 +946,11 @@ extern "C" int klas_dev_read_umma_profile(unsigned long long *out) {
     return cudaMemcpyFromSymbol(out, umma::g_umma_prof, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? 0 : 1;
 }
 #endif
+
+int umma_wait_probe(uint32_t limit_ms, int *gave_up, cudaStream_t stream) {
+    umma::wait_probe_kernel<<<1, 32, 0, stream>>>(uint64_t(limit_ms) * 1000000ull, nullptr, gave_up);
+    return check_cuda(cudaGetLastError(), "wait_probe_kernel launch");
+}
 
 int umma_read_status(int *value) {
     return check_cuda(cudaMemcpyFromSymbol(value, umma::g_umma_status, sizeof(int)),
