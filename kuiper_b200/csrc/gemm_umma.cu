@@ -119,13 +119,18 @@ struct Ctl {
 // Spins on an mbarrier phase for at most WAIT_LIMIT_NS.  On give-up records
 // `site` in the status words and returns false; also returns false early when
 // another role of this CTA (or another CTA) has already given up.
+// `backoff_ns` > 0 makes the thread sleep between polls: used by the roles whose waits are long
+// and not on the critical path (epilogue, producer), so that they do not burn issue slots and
+// power while the tensor pipe works.
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const Ctl &ctl,
-                                             int site, uint64_t limit_ns = WAIT_LIMIT_NS) {
+                                             int site, uint64_t limit_ns = WAIT_LIMIT_NS,
+                                             uint32_t backoff_ns = 0) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
     for (;;) {
         if (ptx::mbar_try_wait(bar, parity)) return true;
+        if (backoff_ns) __nanosleep(backoff_ns);
         if ((++spins & 0x3F) == 0) {
             if (*ctl.abort_flag != 0) return false;
             if (*reinterpret_cast<volatile int *>(&g_umma_status) != 0) {
@@ -297,7 +302,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (stage % S::RELEASE_GROUP == 0) {
                     // stages are handed back in groups; the group's last stage carries the barrier
                     KLAS_PROF_BEGIN;
-                    ok = bounded_wait(empty_bar(stage + S::RELEASE_GROUP - 1), phase ^ 1u, ctl, SITE_PRODUCER_EMPTY);
+                    ok = bounded_wait(empty_bar(stage + S::RELEASE_GROUP - 1), phase ^ 1u, ctl, SITE_PRODUCER_EMPTY, WAIT_LIMIT_NS, 64);
                     KLAS_PROF_END(prof_acc0);
                     if (!ok) break;
                 }
@@ -431,9 +436,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             decode_tile(t, p, b, tm, tn);
             if (p.num_kb > 0) {
                 KLAS_PROF_BEGIN;
-                ok = bounded_wait(tfull_bar(acc), acc_phase, ctl, SITE_EPI_TMEM_FULL);
+                ok = lane != 0 || bounded_wait(tfull_bar(acc), acc_phase, ctl, SITE_EPI_TMEM_FULL, WAIT_LIMIT_NS, 128);
                 KLAS_PROF_END(prof_acc0);
-                ok = __all_sync(0xffffffffu, ok);
+                ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;   // lane 0 polls, the warp follows
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
             }
@@ -595,7 +600,7 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
             const int32_t a_row = int32_t(tm * TILE_M + cta_rank * A_ROWS);
             const int32_t b_col = int32_t(tn * BN + cta_rank * B_COLS);
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-                ok = bounded_wait(empty_bar(stage), phase ^ 1u, ctl, SITE_WIDE | SITE_PRODUCER_EMPTY);
+                ok = bounded_wait(empty_bar(stage), phase ^ 1u, ctl, SITE_WIDE | SITE_PRODUCER_EMPTY, WAIT_LIMIT_NS, 64);
                 if (!ok) break;
                 const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
                 const uint32_t b_dst = a_dst + A_BYTES;
@@ -702,8 +707,8 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
             decode_tile(t, p, b, tm, tn);
             const bool have_acc = p.num_kb > 0;
             if (have_acc) {
-                ok = bounded_wait(tfull_bar, tile_phase, ctl, SITE_WIDE | SITE_EPI_TMEM_FULL);
-                ok = __all_sync(0xffffffffu, ok);
+                ok = lane != 0 || bounded_wait(tfull_bar, tile_phase, ctl, SITE_WIDE | SITE_EPI_TMEM_FULL, WAIT_LIMIT_NS, 128);
+                ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;   // lane 0 polls, the warp follows
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
             }
