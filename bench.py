@@ -510,11 +510,19 @@ def main():
             else:
                 peak, runit = 2 * 128 * 148 * 1.965e9 / 1e12, "TFLOP/s"
                 peak_note = "2*128 lanes*148 SMs*1965 MHz FP32 issue peak (nominal)"
+        extra = {}
+        if wl.name == "spmm":
+            # every nonzero moves 4*cols bytes of a random row of B through L2 whatever the schedule
+            gather = wl.nnz * (8 + 4 * wl.COLS) + 4 * wl.rows * wl.COLS + 8 * wl.rows
+            extra = {"l2_gather_bytes_per_launch": gather,
+                     "l2_gather_achieved_gbs": gather / (per_launch_ms * 1e-3) / 1e9,
+                     "l2_gather_note": "random 512-byte row segments of B; highest L2->SM rate measured on this GPU "
+                                       "(tensor-core GEMM, 128x256 tiles) is 15600 GB/s"}
         roofline = {"bound": "tensor" if wl.bound == "tensor" else "hbm" if wl.bound == "hbm" else "issue",
                     "achieved": achieved, "peak": peak, "unit": runit, "frac": achieved / peak,
                     "traffic": NCU_TRAFFIC.get(wl.name), "peak_note": peak_note,
                     "algorithmic_bytes_per_launch": wl.algorithmic_bytes,
-                    "kernel_ms": per_launch_ms}
+                    "kernel_ms": per_launch_ms, **extra}
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": per_launch_ms, "higher_is_better": True, "scaling": "weak" if wl.name in ("gemm_bf16",) else "strong",
