@@ -21,6 +21,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "klas_internal.h"
 
 namespace klas {
@@ -327,8 +329,13 @@ static int launch_type(uint32_t batch, uint64_t m, uint64_t n, uint64_t k, T alp
     if constexpr (sizeof(T) == 4) {
         // Large tiles once they fill the machine; small ones otherwise.
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 127) / 128) * batch;
-        if (big_tiles >= uint64_t(sm_count))
+        const uint64_t mid_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
+        int pick = big_tiles >= uint64_t(sm_count) ? 2 : (mid_tiles * 10 >= uint64_t(sm_count) * 8 ? 1 : 0);
+        if (const char *t = getenv("KLAS_SIMT_TILE")) pick = atoi(t);
+        if (pick == 2)
             return launch_cfg<S, T, 128, 128, 16>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
+        if (pick == 1)
+            return launch_cfg<S, T, 128, 64, 16>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
         return launch_cfg<S, T, 64, 64, 16>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
     } else {
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
