@@ -438,9 +438,12 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    # Libraries (NCCL's version banner, for one) may write to stdout; the contract is ONE JSON
+    # line there, so stdout is parked on stderr until the line is printed.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"   # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=device)
     from kuiper_b200 import klas  # noqa: F401  (fails loudly if libklas_b200.so is missing)
 
@@ -537,7 +540,10 @@ def main():
             cb = cpu_baseline_leg(wl.name)
             if cb:
                 line["cpu_baseline"] = cb
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     if world > 1:
         dist.destroy_process_group()
     return 0
