@@ -104,4 +104,39 @@
     KLAS_ENTRY(Klas_SPMM_spmm_f32, (KLAS_SPMM_PARAMS(Kuiper_Sparse_Matrix_smatrix__float, float)), SPMM, \
                KLAS_F32, float, 0)
 
+/* ---- Softmax / LogSoftmax (dist/Klas_Softmax.h, dist/Klas_LogSoftmax.h): in-place vector ------
+ * softmax; _gpu names take a device pointer, the others a host pointer; _n names carry a
+ * thread-count hint.  X(unit, function stem, label, C type). */
+#define KLAS_SOFTMAX_TYPES(X, U, F) X(U, F, f16, half) X(U, F, f32, float) X(U, F, f64, double)
+#define KLAS_SOFTMAX_ENTRIES(U, F, L, T)                                                                \
+    KLAS_ENTRY(Klas_##U##_##F##_gpu_n_##L, (uint32_t nth, uint32_t lena, T *a), SOFTMAX_DEV, U, L)      \
+    KLAS_ENTRY(Klas_##U##_##F##_gpu_##L, (uint32_t lena, T *a), SOFTMAX_DEV, U, L)                      \
+    KLAS_ENTRY(Klas_##U##_##F##_n_##L, (uint32_t nth, uint32_t lena, T *a), SOFTMAX_HOST, U, L)         \
+    KLAS_ENTRY(Klas_##U##_##F##_##L, (uint32_t lena, T *a), SOFTMAX_HOST, U, L)
+
+/* ---- RowSoftmax (dist/Klas_RowSoftmax.h:7-11): rows of a row-major m x n device matrix ------- */
+#define KLAS_ROWSOFTMAX_ENTRIES                                                                          \
+    KLAS_ENTRY(Klas_RowSoftmax_row_softmax_rm_f32, (uint32_t m, uint32_t n, uint32_t nth, float *a), ROWSOFTMAX, f32) \
+    KLAS_ENTRY(Klas_RowSoftmax_row_softmax_rm_f64, (uint32_t m, uint32_t n, uint32_t nth, double *a), ROWSOFTMAX, f64)
+
+/* ---- RowScale (dist/Klas_RowScale.h:7-23): b[r][c] = a[r] * b[r][c] --------------------------- */
+#define KLAS_ROWSCALE_TYPES(X) X(f16, half) X(f32, float) X(f64, double)
+#define KLAS_ROWSCALE_ENTRIES(L, T)                                                                     \
+    KLAS_ENTRY(Klas_RowScale_rowscale_##L##_rowmajor, (uint32_t m, uint32_t n, T *a, T *b), ROWSCALE, L, 0) \
+    KLAS_ENTRY(Klas_RowScale_rowscale_##L##_colmajor, (uint32_t m, uint32_t n, T *a, T *b), ROWSCALE, L, 1)
+
+/* ---- HReduce / AtomicReduce (dist/Klas_HReduce.h:7-20, dist/Klas_AtomicReduce.h:7-13) ---------
+ * return the sum of a device vector to the host: KLAS_RENTRY(return type, name, params, label). */
+#define KLAS_HREDUCE_ENTRIES                                                                            \
+    KLAS_RENTRY(half, Klas_HReduce_reduce_f16_plus, (uint32_t nth, uint32_t lena, half *a), f16, lena)  \
+    KLAS_RENTRY(float, Klas_HReduce_reduce_f32_plus, (uint32_t nth, uint32_t lena, float *a), f32, lena) \
+    KLAS_RENTRY(double, Klas_HReduce_reduce_f64_plus, (uint32_t nth, uint32_t lena, double *a), f64, lena) \
+    KLAS_RENTRY(uint32_t, Klas_HReduce_reduce_u32_plus, (uint32_t nth, uint32_t lena, uint32_t *a), u32, lena) \
+    KLAS_RENTRY(uint64_t, Klas_HReduce_reduce_u64_plus, (uint32_t nth, uint32_t lena, uint64_t *a), u64, lena)
+#define KLAS_ATOMICREDUCE_ENTRIES                                                                       \
+    KLAS_RENTRY(uint32_t, Klas_AtomicReduce_reduce_u32, (uint32_t n, uint32_t *a), u32, n)              \
+    KLAS_RENTRY(uint64_t, Klas_AtomicReduce_reduce_u64, (uint32_t n, uint64_t *a), u64, n)              \
+    KLAS_RENTRY(float, Klas_AtomicReduce_reduce_f32, (uint32_t n, float *a), f32, n)                    \
+    KLAS_RENTRY(double, Klas_AtomicReduce_reduce_f64, (uint32_t n, double *a), f64, n)
+
 #endif /* KLAS_SIGNATURES_H */

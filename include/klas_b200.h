@@ -164,6 +164,46 @@ int klas_b200_spmm_host(int dtype, uint32_t rows, uint32_t shared, uint32_t cols
                         const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
                         const uint32_t *row_indices, const void *B, void *C);
 
+/*
+ * Row-wise neighbours of the products (what sits either side of Q.K^T and P.V in an
+ * attention block).  dtype KLAS_F16 / KLAS_F32 / KLAS_F64 unless said otherwise; fp16 data is
+ * processed in fp32 and rounded once.
+ *
+ * klas_b200_softmax: in place, a[r][c] = exp(a[r][c] - max_r) / sum_c exp(a[r][c] - max_r) for
+ * every row of the row-major rows x cols matrix `a` (log_softmax != 0: a[r][c] - max_r - log(sum)).
+ * rows == 1 is the vector case: the vector is cut into 16384-element chunks folded by separate
+ * CTAs, which needs `scratch`: klas_b200_softmax_scratch_bytes(rows, cols) bytes of 16-byte
+ * aligned device memory (0 for rows > 1), caller-owned, overwritten.
+ * Replaces: Klas_Softmax_softmax_gpu{,_n}_* (dist/Klas_Softmax.h), Klas_LogSoftmax_log_softmax_gpu{,_n}_*
+ * (dist/Klas_LogSoftmax.h), Klas_RowSoftmax_row_softmax_rm_* (dist/Klas_RowSoftmax.h:7-11).
+ * klas_b200_softmax_host: the same on a HOST buffer (copy in, compute, copy out); replaces the
+ * host-pointer variants Klas_Softmax_softmax{,_n}_* and Klas_LogSoftmax_log_softmax{,_n}_*.
+ */
+size_t klas_b200_softmax_scratch_bytes(uint64_t rows, uint64_t cols);
+int klas_b200_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a,
+                      void *scratch, size_t scratch_bytes, void *stream);
+int klas_b200_softmax_host(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a);
+
+/*
+ * b[r][c] = scale[r] * b[r][c] for the m x n matrix b, row-major (col_major == 0) or
+ * column-major.  Replaces: Klas_RowScale_rowscale_*_{rowmajor,colmajor} (dist/Klas_RowScale.h:7-23).
+ */
+int klas_b200_rowscale(int dtype, int col_major, uint64_t m, uint64_t n, const void *scale, void *b,
+                       void *stream);
+
+/*
+ * *result = sum of a[0..n) (dtype F16, F32, F64, U32 or U64; integers wrap; floating-point sums
+ * are folded in a fixed order, so repeated calls agree bit for bit).  `result` is a device
+ * scalar; `scratch` = klas_b200_reduce_scratch_bytes(n) bytes of 8-byte aligned device memory.
+ * klas_b200_reduce_sum_host: `a` on the device, `result` on the host, blocking.
+ * Replaces: Klas_HReduce_reduce_*_plus (dist/Klas_HReduce.h:7-20) and
+ * Klas_AtomicReduce_reduce_* (dist/Klas_AtomicReduce.h:7-13).
+ */
+size_t klas_b200_reduce_scratch_bytes(uint64_t n);
+int klas_b200_reduce_sum(int dtype, uint64_t n, const void *a, void *result, void *scratch,
+                         size_t scratch_bytes, void *stream);
+int klas_b200_reduce_sum_host(int dtype, uint64_t n, const void *a, void *result);
+
 /* Frees the calling device's host-variant workspace. */
 int klas_b200_release_workspace(void);
 

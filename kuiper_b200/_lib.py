@@ -30,6 +30,13 @@ SIGNATURES = {
     "klas_b200_gemm_tc_host": (_int, [_int, _int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp,
                                        _f32, _f32]),
     "klas_b200_spmm_host": (_int, [_int, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "klas_b200_softmax_scratch_bytes": (C.c_size_t, [_u64, _u64]),
+    "klas_b200_softmax": (_int, [_int, _int, _u64, _u64, _vp, _vp, C.c_size_t, _vp]),
+    "klas_b200_softmax_host": (_int, [_int, _int, _u64, _u64, _vp]),
+    "klas_b200_rowscale": (_int, [_int, _int, _u64, _u64, _vp, _vp, _vp]),
+    "klas_b200_reduce_scratch_bytes": (C.c_size_t, [_u64]),
+    "klas_b200_reduce_sum": (_int, [_int, _u64, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "klas_b200_reduce_sum_host": (_int, [_int, _u64, _vp, _vp]),
     "klas_b200_release_workspace": (_int, []),
 }
 

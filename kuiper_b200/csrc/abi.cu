@@ -292,6 +292,60 @@ int klas_b200_spmm_host(int dtype, uint32_t rows, uint32_t shared, uint32_t cols
     return KLAS_OK;
 }
 
+size_t klas_b200_softmax_scratch_bytes(uint64_t rows, uint64_t cols) { return softmax_scratch_bytes(rows, cols); }
+
+int klas_b200_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a, void *scratch,
+                      size_t scratch_bytes, void *stream) {
+    clear_error();
+    return launch_softmax(dtype, log_softmax, rows, cols, a, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int klas_b200_softmax_host(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a) {
+    clear_error();
+    const size_t es = dtype_size(dtype), bytes = size_t(rows) * cols * es;
+    if (es == 0) return fail(KLAS_ERR_INVALID, "softmax_host: bad dtype");
+    if (bytes == 0) return KLAS_OK;
+    if (!a) return fail(KLAS_ERR_INVALID, "softmax_host: null data pointer");
+    cudaStream_t s = nullptr;
+    void *dA, *dS;
+    if (int rc = stage_in(0, a, bytes, s, &dA)) return rc;
+    const size_t sb = softmax_scratch_bytes(rows, cols);
+    if (int rc = workspace_reserve(1, sb, &dS)) return rc;
+    if (int rc = launch_softmax(dtype, log_softmax, rows, cols, dA, dS, sb, s)) return rc;
+    KLAS_TRY_CUDA(cudaMemcpyAsync(a, dA, bytes, cudaMemcpyDeviceToHost, s));
+    KLAS_TRY_CUDA(cudaStreamSynchronize(s));
+    return KLAS_OK;
+}
+
+int klas_b200_rowscale(int dtype, int col_major, uint64_t m, uint64_t n, const void *scale, void *b, void *stream) {
+    clear_error();
+    return launch_rowscale(dtype, col_major, m, n, scale, b, static_cast<cudaStream_t>(stream));
+}
+
+size_t klas_b200_reduce_scratch_bytes(uint64_t n) { return reduce_scratch_bytes(n); }
+
+int klas_b200_reduce_sum(int dtype, uint64_t n, const void *a, void *result, void *scratch, size_t scratch_bytes,
+                         void *stream) {
+    clear_error();
+    return launch_reduce_sum(dtype, n, a, result, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int klas_b200_reduce_sum_host(int dtype, uint64_t n, const void *a, void *result) {
+    clear_error();
+    const size_t es = dtype_size(dtype);
+    if (es == 0 || dtype == KLAS_BF16) return fail(KLAS_ERR_INVALID, "reduce_host: bad dtype");
+    if (!result) return fail(KLAS_ERR_INVALID, "reduce_host: null result pointer");
+    cudaStream_t s = nullptr;
+    void *dS, *dOut;
+    const size_t sb = reduce_scratch_bytes(n);
+    if (int rc = workspace_reserve(6, sb, &dS)) return rc;
+    if (int rc = workspace_reserve(7, 16, &dOut)) return rc;
+    if (int rc = launch_reduce_sum(dtype, n, a, dOut, dS, sb, s)) return rc;
+    KLAS_TRY_CUDA(cudaMemcpyAsync(result, dOut, es, cudaMemcpyDeviceToHost, s));
+    KLAS_TRY_CUDA(cudaStreamSynchronize(s));
+    return KLAS_OK;
+}
+
 int klas_b200_release_workspace(void) {
     clear_error();
     return workspace_release();

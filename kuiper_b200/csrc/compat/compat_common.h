@@ -99,5 +99,44 @@ static inline void finish(int status, const char *entry, bool tensor_core) {
     klas_compat::finish(klas_b200_spmm(CODE, rows, shared, cols, gA.nnz, gA.elems, gA.col_ind, gA.row_off, \
                                        row_indices, gB, gC, NULL), NAME, false);
 
+// ---- row-wise neighbours ------------------------------------------------------------------------
+#define KLAS_IS_LOG_Softmax 0
+#define KLAS_IS_LOG_LogSoftmax 1
+
+namespace klas_compat {
+// Device-pointer softmax entry points: scratch for the chunked vector path is allocated for the
+// call, as the reference allocates its maxs/sums scalars (dist/Klas_Softmax.cu:210-213).
+static inline void softmax_device(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a,
+                                  const char *entry) {
+    void *scratch = NULL;
+    const size_t bytes = klas_b200_softmax_scratch_bytes(rows, cols);
+    if (bytes) __MUST(cudaMalloc(&scratch, bytes), "cudaMalloc(scratch)", entry, __FILE__, __LINE__);
+    finish(klas_b200_softmax(dtype, log_softmax, rows, cols, a, scratch, bytes, NULL), entry, false);
+    if (scratch) __MUST(cudaFree(scratch), "cudaFree(scratch)", entry, __FILE__, __LINE__);
+}
+static inline void check(int status, const char *entry) {
+    if (status != KLAS_OK) {
+        fprintf(stderr, "*** ABORTING ***\n %s failed: %s\n", entry, klas_b200_last_error());
+        exit(1);
+    }
+}
+}  // namespace klas_compat
+
+#define KLAS_BODY_SOFTMAX_DEV(NAME, U, L) \
+    klas_compat::softmax_device(KLAS_CODE_##L, KLAS_IS_LOG_##U, 1, lena, a, NAME);
+#define KLAS_BODY_SOFTMAX_HOST(NAME, U, L) \
+    klas_compat::check(klas_b200_softmax_host(KLAS_CODE_##L, KLAS_IS_LOG_##U, 1, lena, a), NAME);
+#define KLAS_BODY_ROWSOFTMAX(NAME, L) klas_compat::softmax_device(KLAS_CODE_##L, 0, m, n, a, NAME);
+#define KLAS_BODY_ROWSCALE(NAME, L, COLMAJOR) \
+    klas_compat::finish(klas_b200_rowscale(KLAS_CODE_##L, COLMAJOR, m, n, a, b, NULL), NAME, false);
+
 #define KLAS_ENTRY(name, params, KIND, ...) \
     void name params { KLAS_BODY_##KIND(#name, __VA_ARGS__) }
+
+// Reductions return their scalar to the host.
+#define KLAS_RENTRY(ret, name, params, L, COUNT)                                                   \
+    ret name params {                                                                              \
+        ret result;                                                                                \
+        klas_compat::check(klas_b200_reduce_sum_host(KLAS_CODE_##L, COUNT, a, &result), #name);    \
+        return result;                                                                             \
+    }

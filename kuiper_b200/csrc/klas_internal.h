@@ -63,4 +63,13 @@ int launch_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32
                 const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
                 const uint32_t *row_indices, const void *B, void *C, cudaStream_t stream);
 
+size_t softmax_scratch_bytes(uint64_t rows, uint64_t cols);
+size_t reduce_scratch_bytes(uint64_t n);
+int launch_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a, void *scratch,
+                   size_t scratch_bytes, cudaStream_t stream);
+int launch_rowscale(int dtype, int col_major, uint64_t m, uint64_t n, const void *scale, void *b,
+                    cudaStream_t stream);
+int launch_reduce_sum(int dtype, uint64_t n, const void *a, void *out, void *scratch, size_t scratch_bytes,
+                      cudaStream_t stream);
+
 }  // namespace klas

@@ -1,0 +1,322 @@
+// Row-wise neighbours of the matrix products: softmax / log-softmax of a vector or of the
+// rows of a matrix, row scaling, and sum reduction.  All are bandwidth-bound; each is written
+// as the minimum number of passes over the data.
+//
+//   softmax, one long vector   two launches: (1) every CTA folds one chunk (>= 16384 elements, at
+//                              most 2048 chunks) into a running (max, sum of exp(x - max)) pair
+//                              and writes it to scratch; (2) every CTA folds the per-chunk pairs
+//                              (<= 32 KiB, L2 resident), then rewrites its chunk.  2 reads + 1
+//                              write of the vector.
+//   softmax, rows of a matrix  one CTA per row, the same two passes inside the CTA, no scratch.
+//   reduce                     per-CTA partial sums to scratch, one CTA folds them in a fixed order
+//                              (deterministic for floating point).
+//
+// Takes over the work of the reference's multi-launch kernels: dist/Klas_Softmax.cu:128-260
+// (block max -> subtract -> block sum of exp -> divide, one CTA for the reductions),
+// dist/Klas_LogSoftmax.cu, dist/Klas_RowSoftmax.cu:3-45, dist/Klas_RowScale.cu:3-30,
+// dist/Klas_HReduce.cu and dist/Klas_AtomicReduce.cu (one atomic per element).
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "klas_internal.h"
+
+namespace klas {
+namespace rowops {
+
+constexpr int THREADS = 256;
+constexpr uint64_t MIN_CHUNK = 16384;   // fewest elements of a long vector one CTA owns
+constexpr uint32_t MAX_PARTS = 2048;    // most CTAs (and per-chunk statistics) of one vector
+
+template <typename T>
+struct Num {
+    using Acc = float;
+    static __device__ __forceinline__ float up(T v) { return float(v); }
+    static __device__ __forceinline__ T down(float v) { return T(v); }
+};
+template <>
+struct Num<__half> {
+    using Acc = float;
+    static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
+};
+template <>
+struct Num<double> {
+    using Acc = double;
+    static __device__ __forceinline__ double up(double v) { return v; }
+    static __device__ __forceinline__ double down(double v) { return v; }
+};
+template <>
+struct Num<uint32_t> {
+    using Acc = uint32_t;
+    static __device__ __forceinline__ uint32_t up(uint32_t v) { return v; }
+    static __device__ __forceinline__ uint32_t down(uint32_t v) { return v; }
+};
+template <>
+struct Num<uint64_t> {
+    using Acc = uint64_t;
+    static __device__ __forceinline__ uint64_t up(uint64_t v) { return v; }
+    static __device__ __forceinline__ uint64_t down(uint64_t v) { return v; }
+};
+
+__device__ __forceinline__ float fexp(float x) { return expf(x); }
+__device__ __forceinline__ double fexp(double x) { return exp(x); }
+__device__ __forceinline__ float flog(float x) { return logf(x); }
+__device__ __forceinline__ double flog(double x) { return log(x); }
+
+// Running softmax statistics of a set of values: their maximum and sum of exp(x - maximum).
+template <typename A>
+struct MaxSum {
+    A m, s;
+};
+template <typename A>
+__device__ __forceinline__ MaxSum<A> ms_empty() {
+    return {A(-INFINITY), A(0)};
+}
+template <typename A>
+__device__ __forceinline__ MaxSum<A> ms_merge(MaxSum<A> x, MaxSum<A> y) {
+    if (y.s == A(0)) return x;
+    if (x.s == A(0)) return y;
+    const A m = x.m > y.m ? x.m : y.m;
+    return {m, x.s * fexp(x.m - m) + y.s * fexp(y.m - m)};
+}
+template <typename A>
+__device__ __forceinline__ MaxSum<A> ms_push(MaxSum<A> x, A v) {
+    if (v <= x.m) return {x.m, x.s + fexp(v - x.m)};
+    return {v, x.s * fexp(x.m - v) + A(1)};   // exp(-inf) = 0 covers the empty state
+}
+
+template <typename A>
+__device__ __forceinline__ MaxSum<A> ms_block_reduce(MaxSum<A> v, MaxSum<A> *smem) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        MaxSum<A> o;
+        o.m = __shfl_xor_sync(0xffffffffu, v.m, off);
+        o.s = __shfl_xor_sync(0xffffffffu, v.s, off);
+        v = ms_merge(v, o);
+    }
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    MaxSum<A> r = ms_empty<A>();
+    for (int w = 0; w < THREADS / 32; ++w) r = ms_merge(r, smem[w]);   // same order in every thread
+    __syncthreads();
+    return r;
+}
+
+template <typename T, bool LOG>
+__device__ __forceinline__ T finish(T x, typename Num<T>::Acc m, typename Num<T>::Acc s_or_logs) {
+    using A = typename Num<T>::Acc;
+    const A v = Num<T>::up(x);
+    if (LOG) return Num<T>::down((v - m) - s_or_logs);   // s_or_logs = log(sum)
+    return Num<T>::down(fexp(v - m) / s_or_logs);          // s_or_logs = sum
+}
+
+// ---- long vector ------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(THREADS) softmax_partials_kernel(const T *__restrict__ a, uint64_t n,
+                                                                  uint64_t chunk,
+                                                                  MaxSum<typename Num<T>::Acc> *partials) {
+    using A = typename Num<T>::Acc;
+    __shared__ MaxSum<A> smem[THREADS / 32];
+    const uint64_t lo = uint64_t(blockIdx.x) * chunk;
+    const uint64_t hi = lo + chunk < n ? lo + chunk : n;
+    MaxSum<A> st = ms_empty<A>();
+    for (uint64_t i = lo + threadIdx.x; i < hi; i += THREADS) st = ms_push(st, A(Num<T>::up(a[i])));
+    st = ms_block_reduce(st, smem);
+    if (threadIdx.x == 0) partials[blockIdx.x] = st;
+}
+
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(THREADS) softmax_apply_kernel(T *a, uint64_t n, uint64_t chunk,
+                                                               const MaxSum<typename Num<T>::Acc> *partials,
+                                                               uint32_t nparts) {
+    using A = typename Num<T>::Acc;
+    __shared__ MaxSum<A> smem[THREADS / 32];
+    MaxSum<A> st = ms_empty<A>();
+    for (uint32_t i = threadIdx.x; i < nparts; i += THREADS) st = ms_merge(st, partials[i]);
+    st = ms_block_reduce(st, smem);
+    const A denom = LOG ? flog(st.s) : st.s;
+    const uint64_t lo = uint64_t(blockIdx.x) * chunk;
+    const uint64_t hi = lo + chunk < n ? lo + chunk : n;
+    for (uint64_t i = lo + threadIdx.x; i < hi; i += THREADS) a[i] = finish<T, LOG>(a[i], st.m, denom);
+}
+
+// ---- rows of a matrix -------------------------------------------------------------------------
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(THREADS) row_softmax_kernel(T *a, uint64_t cols) {
+    using A = typename Num<T>::Acc;
+    __shared__ MaxSum<A> smem[THREADS / 32];
+    T *row = a + uint64_t(blockIdx.x) * cols;
+    MaxSum<A> st = ms_empty<A>();
+    for (uint64_t i = threadIdx.x; i < cols; i += THREADS) st = ms_push(st, A(Num<T>::up(row[i])));
+    st = ms_block_reduce(st, smem);
+    const A denom = LOG ? flog(st.s) : st.s;
+    for (uint64_t i = threadIdx.x; i < cols; i += THREADS) row[i] = finish<T, LOG>(row[i], st.m, denom);
+}
+
+// ---- row scaling: b[r][c] = scale[r] * b[r][c], b row- or column-major -------------------------
+template <typename T>
+__global__ void __launch_bounds__(THREADS) rowscale_kernel(const T *__restrict__ scale, T *b, uint64_t m,
+                                                          uint64_t n, int col_major) {
+    const uint64_t total = m * n;
+    for (uint64_t i = uint64_t(blockIdx.x) * THREADS + threadIdx.x; i < total; i += uint64_t(gridDim.x) * THREADS) {
+        const uint64_t r = col_major ? i % m : i / n;   // i walks memory order in both layouts
+        b[i] = scale[r] * b[i];
+    }
+}
+
+// ---- sum reduction ----------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(THREADS) reduce_partials_kernel(const T *__restrict__ a, uint64_t n,
+                                                                 typename Num<T>::Acc *partials) {
+    using A = typename Num<T>::Acc;
+    __shared__ A smem[THREADS / 32];
+    A acc = A(0);
+    for (uint64_t i = uint64_t(blockIdx.x) * THREADS + threadIdx.x; i < n; i += uint64_t(gridDim.x) * THREADS)
+        acc += A(Num<T>::up(a[i]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        A r = A(0);
+        for (int w = 0; w < THREADS / 32; ++w) r += smem[w];
+        partials[blockIdx.x] = r;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS) reduce_final_kernel(const typename Num<T>::Acc *partials, uint32_t nparts,
+                                                              T *out) {
+    using A = typename Num<T>::Acc;
+    __shared__ A smem[THREADS];
+    A acc = A(0);
+    for (uint32_t i = threadIdx.x; i < nparts; i += THREADS) acc += partials[i];
+    smem[threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        A r = A(0);
+        for (int i = 0; i < THREADS; ++i) r += smem[i];
+        *out = Num<T>::down(r);
+    }
+}
+
+// Elements per CTA of an n-element vector: a multiple of 1024, at least MIN_CHUNK, and large
+// enough that no more than MAX_PARTS CTAs are needed.
+static uint64_t vector_chunk(uint64_t n) {
+    uint64_t c = (n + MAX_PARTS - 1) / MAX_PARTS;
+    c = (c + 1023) / 1024 * 1024;
+    return c < MIN_CHUNK ? MIN_CHUNK : c;
+}
+static uint32_t vector_chunks(uint64_t n) {
+    const uint64_t c = vector_chunk(n);
+    return uint32_t((n + c - 1) / c);
+}
+static uint32_t reduce_blocks(uint64_t n) {
+    const uint64_t want = (n + uint64_t(THREADS) * 16 - 1) / (uint64_t(THREADS) * 16);
+    return uint32_t(want < 1 ? 1 : (want > 1024 ? 1024 : want));
+}
+
+template <typename T>
+static int softmax_t(int log_softmax, uint64_t rows, uint64_t cols, void *a, void *scratch, cudaStream_t s) {
+    T *p = static_cast<T *>(a);
+    if (rows > 1) {
+        if (rows > 0x7fffffffull) return fail(KLAS_ERR_TOO_LARGE, "softmax: too many rows");
+        if (log_softmax)
+            row_softmax_kernel<T, true><<<unsigned(rows), THREADS, 0, s>>>(p, cols);
+        else
+            row_softmax_kernel<T, false><<<unsigned(rows), THREADS, 0, s>>>(p, cols);
+        return check_cuda(cudaGetLastError(), "row_softmax_kernel launch");
+    }
+    using A = typename Num<T>::Acc;
+    const uint64_t chunk = vector_chunk(cols);
+    const uint32_t parts = vector_chunks(cols);
+    auto *partials = static_cast<MaxSum<A> *>(scratch);
+    softmax_partials_kernel<T><<<parts, THREADS, 0, s>>>(p, cols, chunk, partials);
+    if (int rc = check_cuda(cudaGetLastError(), "softmax_partials_kernel launch")) return rc;
+    if (log_softmax)
+        softmax_apply_kernel<T, true><<<parts, THREADS, 0, s>>>(p, cols, chunk, partials, parts);
+    else
+        softmax_apply_kernel<T, false><<<parts, THREADS, 0, s>>>(p, cols, chunk, partials, parts);
+    return check_cuda(cudaGetLastError(), "softmax_apply_kernel launch");
+}
+
+template <typename T>
+static int reduce_t(uint64_t n, const void *a, void *out, void *scratch, cudaStream_t s) {
+    using A = typename Num<T>::Acc;
+    const uint32_t blocks = reduce_blocks(n);
+    reduce_partials_kernel<T><<<blocks, THREADS, 0, s>>>(static_cast<const T *>(a), n, static_cast<A *>(scratch));
+    if (int rc = check_cuda(cudaGetLastError(), "reduce_partials_kernel launch")) return rc;
+    reduce_final_kernel<T><<<1, THREADS, 0, s>>>(static_cast<const A *>(scratch), blocks, static_cast<T *>(out));
+    return check_cuda(cudaGetLastError(), "reduce_final_kernel launch");
+}
+
+}  // namespace rowops
+
+size_t softmax_scratch_bytes(uint64_t rows, uint64_t cols) {
+    if (rows != 1) return 0;
+    return size_t(rowops::vector_chunks(cols)) * 16;
+}
+
+size_t reduce_scratch_bytes(uint64_t n) { return size_t(rowops::reduce_blocks(n)) * 8; }
+
+int launch_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a, void *scratch,
+                   size_t scratch_bytes, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return KLAS_OK;
+    if (!a) return fail(KLAS_ERR_INVALID, "softmax: null data pointer");
+    const size_t need = softmax_scratch_bytes(rows, cols);
+    if (need > 0 && (!scratch || scratch_bytes < need))
+        return fail(KLAS_ERR_INVALID, "softmax: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
+    if (need > 0 && (reinterpret_cast<uintptr_t>(scratch) & 15u))
+        return fail(KLAS_ERR_INVALID, "softmax: scratch must be 16-byte aligned");
+    switch (dtype) {
+        case KLAS_F16: return rowops::softmax_t<__half>(log_softmax, rows, cols, a, scratch, stream);
+        case KLAS_F32: return rowops::softmax_t<float>(log_softmax, rows, cols, a, scratch, stream);
+        case KLAS_F64: return rowops::softmax_t<double>(log_softmax, rows, cols, a, scratch, stream);
+        default: return fail(KLAS_ERR_INVALID, "softmax: dtype must be F16, F32 or F64");
+    }
+}
+
+int launch_rowscale(int dtype, int col_major, uint64_t m, uint64_t n, const void *scale, void *b,
+                    cudaStream_t stream) {
+    if (m == 0 || n == 0) return KLAS_OK;
+    if (!scale || !b) return fail(KLAS_ERR_INVALID, "rowscale: null pointer");
+    const uint64_t total = m * n;
+    uint64_t blocks = (total + rowops::THREADS - 1) / rowops::THREADS;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    switch (dtype) {
+        case KLAS_F16:
+            rowops::rowscale_kernel<__half><<<unsigned(blocks), rowops::THREADS, 0, stream>>>(
+                static_cast<const __half *>(scale), static_cast<__half *>(b), m, n, col_major);
+            break;
+        case KLAS_F32:
+            rowops::rowscale_kernel<float><<<unsigned(blocks), rowops::THREADS, 0, stream>>>(
+                static_cast<const float *>(scale), static_cast<float *>(b), m, n, col_major);
+            break;
+        case KLAS_F64:
+            rowops::rowscale_kernel<double><<<unsigned(blocks), rowops::THREADS, 0, stream>>>(
+                static_cast<const double *>(scale), static_cast<double *>(b), m, n, col_major);
+            break;
+        default: return fail(KLAS_ERR_INVALID, "rowscale: dtype must be F16, F32 or F64");
+    }
+    return check_cuda(cudaGetLastError(), "rowscale_kernel launch");
+}
+
+int launch_reduce_sum(int dtype, uint64_t n, const void *a, void *out, void *scratch, size_t scratch_bytes,
+                      cudaStream_t stream) {
+    if (!out) return fail(KLAS_ERR_INVALID, "reduce: null result pointer");
+    if (n > 0 && !a) return fail(KLAS_ERR_INVALID, "reduce: null data pointer");
+    const size_t need = reduce_scratch_bytes(n);
+    if (!scratch || scratch_bytes < need)
+        return fail(KLAS_ERR_INVALID, "reduce: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
+    switch (dtype) {
+        case KLAS_F16: return rowops::reduce_t<__half>(n, a, out, scratch, stream);
+        case KLAS_F32: return rowops::reduce_t<float>(n, a, out, scratch, stream);
+        case KLAS_F64: return rowops::reduce_t<double>(n, a, out, scratch, stream);
+        case KLAS_U32: return rowops::reduce_t<uint32_t>(n, a, out, scratch, stream);
+        case KLAS_U64: return rowops::reduce_t<uint64_t>(n, a, out, scratch, stream);
+        default: return fail(KLAS_ERR_INVALID, "reduce: bad dtype");
+    }
+}
+
+}  // namespace klas

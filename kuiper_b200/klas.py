@@ -186,6 +186,46 @@ def spmm(A: Csr, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
     return C_
 
 
+def softmax(a: torch.Tensor, *, log: bool = False) -> torch.Tensor:
+    """In-place softmax (log-softmax with log=True) of a vector, or of every row of a row-major
+    matrix; f16 / f32 / f64.  Returns `a`."""
+    if a.dtype not in (torch.float16, torch.float32, torch.float64) or a.dim() not in (1, 2):
+        raise TypeError("softmax needs a 1-D or 2-D f16/f32/f64 tensor")
+    rows, cols = (1, a.shape[0]) if a.dim() == 1 else a.shape
+    lib = _lib.load()
+    with torch.cuda.device(a.device):
+        need = lib.klas_b200_softmax_scratch_bytes(rows, cols)
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=a.device) if need else None
+        check(lib.klas_b200_softmax(_code(a), int(log), rows, cols, _dev(a, "a"),
+                                    scratch.data_ptr() if need else None, need, _stream()))
+    return a
+
+
+def rowscale(scale: torch.Tensor, b: torch.Tensor, *, col_major: bool = False) -> torch.Tensor:
+    """In place b[r][c] = scale[r] * b[r][c].  `b` is m x n row-major, or (col_major) the n x m
+    tensor that holds the column-major data of an m x n matrix.  Returns `b`."""
+    if b.dtype != scale.dtype or b.dtype not in (torch.float16, torch.float32, torch.float64):
+        raise TypeError("rowscale needs matching f16/f32/f64 tensors")
+    m, n = (b.shape[1], b.shape[0]) if col_major else b.shape
+    if scale.numel() != m:
+        raise ValueError("scale has %d entries, the matrix %d rows" % (scale.numel(), m))
+    with torch.cuda.device(b.device):
+        check(_lib.load().klas_b200_rowscale(_code(b), int(col_major), m, n, _dev(scale, "scale"), _dev(b, "b"), _stream()))
+    return b
+
+
+def reduce_sum(a: torch.Tensor) -> torch.Tensor:
+    """Sum of a 1-D tensor (f16/f32/f64 or wrapping 32/64-bit integers) as a 0-D device tensor."""
+    lib = _lib.load()
+    out = torch.empty((), dtype=a.dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        need = lib.klas_b200_reduce_scratch_bytes(a.numel())
+        scratch = torch.empty(need, dtype=torch.uint8, device=a.device)
+        check(lib.klas_b200_reduce_sum(_code(a), a.numel(), _dev(a, "a") if a.numel() else None, out.data_ptr(),
+                                       scratch.data_ptr(), need, _stream()))
+    return out
+
+
 # --------------------------------------------------------------------------- reference names
 _TORCH_OF = {"f32": torch.float32, "f64": torch.float64, "u32": torch.int32, "u64": torch.int64,
              "bf16": torch.bfloat16, "f16": torch.float16}
@@ -200,6 +240,10 @@ _RE_TC2D = re.compile(r"^Klas_GEMM_TensorCore2D_g_gemm_(bf16_f32|f16_f16)_(\d+)x
 _RE_TC2D_TO = re.compile(r"^Klas_GEMM_TensorCore2D_To_g_gemm_bf16_f32_bf16_(\d+)x(\d+)x(\d+)"
                          r"_16x16x16_(\d+)x(\d+)$")
 _RE_TC1D = re.compile(r"^Klas_GEMM_TensorCore_g_gemm_f16_(f16|f32)_(\d+)x(\d+)x(\d+)_(\d+)x(\d+)x(\d+)$")
+_RE_SOFTMAX = re.compile(r"^Klas_(Softmax_softmax|LogSoftmax_log_softmax)_(gpu_)?(n_)?(f16|f32|f64)$")
+_RE_ROWSOFTMAX = re.compile(r"^Klas_RowSoftmax_row_softmax_rm_(f32|f64)$")
+_RE_ROWSCALE = re.compile(r"^Klas_RowScale_rowscale_(f16|f32|f64)_(rowmajor|colmajor)$")
+_RE_REDUCE = re.compile(r"^Klas_(?:HReduce_reduce_(f16|f32|f64|u32|u64)_plus|AtomicReduce_reduce_(u32|u64|f32|f64))$")
 _RE_SPMM = re.compile(r"^Klas_SPMM_(?:spmm_(f32|u32)|g_spmm_f32_(\d+)x(\d+)x(\d+))$")
 
 
@@ -322,4 +366,39 @@ def call(name: str, *args):
         csr = Csr(rows, shared, A.elems, A.col_ind, A.row_off, row_indices)
         spmm(csr, _view(B, dt, shared, cols), _view(Cc, dt, rows, cols))
         return None
+    m_ = _RE_SOFTMAX.match(name)
+    if m_:
+        unit, gpu, has_n, dt = m_.groups()
+        args = list(args)
+        if has_n:
+            args.pop(0)                     # thread-count hint
+        lena, a = args
+        t = _TORCH_OF[dt]
+        if gpu:
+            softmax(_view(a, t, lena), log=unit.startswith("Log"))
+        else:                               # host-pointer variants: the tensor lives on the CPU
+            if a.is_cuda or a.dtype != t:
+                raise TypeError("%s takes a host tensor of %s" % (name, t))
+            check(_lib.load().klas_b200_softmax_host(_DTYPES[t], int(unit.startswith("Log")), 1, lena, a.data_ptr()))
+        return None
+    m_ = _RE_ROWSOFTMAX.match(name)
+    if m_:
+        m, n, _nth, a = args
+        softmax(_view(a, _TORCH_OF[m_.group(1)], m, n))
+        return None
+    m_ = _RE_ROWSCALE.match(name)
+    if m_:
+        m, n, a, b = args
+        t = _TORCH_OF[m_.group(1)]
+        if m_.group(2) == "rowmajor":
+            rowscale(_view(a, t, m), _view(b, t, m, n))
+        else:
+            rowscale(_view(a, t, m), _view(b, t, n, m), col_major=True)
+        return None
+    m_ = _RE_REDUCE.match(name)
+    if m_:
+        a = args[-1]
+        count = args[-2]
+        t = _TORCH_OF[m_.group(1) or m_.group(2)]
+        return reduce_sum(_view(a, t, count)).item()
     raise KeyError("unknown Klas entry point: %s" % name)

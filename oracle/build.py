@@ -30,6 +30,7 @@ REF_GPU_UNITS = [
     "Klas_GEMM_SHMem", "Klas_GEMM_Tiled", "Klas_GEMM_BlockTiling1D", "Klas_GEMM_BlockTiling2D",
     "Klas_GEMM_Naive1", "Klas_GEMM_Naive2", "Klas_GEMM_Naive3", "Klas_GEMM_TensorCore",
     "Klas_GEMM_TensorCore2D", "Klas_GEMM_TensorCore2D_To", "Klas_SPMM",
+    "Klas_Softmax", "Klas_LogSoftmax", "Klas_RowSoftmax", "Klas_RowScale", "Klas_HReduce", "Klas_AtomicReduce",
 ]
 
 
@@ -56,12 +57,13 @@ def build_ref_cpu(ref_root: Path, force: bool = False) -> Path:
     """The reference's host gold loops (test/matmul_common.c.inc, dist/Kuiper_Example_Sparse_MM.cu)."""
     out = REF_DIR / "libklas_ref_cpu.so"
     wrap = ORACLE_DIR / "ref_wrap" / "ref_cpu.cu"
-    if not force and _newer(out, wrap):
+    wrap2 = ORACLE_DIR / "ref_wrap" / "ref_softmax.cu"
+    if not force and _newer(out, wrap, wrap2):
         return out
     REF_DIR.mkdir(exist_ok=True)
     _run(["nvcc", "-O3", "-std=c++17", *ARCH, "-Xcompiler", "-fPIC", "-shared",
           "-I", ref_root / "include", "-I", ref_root / "test", "-I", ref_root / "dist",
-          "-o", out, wrap, ref_root / "dist" / "Kuiper_Example_Sparse_MM.cu"])
+          "-o", out, wrap, wrap2, ref_root / "dist" / "Kuiper_Example_Sparse_MM.cu"])
     return out
 
 
@@ -69,7 +71,8 @@ def build_ref_gpu(ref_root: Path, force: bool = False) -> Path:
     """The reference's extracted kernels (dist/Klas_*.cu) for sm_100a, one shared library,
     plus symbols.json mapping each entry-point name to its mangled symbol."""
     out = REF_DIR / "libklas_ref_gpu.so"
-    if not force and out.exists() and (REF_DIR / "symbols.json").exists():
+    if not force and out.exists() and (REF_DIR / "symbols.json").exists() and \
+            all((REF_DIR / "obj" / (u + ".o")).exists() for u in REF_GPU_UNITS):
         return out
     obj_dir = REF_DIR / "obj"
     obj_dir.mkdir(parents=True, exist_ok=True)
@@ -95,7 +98,8 @@ def build_ref_gpu(ref_root: Path, force: bool = False) -> Path:
     return out
 
 
-HOT_PATH_DRIVER_GLOBS = ("Test_Klas_GEMM_*.cu", "Test_Klas_SPMM__*.cu")
+HOT_PATH_DRIVER_GLOBS = ("Test_Klas_GEMM_*.cu", "Test_Klas_SPMM__*.cu", "Test_Klas_Softmax__*.cu",
+                         "Test_Klas_LogSoftmax__*.cu", "Test_Klas_HReduce__*.cu", "Test_Klas_AtomicReduce__*.cu")
 
 
 def build_ref_drivers(ref_root: Path, force: bool = False) -> Path:

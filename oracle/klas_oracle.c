@@ -7,7 +7,7 @@
  *
  * Parity pin: tests/test_oracle.py checks these functions bit-for-bit
  * against the reference's own host loops compiled from where they lie
- * (oracle/_ref, built by oracle/build_ref.py) on the reference drivers'
+ * (oracle/_ref, built by oracle/build.py) on the reference drivers'
  * deterministic inputs, and against the golden values committed under
  * tests/golden/ that were produced by those loops.
  *
@@ -334,6 +334,37 @@ void klas_oracle_dense_matmul_f32(size_t rows, size_t shared, size_t cols, const
             }
             C[i * cols + j] = sum;
         }
+}
+
+/* ------------------------------------------------------------------ row-wise neighbours */
+
+/* Softmax / log-softmax of n doubles: maximum, then sum of exp(x - max), then the quotient (or
+ * x - (max + log sum)) -- the gold of the softmax drivers, cpu_softmax / cpu_logsoftmax
+ * (test/softmax_test_common.c.inc:37-63). */
+void klas_oracle_softmax_f64(const double *in, double *out, size_t n, int log_softmax)
+{
+    if (n == 0) return;
+    double mx = in[0];
+    for (size_t i = 1; i < n; i++)
+        if (in[i] > mx) mx = in[i];
+    double sum = 0.0;
+    for (size_t i = 0; i < n; i++) {
+        out[i] = exp(in[i] - mx);
+        sum += out[i];
+    }
+    if (log_softmax) {
+        const double lse = mx + log(sum);
+        for (size_t i = 0; i < n; i++) out[i] = in[i] - lse;
+    } else {
+        for (size_t i = 0; i < n; i++) out[i] /= sum;
+    }
+}
+
+/* b[r][c] = a[r] * b[r][c] in double, b row-major (dist/Klas_RowScale.cu:9-15). */
+void klas_oracle_rowscale_f64(size_t m, size_t n, const double *a, double *b)
+{
+    for (size_t r = 0; r < m; r++)
+        for (size_t c = 0; c < n; c++) b[r * n + c] = a[r] * b[r * n + c];
 }
 
 int klas_oracle_max_threads(void)

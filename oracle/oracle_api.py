@@ -54,6 +54,17 @@ class Oracle:
         for name in ("klas_oracle_f64_to_f16_bits", "klas_oracle_f64_to_bf16_bits", "klas_oracle_f16_bits_to_f64"):
             getattr(self.lib, name).argtypes = [_vp, _vp, _sz]
 
+    def softmax(self, x: np.ndarray, log: bool = False) -> np.ndarray:
+        """Row-wise softmax (or log-softmax) in float64 of a 1-D or 2-D array."""
+        x = np.ascontiguousarray(x, np.float64)
+        out = np.empty_like(x)
+        rows = x.reshape(-1, x.shape[-1])
+        o2 = out.reshape(-1, x.shape[-1])
+        self.lib.klas_oracle_softmax_f64.argtypes = [_vp, _vp, _sz, _int]
+        for r in range(rows.shape[0]):
+            self.lib.klas_oracle_softmax_f64(rows[r].ctypes.data, o2[r].ctypes.data, rows.shape[1], int(log))
+        return out
+
     @property
     def max_threads(self) -> int:
         return self.lib.klas_oracle_max_threads()
@@ -206,6 +217,14 @@ class RefCpu:
         fn = getattr(self.lib, "ref_cpu_sgemm_" + kind)
         fn.argtypes = [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp]
         fn(A.shape[0], A.shape[1], B.shape[1], _p(A), _p(B), _p(Cin), _p(al), _p(be), _p(out))
+        return out
+
+    def cpu_softmax(self, x: np.ndarray, log: bool = False) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float64)
+        out = np.empty_like(x)
+        fn = self.lib.ref_cpu_logsoftmax if log else self.lib.ref_cpu_softmax
+        fn.argtypes = [_vp, _vp, _int]
+        fn(_p(x), _p(out), x.size)
         return out
 
     def mmsd_u32_rr(self, rows, shared, cols, elems, col_ind, row_off, B) -> np.ndarray:

@@ -60,6 +60,10 @@ def main():
                                             csr.col_ind.numpy().view(np.uint32),
                                             csr.row_off.numpy().view(np.uint32),
                                             Bd.numpy().view(np.uint32))
+    # softmax drivers' gold functions on their ramp pattern (test/softmax_test_common.c.inc:66-72)
+    ramp = (np.arange(100) % 16) * 0.5 - 4.0
+    out["softmax_ramp"] = ref.cpu_softmax(ramp)
+    out["logsoftmax_ramp"] = ref.cpu_softmax(ramp, log=True)
     np.savez_compressed(HERE / "klas_golden.npz", **out)
     print("wrote", HERE / "klas_golden.npz", {k: v.shape for k, v in out.items()})
 

@@ -26,7 +26,7 @@ def test_driver_prints_its_expected_output(name):
 
 
 def test_all_hot_path_drivers_are_covered():
-    assert len(EXPECTED) == 39   # 37 GEMM + 2 SpMM
+    assert len(EXPECTED) == 50   # 37 GEMM + 2 SpMM + 6 softmax / log-softmax + 5 reductions
     if DRIVERS.exists():
         built = {p.stem for p in DRIVERS.glob("*.exe")}
         assert built == set(EXPECTED)

@@ -130,6 +130,22 @@ def test_spmm_f32_matches_dense_product(oracle):
     assert np.allclose(oracle.dense_matmul_f32(dense, Bd.numpy()), want, rtol=1e-5, atol=1e-5)
 
 
+def test_softmax_gold(oracle):
+    ramp = (np.arange(100) % 16) * 0.5 - 4.0
+    assert np.array_equal(oracle.softmax(ramp), GOLD["softmax_ramp"])
+    assert np.array_equal(oracle.softmax(ramp, log=True), GOLD["logsoftmax_ramp"])
+    x = np.random.default_rng(1).normal(size=(5, 37)) * 4
+    sm = oracle.softmax(x)
+    assert np.allclose(sm.sum(axis=1), 1.0, atol=1e-14)
+    assert np.allclose(np.log(sm), oracle.softmax(x, log=True), atol=1e-12)
+
+
+def test_live_reference_softmax(oracle, refcpu):
+    x = np.random.default_rng(2).normal(size=4097) * 5
+    assert np.array_equal(oracle.softmax(x), refcpu.cpu_softmax(x))
+    assert np.array_equal(oracle.softmax(x, log=True), refcpu.cpu_softmax(x, log=True))
+
+
 # ------------------------------------------------------------------ live checks against oracle/_ref
 @pytest.mark.parametrize("shape", [(7, 5, 3), (33, 65, 17), (128, 96, 64)])
 def test_live_reference_loops(oracle, refcpu, shape):
