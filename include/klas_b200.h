@@ -171,8 +171,8 @@ int klas_b200_spmm_host(int dtype, uint32_t rows, uint32_t shared, uint32_t cols
  *
  * klas_b200_softmax: in place, a[r][c] = exp(a[r][c] - max_r) / sum_c exp(a[r][c] - max_r) for
  * every row of the row-major rows x cols matrix `a` (log_softmax != 0: a[r][c] - max_r - log(sum)).
- * rows == 1 is the vector case: the vector is cut into 16384-element chunks folded by separate
- * CTAs, which needs `scratch`: klas_b200_softmax_scratch_bytes(rows, cols) bytes of 16-byte
+ * rows == 1 is the vector case: the vector is cut into chunks (16384 elements or more, at most
+ * 2048 chunks) folded by separate CTAs, which needs `scratch`: klas_b200_softmax_scratch_bytes(rows, cols) bytes of 16-byte
  * aligned device memory (0 for rows > 1), caller-owned, overwritten.
  * Replaces: Klas_Softmax_softmax_gpu{,_n}_* (dist/Klas_Softmax.h), Klas_LogSoftmax_log_softmax_gpu{,_n}_*
  * (dist/Klas_LogSoftmax.h), Klas_RowSoftmax_row_softmax_rm_* (dist/Klas_RowSoftmax.h:7-11).
