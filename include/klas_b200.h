@@ -185,6 +185,27 @@ int klas_b200_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, 
 int klas_b200_softmax_host(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a);
 
 /*
+ * klas_b200_softmax_static: the vector case (rows == 1) of klas_b200_softmax without a scratch
+ * argument and without any allocation.  No counterpart in the reference.
+ *
+ * For callers that cannot supply scratch and must not allocate: a process that gave all device
+ * memory to its own arena at start-up, or a latency-critical loop where cudaMalloc / cudaFree
+ * are off limits because they synchronise the device.  The per-chunk statistics go to a fixed
+ * 16 KiB array inside the library's device image instead, which limits the vector to
+ * KLAS_B200_SOFTMAX_STATIC_MAX_COLS elements; a longer vector is refused with KLAS_ERR_TOO_LARGE
+ * (use klas_b200_softmax).  Same kernels, same results as klas_b200_softmax.
+ *
+ * The function calls no allocator (CUDA's or the host library's workspace).  The first call on
+ * each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call outside any stream capture.  All calls on one device share the
+ * array: calls that may overlap in time (several streams or threads) race on it and must be
+ * serialised by the caller.  The array keeps the previous call's statistics; none of it needs
+ * clearing, every entry read is written first by the same call.
+ */
+#define KLAS_B200_SOFTMAX_STATIC_MAX_COLS 16777216ull   /* 1024 chunks of 16384 elements */
+int klas_b200_softmax_static(int dtype, int log_softmax, uint64_t cols, void *a, void *stream);
+
+/*
  * b[r][c] = scale[r] * b[r][c] for the m x n matrix b, row-major (col_major == 0) or
  * column-major.  Replaces: Klas_RowScale_rowscale_*_{rowmajor,colmajor} (dist/Klas_RowScale.h:7-23).
  */

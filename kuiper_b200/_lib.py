@@ -33,6 +33,7 @@ SIGNATURES = {
     "klas_b200_softmax_scratch_bytes": (C.c_size_t, [_u64, _u64]),
     "klas_b200_softmax": (_int, [_int, _int, _u64, _u64, _vp, _vp, C.c_size_t, _vp]),
     "klas_b200_softmax_host": (_int, [_int, _int, _u64, _u64, _vp]),
+    "klas_b200_softmax_static": (_int, [_int, _int, _u64, _vp, _vp]),
     "klas_b200_rowscale": (_int, [_int, _int, _u64, _u64, _vp, _vp, _vp]),
     "klas_b200_reduce_scratch_bytes": (C.c_size_t, [_u64]),
     "klas_b200_reduce_sum": (_int, [_int, _u64, _vp, _vp, _vp, C.c_size_t, _vp]),

@@ -18,6 +18,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "klas_internal.h"
 
 namespace klas {
@@ -320,3 +322,69 @@ int launch_reduce_sum(int dtype, uint64_t n, const void *a, void *out, void *scr
 }
 
 }  // namespace klas
+
+// ---- vector softmax that allocates nothing ------------------------------------------------------
+// Some callers have nowhere to get the per-chunk scratch of the vector softmax from: a process
+// that handed all device memory to its own arena at start-up (a later cudaMalloc fails or
+// fragments it), or a latency-critical loop that must not call cudaMalloc / cudaFree because
+// both synchronise the whole device and stall every other stream.  For them the statistics live
+// in the fixed array below, which is part of the loaded module, so no allocator is involved.
+//
+// The array holds one (max, sum) pair per chunk and so bounds the vector length:
+// KLAS_B200_SOFTMAX_STATIC_MAX_COLS elements.  Every call on a device uses the same array, and it
+// keeps what the last call left there.  Nothing in it has to start at zero -- the first launch
+// writes every pair the second launch reads -- but two calls that overlap in time on one device
+// (different streams or threads) would overwrite each other's pairs: serialise them.
+namespace klas {
+namespace rowops {
+
+constexpr uint32_t STATIC_PARTS = 1024;
+static_assert(uint64_t(STATIC_PARTS) * MIN_CHUNK == KLAS_B200_SOFTMAX_STATIC_MAX_COLS,
+              "the documented limit is what the static array can hold");
+static __device__ __align__(256) unsigned char g_static_softmax_scratch[STATIC_PARTS * 16];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+static void *g_static_scratch_addr[STATIC_MAX_DEVICES];   // device address of the array, per device
+static std::mutex g_static_scratch_mutex;
+
+// Device address of the array on the current device.  Looked up once per device, with that
+// device current, on the first call there (a symbol has one address per device).
+static int static_scratch(void **out) {
+    int dev = -1;
+    KLAS_TRY_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES)
+        return fail(KLAS_ERR_UNSUPPORTED, "softmax_static: device ordinal %d beyond %d", dev, STATIC_MAX_DEVICES - 1);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_addr[dev]) {
+        void *ptr = nullptr;
+        const cudaError_t rc = cudaGetSymbolAddress(&ptr, g_static_softmax_scratch);
+        if (rc != cudaSuccess)
+            return fail(KLAS_ERR_CUDA, "softmax_static: cudaGetSymbolAddress: %s", cudaGetErrorString(rc));
+        if (!ptr || (reinterpret_cast<uintptr_t>(ptr) & 255u))
+            return fail(KLAS_ERR_CUDA, "softmax_static: the scratch symbol resolved to %p", ptr);
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return KLAS_OK;
+}
+
+}  // namespace rowops
+}  // namespace klas
+
+extern "C" int klas_b200_softmax_static(int dtype, int log_softmax, uint64_t cols, void *a, void *stream) {
+    using namespace klas;
+    clear_error();
+    if (cols == 0) return KLAS_OK;
+    if (cols > KLAS_B200_SOFTMAX_STATIC_MAX_COLS)
+        return fail(KLAS_ERR_TOO_LARGE,
+                    "softmax_static: %llu elements, the built-in scratch holds the statistics of at most %llu; "
+                    "use klas_b200_softmax with caller scratch",
+                    (unsigned long long)cols, (unsigned long long)KLAS_B200_SOFTMAX_STATIC_MAX_COLS);
+    const size_t need = softmax_scratch_bytes(1, cols);
+    if (need > sizeof(rowops::g_static_softmax_scratch))   // cannot happen below the limit; kept as a guard
+        return fail(KLAS_ERR_TOO_LARGE, "softmax_static: %zu bytes of statistics exceed the built-in %zu", need,
+                    sizeof(rowops::g_static_softmax_scratch));
+    void *scratch = nullptr;
+    if (int rc = rowops::static_scratch(&scratch)) return rc;
+    return launch_softmax(dtype, log_softmax, 1, cols, a, scratch, need, static_cast<cudaStream_t>(stream));
+}
