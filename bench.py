@@ -124,6 +124,7 @@ class Workload:
     unit = ""
     dtype = ""
     bound = "tensor"
+    launches_per_step = 1
 
     def per_step_units(self) -> float:        # flop (or bytes) this rank performs per step
         raise NotImplementedError
@@ -317,7 +318,45 @@ class Spmm(Workload):
         return float(cc[0, 0])
 
 
+class Softmax(Workload):
+    name, metric, unit, dtype, bound = "softmax_f32", "softmax_gbs", "GB/s", "f32", "hbm"
+    launches_per_step = 2          # per-chunk statistics, then the rewrite
+    N = 1 << 28                    # elements per GPU (1 GiB of f32)
+
+    def __init__(self, rank, world, device):
+        import torch
+        from kuiper_b200 import _lib, synth
+        self.torch = torch
+        self.x = synth.normal(5 + rank, 21, 0, self.N, dtype=torch.float32, device=device) * 4.0
+        need = _lib.load().klas_b200_softmax_scratch_bytes(1, self.N)
+        self.scratch = torch.empty(need, dtype=torch.uint8, device=device)
+        self.algorithmic_bytes = 3 * 4 * self.N          # two reads and one write of the vector
+        self.config = {"workload": "in-place softmax of one f32 vector of 2^28 elements per GPU, N(0,16) values, seed 5+rank; "
+                                   "steps after the first run on the previous step's output (same traffic and instruction count)",
+                       "sharding": "one independent vector per GPU, no collective", "cache": "1 GiB vector > 126 MB L2",
+                       "bytes_model": "3 x 4 bytes per element: read for the statistics, read and write for the result"}
+        self.h2d = self.d2h = 4 * self.N
+        self._host = None
+
+    def per_step_units(self):
+        return float(self.algorithmic_bytes)
+
+    def launch(self):
+        from kuiper_b200 import _lib
+        _lib.check(_lib.load().klas_b200_softmax(_lib.F32, 0, 1, self.N, self.x.data_ptr(), self.scratch.data_ptr(),
+                                                 self.scratch.numel(), self.torch.cuda.current_stream().cuda_stream))
+
+    def e2e_step(self):
+        from kuiper_b200 import _lib
+        if self._host is None:
+            self._host = self.x.cpu().pin_memory()
+        _lib.check(_lib.load().klas_b200_softmax_host(_lib.F32, 0, 1, self.N, self._host.data_ptr()))
+        return float(self._host[0])
+
+
 def make_workload(name, rank, world, device):
+    if name == "softmax_f32":
+        return Softmax(rank, world, device)
     if name == "gemm_bf16":
         return GemmBf16(rank, world, device)
     if name == "gemm_f16b":
@@ -401,8 +440,36 @@ def run_reference_arm(args, rank, world):
     return 0
 
 
+def cpu_baseline_softmax():
+    """The reference drivers' gold softmax (test/softmax_test_common.c.inc, compiled unmodified into
+    oracle/_ref; float64, one thread) -- or the oracle port -- on a 2^24-element sample."""
+    import numpy as np
+    sys.path.insert(0, str(REPO / "oracle"))
+    import build as oracle_build
+    from oracle_api import Oracle, RefCpu
+    n = 1 << 24
+    x = np.random.default_rng(5).normal(size=n) * 4.0
+    if RefCpu.available():
+        fn, kind = RefCpu().cpu_softmax, "reference"
+    else:
+        oracle_build.build_oracle()
+        fn, kind = Oracle().softmax, "port"
+    fn(x[:1024])
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 10.0:
+        fn(x)
+        reps += 1
+    t = time.perf_counter() - t0
+    # same byte model as the GPU line, on the sample's f32-equivalent size
+    return {"value": 3 * 4 * n * reps / t / 1e9, "unit": "GB/s", "cores": 1, "kind": kind,
+            "sample": "%d x softmax of 2^24 elements in float64, single thread as written; bytes counted as 12 per element" % reps}
+
+
 def cpu_baseline_leg(workload_name):
     """Single-threaded, as the reference's loop is written; ~10-20 s of CPU work."""
+    if workload_name == "softmax_f32":
+        return cpu_baseline_softmax()
     if workload_name != "gemm_bf16":
         return None
     one_pass, kind, rows, units = reference_cpu_gemm_bf16(0, 1)
@@ -528,12 +595,12 @@ def main():
                     "kernel_ms": per_launch_ms, **extra}
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": warm, "ms_per_step": per_launch_ms, "higher_is_better": True, "scaling": "weak" if wl.name in ("gemm_bf16",) else "strong",
+            "warmup": warm, "ms_per_step": per_launch_ms, "higher_is_better": True, "scaling": "weak" if wl.name in ("gemm_bf16", "softmax_f32") else "strong",
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
             "clocks": sampler.summary(),
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                     "steps": args.e2e_steps, "api": "klas_b200_*_host (C ABI, pinned host buffers)"},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * wl.launches_per_step,
             "roofline": roofline,
         }
         if not args.no_cpu_baseline and world == 1:

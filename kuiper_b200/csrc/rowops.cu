@@ -82,12 +82,6 @@ __device__ __forceinline__ MaxSum<A> ms_merge(MaxSum<A> x, MaxSum<A> y) {
     return {m, x.s * fexp(x.m - m) + y.s * fexp(y.m - m)};
 }
 template <typename A>
-__device__ __forceinline__ MaxSum<A> ms_push(MaxSum<A> x, A v) {
-    if (v <= x.m) return {x.m, x.s + fexp(v - x.m)};
-    return {v, x.s * fexp(x.m - v) + A(1)};   // exp(-inf) = 0 covers the empty state
-}
-
-template <typename A>
 __device__ __forceinline__ MaxSum<A> ms_block_reduce(MaxSum<A> v, MaxSum<A> *smem) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -106,11 +100,115 @@ __device__ __forceinline__ MaxSum<A> ms_block_reduce(MaxSum<A> v, MaxSum<A> *sme
 }
 
 template <typename T, bool LOG>
-__device__ __forceinline__ T finish(T x, typename Num<T>::Acc m, typename Num<T>::Acc s_or_logs) {
+__device__ __forceinline__ T finish(T x, typename Num<T>::Acc m, typename Num<T>::Acc inv_or_logs) {
     using A = typename Num<T>::Acc;
     const A v = Num<T>::up(x);
-    if (LOG) return Num<T>::down((v - m) - s_or_logs);   // s_or_logs = log(sum)
-    return Num<T>::down(fexp(v - m) / s_or_logs);          // s_or_logs = sum
+    if (LOG) return Num<T>::down((v - m) - inv_or_logs);   // inv_or_logs = log(sum)
+    return Num<T>::down(fexp(v - m) * inv_or_logs);          // inv_or_logs = 1 / sum
+}
+
+// 16 bytes of T, moved with one access where the address allows it.
+template <typename T>
+struct alignas(16) Pack {
+    static constexpr int N = 16 / sizeof(T);
+    T v[N];
+};
+
+// Folds k values into the running statistics: one exp per value plus one per new maximum.
+// A state whose maximum is still -inf (nothing finite seen yet) accumulates nothing, so -inf
+// entries (masked positions) contribute exactly zero wherever they stand.
+template <typename A, int K>
+__device__ __forceinline__ void ms_fold(MaxSum<A> &st, const A (&v)[K]) {
+    A bm = v[0];
+#pragma unroll
+    for (int j = 1; j < K; ++j) bm = v[j] > bm ? v[j] : bm;
+    if (bm > st.m) {
+        st.s *= fexp(st.m - bm);   // exp(-inf) = 0 on the first finite value; s is 0 then anyway
+        st.m = bm;
+    }
+    if (st.m > A(-INFINITY)) {
+#pragma unroll
+        for (int j = 0; j < K; ++j) st.s += fexp(v[j] - st.m);
+    }
+}
+
+// Elements of a[lo, hi) in front of the first 16-byte boundary (all of them if none is reached).
+template <typename T>
+__device__ __forceinline__ uint64_t head_elems(const T *a, uint64_t lo, uint64_t hi) {
+    const uint64_t h = ((16u - (reinterpret_cast<uintptr_t>(a + lo) & 15u)) & 15u) / sizeof(T);
+    return h < hi - lo ? h : hi - lo;
+}
+
+// Statistics of a[lo, hi) gathered by the whole CTA; every thread returns the CTA's result.
+// Scalar accesses up to the first 16-byte boundary and after the last, 16-byte packs between,
+// four in flight per thread.
+template <typename T>
+__device__ __forceinline__ MaxSum<typename Num<T>::Acc> cta_stats(const T *a, uint64_t lo, uint64_t hi,
+                                                                   MaxSum<typename Num<T>::Acc> *smem) {
+    using A = typename Num<T>::Acc;
+    constexpr int N = Pack<T>::N;
+    constexpr int UNROLL = 4;
+    MaxSum<A> st = ms_empty<A>();
+    const uint64_t head = head_elems(a, lo, hi);
+    if (threadIdx.x < head) {
+        const A one[1] = {A(Num<T>::up(a[lo + threadIdx.x]))};
+        ms_fold(st, one);
+    }
+    lo += head;
+    uint64_t done = lo;
+    {
+        const uint64_t packs = (hi - lo) / N;
+        const Pack<T> *p = reinterpret_cast<const Pack<T> *>(a + lo);
+        uint64_t i = threadIdx.x;
+        for (; i + uint64_t(UNROLL - 1) * THREADS < packs; i += uint64_t(UNROLL) * THREADS) {
+            Pack<T> buf[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) buf[u] = p[i + uint64_t(u) * THREADS];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                A vals[N];
+#pragma unroll
+                for (int j = 0; j < N; ++j) vals[j] = A(Num<T>::up(buf[u].v[j]));
+                ms_fold(st, vals);
+            }
+        }
+        for (; i < packs; i += THREADS) {
+            const Pack<T> one = p[i];
+            A vals[N];
+#pragma unroll
+            for (int j = 0; j < N; ++j) vals[j] = A(Num<T>::up(one.v[j]));
+            ms_fold(st, vals);
+        }
+        done = lo + packs * N;
+    }
+    for (uint64_t i = done + threadIdx.x; i < hi; i += THREADS) {
+        const A one[1] = {A(Num<T>::up(a[i]))};
+        ms_fold(st, one);
+    }
+    return ms_block_reduce(st, smem);
+}
+
+// Rewrites a[lo, hi) as the (log-)softmax given the statistics of the whole row or vector.
+template <typename T, bool LOG>
+__device__ __forceinline__ void cta_apply(T *a, uint64_t lo, uint64_t hi, typename Num<T>::Acc m,
+                                          typename Num<T>::Acc scale_or_logs) {
+    constexpr int N = Pack<T>::N;
+    const uint64_t head = head_elems(a, lo, hi);
+    if (threadIdx.x < head) a[lo + threadIdx.x] = finish<T, LOG>(a[lo + threadIdx.x], m, scale_or_logs);
+    lo += head;
+    uint64_t done = lo;
+    {
+        const uint64_t packs = (hi - lo) / N;
+        Pack<T> *p = reinterpret_cast<Pack<T> *>(a + lo);
+        for (uint64_t i = threadIdx.x; i < packs; i += THREADS) {
+            Pack<T> one = p[i];
+#pragma unroll
+            for (int j = 0; j < N; ++j) one.v[j] = finish<T, LOG>(one.v[j], m, scale_or_logs);
+            p[i] = one;
+        }
+        done = lo + packs * N;
+    }
+    for (uint64_t i = done + threadIdx.x; i < hi; i += THREADS) a[i] = finish<T, LOG>(a[i], m, scale_or_logs);
 }
 
 // ---- long vector ------------------------------------------------------------------------------
@@ -122,9 +220,7 @@ __global__ void __launch_bounds__(THREADS) softmax_partials_kernel(const T *__re
     __shared__ MaxSum<A> smem[THREADS / 32];
     const uint64_t lo = uint64_t(blockIdx.x) * chunk;
     const uint64_t hi = lo + chunk < n ? lo + chunk : n;
-    MaxSum<A> st = ms_empty<A>();
-    for (uint64_t i = lo + threadIdx.x; i < hi; i += THREADS) st = ms_push(st, A(Num<T>::up(a[i])));
-    st = ms_block_reduce(st, smem);
+    const MaxSum<A> st = cta_stats<T>(a, lo, hi, smem);
     if (threadIdx.x == 0) partials[blockIdx.x] = st;
 }
 
@@ -137,10 +233,11 @@ __global__ void __launch_bounds__(THREADS) softmax_apply_kernel(T *a, uint64_t n
     MaxSum<A> st = ms_empty<A>();
     for (uint32_t i = threadIdx.x; i < nparts; i += THREADS) st = ms_merge(st, partials[i]);
     st = ms_block_reduce(st, smem);
-    const A denom = LOG ? flog(st.s) : st.s;
-    const uint64_t lo = uint64_t(blockIdx.x) * chunk;
+    const A denom = LOG ? flog(st.s) : A(1) / st.s;
+    // Last chunk first: the end of the vector is what the first launch left in L2.
+    const uint64_t lo = uint64_t(nparts - 1 - blockIdx.x) * chunk;
     const uint64_t hi = lo + chunk < n ? lo + chunk : n;
-    for (uint64_t i = lo + threadIdx.x; i < hi; i += THREADS) a[i] = finish<T, LOG>(a[i], st.m, denom);
+    cta_apply<T, LOG>(a, lo, hi, st.m, denom);
 }
 
 // ---- rows of a matrix -------------------------------------------------------------------------
@@ -149,21 +246,39 @@ __global__ void __launch_bounds__(THREADS) row_softmax_kernel(T *a, uint64_t col
     using A = typename Num<T>::Acc;
     __shared__ MaxSum<A> smem[THREADS / 32];
     T *row = a + uint64_t(blockIdx.x) * cols;
-    MaxSum<A> st = ms_empty<A>();
-    for (uint64_t i = threadIdx.x; i < cols; i += THREADS) st = ms_push(st, A(Num<T>::up(row[i])));
-    st = ms_block_reduce(st, smem);
-    const A denom = LOG ? flog(st.s) : st.s;
-    for (uint64_t i = threadIdx.x; i < cols; i += THREADS) row[i] = finish<T, LOG>(row[i], st.m, denom);
+    const MaxSum<A> st = cta_stats<T>(row, 0, cols, smem);
+    const A denom = LOG ? flog(st.s) : A(1) / st.s;
+    cta_apply<T, LOG>(row, 0, cols, st.m, denom);   // second read of the row comes from L2
 }
 
 // ---- row scaling: b[r][c] = scale[r] * b[r][c], b row- or column-major -------------------------
 template <typename T>
 __global__ void __launch_bounds__(THREADS) rowscale_kernel(const T *__restrict__ scale, T *b, uint64_t m,
                                                           uint64_t n, int col_major) {
-    const uint64_t total = m * n;
-    for (uint64_t i = uint64_t(blockIdx.x) * THREADS + threadIdx.x; i < total; i += uint64_t(gridDim.x) * THREADS) {
-        const uint64_t r = col_major ? i % m : i / n;   // i walks memory order in both layouts
-        b[i] = scale[r] * b[i];
+    // i walks memory order in both layouts; the row index follows it incrementally (one division
+    // per thread instead of one per element).
+    const uint64_t total = m * n, stride = uint64_t(gridDim.x) * THREADS;
+    uint64_t i = uint64_t(blockIdx.x) * THREADS + threadIdx.x;
+    if (col_major) {
+        uint64_t r = i % m;
+        const uint64_t dr = stride % m;
+        for (; i < total; i += stride) {
+            b[i] = scale[r] * b[i];
+            r += dr;
+            if (r >= m) r -= m;
+        }
+    } else {
+        uint64_t r = i / n, c = i % n;
+        const uint64_t dr = stride / n, dc = stride % n;
+        for (; i < total; i += stride) {
+            b[i] = scale[r] * b[i];
+            r += dr;
+            c += dc;
+            if (c >= n) {
+                c -= n;
+                ++r;
+            }
+        }
     }
 }
 
@@ -173,8 +288,17 @@ __global__ void __launch_bounds__(THREADS) reduce_partials_kernel(const T *__res
                                                                  typename Num<T>::Acc *partials) {
     using A = typename Num<T>::Acc;
     __shared__ A smem[THREADS / 32];
+    constexpr int N = Pack<T>::N;
     A acc = A(0);
-    for (uint64_t i = uint64_t(blockIdx.x) * THREADS + threadIdx.x; i < n; i += uint64_t(gridDim.x) * THREADS)
+    const uint64_t packs = (reinterpret_cast<uintptr_t>(a) & 15u) == 0 ? n / N : 0;
+    const Pack<T> *p = reinterpret_cast<const Pack<T> *>(a);
+    for (uint64_t i = uint64_t(blockIdx.x) * THREADS + threadIdx.x; i < packs; i += uint64_t(gridDim.x) * THREADS) {
+        const Pack<T> one = p[i];
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc += A(Num<T>::up(one.v[j]));
+    }
+    for (uint64_t i = packs * N + uint64_t(blockIdx.x) * THREADS + threadIdx.x; i < n;
+         i += uint64_t(gridDim.x) * THREADS)
         acc += A(Num<T>::up(a[i]));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);

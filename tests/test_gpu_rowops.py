@@ -55,6 +55,39 @@ def test_softmax_extreme_values(oracle):
     assert torch.allclose(got, torch.full_like(got, 1 / 50000), rtol=1e-5)
 
 
+@pytest.mark.parametrize("log", [False, True])
+def test_masked_entries_contribute_nothing(oracle, log):
+    # -inf marks a masked position: leading runs (whole packs, whole threads' shares), scattered ones.
+    x = values(17, 70001)
+    x[:5000] = -float("inf")
+    x[20000:20003] = -float("inf")
+    x[-1] = -float("inf")
+    want = oracle.softmax(x.double().numpy(), log=log)
+    masked = np.isneginf(x.numpy())
+    for got in (klas.softmax(x.cuda(), log=log).cpu().double().numpy(),                        # one vector
+                klas.softmax(x[:70000].reshape(7, 10000).cuda(), log=log).cpu().double().numpy()):  # rows
+        ref = want if got.ndim == 1 else oracle.softmax(x[:70000].reshape(7, 10000).double().numpy(), log=log)
+        mk = masked if got.ndim == 1 else masked[:70000].reshape(7, 10000)
+        assert np.all(got[mk] == (-np.inf if log else 0.0))
+        assert np.max(np.abs(got[~mk] - ref[~mk])) <= (2e-5 if log else 2e-6)
+
+
+def test_unaligned_rows_and_offsets(oracle):
+    # Rows that start off the 16-byte grid (odd column count) and a vector at an odd offset.
+    x = values(19, 33, 1001)
+    got = klas.softmax(x.cuda()).cpu().double().numpy()
+    assert np.max(np.abs(got - oracle.softmax(x.double().numpy()))) <= 2e-6
+    for dtype, off in [(torch.float32, 1), (torch.float16, 3), (torch.float64, 1)]:
+        base = values(23, 50000 + off, dtype=dtype).cuda()
+        view = base[off:]
+        want = oracle.softmax(view.double().cpu().numpy())
+        klas.softmax(view)
+        assert np.max(np.abs(view.double().cpu().numpy() - want)) <= TOL_SOFTMAX[dtype]
+        y = values(29, 4099 + off, dtype=dtype, spread=1.0)[off:]
+        got = klas.reduce_sum(y.cuda()).item()
+        assert abs(got - float(y.double().sum())) <= TOL_SOFTMAX[dtype] * float(y.double().abs().sum())
+
+
 def test_softmax_empty_is_a_no_op():
     klas.softmax(torch.empty(0, device="cuda"))
     klas.softmax(torch.empty((0, 8), device="cuda"))
