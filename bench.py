@@ -323,17 +323,20 @@ class Softmax(Workload):
     launches_per_step = 2          # per-chunk statistics, then the rewrite
     N = 1 << 28                    # elements per GPU (1 GiB of f32)
 
-    def __init__(self, rank, world, device):
+    def __init__(self, rank, world, device, log2n=28):
         import torch
         from kuiper_b200 import _lib, synth
         self.torch = torch
+        self.N = 1 << log2n
         self.x = synth.normal(5 + rank, 21, 0, self.N, dtype=torch.float32, device=device) * 4.0
+        torch.cuda.empty_cache()       # the generator's float64 temporaries
         need = _lib.load().klas_b200_softmax_scratch_bytes(1, self.N)
         self.scratch = torch.empty(need, dtype=torch.uint8, device=device)
         self.algorithmic_bytes = 3 * 4 * self.N          # two reads and one write of the vector
-        self.config = {"workload": "in-place softmax of one f32 vector of 2^28 elements per GPU, N(0,16) values, seed 5+rank; "
-                                   "steps after the first run on the previous step's output (same traffic and instruction count)",
-                       "sharding": "one independent vector per GPU, no collective", "cache": "1 GiB vector > 126 MB L2",
+        self.config = {"workload": "in-place softmax of one f32 vector of 2^%d elements per GPU, N(0,16) values, seed 5+rank; "
+                                   "steps after the first run on the previous step's output (same traffic and instruction count)" % log2n,
+                       "sharding": "one independent vector per GPU, no collective",
+                       "cache": "%d MiB vector > 126 MB L2" % (self.N * 4 >> 20),
                        "bytes_model": "3 x 4 bytes per element: read for the statistics, read and write for the result"}
         self.h2d = self.d2h = 4 * self.N
         self._host = None
@@ -354,9 +357,9 @@ class Softmax(Workload):
         return float(self._host[0])
 
 
-def make_workload(name, rank, world, device):
+def make_workload(name, rank, world, device, args=None):
     if name == "softmax_f32":
-        return Softmax(rank, world, device)
+        return Softmax(rank, world, device, args.softmax_log2n if args else 28)
     if name == "gemm_bf16":
         return GemmBf16(rank, world, device)
     if name == "gemm_f16b":
@@ -494,6 +497,8 @@ def main():
     ap.add_argument("--workload", default="gemm_bf16")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--softmax-log2n", type=int, default=28,
+                    help="softmax_f32 only: log2 of the vector length (28 is the bench size; smaller for profiler captures)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":
@@ -514,7 +519,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     from kuiper_b200 import klas  # noqa: F401  (fails loudly if libklas_b200.so is missing)
 
-    wl = make_workload(args.workload, rank, world, device)
+    wl = make_workload(args.workload, rank, world, device, args)
     warm = max(args.warmup, 3)
     for _ in range(warm):
         wl.launch()

@@ -52,6 +52,32 @@ typedef enum klas_b_major_e {
     KLAS_B_COL_MAJOR = 1   /* B is stored as cols x shared, shared contiguous ("TN" GEMM) */
 } klas_b_major;
 
+/*
+ * Element-wise hooks of klas_b200_gemm_tc_fused.  The reference threads arbitrary functions
+ * through its tensor-core kernels when they are extracted (mapA / mapB / comb:
+ * include/kuiper/tensorcores.h:30-59); a compiled library offers a fixed menu.
+ * A map is evaluated in f32 on each 16-bit element and rounded back once to the element type.
+ * Every map sends 0 to 0.
+ */
+typedef enum klas_map_e {
+    KLAS_MAP_ID = 0,      /* x */
+    KLAS_MAP_SQRT = 1,    /* sqrt(x); hardware approximation, at most 1 ulp of f32 before rounding; NaN for x < 0 */
+    KLAS_MAP_ABS = 2,     /* |x| */
+    KLAS_MAP_SQUARE = 3,  /* x * x */
+    KLAS_MAP_RELU = 4,    /* max(x, 0) */
+    KLAS_MAP_NEG = 5      /* -x */
+} klas_map;
+
+/* How the accumulator acc = map_a(A).map_b(B) meets the old value c of C. */
+typedef enum klas_comb_e {
+    KLAS_COMB_NEW = 0,    /* acc (C not read) */
+    KLAS_COMB_AXPBY = 1,  /* alpha * acc + beta * c */
+    KLAS_COMB_MAX = 2,    /* max(c, acc) */
+    KLAS_COMB_MIN = 3,    /* min(c, acc) */
+    KLAS_COMB_MUL = 4,    /* c * acc */
+    KLAS_COMB_RELU = 5    /* max(acc, 0) (C not read) */
+} klas_comb;
+
 /* Last error message of the calling thread ("" if none). Never NULL. */
 const char *klas_b200_last_error(void);
 
@@ -106,6 +132,29 @@ int klas_b200_gemm_tc(int in_dtype, int out_dtype, int b_major, uint32_t batch,
                       uint64_t rows, uint64_t shared, uint64_t cols,
                       const void *A, const void *B, const void *C, void *D,
                       float alpha, float beta, int *status_word, void *stream);
+
+/*
+ * Tensor-core GEMM with element-wise hooks fused into the kernel:
+ *
+ *   D = out_dtype( comb( C, map_a(A) . map_b(B) ) )
+ *
+ * map_a / map_b (klas_map) are applied to the operand tiles in shared memory, between the
+ * copy from global memory and the tensor-core instruction, by dedicated warps: no mapped copy
+ * of A or B is ever written to global memory.  comb (klas_comb) runs in the epilogue on the
+ * fp32 accumulator.  C is required for AXPBY / MAX / MIN / MUL and ignored otherwise; alpha and
+ * beta matter for AXPBY only.  Everything else as klas_b200_gemm_tc (which is the case
+ * map_a = map_b = KLAS_MAP_ID, comb = C ? AXPBY : NEW).
+ *
+ * Replaces: the fused tensor-core kernels the reference generates from
+ * Kuiper.Kernel.GEMM.TensorCore2D (mapA / mapB / comb hooks, include/kuiper/tensorcores.h:30-59)
+ * and the demonstration Kuiper_Example_Fused_GEMM_gemm_sqrt_fused, C = sqrt(A).B in f16
+ * (dist/Kuiper_Example_Fused_GEMM.h:9-15), which runs one thread per output element.
+ */
+int klas_b200_gemm_tc_fused(int in_dtype, int out_dtype, int b_major, uint32_t batch,
+                            uint64_t rows, uint64_t shared, uint64_t cols,
+                            const void *A, const void *B, const void *C, void *D,
+                            float alpha, float beta, int map_a, int map_b, int comb,
+                            int *status_word, void *stream);
 
 /*
  * Reads (and then clears) the current device's tensor-core status word.

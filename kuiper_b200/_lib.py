@@ -12,6 +12,8 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE = range(6
 F32, F64, U32, U64, BF16, F16 = range(6)
 RRR, CCC = 0, 1
 B_ROW_MAJOR, B_COL_MAJOR = 0, 1
+MAP_ID, MAP_SQRT, MAP_ABS, MAP_SQUARE, MAP_RELU, MAP_NEG = range(6)
+COMB_NEW, COMB_AXPBY, COMB_MAX, COMB_MIN, COMB_MUL, COMB_RELU = range(6)
 
 _u32, _u64, _vp, _int, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int, C.c_float
 
@@ -23,6 +25,8 @@ SIGNATURES = {
     "klas_b200_gemm": (_int, [_int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _vp, _vp]),
     "klas_b200_gemm_tc": (_int, [_int, _int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp,
                                   _f32, _f32, _vp, _vp]),
+    "klas_b200_gemm_tc_fused": (_int, [_int, _int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp,
+                                        _f32, _f32, _int, _int, _int, _vp, _vp]),
     "klas_b200_gemm_tc_status": (_int, [C.POINTER(_int)]),
     "klas_b200_debug_wait_probe": (_int, [_u32, _vp, _vp]),
     "klas_b200_spmm": (_int, [_int, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -156,6 +156,15 @@ int klas_b200_gemm_tc(int in_dtype, int out_dtype, int b_major, uint32_t batch, 
                             alpha, beta, status_word, static_cast<cudaStream_t>(stream));
 }
 
+int klas_b200_gemm_tc_fused(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                            uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
+                            void *D, float alpha, float beta, int map_a, int map_b, int comb,
+                            int *status_word, void *stream) {
+    clear_error();
+    return launch_gemm_umma_fused(in_dtype, out_dtype, b_major, batch, rows, shared, cols, A, B, C, D, alpha, beta,
+                                  map_a, map_b, comb, status_word, static_cast<cudaStream_t>(stream));
+}
+
 int klas_b200_gemm_tc_status(int *site) {
     clear_error();
     int v = 0;

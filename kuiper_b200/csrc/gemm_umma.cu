@@ -48,6 +48,9 @@ constexpr uint32_t ACC_STAGES = 2;
 constexpr uint32_t TMEM_COLS = ACC_STAGES * BN;  // 512 = all of tensor memory
 constexpr uint32_t NUM_THREADS = 192;
 constexpr uint32_t NUM_EPI_WARPS = 4;
+constexpr uint32_t XFORM_WARPS = 4;       // extra warps of the kernels that map A / B in shared memory
+constexpr uint32_t XFORM_THREADS = XFORM_WARPS * 32;
+constexpr uint32_t XFULL_OFFSET = 192;    // byte offset of the "operands mapped" barriers in the barrier block
 constexpr uint32_t BARRIER_BYTES = 256;
 constexpr uint32_t DEFAULT_RASTER_GROUP = 8;  // tile columns swept together for L2 reuse
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
@@ -101,6 +104,9 @@ struct Params {
     uint32_t idesc;
     uint32_t b_row_major;  // 1: B is K x N (N contiguous) -> MN-major operand
     uint32_t raster_group; // tile columns swept together before moving down the rows
+    uint32_t in_bf16;      // element type of A and B: 1 = bf16, 0 = f16
+    uint32_t map_a, map_b; // element-wise maps applied to the staged operands (klas_map)
+    uint32_t comb;         // how the accumulator meets the old output value (klas_comb)
     int *status;           // optional caller-visible copy of the status word
 };
 
@@ -109,6 +115,7 @@ enum WaitSite : int {
     SITE_MMA_FULL = 0x21,
     SITE_MMA_TMEM_EMPTY = 0x22,
     SITE_EPI_TMEM_FULL = 0x31,
+    SITE_XFORM_FULL = 0x41,
 };
 
 struct Ctl {
@@ -122,14 +129,20 @@ struct Ctl {
 // `backoff_ns` > 0 makes the thread sleep between polls: used by the roles whose waits are long
 // and not on the critical path (epilogue, producer), so that they do not burn issue slots and
 // power while the tensor pipe works.
+// CLUSTER_ACQUIRE: the phase is completed by arrivals from the other CTA of the pair that
+// publish shared-memory writes of that CTA.
+template <bool CLUSTER_ACQUIRE = false>
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const Ctl &ctl,
                                              int site, uint64_t limit_ns = WAIT_LIMIT_NS,
                                              uint32_t backoff_ns = 0) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
+    auto poll = [&] {
+        return CLUSTER_ACQUIRE ? ptx::mbar_try_wait_cluster(bar, parity) : ptx::mbar_try_wait(bar, parity);
+    };
+    if (poll()) return true;
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
     for (;;) {
-        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if (poll()) return true;
         if (backoff_ns) __nanosleep(backoff_ns);
         if ((++spins & 0x3F) == 0) {
             if (*ctl.abort_flag != 0) return false;
@@ -184,13 +197,119 @@ struct OutTraits<__nv_bfloat16> {
     }
 };
 
+// ---- element-wise hooks ----------------------------------------------------------------------
+// Pre-maps of the staged operands and the rule that merges the accumulator into the output:
+// the run-time counterparts of the map / combine functions the reference inlines into its
+// tensor-core kernels at extraction time (include/kuiper/tensorcores.h:30-59, KPR_LOAD_MAP and
+// KPR_STORE_COMB).  A map is evaluated in f32 on the 16-bit element and rounded back once.
+// Every map sends 0 to 0, so the zero fill of ragged K edges stays neutral.
+template <uint32_t OP>
+__device__ __forceinline__ float map_f32(float x) {
+    if constexpr (OP == KLAS_MAP_SQRT) {
+        float r;
+        asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));   // <= 1 ulp of f32, before the 16-bit rounding
+        return r;
+    } else if constexpr (OP == KLAS_MAP_ABS) {
+        return fabsf(x);
+    } else if constexpr (OP == KLAS_MAP_SQUARE) {
+        return x * x;
+    } else if constexpr (OP == KLAS_MAP_RELU) {
+        return fmaxf(x, 0.0f);
+    } else if constexpr (OP == KLAS_MAP_NEG) {
+        return -x;
+    } else {
+        return x;
+    }
+}
+
+template <bool BF16, uint32_t OP>
+__device__ __forceinline__ uint32_t map_pair(uint32_t w) {
+    if constexpr (BF16) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w));
+        const __nv_bfloat162 r = __floats2bfloat162_rn(map_f32<OP>(f.x), map_f32<OP>(f.y));
+        return *reinterpret_cast<const uint32_t *>(&r);
+    } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+        const __half2 r = __floats2half2_rn(map_f32<OP>(f.x), map_f32<OP>(f.y));
+        return *reinterpret_cast<const uint32_t *>(&r);
+    }
+}
+
+// Maps `bytes` (a multiple of 4 * XFORM_THREADS * 16) of shared memory in place, 16 bytes per
+// thread per access, four accesses in flight.  The operand tiles are swizzled, which an
+// element-wise map does not care about.
+template <bool BF16, uint32_t OP>
+__device__ __forceinline__ void xform_region(uint32_t addr, uint32_t bytes, uint32_t tid) {
+    constexpr uint32_t STEP = XFORM_THREADS * 16;
+    for (uint32_t off = tid * 16; off < bytes; off += 4 * STEP) {
+        uint32_t w[4][4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) ptx::lds128(addr + off + u * STEP, w[u]);
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) w[u][j] = map_pair<BF16, OP>(w[u][j]);
+            ptx::sts128(addr + off + u * STEP, w[u]);
+        }
+    }
+}
+
+template <bool BF16>
+__device__ __forceinline__ void xform_dispatch(uint32_t op, uint32_t addr, uint32_t bytes, uint32_t tid) {
+    switch (op) {
+        case KLAS_MAP_SQRT: xform_region<BF16, KLAS_MAP_SQRT>(addr, bytes, tid); break;
+        case KLAS_MAP_ABS: xform_region<BF16, KLAS_MAP_ABS>(addr, bytes, tid); break;
+        case KLAS_MAP_SQUARE: xform_region<BF16, KLAS_MAP_SQUARE>(addr, bytes, tid); break;
+        case KLAS_MAP_RELU: xform_region<BF16, KLAS_MAP_RELU>(addr, bytes, tid); break;
+        case KLAS_MAP_NEG: xform_region<BF16, KLAS_MAP_NEG>(addr, bytes, tid); break;
+        default: break;
+    }
+}
+
+// One ring stage of a mapping kernel: waits (bounded) until the stage's copies have landed,
+// maps the A and / or B bytes in place, makes the writes visible to the tensor core's reads and
+// counts this warp on `xfull_bar` (possibly a barrier of the pair's even CTA).
+__device__ __forceinline__ bool xform_stage(const Params &p, uint32_t full_bar, uint32_t parity, const Ctl &ctl,
+                                            int site, uint32_t a_addr, uint32_t a_bytes, uint32_t b_bytes,
+                                            uint32_t xfull_bar_cluster, uint32_t tid) {
+    const uint32_t lane = tid & 31u;
+    bool ok = lane != 0 || bounded_wait(full_bar, parity, ctl, site, WAIT_LIMIT_NS, 32);
+    ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+    if (!ok) return false;
+    // Each lane observes the completed phase itself (immediate: the phase cannot advance before
+    // this warp's own arrival below), which orders the copies' writes before its reads.
+    for (uint32_t i = 0; i < 1024 && !ptx::mbar_try_wait(full_bar, parity); ++i) {
+    }
+    if (p.in_bf16) {
+        xform_dispatch<true>(p.map_a, a_addr, a_bytes, tid);
+        xform_dispatch<true>(p.map_b, a_addr + a_bytes, b_bytes, tid);
+    } else {
+        xform_dispatch<false>(p.map_a, a_addr, a_bytes, tid);
+        xform_dispatch<false>(p.map_b, a_addr + a_bytes, b_bytes, tid);
+    }
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive_cluster(xfull_bar_cluster);
+    return true;
+}
+
+template <uint32_t COMB>
+__device__ __forceinline__ float comb_f32(float old, float acc, float alpha, float beta) {
+    if constexpr (COMB == KLAS_COMB_MAX) return fmaxf(old, acc);
+    else if constexpr (COMB == KLAS_COMB_MIN) return fminf(old, acc);
+    else if constexpr (COMB == KLAS_COMB_MUL) return old * acc;
+    else return fmaf(alpha, acc, beta * old);
+}
+
 // Writes 32 consecutive columns of one output row (`acc` = this lane's slice of
 // the accumulator) with 16-byte accesses.  `ncols_left` = columns of the matrix
 // remaining from the first of the 32 (a multiple of 8 by the entry point's contract).
-template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT *drow,
-                                                const OutT *crow, float alpha,
-                                                float beta, uint32_t ncols_left) {
+// COMB says how the old values at `crow` enter; without `crow` the accumulator is written
+// as it is (`relu`: its positive part).
+template <typename OutT, uint32_t COMB>
+__device__ __forceinline__ void store_row_chunk_t(const uint32_t (&acc)[32], OutT *drow,
+                                                  const OutT *crow, float alpha, float beta,
+                                                  uint32_t ncols_left, bool relu) {
     constexpr uint32_t VEC = 16 / sizeof(OutT);  // elements per 16-byte access
 #pragma unroll
     for (uint32_t v0 = 0; v0 < 32; v0 += VEC) {
@@ -202,25 +321,41 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT 
             if (crow != nullptr) {
                 cin.raw = *reinterpret_cast<const uint4 *>(crow + v0);
 #pragma unroll
-                for (uint32_t j = 0; j < VEC; ++j) {
-                    const float a = __uint_as_float(acc[v0 + j]);
-                    out.e[j] = OutTraits<OutT>::from_f32(
-                        fmaf(alpha, a, beta * OutTraits<OutT>::to_f32(cin.e[j])));
-                }
+                for (uint32_t j = 0; j < VEC; ++j)
+                    out.e[j] = OutTraits<OutT>::from_f32(comb_f32<COMB>(
+                        OutTraits<OutT>::to_f32(cin.e[j]), __uint_as_float(acc[v0 + j]), alpha, beta));
             } else {
 #pragma unroll
-                for (uint32_t j = 0; j < VEC; ++j)
-                    out.e[j] = OutTraits<OutT>::from_f32(__uint_as_float(acc[v0 + j]));
+                for (uint32_t j = 0; j < VEC; ++j) {
+                    const float a = __uint_as_float(acc[v0 + j]);
+                    out.e[j] = OutTraits<OutT>::from_f32(relu ? fmaxf(a, 0.0f) : a);
+                }
             }
             *reinterpret_cast<uint4 *>(drow + v0) = out.raw;
         }
     }
 }
 
-template <typename OutT, bool PAIR>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT *drow, const OutT *crow,
+                                                float alpha, float beta, uint32_t ncols_left, uint32_t comb) {
+    switch (comb) {
+        case KLAS_COMB_MAX: store_row_chunk_t<OutT, KLAS_COMB_MAX>(acc, drow, crow, alpha, beta, ncols_left, false); break;
+        case KLAS_COMB_MIN: store_row_chunk_t<OutT, KLAS_COMB_MIN>(acc, drow, crow, alpha, beta, ncols_left, false); break;
+        case KLAS_COMB_MUL: store_row_chunk_t<OutT, KLAS_COMB_MUL>(acc, drow, crow, alpha, beta, ncols_left, false); break;
+        default:
+            store_row_chunk_t<OutT, KLAS_COMB_AXPBY>(acc, drow, crow, alpha, beta, ncols_left, comb == KLAS_COMB_RELU);
+            break;
+    }
+}
+
+// XFORM adds four warps that map the staged A / B bytes in place between the copy and the MMA
+// (single-CTA tiles only).
+template <typename OutT, bool PAIR, bool XFORM = false>
+__global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
     gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b, const Params p) {
+    static_assert(!(PAIR && XFORM), "operand maps are built for the single-CTA and the wide tiles");
     using S = Shape<PAIR>;
     constexpr uint32_t STAGES = S::STAGES;
     constexpr uint32_t STAGE_BYTES = S::STAGE_BYTES;
@@ -242,6 +377,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + ACC_STAGES + a); };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_region + 8u * (2 * STAGES + 2 * ACC_STAGES));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    [[maybe_unused]] auto xfull_bar = [&](uint32_t s) { return bar_base + XFULL_OFFSET + 8u * s; };
+    static_assert(8u * (2 * STAGES + 2 * ACC_STAGES) + 8u <= XFULL_OFFSET && XFULL_OFFSET + 8u * STAGES <= BARRIER_BYTES,
+                  "barrier block layout");
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -254,6 +392,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         for (uint32_t s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
+            if constexpr (XFORM) ptx::mbar_init(xfull_bar(s), XFORM_WARPS);
         }
         for (uint32_t a = 0; a < ACC_STAGES; ++a) {
             ptx::mbar_init(tfull_bar(a), 1);
@@ -368,7 +507,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const uint32_t d_tmem = tmem_base + acc * BN;
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 KLAS_PROF_BEGIN;
-                ok = bounded_wait(full_bar(stage), phase, ctl, SITE_MMA_FULL);
+                ok = bounded_wait(XFORM ? xfull_bar(stage) : full_bar(stage), phase, ctl, SITE_MMA_FULL);
                 KLAS_PROF_END(prof_acc0);
                 if (!ok) break;
                 {
@@ -420,6 +559,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         KLAS_PROF_STORE(6, prof_acc1);
         KLAS_PROF_STORE(7, prof_mma0);
         KLAS_PROF_STORE(4, prof_mma3);
+    } else if (XFORM && warp >= 2 + NUM_EPI_WARPS) {
+        // ------------------------------------------------------------ operand maps
+        const uint32_t tid = threadIdx.x - (2 + NUM_EPI_WARPS) * 32;
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
+            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                ok = xform_stage(p, full_bar(stage), phase, ctl, SITE_XFORM_FULL, smem_base + stage * STAGE_BYTES,
+                                 A_STAGE_BYTES, S::B_STAGE_BYTES, xfull_bar(stage), tid);
+                if (!ok) break;
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
@@ -458,7 +613,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 const uint32_t col = col0 + c * 32u;
                 if (row < p.M && col < p.N) {
                     store_row_chunk<OutT>(v, D + row_off + col, C ? C + row_off + col : nullptr,
-                                          p.alpha, p.beta, p.N - col);
+                                          p.alpha, p.beta, p.N - col, p.comb);
                 }
             }
             if (p.num_kb > 0) {
@@ -535,8 +690,11 @@ constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BARRIER_BYTES
 
 enum : int { SITE_WIDE = 0x100 };
 
-template <typename OutT>
-__global__ void __launch_bounds__(wide::THREADS, 1)
+// XFORM adds four warps per CTA that map the staged A / B bytes in place.  Each CTA then counts
+// its own copies on its own barrier, its mapping warps wait there, and all eight warps of the
+// pair report to a barrier of the even CTA that the MMA thread waits on.
+template <typename OutT, bool XFORM = false>
+__global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1)
     gemm_umma_wide_kernel(const __grid_constant__ CUtensorMap tm_a,
                           const __grid_constant__ CUtensorMap tm_b, const Params p) {
     using namespace wide;
@@ -555,6 +713,9 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
     const uint32_t tempty_bar = bar_base + 8u * (2 * STAGES + 1);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_region + 8u * (2 * STAGES + 2));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    [[maybe_unused]] auto xfull_bar = [&](uint32_t s) { return bar_base + XFULL_OFFSET + 8u * s; };
+    static_assert(8u * (2 * STAGES + 2) + 8u <= XFULL_OFFSET && XFULL_OFFSET + 8u * STAGES <= BARRIER_BYTES,
+                  "barrier block layout");
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -567,6 +728,7 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
         for (uint32_t s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
+            if constexpr (XFORM) ptx::mbar_init(xfull_bar(s), 2 * XFORM_WARPS);
         }
         ptx::mbar_init(tfull_bar, 1);
         ptx::mbar_init(tempty_bar, EPI_WARPS * 2);
@@ -593,7 +755,7 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
         // ------------------------------------------------------------ producer (one thread)
         uint32_t stage = 0, phase = 0;
         bool ok = lane == 0;
-        const uint32_t full_bars_cta0 = ptx::map_to_cta(full_bar(0), 0);
+        [[maybe_unused]] const uint32_t full_bars_cta0 = ptx::map_to_cta(full_bar(0), 0);
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             uint32_t b, tm, tn;
             decode_tile(t, p, b, tm, tn);
@@ -605,17 +767,31 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
                 const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
                 const uint32_t b_dst = a_dst + A_BYTES;
                 const int32_t k0 = int32_t(kb * BK);
-                // the even CTA's barrier counts the bytes of both CTAs' loads
-                if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
-                const uint32_t bar = full_bars_cta0 + 8u * stage;
-                ptx::tma_load_3d_pair(a_dst, &tm_a, bar, k0, a_row, int32_t(b));
-                if (p.b_row_major) {
+                if constexpr (XFORM) {
+                    // each CTA counts its own copies: its mapping warps wait on this barrier
+                    ptx::mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+                    ptx::tma_load_3d(a_dst, &tm_a, full_bar(stage), k0, a_row, int32_t(b));
+                    if (p.b_row_major) {
 #pragma unroll
-                    for (uint32_t j = 0; j < B_COLS / 64; ++j)
-                        ptx::tma_load_3d_pair(b_dst + j * B_CHUNK_BYTES, &tm_b, bar,
-                                              b_col + int32_t(j * 64), k0, int32_t(b));
+                        for (uint32_t j = 0; j < B_COLS / 64; ++j)
+                            ptx::tma_load_3d(b_dst + j * B_CHUNK_BYTES, &tm_b, full_bar(stage),
+                                             b_col + int32_t(j * 64), k0, int32_t(b));
+                    } else {
+                        ptx::tma_load_3d(b_dst, &tm_b, full_bar(stage), k0, b_col, int32_t(b));
+                    }
                 } else {
-                    ptx::tma_load_3d_pair(b_dst, &tm_b, bar, k0, b_col, int32_t(b));
+                    // the even CTA's barrier counts the bytes of both CTAs' loads
+                    if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+                    const uint32_t bar = full_bars_cta0 + 8u * stage;
+                    ptx::tma_load_3d_pair(a_dst, &tm_a, bar, k0, a_row, int32_t(b));
+                    if (p.b_row_major) {
+#pragma unroll
+                        for (uint32_t j = 0; j < B_COLS / 64; ++j)
+                            ptx::tma_load_3d_pair(b_dst + j * B_CHUNK_BYTES, &tm_b, bar,
+                                                  b_col + int32_t(j * 64), k0, int32_t(b));
+                    } else {
+                        ptx::tma_load_3d_pair(b_dst, &tm_b, bar, k0, b_col, int32_t(b));
+                    }
                 }
                 if (++stage == STAGES) {
                     stage = 0;
@@ -648,7 +824,10 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 {
                     KLAS_PROF_BEGIN;
-                    ok = bounded_wait(full_bar(stage), phase, ctl, SITE_WIDE | SITE_MMA_FULL);
+                    if constexpr (XFORM)
+                        ok = bounded_wait<true>(xfull_bar(stage), phase, ctl, SITE_WIDE | SITE_MMA_FULL);
+                    else
+                        ok = bounded_wait(full_bar(stage), phase, ctl, SITE_WIDE | SITE_MMA_FULL);
                     KLAS_PROF_END(prof_acc0);
                 }
                 if (!ok) break;
@@ -683,6 +862,23 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
         }
 #endif
         __syncwarp();
+    } else if (XFORM && warp >= 2 + EPI_WARPS) {
+        // ------------------------------------------------------------ operand maps (4 warps per CTA)
+        const uint32_t tid = threadIdx.x - (2 + EPI_WARPS) * 32;
+        const uint32_t xfull_cta0 = ptx::map_to_cta(xfull_bar(0), 0);
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
+            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                ok = xform_stage(p, full_bar(stage), phase, ctl, SITE_WIDE | SITE_XFORM_FULL,
+                                 smem_base + stage * STAGE_BYTES, A_BYTES, B_BYTES, xfull_cta0 + 8u * stage, tid);
+                if (!ok) break;
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
     } else {
         // ------------------------------------------------------------ epilogue (8 warps)
         // Warps 2-5 drain accumulator half 0, warps 6-9 half 1; within a group warp w owns the
@@ -700,6 +896,7 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
         const uint32_t buf = epi_base + (warp - 2) * EPI_BUF_BYTES;
         const uint32_t tempty_cta0 = ptx::map_to_cta(tempty_bar, 0);
         const uint32_t taddr0 = tmem_base + ((quad * 32u) << 16) + h * BN;
+        const bool relu = p.comb == KLAS_COMB_RELU;
         uint32_t tile_phase = 0;
         bool ok = true;
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
@@ -726,7 +923,7 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
                 if (C != nullptr) {
                     if (row < p.M && col < p.N)
                         store_row_chunk<OutT>(v, D + row_off + col, C + row_off + col, p.alpha, p.beta,
-                                              p.N - col);
+                                              p.N - col, p.comb);
                     return;
                 }
                 const uint32_t sub = c % CHUNKS_PER_BLOCK;
@@ -737,8 +934,10 @@ __global__ void __launch_bounds__(wide::THREADS, 1)
                         OutT e[16 / sizeof(OutT)];
                     } pk;
 #pragma unroll
-                    for (uint32_t e = 0; e < 16 / sizeof(OutT); ++e)
-                        pk.e[e] = OutTraits<OutT>::from_f32(__uint_as_float(v[j * (16 / sizeof(OutT)) + e]));
+                    for (uint32_t e = 0; e < 16 / sizeof(OutT); ++e) {
+                        const float a = __uint_as_float(v[j * (16 / sizeof(OutT)) + e]);
+                        pk.e[e] = OutTraits<OutT>::from_f32(relu ? fmaxf(a, 0.0f) : a);
+                    }
                     const uint32_t piece = (sub * PIECES + j) ^ (lane & 7u);
                     const uint32_t addr = buf + lane * 128u + piece * 16u;
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.raw.x),
@@ -879,20 +1078,20 @@ static int make_map_16bit(CUtensorMap *map, int dtype, const void *base, uint64_
     return make_map(map, dtype, base, inner, outer, batch, box_inner, box_outer);
 }
 
-template <typename OutT>
+template <typename OutT, bool XFORM>
 static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
                              cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_wide_kernel<OutT>,
+        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_wide_kernel<OutT, XFORM>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(grid), 1, 1);
-    cfg.blockDim = dim3(wide::THREADS, 1, 1);
+    cfg.blockDim = dim3(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1, 1);
     cfg.dynamicSmemBytes = wide::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -902,11 +1101,11 @@ static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_wide_kernel<OutT>, ta, tb, p),
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_wide_kernel<OutT, XFORM>, ta, tb, p),
                       "gemm_umma_wide_kernel launch");
 }
 
-template <typename OutT, bool PAIR>
+template <typename OutT, bool PAIR, bool XFORM>
 static int launch_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
                         cudaStream_t stream) {
     constexpr uint32_t SMEM = Shape<PAIR>::SMEM_BYTES;
@@ -914,13 +1113,13 @@ static int launch_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Para
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<OutT, PAIR>,
+        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<OutT, PAIR, XFORM>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(grid), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1, 1);
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -930,17 +1129,27 @@ static int launch_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Para
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_kernel<OutT, PAIR>, ta, tb, p),
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_kernel<OutT, PAIR, XFORM>, ta, tb, p),
                       "gemm_umma_kernel launch");
 }
 
-template <bool PAIR>
+template <bool PAIR, bool XFORM>
 static int launch_mode(int out_dtype, const CUtensorMap &ta, const CUtensorMap &tb, const Params &p,
                        int grid, cudaStream_t stream) {
     switch (out_dtype) {
-        case KLAS_F32: return launch_typed<float, PAIR>(ta, tb, p, grid, stream);
-        case KLAS_F16: return launch_typed<__half, PAIR>(ta, tb, p, grid, stream);
-        default: return launch_typed<__nv_bfloat16, PAIR>(ta, tb, p, grid, stream);
+        case KLAS_F32: return launch_typed<float, PAIR, XFORM>(ta, tb, p, grid, stream);
+        case KLAS_F16: return launch_typed<__half, PAIR, XFORM>(ta, tb, p, grid, stream);
+        default: return launch_typed<__nv_bfloat16, PAIR, XFORM>(ta, tb, p, grid, stream);
+    }
+}
+
+template <bool XFORM>
+static int launch_wide_mode(int out_dtype, const CUtensorMap &ta, const CUtensorMap &tb, const Params &p,
+                            int grid, cudaStream_t stream) {
+    switch (out_dtype) {
+        case KLAS_F32: return launch_wide_typed<float, XFORM>(ta, tb, p, grid, stream);
+        case KLAS_F16: return launch_wide_typed<__half, XFORM>(ta, tb, p, grid, stream);
+        default: return launch_wide_typed<__nv_bfloat16, XFORM>(ta, tb, p, grid, stream);
     }
 }
 
@@ -971,7 +1180,22 @@ int umma_clear_status() {
 int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
                      uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
                      void *D, float alpha, float beta, int *status_word, cudaStream_t stream) {
+    return launch_gemm_umma_fused(in_dtype, out_dtype, b_major, batch, rows, shared, cols, A, B, C, D, alpha, beta,
+                                  KLAS_MAP_ID, KLAS_MAP_ID, C ? KLAS_COMB_AXPBY : KLAS_COMB_NEW, status_word, stream);
+}
+
+int launch_gemm_umma_fused(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                           uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
+                           void *D, float alpha, float beta, int map_a, int map_b, int comb,
+                           int *status_word, cudaStream_t stream) {
     using namespace umma;
+    if (map_a < KLAS_MAP_ID || map_a > KLAS_MAP_NEG || map_b < KLAS_MAP_ID || map_b > KLAS_MAP_NEG)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: unknown operand map (%d, %d)", map_a, map_b);
+    if (comb < KLAS_COMB_NEW || comb > KLAS_COMB_RELU) return fail(KLAS_ERR_INVALID, "gemm_tc: unknown combine rule %d", comb);
+    const bool reads_c = comb != KLAS_COMB_NEW && comb != KLAS_COMB_RELU;
+    if (reads_c && !C && rows && cols && batch) return fail(KLAS_ERR_INVALID, "gemm_tc: this combine rule needs C");
+    if (!reads_c) C = nullptr;
+    const bool xform = (map_a != KLAS_MAP_ID || map_b != KLAS_MAP_ID) && shared > 0;
     if (in_dtype != KLAS_BF16 && in_dtype != KLAS_F16)
         return fail(KLAS_ERR_INVALID, "gemm_tc: in_dtype must be KLAS_BF16 or KLAS_F16");
     if (out_dtype != KLAS_F32 && out_dtype != KLAS_F16 && out_dtype != KLAS_BF16)
@@ -1003,11 +1227,11 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
     const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
     const uint64_t wide_tiles = ((rows + wide::TILE_M - 1) / wide::TILE_M) * ((cols + BN - 1) / BN) * batch;
     const bool can_pair = info.sm_count >= 2;
-    bool pair = can_pair && rows > BM && single_tiles >= uint64_t(info.sm_count);
+    bool pair = can_pair && rows > BM && single_tiles >= uint64_t(info.sm_count) && !xform;
     bool use_wide = can_pair && wide_tiles >= uint64_t(info.sm_count / 2);
     if (const char *mode = getenv("KLAS_TC_MODE")) {
         if (!strcmp(mode, "single")) pair = use_wide = false;
-        else if (!strcmp(mode, "pair")) { pair = can_pair; use_wide = false; }
+        else if (!strcmp(mode, "pair")) { pair = can_pair && !xform; use_wide = false; }
         else if (!strcmp(mode, "wide")) use_wide = can_pair;
     }
     if (use_wide) {
@@ -1028,6 +1252,10 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
         p.b_row_major = (b_major == KLAS_B_ROW_MAJOR) ? 1u : 0u;
         p.idesc = ptx::umma_idesc_f16(in_dtype == KLAS_BF16, false, p.b_row_major != 0, 256, BN);
         p.status = status_word;
+        p.in_bf16 = in_dtype == KLAS_BF16 ? 1u : 0u;
+        p.map_a = uint32_t(map_a);
+        p.map_b = uint32_t(map_b);
+        p.comb = uint32_t(comb);
         p.raster_group = DEFAULT_RASTER_GROUP;
         if (const char *rg = getenv("KLAS_TC_RASTER")) {
             const int v = atoi(rg);
@@ -1043,11 +1271,8 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
             }
         }
         const uint64_t groups = wide_tiles < uint64_t(info.sm_count / 2) ? wide_tiles : uint64_t(info.sm_count / 2);
-        switch (out_dtype) {
-            case KLAS_F32: return launch_wide_typed<float>(ta, tb, p, int(groups * 2), stream);
-            case KLAS_F16: return launch_wide_typed<__half>(ta, tb, p, int(groups * 2), stream);
-            default: return launch_wide_typed<__nv_bfloat16>(ta, tb, p, int(groups * 2), stream);
-        }
+        return xform ? launch_wide_mode<true>(out_dtype, ta, tb, p, int(groups * 2), stream)
+                     : launch_wide_mode<false>(out_dtype, ta, tb, p, int(groups * 2), stream);
     }
     const uint32_t tile_m = pair ? Shape<true>::TILE_M : Shape<false>::TILE_M;
 
@@ -1069,6 +1294,10 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
     p.b_row_major = (b_major == KLAS_B_ROW_MAJOR) ? 1u : 0u;
     p.idesc = ptx::umma_idesc_f16(in_dtype == KLAS_BF16, false, p.b_row_major != 0, tile_m, BN);
     p.status = status_word;
+    p.in_bf16 = in_dtype == KLAS_BF16 ? 1u : 0u;
+    p.map_a = uint32_t(map_a);
+    p.map_b = uint32_t(map_b);
+    p.comb = uint32_t(comb);
     p.raster_group = DEFAULT_RASTER_GROUP;
     if (const char *rg = getenv("KLAS_TC_RASTER")) {
         const int v = atoi(rg);
@@ -1087,10 +1316,11 @@ int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, u
     }
     if (pair) {
         const uint64_t groups = num_tiles < uint64_t(info.sm_count / 2) ? num_tiles : uint64_t(info.sm_count / 2);
-        return launch_mode<true>(out_dtype, ta, tb, p, int(groups * 2), stream);
+        return launch_mode<true, false>(out_dtype, ta, tb, p, int(groups * 2), stream);
     }
     const int grid = int(num_tiles < uint64_t(info.sm_count) ? num_tiles : uint64_t(info.sm_count));
-    return launch_mode<false>(out_dtype, ta, tb, p, grid, stream);
+    return xform ? launch_mode<false, true>(out_dtype, ta, tb, p, grid, stream)
+                 : launch_mode<false, false>(out_dtype, ta, tb, p, grid, stream);
 }
 
 }  // namespace klas

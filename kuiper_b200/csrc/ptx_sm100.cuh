@@ -183,6 +183,35 @@ __device__ __forceinline__ void cluster_wait() {
 }
 
 // Arrive on a barrier given by its shared::cluster address (own or peer CTA).
+// try_wait whose acquire covers the whole cluster: for phases completed by arrivals of the
+// other CTA of a pair that publish that CTA's shared-memory writes.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ void lds128(uint32_t addr, uint32_t (&w)[4]) {
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                 : "r"(addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void sts128(uint32_t addr, const uint32_t (&w)[4]) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3])
+                 : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
                  : "memory");

@@ -119,12 +119,23 @@ def gemm(A: torch.Tensor, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
     return C_
 
 
+_MAPS = {None: _lib.MAP_ID, "id": _lib.MAP_ID, "sqrt": _lib.MAP_SQRT, "abs": _lib.MAP_ABS,
+         "square": _lib.MAP_SQUARE, "relu": _lib.MAP_RELU, "neg": _lib.MAP_NEG}
+_COMBS = {"new": _lib.COMB_NEW, "axpby": _lib.COMB_AXPBY, "max": _lib.COMB_MAX, "min": _lib.COMB_MIN,
+          "mul": _lib.COMB_MUL, "relu": _lib.COMB_RELU}
+
+
 def gemm_tc(A: torch.Tensor, B: torch.Tensor, *, out_dtype=torch.float32, b_col_major: bool = False,
             C_: Optional[torch.Tensor] = None, D: Optional[torch.Tensor] = None,
-            alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+            alpha: float = 1.0, beta: float = 0.0, map_a: Optional[str] = None,
+            map_b: Optional[str] = None, comb: Optional[str] = None) -> torch.Tensor:
     """Tensor-core GEMM D = out_dtype(alpha*A.B + beta*C) (or A.B when C_ is None).
     A: [batch,] rows x shared; B: [batch,] shared x cols, or [batch,] cols x shared when
-    `b_col_major`.  Returns D (allocated when not given; pass D=C_ to accumulate in place)."""
+    `b_col_major`.  Returns D (allocated when not given; pass D=C_ to accumulate in place).
+
+    Fused hooks: `map_a` / `map_b` in {"sqrt", "abs", "square", "relu", "neg"} are applied to the
+    operands inside the kernel; `comb` in {"new", "axpby", "max", "min", "mul", "relu"} says how
+    the product meets C_ (default: "axpby" with C_, "new" without)."""
     if A.dtype not in (torch.bfloat16, torch.float16) or B.dtype != A.dtype:
         raise TypeError("A and B must both be bf16 or both be f16")
     batch = A.shape[0] if A.dim() == 3 else 1
@@ -146,11 +157,21 @@ def gemm_tc(A: torch.Tensor, B: torch.Tensor, *, out_dtype=torch.float32, b_col_
             raise ValueError("C has the wrong shape or dtype")
         pc = _dev(C_, "C")
     lib = _lib.load()
+    try:
+        ma, mb = _MAPS[map_a], _MAPS[map_b]
+        cb = _COMBS[comb] if comb is not None else (_lib.COMB_AXPBY if C_ is not None else _lib.COMB_NEW)
+    except KeyError as e:
+        raise ValueError("unknown map or combine rule %s" % e) from None
+    bmaj = _lib.B_COL_MAJOR if b_col_major else _lib.B_ROW_MAJOR
     with torch.cuda.device(A.device):
-        check(lib.klas_b200_gemm_tc(_code(A), _DTYPES[out_dtype],
-                                    _lib.B_COL_MAJOR if b_col_major else _lib.B_ROW_MAJOR, batch,
-                                    rows, shared, cols, _dev(A, "A"), _dev(B, "B"), pc, _dev(D, "D"),
-                                    float(alpha), float(beta), None, _stream()))
+        if map_a is None and map_b is None and comb is None:
+            check(lib.klas_b200_gemm_tc(_code(A), _DTYPES[out_dtype], bmaj, batch, rows, shared, cols,
+                                        _dev(A, "A"), _dev(B, "B"), pc, _dev(D, "D"),
+                                        float(alpha), float(beta), None, _stream()))
+        else:
+            check(lib.klas_b200_gemm_tc_fused(_code(A), _DTYPES[out_dtype], bmaj, batch, rows, shared, cols,
+                                              _dev(A, "A"), _dev(B, "B"), pc, _dev(D, "D"),
+                                              float(alpha), float(beta), ma, mb, cb, None, _stream()))
     return D
 
 

@@ -367,6 +367,28 @@ void klas_oracle_rowscale_f64(size_t m, size_t n, const double *a, double *b)
         for (size_t c = 0; c < n; c++) b[r * n + c] = a[r] * b[r * n + c];
 }
 
+/* Element-wise operand maps of the fused tensor-core GEMM: evaluated in float on the 16-bit
+ * value and rounded once (nearest even) back to the 16-bit type -- what the reference's
+ * KPR_LOAD_MAP does to the registers of a loaded wmma fragment (include/kuiper/tensorcores.h:30-38),
+ * e.g. sqrt in the demo dist/Kuiper_Example_Fused_GEMM.cu:8-27.
+ * map: 0 id, 1 sqrt, 2 abs, 3 square, 4 relu, 5 neg. */
+void klas_oracle_map16(const uint16_t *in, uint16_t *out, size_t n, int bf16, int map)
+{
+    for (size_t i = 0; i < n; ++i) {
+        const float x = (float)(bf16 ? bf16_bits_to_double(in[i]) : f16_bits_to_double(in[i]));
+        float y;
+        switch (map) {
+            case 1: y = sqrtf(x); break;
+            case 2: y = fabsf(x); break;
+            case 3: y = x * x; break;
+            case 4: y = x > 0.0f ? x : 0.0f; break;
+            case 5: y = -x; break;
+            default: y = x; break;
+        }
+        out[i] = bf16 ? double_to_bf16_bits((double)y) : double_to_f16_bits((double)y);
+    }
+}
+
 int klas_oracle_max_threads(void)
 {
 #ifdef _OPENMP

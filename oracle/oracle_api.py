@@ -65,6 +65,15 @@ class Oracle:
             self.lib.klas_oracle_softmax_f64(rows[r].ctypes.data, o2[r].ctypes.data, rows.shape[1], int(log))
         return out
 
+    def map16(self, bits: np.ndarray, kind: str, op: int) -> np.ndarray:
+        """Element-wise operand map (0 id, 1 sqrt, 2 abs, 3 square, 4 relu, 5 neg) on bf16 / f16 bit
+        patterns: evaluated in float, rounded once back to the 16-bit type."""
+        bits = np.ascontiguousarray(bits, dtype=np.uint16)
+        out = np.empty_like(bits)
+        self.lib.klas_oracle_map16.argtypes = [_vp, _vp, _sz, _int, _int]
+        self.lib.klas_oracle_map16(_p(bits), _p(out), bits.size, int(kind == "bf16"), int(op))
+        return out
+
     @property
     def max_threads(self) -> int:
         return self.lib.klas_oracle_max_threads()
