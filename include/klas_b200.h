@@ -61,7 +61,8 @@ typedef enum klas_b_major_e {
  */
 typedef enum klas_map_e {
     KLAS_MAP_ID = 0,      /* x */
-    KLAS_MAP_SQRT = 1,    /* sqrt(x); hardware approximation, at most 1 ulp of f32 before rounding; NaN for x < 0 */
+    KLAS_MAP_SQRT = 1,    /* sqrt(x); NaN for x < 0.  Tensor-core path: hardware approximation, at most 1 ulp of f32
+                             before the rounding, bf16 inputs below 1.2e-38 give 0 */
     KLAS_MAP_ABS = 2,     /* |x| */
     KLAS_MAP_SQUARE = 3,  /* x * x */
     KLAS_MAP_RELU = 4,    /* max(x, 0) */
@@ -108,6 +109,31 @@ int klas_b200_gemm(int dtype, int layout, uint32_t batch,
                    uint64_t m, uint64_t n, uint64_t k,
                    const void *alpha, const void *beta,
                    const void *A, const void *B, void *C, void *stream);
+
+/*
+ * General batched CUDA-core GEMM: `batch` row-major products
+ *
+ *   C_p = comb( C_p, map_a(A_p) . map_b(B_p) ),     p = 0 .. batch-1
+ *
+ * where X_p starts `stride_x` elements after X_(p-1) and consecutive rows of X are `ldx`
+ * elements apart (lda >= k, ldb >= n, ldc >= n).  stride_a or stride_b may be 0: every page
+ * then multiplies the same matrix.  Pages of C must not overlap.  dtype as klas_b200_gemm;
+ * map_a / map_b: klas_map (KLAS_MAP_SQRT needs a floating type; on the unsigned types abs and
+ * relu are the identity and neg, square wrap); comb: klas_comb, with alpha / beta (host
+ * scalars of the matrix dtype) required for KLAS_COMB_AXPBY and ignored otherwise.  Maps are
+ * evaluated in the arithmetic type (f32 for bf16 storage) on the way into shared memory.
+ *
+ * Replaces: the rank-3 strided entries with mapA / mapB / comb that the reference's sources
+ * define for its shared-memory and 2-D block-tiling kernels and derive the rank-2 ones from
+ * (src/lib/kernel/gemm/Kuiper.Kernel.GEMM.SHMem.fsti:40-97, ...BlockTiling2D.fsti:34-60), of
+ * which it exports the contiguous f32 case as Klas_GEMM_Naive1_g_batched_* (dist/Klas_GEMM_Naive1.h:54-66).
+ */
+int klas_b200_gemm_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, uint64_t k,
+                           const void *alpha, const void *beta,
+                           const void *A, uint64_t lda, uint64_t stride_a,
+                           const void *B, uint64_t ldb, uint64_t stride_b,
+                           void *C, uint64_t ldc, uint64_t stride_c,
+                           int map_a, int map_b, int comb, void *stream);
 
 /*
  * Tensor-core GEMM (tcgen05 UMMA, fp32 accumulation in tensor memory):

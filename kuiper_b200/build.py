@@ -85,7 +85,7 @@ def build_compat(force: bool = False) -> Path:
     hdrs = sorted((INCLUDE_DIR / "klas").rglob("*.h")) + sorted((INCLUDE_DIR / "klas").rglob("*.inc")) + \
         [COMPAT_DIR / "compat_common.h", INCLUDE_DIR / "klas_b200.h"]
     procs, objs = [], []
-    for src in sorted(COMPAT_DIR.glob("Klas_*.cu")):
+    for src in sorted(COMPAT_DIR.glob("Klas_*.cu")) + sorted(COMPAT_DIR.glob("Kuiper_*.cu")):
         obj = COMPAT_OUT / (src.stem + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + hdrs):

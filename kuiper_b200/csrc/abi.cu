@@ -156,6 +156,15 @@ int klas_b200_gemm_tc(int in_dtype, int out_dtype, int b_major, uint32_t batch, 
                             alpha, beta, status_word, static_cast<cudaStream_t>(stream));
 }
 
+int klas_b200_gemm_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, uint64_t k, const void *alpha,
+                           const void *beta, const void *A, uint64_t lda, uint64_t stride_a, const void *B,
+                           uint64_t ldb, uint64_t stride_b, void *C, uint64_t ldc, uint64_t stride_c, int map_a,
+                           int map_b, int comb, void *stream) {
+    clear_error();
+    return launch_gemm_simt_strided(dtype, batch, m, n, k, alpha, beta, A, lda, stride_a, B, ldb, stride_b, C, ldc,
+                                    stride_c, map_a, map_b, comb, static_cast<cudaStream_t>(stream));
+}
+
 int klas_b200_gemm_tc_fused(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
                             uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
                             void *D, float alpha, float beta, int map_a, int map_b, int comb,

@@ -15,6 +15,11 @@
 // A "fast" instantiation (sizes multiples of the tile, 16-byte aligned rows)
 // uses unpredicated vector loads; every other shape takes the predicated one.
 //
+// The strided entry point adds row strides, page strides (0 = one matrix shared by every page)
+// and the element-wise hooks of the reference's general batched interface (mapA / mapB / comb of
+// src/lib/kernel/gemm/Kuiper.Kernel.GEMM.SHMem.fsti:40-64 and ...BlockTiling2D.fsti:34-60) in
+// separate instantiations, so the plain kernels keep their code.
+//
 // Takes over the work of dist/Klas_GEMM_SHMem.cu:9-72, dist/Klas_GEMM_Tiled.cu:8-54,
 // dist/Klas_GEMM_BlockTiling1D.cu:8-69, dist/Klas_GEMM_BlockTiling2D.cu:9-214 and
 // dist/Klas_GEMM_Naive{1,2,3}.cu.
@@ -22,6 +27,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "klas_internal.h"
 
@@ -79,10 +85,54 @@ struct Args {
     const void *B;
     void *C;
     uint64_t M, N, K;
+    uint64_t lda, ldb, ldc;   // row strides in elements
+    uint64_t sa, sb, sc;      // page strides in elements
     uint64_t tiles_m, tiles_n;
     T alpha, beta;
     int scaled;  // 0: C = A.B   1: C = beta*C + alpha*A.B
+    int map_a, map_b, comb;   // klas_map / klas_comb, read by the HOOKS instantiations only
 };
+
+// What one call asks for, as the launch helpers pass it down.
+struct Problem {
+    uint32_t batch;
+    uint64_t m, n, k;
+    uint64_t lda, ldb, ldc, sa, sb, sc;
+    int map_a, map_b, comb;
+    bool hooks;   // any map or a combine rule other than overwrite / axpby
+};
+
+template <typename T>
+__device__ __forceinline__ T map_val(T x, int op) {
+    if constexpr (std::is_floating_point<T>::value) {
+        switch (op) {
+            case KLAS_MAP_SQRT: return sqrt(x);
+            case KLAS_MAP_ABS: return fabs(x);
+            case KLAS_MAP_SQUARE: return x * x;
+            case KLAS_MAP_RELU: return x > T(0) ? x : T(0);
+            case KLAS_MAP_NEG: return -x;
+            default: return x;
+        }
+    } else {
+        switch (op) {   // unsigned, wrapping: abs and relu are the identity, sqrt is refused by the host
+            case KLAS_MAP_SQUARE: return x * x;
+            case KLAS_MAP_NEG: return T(0) - x;
+            default: return x;
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ T comb_val(T old, T acc, T alpha, T beta, int comb) {
+    switch (comb) {
+        case KLAS_COMB_NEW: return acc;
+        case KLAS_COMB_MAX: return old > acc ? old : acc;
+        case KLAS_COMB_MIN: return old < acc ? old : acc;
+        case KLAS_COMB_MUL: return old * acc;
+        case KLAS_COMB_RELU: return acc > T(0) ? acc : T(0);
+        default: return beta * old + alpha * acc;
+    }
+}
 
 template <typename T, int N>
 struct alignas(16) Vec {
@@ -90,7 +140,7 @@ struct alignas(16) Vec {
 };
 
 // S = storage type in global memory, T = arithmetic type.
-template <typename S, typename T, int BM, int BN, int BK, bool FAST>
+template <typename S, typename T, int BM, int BN, int BK, bool FAST, bool HOOKS = false>
 __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) ? 3 : 2) gemm_simt_kernel(const Args<T> a) {
     constexpr int VEC = 16 / sizeof(T);
     constexpr int TM = BM / TY;
@@ -118,9 +168,9 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
     const uint64_t m0 = (rem / a.tiles_n) * BM;
     const uint64_t n0 = (rem % a.tiles_n) * BN;
 
-    const S *__restrict__ A = static_cast<const S *>(a.A) + bidx * a.M * a.K;
-    const S *__restrict__ B = static_cast<const S *>(a.B) + bidx * a.K * a.N;
-    S *C = static_cast<S *>(a.C) + bidx * a.M * a.N;
+    const S *__restrict__ A = static_cast<const S *>(a.A) + bidx * a.sa;
+    const S *__restrict__ B = static_cast<const S *>(a.B) + bidx * a.sb;
+    S *C = static_cast<S *>(a.C) + bidx * a.sc;
 
     constexpr bool PACKED = IsF32<T>::value;   // f32: accumulate column pairs with fma.rn.f32x2
     T acc[PACKED ? 1 : TM][PACKED ? 1 : TN];
@@ -145,12 +195,18 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
                 const int kv = (idx % (BK / VEC)) * VEC;
                 if constexpr (FAST) {
                     ra[i] = *reinterpret_cast<const Vec<T, VEC> *>(
-                        reinterpret_cast<const T *>(A) + (m0 + r) * a.K + k0 + kv);
+                        reinterpret_cast<const T *>(A) + (m0 + r) * a.lda + k0 + kv);
                 } else {
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) {
                         const uint64_t gr = m0 + r, gk = k0 + kv + e;
-                        ra[i].v[e] = (gr < a.M && gk < a.K) ? Conv<S, T>::load(A[gr * a.K + gk]) : T(0);
+                        ra[i].v[e] = (gr < a.M && gk < a.K) ? Conv<S, T>::load(A[gr * a.lda + gk]) : T(0);
+                    }
+                }
+                if constexpr (HOOKS) {
+                    if (a.map_a != KLAS_MAP_ID) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) ra[i].v[e] = map_val<T>(ra[i].v[e], a.map_a);   // map(0) = 0 keeps the padding neutral
                     }
                 }
             }
@@ -163,12 +219,18 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
                 const int nv = (idx % (BN / VEC)) * VEC;
                 if constexpr (FAST) {
                     rb[i] = *reinterpret_cast<const Vec<T, VEC> *>(
-                        reinterpret_cast<const T *>(B) + (k0 + kr) * a.N + n0 + nv);
+                        reinterpret_cast<const T *>(B) + (k0 + kr) * a.ldb + n0 + nv);
                 } else {
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) {
                         const uint64_t gk = k0 + kr, gc = n0 + nv + e;
-                        rb[i].v[e] = (gk < a.K && gc < a.N) ? Conv<S, T>::load(B[gk * a.N + gc]) : T(0);
+                        rb[i].v[e] = (gk < a.K && gc < a.N) ? Conv<S, T>::load(B[gk * a.ldb + gc]) : T(0);
+                    }
+                }
+                if constexpr (HOOKS) {
+                    if (a.map_b != KLAS_MAP_ID) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) rb[i].v[e] = map_val<T>(rb[i].v[e], a.map_b);
                     }
                 }
             }
@@ -261,8 +323,14 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
             const uint64_t c = n0 + g * (BN / GN) + tx * VEC;
             if constexpr (FAST) {
                 Vec<T, VEC> out;
-                T *cp = reinterpret_cast<T *>(C) + r * a.N + c;
-                if (a.scaled) {
+                T *cp = reinterpret_cast<T *>(C) + r * a.ldc + c;
+                if (HOOKS && a.comb != KLAS_COMB_AXPBY) {
+                    Vec<T, VEC> old{};
+                    if (a.comb != KLAS_COMB_NEW && a.comb != KLAS_COMB_RELU) old = *reinterpret_cast<const Vec<T, VEC> *>(cp);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e)
+                        out.v[e] = comb_val<T>(old.v[e], acc_at(i, g * VEC + e), a.alpha, a.beta, a.comb);
+                } else if (a.scaled) {
                     const Vec<T, VEC> old = *reinterpret_cast<const Vec<T, VEC> *>(cp);
 #pragma unroll
                     for (int e = 0; e < VEC; ++e)
@@ -277,9 +345,14 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) {
                         if (c + e < a.N) {
-                            S *cp = C + r * a.N + c + e;
+                            S *cp = C + r * a.ldc + c + e;
                             T val = acc_at(i, g * VEC + e);
-                            if (a.scaled) val = a.beta * Conv<S, T>::load(*cp) + a.alpha * val;
+                            if (HOOKS && a.comb != KLAS_COMB_AXPBY) {
+                                const T old = (a.comb != KLAS_COMB_NEW && a.comb != KLAS_COMB_RELU) ? Conv<S, T>::load(*cp) : T(0);
+                                val = comb_val<T>(old, val, a.alpha, a.beta, a.comb);
+                            } else if (a.scaled) {
+                                val = a.beta * Conv<S, T>::load(*cp) + a.alpha * val;
+                            }
                             *cp = Conv<S, T>::store(val);
                         }
                     }
@@ -290,58 +363,105 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
 }
 
 template <typename S, typename T, int BM, int BN, int BK>
-static int launch_cfg(uint32_t batch, uint64_t m, uint64_t n, uint64_t k, T alpha, T beta,
-                      int scaled, const void *A, const void *B, void *C, cudaStream_t stream) {
+static int launch_cfg(const Problem &q, T alpha, T beta, int scaled, const void *A, const void *B, void *C,
+                      cudaStream_t stream) {
     Args<T> a;
     a.A = A;
     a.B = B;
     a.C = C;
-    a.M = m;
-    a.N = n;
-    a.K = k;
-    a.tiles_m = (m + BM - 1) / BM;
-    a.tiles_n = (n + BN - 1) / BN;
+    a.M = q.m;
+    a.N = q.n;
+    a.K = q.k;
+    a.lda = q.lda;
+    a.ldb = q.ldb;
+    a.ldc = q.ldc;
+    a.sa = q.sa;
+    a.sb = q.sb;
+    a.sc = q.sc;
+    a.tiles_m = (q.m + BM - 1) / BM;
+    a.tiles_n = (q.n + BN - 1) / BN;
     a.alpha = alpha;
     a.beta = beta;
     a.scaled = scaled;
-    const uint64_t blocks = a.tiles_m * a.tiles_n * batch;
+    a.map_a = q.map_a;
+    a.map_b = q.map_b;
+    a.comb = q.comb;
+    const uint64_t blocks = a.tiles_m * a.tiles_n * q.batch;
     if (blocks > 0x7fffffffull) return fail(KLAS_ERR_TOO_LARGE, "gemm: too many tiles for one grid");
     constexpr int VEC = 16 / sizeof(T);
     const bool same_storage = sizeof(S) == sizeof(T);
-    const bool fast = same_storage && m % BM == 0 && n % BN == 0 && k % BK == 0 && k > 0 &&
-                      n % VEC == 0 && k % VEC == 0 &&
+    const bool fast = same_storage && q.m % BM == 0 && q.n % BN == 0 && q.k % BK == 0 && q.k > 0 &&
+                      (q.lda | q.ldb | q.ldc | q.sa | q.sb | q.sc) % VEC == 0 &&
                       ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
                         reinterpret_cast<uintptr_t>(C)) & 15u) == 0;
     if constexpr (sizeof(S) == sizeof(T)) {
         if (fast) {
-            gemm_simt_kernel<S, T, BM, BN, BK, true><<<unsigned(blocks), THREADS, 0, stream>>>(a);
+            if (q.hooks)
+                gemm_simt_kernel<S, T, BM, BN, BK, true, true><<<unsigned(blocks), THREADS, 0, stream>>>(a);
+            else
+                gemm_simt_kernel<S, T, BM, BN, BK, true><<<unsigned(blocks), THREADS, 0, stream>>>(a);
             return check_cuda(cudaGetLastError(), "gemm_simt_kernel launch");
         }
     }
-    gemm_simt_kernel<S, T, BM, BN, BK, false><<<unsigned(blocks), THREADS, 0, stream>>>(a);
+    if (q.hooks)
+        gemm_simt_kernel<S, T, BM, BN, BK, false, true><<<unsigned(blocks), THREADS, 0, stream>>>(a);
+    else
+        gemm_simt_kernel<S, T, BM, BN, BK, false><<<unsigned(blocks), THREADS, 0, stream>>>(a);
     return check_cuda(cudaGetLastError(), "gemm_simt_kernel launch");
 }
 
 template <typename S, typename T>
-static int launch_type(uint32_t batch, uint64_t m, uint64_t n, uint64_t k, T alpha, T beta,
-                       int scaled, const void *A, const void *B, void *C, int sm_count,
-                       cudaStream_t stream) {
+static int launch_type(const Problem &q, T alpha, T beta, int scaled, const void *A, const void *B, void *C,
+                       int sm_count, cudaStream_t stream) {
+    const uint64_t m = q.m, n = q.n, batch = q.batch;
     if constexpr (sizeof(T) == 4) {
         // Large tiles once they fill the machine; small ones otherwise.
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 127) / 128) * batch;
         const uint64_t mid_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
         int pick = big_tiles >= uint64_t(sm_count) ? 2 : (mid_tiles * 10 >= uint64_t(sm_count) * 8 ? 1 : 0);
         if (const char *t = getenv("KLAS_SIMT_TILE")) pick = atoi(t);
-        if (pick == 2)
-            return launch_cfg<S, T, 128, 128, 16>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
-        if (pick == 1)
-            return launch_cfg<S, T, 128, 64, 16>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
-        return launch_cfg<S, T, 64, 64, 16>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
+        if (pick == 2) return launch_cfg<S, T, 128, 128, 16>(q, alpha, beta, scaled, A, B, C, stream);
+        if (pick == 1) return launch_cfg<S, T, 128, 64, 16>(q, alpha, beta, scaled, A, B, C, stream);
+        return launch_cfg<S, T, 64, 64, 16>(q, alpha, beta, scaled, A, B, C, stream);
     } else {
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
-        if (big_tiles >= uint64_t(sm_count))
-            return launch_cfg<S, T, 128, 64, 8>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
-        return launch_cfg<S, T, 64, 32, 8>(batch, m, n, k, alpha, beta, scaled, A, B, C, stream);
+        if (big_tiles >= uint64_t(sm_count)) return launch_cfg<S, T, 128, 64, 8>(q, alpha, beta, scaled, A, B, C, stream);
+        return launch_cfg<S, T, 64, 32, 8>(q, alpha, beta, scaled, A, B, C, stream);
+    }
+}
+
+static int dispatch(int dtype, const Problem &q, const void *alpha, const void *beta, const void *A, const void *B,
+                    void *C, cudaStream_t stream) {
+    DeviceInfo info;
+    if (int rc = device_info(&info)) return rc;
+    const int scaled = alpha != nullptr;
+    switch (dtype) {
+        case KLAS_F32:
+            return launch_type<float, float>(q, scaled ? *static_cast<const float *>(alpha) : 1.0f,
+                                             scaled ? *static_cast<const float *>(beta) : 0.0f, scaled, A, B, C,
+                                             info.sm_count, stream);
+        case KLAS_F64:
+            return launch_type<double, double>(q, scaled ? *static_cast<const double *>(alpha) : 1.0,
+                                               scaled ? *static_cast<const double *>(beta) : 0.0, scaled, A, B, C,
+                                               info.sm_count, stream);
+        case KLAS_U32:
+            return launch_type<uint32_t, uint32_t>(q, scaled ? *static_cast<const uint32_t *>(alpha) : 1u,
+                                                   scaled ? *static_cast<const uint32_t *>(beta) : 0u, scaled, A, B, C,
+                                                   info.sm_count, stream);
+        case KLAS_U64:
+            return launch_type<uint64_t, uint64_t>(q, scaled ? *static_cast<const uint64_t *>(alpha) : 1ull,
+                                                   scaled ? *static_cast<const uint64_t *>(beta) : 0ull, scaled, A, B, C,
+                                                   info.sm_count, stream);
+        case KLAS_BF16: {
+            float fa = 1.0f, fb = 0.0f;
+            if (scaled) {
+                fa = __bfloat162float(*static_cast<const __nv_bfloat16 *>(alpha));
+                fb = __bfloat162float(*static_cast<const __nv_bfloat16 *>(beta));
+            }
+            return launch_type<__nv_bfloat16, float>(q, fa, fb, scaled, A, B, C, info.sm_count, stream);
+        }
+        default:
+            return fail(KLAS_ERR_INVALID, "gemm: dtype must be F32, F64, U32, U64 or BF16");
     }
 }
 
@@ -364,38 +484,56 @@ int launch_gemm_simt(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t
         m = n;
         n = tm;
     }
-    DeviceInfo info;
-    if (int rc = device_info(&info)) return rc;
-    const int scaled = alpha != nullptr;
-    switch (dtype) {
-        case KLAS_F32:
-            return simt::launch_type<float, float>(
-                batch, m, n, k, scaled ? *static_cast<const float *>(alpha) : 1.0f,
-                scaled ? *static_cast<const float *>(beta) : 0.0f, scaled, A, B, C, info.sm_count, stream);
-        case KLAS_F64:
-            return simt::launch_type<double, double>(
-                batch, m, n, k, scaled ? *static_cast<const double *>(alpha) : 1.0,
-                scaled ? *static_cast<const double *>(beta) : 0.0, scaled, A, B, C, info.sm_count, stream);
-        case KLAS_U32:
-            return simt::launch_type<uint32_t, uint32_t>(
-                batch, m, n, k, scaled ? *static_cast<const uint32_t *>(alpha) : 1u,
-                scaled ? *static_cast<const uint32_t *>(beta) : 0u, scaled, A, B, C, info.sm_count, stream);
-        case KLAS_U64:
-            return simt::launch_type<uint64_t, uint64_t>(
-                batch, m, n, k, scaled ? *static_cast<const uint64_t *>(alpha) : 1ull,
-                scaled ? *static_cast<const uint64_t *>(beta) : 0ull, scaled, A, B, C, info.sm_count, stream);
-        case KLAS_BF16: {
-            float fa = 1.0f, fb = 0.0f;
-            if (scaled) {
-                fa = __bfloat162float(*static_cast<const __nv_bfloat16 *>(alpha));
-                fb = __bfloat162float(*static_cast<const __nv_bfloat16 *>(beta));
-            }
-            return simt::launch_type<__nv_bfloat16, float>(batch, m, n, k, fa, fb, scaled, A, B, C,
-                                                           info.sm_count, stream);
-        }
-        default:
-            return fail(KLAS_ERR_INVALID, "gemm: dtype must be F32, F64, U32, U64 or BF16");
-    }
+    simt::Problem q{};
+    q.batch = batch;
+    q.m = m;
+    q.n = n;
+    q.k = k;
+    q.lda = k;
+    q.ldb = n;
+    q.ldc = n;
+    q.sa = m * k;
+    q.sb = k * n;
+    q.sc = m * n;
+    q.map_a = q.map_b = KLAS_MAP_ID;
+    q.comb = alpha ? KLAS_COMB_AXPBY : KLAS_COMB_NEW;
+    q.hooks = false;
+    return simt::dispatch(dtype, q, alpha, beta, A, B, C, stream);
+}
+
+int launch_gemm_simt_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, uint64_t k, const void *alpha,
+                             const void *beta, const void *A, uint64_t lda, uint64_t stride_a, const void *B,
+                             uint64_t ldb, uint64_t stride_b, void *C, uint64_t ldc, uint64_t stride_c, int map_a,
+                             int map_b, int comb, cudaStream_t stream) {
+    if (map_a < KLAS_MAP_ID || map_a > KLAS_MAP_NEG || map_b < KLAS_MAP_ID || map_b > KLAS_MAP_NEG)
+        return fail(KLAS_ERR_INVALID, "gemm_strided: unknown operand map (%d, %d)", map_a, map_b);
+    if (comb < KLAS_COMB_NEW || comb > KLAS_COMB_RELU) return fail(KLAS_ERR_INVALID, "gemm_strided: unknown combine rule %d", comb);
+    if (comb == KLAS_COMB_AXPBY && (!alpha || !beta))
+        return fail(KLAS_ERR_INVALID, "gemm_strided: the axpby rule needs alpha and beta");
+    if ((dtype == KLAS_U32 || dtype == KLAS_U64) && (map_a == KLAS_MAP_SQRT || map_b == KLAS_MAP_SQRT))
+        return fail(KLAS_ERR_UNSUPPORTED, "gemm_strided: sqrt is not defined on the wrapping integer types");
+    if (m == 0 || n == 0 || batch == 0) return KLAS_OK;
+    if (!C || (k > 0 && (!A || !B))) return fail(KLAS_ERR_INVALID, "gemm_strided: null matrix pointer");
+    if (lda < k || ldb < n || ldc < n) return fail(KLAS_ERR_INVALID, "gemm_strided: a row stride is shorter than the row");
+    if (batch > 1 && stride_c < (m - 1) * ldc + n)
+        return fail(KLAS_ERR_INVALID, "gemm_strided: pages of C overlap (stride_c too small)");
+    simt::Problem q{};
+    q.batch = batch;
+    q.m = m;
+    q.n = n;
+    q.k = k;
+    q.lda = lda;
+    q.ldb = ldb;
+    q.ldc = ldc;
+    q.sa = stride_a;
+    q.sb = stride_b;
+    q.sc = stride_c;
+    q.map_a = map_a;
+    q.map_b = map_b;
+    q.comb = comb;
+    q.hooks = map_a != KLAS_MAP_ID || map_b != KLAS_MAP_ID || (comb != KLAS_COMB_AXPBY && comb != KLAS_COMB_NEW);
+    const bool scaled = comb == KLAS_COMB_AXPBY;
+    return simt::dispatch(dtype, q, scaled ? alpha : nullptr, scaled ? beta : nullptr, A, B, C, stream);
 }
 
 }  // namespace klas

@@ -48,7 +48,10 @@ constexpr uint32_t ACC_STAGES = 2;
 constexpr uint32_t TMEM_COLS = ACC_STAGES * BN;  // 512 = all of tensor memory
 constexpr uint32_t NUM_THREADS = 192;
 constexpr uint32_t NUM_EPI_WARPS = 4;
-constexpr uint32_t XFORM_WARPS = 4;       // extra warps of the kernels that map A / B in shared memory
+#ifndef KLAS_XFORM_WARPS
+#define KLAS_XFORM_WARPS 4
+#endif
+constexpr uint32_t XFORM_WARPS = KLAS_XFORM_WARPS;   // extra warps of the kernels that map A / B in shared memory
 constexpr uint32_t XFORM_THREADS = XFORM_WARPS * 32;
 constexpr uint32_t XFULL_OFFSET = 192;    // byte offset of the "operands mapped" barriers in the barrier block
 constexpr uint32_t BARRIER_BYTES = 256;
@@ -207,7 +210,9 @@ template <uint32_t OP>
 __device__ __forceinline__ float map_f32(float x) {
     if constexpr (OP == KLAS_MAP_SQRT) {
         float r;
-        asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));   // <= 1 ulp of f32, before the 16-bit rounding
+        // <= 1 ulp of f32 before the 16-bit rounding; f32 subnormals (only bf16 inputs below
+        // 1.2e-38 convert to those) count as 0
+        asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
         return r;
     } else if constexpr (OP == KLAS_MAP_ABS) {
         return fabsf(x);
@@ -222,31 +227,55 @@ __device__ __forceinline__ float map_f32(float x) {
     }
 }
 
+// Two packed 16-bit elements at a time.  Sign manipulations are bit operations, max and the
+// (exactly representable in f32, hence once-rounded) square are native packed instructions;
+// only sqrt goes through f32 and the special-function unit.
 template <bool BF16, uint32_t OP>
 __device__ __forceinline__ uint32_t map_pair(uint32_t w) {
-    if constexpr (BF16) {
-        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w));
-        const __nv_bfloat162 r = __floats2bfloat162_rn(map_f32<OP>(f.x), map_f32<OP>(f.y));
+    if constexpr (OP == KLAS_MAP_ABS) {
+        return w & 0x7fff7fffu;
+    } else if constexpr (OP == KLAS_MAP_NEG) {
+        return w ^ 0x80008000u;
+    } else if constexpr (BF16) {
+        const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162 *>(&w);
+        __nv_bfloat162 r;
+        if constexpr (OP == KLAS_MAP_RELU) {
+            r = __hmax2(x, __floats2bfloat162_rn(0.0f, 0.0f));
+        } else if constexpr (OP == KLAS_MAP_SQUARE) {
+            r = __hmul2(x, x);
+        } else {
+            const float2 f = __bfloat1622float2(x);
+            r = __floats2bfloat162_rn(map_f32<OP>(f.x), map_f32<OP>(f.y));
+        }
         return *reinterpret_cast<const uint32_t *>(&r);
     } else {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
-        const __half2 r = __floats2half2_rn(map_f32<OP>(f.x), map_f32<OP>(f.y));
+        const __half2 x = *reinterpret_cast<const __half2 *>(&w);
+        __half2 r;
+        if constexpr (OP == KLAS_MAP_RELU) {
+            r = __hmax2(x, __floats2half2_rn(0.0f, 0.0f));
+        } else if constexpr (OP == KLAS_MAP_SQUARE) {
+            r = __hmul2(x, x);
+        } else {
+            const float2 f = __half22float2(x);
+            r = __floats2half2_rn(map_f32<OP>(f.x), map_f32<OP>(f.y));
+        }
         return *reinterpret_cast<const uint32_t *>(&r);
     }
 }
 
-// Maps `bytes` (a multiple of 4 * XFORM_THREADS * 16) of shared memory in place, 16 bytes per
-// thread per access, four accesses in flight.  The operand tiles are swizzled, which an
-// element-wise map does not care about.
+// One warp maps `bytes` (a multiple of 4 KiB) of shared memory in place, 16 bytes per lane per
+// access, eight accesses in flight.  The operand tiles are swizzled, which an element-wise map
+// does not care about.
 template <bool BF16, uint32_t OP>
-__device__ __forceinline__ void xform_region(uint32_t addr, uint32_t bytes, uint32_t tid) {
-    constexpr uint32_t STEP = XFORM_THREADS * 16;
-    for (uint32_t off = tid * 16; off < bytes; off += 4 * STEP) {
-        uint32_t w[4][4];
+__device__ __forceinline__ void xform_region(uint32_t addr, uint32_t bytes, uint32_t lane) {
+    constexpr uint32_t STEP = 32 * 16;
+    constexpr uint32_t DEPTH = 8;
+    for (uint32_t off = lane * 16; off < bytes; off += DEPTH * STEP) {
+        uint32_t w[DEPTH][4];
 #pragma unroll
-        for (uint32_t u = 0; u < 4; ++u) ptx::lds128(addr + off + u * STEP, w[u]);
+        for (uint32_t u = 0; u < DEPTH; ++u) ptx::lds128(addr + off + u * STEP, w[u]);
 #pragma unroll
-        for (uint32_t u = 0; u < 4; ++u) {
+        for (uint32_t u = 0; u < DEPTH; ++u) {
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) w[u][j] = map_pair<BF16, OP>(w[u][j]);
             ptx::sts128(addr + off + u * STEP, w[u]);
@@ -255,24 +284,29 @@ __device__ __forceinline__ void xform_region(uint32_t addr, uint32_t bytes, uint
 }
 
 template <bool BF16>
-__device__ __forceinline__ void xform_dispatch(uint32_t op, uint32_t addr, uint32_t bytes, uint32_t tid) {
+__device__ __forceinline__ void xform_dispatch(uint32_t op, uint32_t addr, uint32_t bytes, uint32_t lane) {
     switch (op) {
-        case KLAS_MAP_SQRT: xform_region<BF16, KLAS_MAP_SQRT>(addr, bytes, tid); break;
-        case KLAS_MAP_ABS: xform_region<BF16, KLAS_MAP_ABS>(addr, bytes, tid); break;
-        case KLAS_MAP_SQUARE: xform_region<BF16, KLAS_MAP_SQUARE>(addr, bytes, tid); break;
-        case KLAS_MAP_RELU: xform_region<BF16, KLAS_MAP_RELU>(addr, bytes, tid); break;
-        case KLAS_MAP_NEG: xform_region<BF16, KLAS_MAP_NEG>(addr, bytes, tid); break;
+        case KLAS_MAP_SQRT: xform_region<BF16, KLAS_MAP_SQRT>(addr, bytes, lane); break;
+        case KLAS_MAP_ABS: xform_region<BF16, KLAS_MAP_ABS>(addr, bytes, lane); break;
+        case KLAS_MAP_SQUARE: xform_region<BF16, KLAS_MAP_SQUARE>(addr, bytes, lane); break;
+        case KLAS_MAP_RELU: xform_region<BF16, KLAS_MAP_RELU>(addr, bytes, lane); break;
+        case KLAS_MAP_NEG: xform_region<BF16, KLAS_MAP_NEG>(addr, bytes, lane); break;
         default: break;
     }
 }
 
-// One ring stage of a mapping kernel: waits (bounded) until the stage's copies have landed,
-// maps the A and / or B bytes in place, makes the writes visible to the tensor core's reads and
-// counts this warp on `xfull_bar` (possibly a barrier of the pair's even CTA).
+// One ring stage of a mapping kernel, handled by ONE warp (the mapping warps take the stages in
+// turn, so that one stage's wait for its stores to drain overlaps the next stages' work): waits
+// (bounded) until the stage's copies have landed, maps the A and / or B bytes in place, makes the
+// writes visible to the tensor core's reads and arrives on `xfull_bar` (possibly a barrier of
+// the pair's even CTA).
 __device__ __forceinline__ bool xform_stage(const Params &p, uint32_t full_bar, uint32_t parity, const Ctl &ctl,
                                             int site, uint32_t a_addr, uint32_t a_bytes, uint32_t b_bytes,
-                                            uint32_t xfull_bar_cluster, uint32_t tid) {
-    const uint32_t lane = tid & 31u;
+                                            uint32_t xfull_bar_cluster, uint32_t lane,
+                                            [[maybe_unused]] unsigned long long *prof = nullptr) {
+#ifdef KLAS_UMMA_PROFILE
+    const long long prof_t0 = clock64();
+#endif
     bool ok = lane != 0 || bounded_wait(full_bar, parity, ctl, site, WAIT_LIMIT_NS, 32);
     ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
     if (!ok) return false;
@@ -280,16 +314,29 @@ __device__ __forceinline__ bool xform_stage(const Params &p, uint32_t full_bar, 
     // this warp's own arrival below), which orders the copies' writes before its reads.
     for (uint32_t i = 0; i < 1024 && !ptx::mbar_try_wait(full_bar, parity); ++i) {
     }
+#ifdef KLAS_UMMA_PROFILE
+    const long long prof_t1 = clock64();
+#endif
     if (p.in_bf16) {
-        xform_dispatch<true>(p.map_a, a_addr, a_bytes, tid);
-        xform_dispatch<true>(p.map_b, a_addr + a_bytes, b_bytes, tid);
+        xform_dispatch<true>(p.map_a, a_addr, a_bytes, lane);
+        xform_dispatch<true>(p.map_b, a_addr + a_bytes, b_bytes, lane);
     } else {
-        xform_dispatch<false>(p.map_a, a_addr, a_bytes, tid);
-        xform_dispatch<false>(p.map_b, a_addr + a_bytes, b_bytes, tid);
+        xform_dispatch<false>(p.map_a, a_addr, a_bytes, lane);
+        xform_dispatch<false>(p.map_b, a_addr + a_bytes, b_bytes, lane);
     }
+#ifdef KLAS_UMMA_PROFILE
+    const long long prof_t2 = clock64();
+#endif
     ptx::fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive_cluster(xfull_bar_cluster);
+#ifdef KLAS_UMMA_PROFILE
+    if (prof) {
+        prof[0] += (unsigned long long)(prof_t1 - prof_t0);
+        prof[1] += (unsigned long long)(prof_t2 - prof_t1);
+        prof[2] += (unsigned long long)(clock64() - prof_t2);
+    }
+#endif
     return true;
 }
 
@@ -392,7 +439,7 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
         for (uint32_t s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
-            if constexpr (XFORM) ptx::mbar_init(xfull_bar(s), XFORM_WARPS);
+            if constexpr (XFORM) ptx::mbar_init(xfull_bar(s), 1);
         }
         for (uint32_t a = 0; a < ACC_STAGES; ++a) {
             ptx::mbar_init(tfull_bar(a), 1);
@@ -561,14 +608,16 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
         KLAS_PROF_STORE(4, prof_mma3);
     } else if (XFORM && warp >= 2 + NUM_EPI_WARPS) {
         // ------------------------------------------------------------ operand maps
-        const uint32_t tid = threadIdx.x - (2 + NUM_EPI_WARPS) * 32;
-        uint32_t stage = 0, phase = 0;
+        const uint32_t xw = warp - (2 + NUM_EPI_WARPS);
+        uint32_t stage = 0, phase = 0, turn = 0;
         bool ok = true;
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-                ok = xform_stage(p, full_bar(stage), phase, ctl, SITE_XFORM_FULL, smem_base + stage * STAGE_BYTES,
-                                 A_STAGE_BYTES, S::B_STAGE_BYTES, xfull_bar(stage), tid);
+                if (turn == xw)
+                    ok = xform_stage(p, full_bar(stage), phase, ctl, SITE_XFORM_FULL, smem_base + stage * STAGE_BYTES,
+                                     A_STAGE_BYTES, S::B_STAGE_BYTES, xfull_bar(stage), lane);
                 if (!ok) break;
+                if (++turn == XFORM_WARPS) turn = 0;
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
@@ -690,9 +739,10 @@ constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BARRIER_BYTES
 
 enum : int { SITE_WIDE = 0x100 };
 
-// XFORM adds four warps per CTA that map the staged A / B bytes in place.  Each CTA then counts
-// its own copies on its own barrier, its mapping warps wait there, and all eight warps of the
-// pair report to a barrier of the even CTA that the MMA thread waits on.
+// XFORM adds four warps per CTA that map the staged A / B bytes in place, taking the ring's
+// stages in turn.  Each CTA then counts its own copies on its own barrier, the stage's mapping
+// warp waits there, and the two warps of the pair (one per CTA) report to a barrier of the even
+// CTA that the MMA thread waits on.
 template <typename OutT, bool XFORM = false>
 __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1)
     gemm_umma_wide_kernel(const __grid_constant__ CUtensorMap tm_a,
@@ -728,7 +778,7 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
         for (uint32_t s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
-            if constexpr (XFORM) ptx::mbar_init(xfull_bar(s), 2 * XFORM_WARPS);
+            if constexpr (XFORM) ptx::mbar_init(xfull_bar(s), 2);
         }
         ptx::mbar_init(tfull_bar, 1);
         ptx::mbar_init(tempty_bar, EPI_WARPS * 2);
@@ -864,21 +914,31 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
         __syncwarp();
     } else if (XFORM && warp >= 2 + EPI_WARPS) {
         // ------------------------------------------------------------ operand maps (4 warps per CTA)
-        const uint32_t tid = threadIdx.x - (2 + EPI_WARPS) * 32;
+        const uint32_t xw = warp - (2 + EPI_WARPS);
         const uint32_t xfull_cta0 = ptx::map_to_cta(xfull_bar(0), 0);
-        uint32_t stage = 0, phase = 0;
+        uint32_t stage = 0, phase = 0, turn = 0;
         bool ok = true;
+        unsigned long long xprof[3] = {0, 0, 0};
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-                ok = xform_stage(p, full_bar(stage), phase, ctl, SITE_WIDE | SITE_XFORM_FULL,
-                                 smem_base + stage * STAGE_BYTES, A_BYTES, B_BYTES, xfull_cta0 + 8u * stage, tid);
+                if (turn == xw)
+                    ok = xform_stage(p, full_bar(stage), phase, ctl, SITE_WIDE | SITE_XFORM_FULL,
+                                     smem_base + stage * STAGE_BYTES, A_BYTES, B_BYTES, xfull_cta0 + 8u * stage, lane, xprof);
                 if (!ok) break;
+                if (++turn == XFORM_WARPS) turn = 0;
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
                 }
             }
         }
+#ifdef KLAS_UMMA_PROFILE
+        if (xw == 0 && lane == 0 && blockIdx.x < 1024) {
+            g_umma_prof[blockIdx.x][3] = xprof[0];
+            g_umma_prof[blockIdx.x][4] = xprof[1];
+            g_umma_prof[blockIdx.x][6] = xprof[2];
+        }
+#endif
     } else {
         // ------------------------------------------------------------ epilogue (8 warps)
         // Warps 2-5 drain accumulator half 0, warps 6-9 half 1; within a group warp w owns the
@@ -1156,6 +1216,11 @@ static int launch_wide_mode(int out_dtype, const CUtensorMap &ta, const CUtensor
 }  // namespace umma
 
 #ifdef KLAS_UMMA_PROFILE
+extern "C" int klas_dev_zero_umma_profile() {
+    void *ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, umma::g_umma_prof) != cudaSuccess) return 1;
+    return cudaMemset(ptr, 0, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? 0 : 1;
+}
 extern "C" int klas_dev_read_umma_profile(unsigned long long *out) {
     return cudaMemcpyFromSymbol(out, umma::g_umma_prof, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? 0 : 1;
 }

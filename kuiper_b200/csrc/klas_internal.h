@@ -55,6 +55,11 @@ int launch_gemm_simt(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t
                      const void *alpha, const void *beta, const void *A, const void *B, void *C,
                      cudaStream_t stream);
 
+int launch_gemm_simt_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, uint64_t k, const void *alpha,
+                             const void *beta, const void *A, uint64_t lda, uint64_t stride_a, const void *B,
+                             uint64_t ldb, uint64_t stride_b, void *C, uint64_t ldc, uint64_t stride_c, int map_a,
+                             int map_b, int comb, cudaStream_t stream);
+
 int launch_gemm_umma(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
                      uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
                      void *D, float alpha, float beta, int *status_word, cudaStream_t stream);

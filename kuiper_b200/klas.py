@@ -119,6 +119,45 @@ def gemm(A: torch.Tensor, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
     return C_
 
 
+def gemm_strided(A: torch.Tensor, B: torch.Tensor, C_: torch.Tensor, *, alpha=None, beta=None,
+                 map_a: Optional[str] = None, map_b: Optional[str] = None, comb: Optional[str] = None) -> torch.Tensor:
+    """General batched CUDA-core GEMM on tensor VIEWS: A [batch, m, k], B [batch, k, n], C_ [batch, m, n]
+    (or 2-D for one page) whose last dimension is contiguous; row and page strides are taken from the
+    views, and an expanded (stride-0) batch dimension of A or B shares one matrix between the pages.
+    C_ = comb(C_, map_a(A) . map_b(B)) in place; default comb: "axpby" when alpha/beta are given, else "new"."""
+    code = _code(A)
+    if B.dtype != A.dtype or C_.dtype != A.dtype:
+        raise TypeError("A, B and C dtypes differ")
+    if A.dim() == 2:
+        A, B, C_ = A[None], B[None], C_[None]
+    batch, m, k = A.shape
+    if tuple(B.shape) != (batch, k, B.shape[2]) or tuple(C_.shape) != (batch, m, B.shape[2]):
+        raise ValueError("shapes do not match: %s %s %s" % (tuple(A.shape), tuple(B.shape), tuple(C_.shape)))
+    n = B.shape[2]
+    for t, name in ((A, "A"), (B, "B"), (C_, "C")):
+        if not t.is_cuda:
+            raise ValueError("%s must be a CUDA tensor" % name)
+        if t.shape[2] > 1 and t.stride(2) != 1:
+            raise ValueError("%s: the last dimension must be contiguous" % name)
+    if (alpha is None) != (beta is None):
+        raise ValueError("give both alpha and beta or neither")
+    try:
+        ma, mb = _MAPS[map_a], _MAPS[map_b]
+        cb = _COMBS[comb] if comb is not None else (_lib.COMB_AXPBY if alpha is not None else _lib.COMB_NEW)
+    except KeyError as e:
+        raise ValueError("unknown map or combine rule %s" % e) from None
+    pa = pb = None
+    if alpha is not None:
+        sa_, sb_ = _scalar(code, alpha), _scalar(code, beta)
+        pa, pb = C.addressof(sa_), C.addressof(sb_)
+    with torch.cuda.device(A.device):
+        check(_lib.load().klas_b200_gemm_strided(
+            code, batch, m, n, k, pa, pb, A.data_ptr(), A.stride(1), A.stride(0) if batch > 1 else 0,
+            B.data_ptr(), B.stride(1), B.stride(0) if batch > 1 else 0,
+            C_.data_ptr(), C_.stride(1), C_.stride(0) if batch > 1 else 0, ma, mb, cb, _stream()))
+    return C_
+
+
 _MAPS = {None: _lib.MAP_ID, "id": _lib.MAP_ID, "sqrt": _lib.MAP_SQRT, "abs": _lib.MAP_ABS,
          "square": _lib.MAP_SQUARE, "relu": _lib.MAP_RELU, "neg": _lib.MAP_NEG}
 _COMBS = {"new": _lib.COMB_NEW, "axpby": _lib.COMB_AXPBY, "max": _lib.COMB_MAX, "min": _lib.COMB_MIN,
@@ -265,6 +304,7 @@ _RE_SOFTMAX = re.compile(r"^Klas_(Softmax_softmax|LogSoftmax_log_softmax)_(gpu_)
 _RE_ROWSOFTMAX = re.compile(r"^Klas_RowSoftmax_row_softmax_rm_(f32|f64)$")
 _RE_ROWSCALE = re.compile(r"^Klas_RowScale_rowscale_(f16|f32|f64)_(rowmajor|colmajor)$")
 _RE_REDUCE = re.compile(r"^Klas_(?:HReduce_reduce_(f16|f32|f64|u32|u64)_plus|AtomicReduce_reduce_(u32|u64|f32|f64))$")
+_RE_FUSED = re.compile(r"^Kuiper_Example_Fused_GEMM_gemm_sqrt_fused$")
 _RE_SPMM = re.compile(r"^Klas_SPMM_(?:spmm_(f32|u32)|g_spmm_f32_(\d+)x(\d+)x(\d+))$")
 
 
@@ -422,4 +462,11 @@ def call(name: str, *args):
         count = args[-2]
         t = _TORCH_OF[m_.group(1) or m_.group(2)]
         return reduce_sum(_view(a, t, count)).item()
+    if _RE_FUSED.match(name):
+        m, n, k, A, B, Cc = args
+        if n % 8 or k % 8:
+            raise KlasGuardError("%s: n and k must be multiples of 8" % name)
+        t = torch.float16
+        gemm_tc(_view(A, t, m, k), _view(B, t, k, n), out_dtype=t, D=_view(Cc, t, m, n), map_a="sqrt")
+        return None
     raise KeyError("unknown Klas entry point: %s" % name)

@@ -31,6 +31,7 @@ REF_GPU_UNITS = [
     "Klas_GEMM_Naive1", "Klas_GEMM_Naive2", "Klas_GEMM_Naive3", "Klas_GEMM_TensorCore",
     "Klas_GEMM_TensorCore2D", "Klas_GEMM_TensorCore2D_To", "Klas_SPMM",
     "Klas_Softmax", "Klas_LogSoftmax", "Klas_RowSoftmax", "Klas_RowScale", "Klas_HReduce", "Klas_AtomicReduce",
+    "Kuiper_Example_Fused_GEMM",
 ]
 
 
@@ -68,7 +69,7 @@ def build_ref_cpu(ref_root: Path, force: bool = False) -> Path:
 
 
 def build_ref_gpu(ref_root: Path, force: bool = False) -> Path:
-    """The reference's extracted kernels (dist/Klas_*.cu) for sm_100a, one shared library,
+    """The reference's extracted kernels (dist/Klas_*.cu and the fused-map demo) for sm_100a, one shared library,
     plus symbols.json mapping each entry-point name to its mangled symbol."""
     out = REF_DIR / "libklas_ref_gpu.so"
     if not force and out.exists() and (REF_DIR / "symbols.json").exists() and \
@@ -91,7 +92,7 @@ def build_ref_gpu(ref_root: Path, force: bool = False) -> Path:
     names = {}
     for line in _run(["nm", "-D", "--defined-only", out]).splitlines():
         parts = line.split()
-        if len(parts) == 3 and parts[1] == "T" and "Klas_" in parts[2]:
+        if len(parts) == 3 and parts[1] == "T" and ("Klas_" in parts[2] or "Kuiper_Example_Fused_GEMM" in parts[2]):
             demangled = _run(["c++filt", parts[2]]).strip()
             names[demangled.split("(")[0]] = parts[2]
     (REF_DIR / "symbols.json").write_text(json.dumps(names, indent=0, sort_keys=True))

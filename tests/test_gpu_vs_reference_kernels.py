@@ -67,6 +67,25 @@ def test_f32_1024(ref):
         "flop": 2 * n ** 3}
 
 
+def test_fused_sqrt_gemm_against_the_reference_demo(ref):
+    """Kuiper_Example_Fused_GEMM_gemm_sqrt_fused: the reference's one-thread-per-element kernel vs
+    the tensor-core GEMM with sqrt applied to the staged A tiles (f16 in and out)."""
+    n = 2048
+    A, B = synth.gemm_f16_batched(21, 1, n, n, n, device="cuda")
+    A, B = A[0].abs(), B[0]
+    mine = torch.zeros((n, n), dtype=torch.float16, device="cuda")
+    theirs = torch.zeros_like(mine)
+    klas.call("Kuiper_Example_Fused_GEMM_gemm_sqrt_fused", n, n, n, A, B, mine)
+    ref.mnk("Kuiper_Example_Fused_GEMM_gemm_sqrt_fused", n, n, n, A, B, theirs)
+    scale = A.double().sqrt() @ B.double().abs()
+    # theirs multiplies the unrounded f32 sqrt, mine rounds it to f16 first; both round the result
+    assert float(((mine.double() - theirs.double()).abs() / scale).max()) <= 2 ** -9
+    TIMINGS["fused_sqrt_f16_2048"] = {
+        "ours_kernel_ms": event_ms(lambda: klas.gemm_tc(A, B, out_dtype=torch.float16, D=mine, map_a="sqrt")),
+        "ref_call_ms": wall_ms(lambda: ref.mnk("Kuiper_Example_Fused_GEMM_gemm_sqrt_fused", n, n, n, A, B, theirs)),
+        "flop": 2 * n ** 3}
+
+
 def test_u64_bit_exact(ref):
     n = 1024
     a, b = synth.gemm_u64(3, n, n, n, full_range=True, device="cuda")
