@@ -219,6 +219,42 @@ int klas_b200_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uin
                    const uint32_t *row_indices, const void *B, void *C, void *stream);
 
 /*
+ * Building the CSR operand of klas_b200_spmm on the device, from a dense row-major rows x cols
+ * matrix (dtype KLAS_F32 or KLAS_U32).  An entry is kept when it compares != 0 (so -0.0 is
+ * dropped and NaN kept), in ascending column order within a row.
+ *
+ *   klas_b200_csr_count      writes row_off[0 .. rows]; row_off[rows] is nnz (read it back to
+ *                            size elems / col_ind).  nnz must stay below 2^32.
+ *   klas_b200_csr_fill       writes elems[nnz], col_ind[nnz] for the row_off of the count step.
+ *   klas_b200_csr_row_order  row_indices[rows] = the rows by decreasing length, equal lengths by
+ *                            increasing row: the schedule klas_b200_spmm takes as `row_indices`.
+ *                            Needs klas_b200_csr_row_order_scratch_bytes(rows) bytes of 8-byte
+ *                            aligned device scratch (sort keys), caller-owned.
+ *
+ * Replaces: the host-side preparation every reference SpMM caller runs first, sparsify_f32 /
+ * sparsify_u32 (test/spmm_common.c.inc:73-137) and mk_row_indices (test/spmm_common.c.inc:139-157;
+ * its std::sort leaves the order of equal-length rows open, here it is fixed).
+ */
+int klas_b200_csr_count(int dtype, uint32_t rows, uint32_t cols, const void *dense, uint32_t *row_off, void *stream);
+int klas_b200_csr_fill(int dtype, uint32_t rows, uint32_t cols, const void *dense, const uint32_t *row_off,
+                       void *elems, uint32_t *col_ind, void *stream);
+size_t klas_b200_csr_row_order_scratch_bytes(uint32_t rows);
+int klas_b200_csr_row_order(uint32_t rows, const uint32_t *row_off, uint32_t *row_indices, void *scratch,
+                            size_t scratch_bytes, void *stream);
+
+/*
+ * (min, +) product on 16-bit path lengths with 0 = "no path":
+ *   C[i][j] = add(C[i][j], add over k of mult(A[i][k], B[k][j])),
+ *   mult(x, y) = 0 if x == 0 or y == 0 else (x + y) mod 2^16,  add = the smaller non-zero one.
+ * A m x k, B k x n, C m x n, row-major device arrays; C must not overlap A or B.  Squaring a
+ * distance matrix is A == B.  Bit-exact with the reference on every input, wrap-around included.
+ * Replaces: Kuiper_GraphDist_matmul_dist_gpu (dist/Kuiper_GraphDist.h:11-12, kernel
+ * dist/Kuiper_GraphDist.cu:9-45), which is the square case m = n = k, A = B.
+ */
+int klas_b200_minplus_u16(uint32_t m, uint32_t n, uint32_t k, const uint16_t *A, const uint16_t *B, uint16_t *C,
+                          void *stream);
+
+/*
  * Host-buffer variants: same semantics, but every data pointer is a HOST
  * pointer (pinned memory makes the copies asynchronous and faster).  The call
  * stages inputs into a per-device workspace that grows on demand and is kept

@@ -174,6 +174,31 @@ int klas_b200_gemm_tc_fused(int in_dtype, int out_dtype, int b_major, uint32_t b
                                   map_a, map_b, comb, status_word, static_cast<cudaStream_t>(stream));
 }
 
+int klas_b200_csr_count(int dtype, uint32_t rows, uint32_t cols, const void *dense, uint32_t *row_off, void *stream) {
+    clear_error();
+    return launch_csr_count(dtype, rows, cols, dense, row_off, static_cast<cudaStream_t>(stream));
+}
+
+int klas_b200_csr_fill(int dtype, uint32_t rows, uint32_t cols, const void *dense, const uint32_t *row_off,
+                       void *elems, uint32_t *col_ind, void *stream) {
+    clear_error();
+    return launch_csr_fill(dtype, rows, cols, dense, row_off, elems, col_ind, static_cast<cudaStream_t>(stream));
+}
+
+size_t klas_b200_csr_row_order_scratch_bytes(uint32_t rows) { return csr_row_order_scratch_bytes(rows); }
+
+int klas_b200_csr_row_order(uint32_t rows, const uint32_t *row_off, uint32_t *row_indices, void *scratch,
+                            size_t scratch_bytes, void *stream) {
+    clear_error();
+    return launch_csr_row_order(rows, row_off, row_indices, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int klas_b200_minplus_u16(uint32_t m, uint32_t n, uint32_t k, const uint16_t *A, const uint16_t *B, uint16_t *C,
+                          void *stream) {
+    clear_error();
+    return launch_minplus_u16(m, n, k, A, B, C, static_cast<cudaStream_t>(stream));
+}
+
 int klas_b200_gemm_tc_status(int *site) {
     clear_error();
     int v = 0;

@@ -73,6 +73,16 @@ int launch_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32
                 const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
                 const uint32_t *row_indices, const void *B, void *C, cudaStream_t stream);
 
+int launch_minplus_u16(uint32_t m, uint32_t n, uint32_t k, const uint16_t *A, const uint16_t *B, uint16_t *C,
+                       cudaStream_t stream);
+
+int launch_csr_count(int dtype, uint32_t rows, uint32_t cols, const void *dense, uint32_t *row_off, cudaStream_t stream);
+int launch_csr_fill(int dtype, uint32_t rows, uint32_t cols, const void *dense, const uint32_t *row_off, void *elems,
+                    uint32_t *col_ind, cudaStream_t stream);
+size_t csr_row_order_scratch_bytes(uint32_t rows);
+int launch_csr_row_order(uint32_t rows, const uint32_t *row_off, uint32_t *row_indices, void *scratch,
+                         size_t scratch_bytes, cudaStream_t stream);
+
 size_t softmax_scratch_bytes(uint64_t rows, uint64_t cols);
 size_t reduce_scratch_bytes(uint64_t n);
 int launch_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a, void *scratch,

@@ -119,6 +119,44 @@ def gemm(A: torch.Tensor, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
     return C_
 
 
+def csr_from_dense(M: torch.Tensor) -> Csr:
+    """CSR form (values != 0 in column order, offsets, longest-first row order) of a dense 2-D f32 or
+    32-bit integer CUDA tensor, built on the device.  One 4-byte read-back (nnz) sizes the arrays."""
+    code = _code(M)
+    if code not in (_lib.F32, _lib.U32) or M.dim() != 2:
+        raise TypeError("csr_from_dense needs a 2-D f32 or 32-bit integer tensor")
+    rows, cols = M.shape
+    lib = _lib.load()
+    dense = _dev(M, "M")
+    with torch.cuda.device(M.device):
+        row_off = torch.empty(rows + 1, dtype=torch.int32, device=M.device)
+        check(lib.klas_b200_csr_count(code, rows, cols, dense, row_off.data_ptr(), _stream()))
+        nnz = int(row_off[-1].item()) & 0xFFFFFFFF
+        elems = torch.empty(nnz, dtype=M.dtype, device=M.device)
+        col_ind = torch.empty(nnz, dtype=torch.int32, device=M.device)
+        check(lib.klas_b200_csr_fill(code, rows, cols, dense, row_off.data_ptr(), elems.data_ptr() if nnz else None,
+                                     col_ind.data_ptr() if nnz else None, _stream()))
+        row_indices = torch.empty(rows, dtype=torch.int32, device=M.device)
+        need = lib.klas_b200_csr_row_order_scratch_bytes(rows)
+        scratch = torch.empty(max(need, 8), dtype=torch.uint8, device=M.device)
+        check(lib.klas_b200_csr_row_order(rows, row_off.data_ptr(), row_indices.data_ptr(), scratch.data_ptr(), need, _stream()))
+    return Csr(rows, cols, elems, col_ind, row_off, row_indices)
+
+
+def minplus_u16(A: torch.Tensor, B: torch.Tensor, C_: torch.Tensor) -> torch.Tensor:
+    """In place C_ = min(C_, A (min,+) B) on 16-bit path lengths held in int16 / uint16 tensors, 0 = no path."""
+    ok = (torch.int16,) + ((torch.uint16,) if hasattr(torch, "uint16") else ())
+    if A.dtype not in ok or B.dtype != A.dtype or C_.dtype != A.dtype:
+        raise TypeError("minplus_u16 needs three 16-bit integer tensors of one dtype")
+    m, k = A.shape
+    k2, n = B.shape
+    if k2 != k or tuple(C_.shape) != (m, n):
+        raise ValueError("shapes do not match")
+    with torch.cuda.device(A.device):
+        check(_lib.load().klas_b200_minplus_u16(m, n, k, _dev(A, "A"), _dev(B, "B"), _dev(C_, "C"), _stream()))
+    return C_
+
+
 def gemm_strided(A: torch.Tensor, B: torch.Tensor, C_: torch.Tensor, *, alpha=None, beta=None,
                  map_a: Optional[str] = None, map_b: Optional[str] = None, comb: Optional[str] = None) -> torch.Tensor:
     """General batched CUDA-core GEMM on tensor VIEWS: A [batch, m, k], B [batch, k, n], C_ [batch, m, n]
@@ -304,6 +342,7 @@ _RE_SOFTMAX = re.compile(r"^Klas_(Softmax_softmax|LogSoftmax_log_softmax)_(gpu_)
 _RE_ROWSOFTMAX = re.compile(r"^Klas_RowSoftmax_row_softmax_rm_(f32|f64)$")
 _RE_ROWSCALE = re.compile(r"^Klas_RowScale_rowscale_(f16|f32|f64)_(rowmajor|colmajor)$")
 _RE_REDUCE = re.compile(r"^Klas_(?:HReduce_reduce_(f16|f32|f64|u32|u64)_plus|AtomicReduce_reduce_(u32|u64|f32|f64))$")
+_RE_GRAPHDIST = re.compile(r"^Kuiper_GraphDist_(matmul_dist_gpu|uu___is_D)$")
 _RE_FUSED = re.compile(r"^Kuiper_Example_Fused_GEMM_gemm_sqrt_fused$")
 _RE_SPMM = re.compile(r"^Klas_SPMM_(?:spmm_(f32|u32)|g_spmm_f32_(\d+)x(\d+)x(\d+))$")
 
@@ -462,6 +501,13 @@ def call(name: str, *args):
         count = args[-2]
         t = _TORCH_OF[m_.group(1) or m_.group(2)]
         return reduce_sum(_view(a, t, count)).item()
+    if name == "Kuiper_GraphDist_uu___is_D":
+        return True
+    if name == "Kuiper_GraphDist_matmul_dist_gpu":
+        size, a, b = args
+        minplus_u16(a.view(-1)[:size * size].view(size, size), a.view(-1)[:size * size].view(size, size),
+                    b.view(-1)[:size * size].view(size, size))
+        return None
     if _RE_FUSED.match(name):
         m, n, k, A, B, Cc = args
         if n % 8 or k % 8:

@@ -31,7 +31,7 @@ REF_GPU_UNITS = [
     "Klas_GEMM_Naive1", "Klas_GEMM_Naive2", "Klas_GEMM_Naive3", "Klas_GEMM_TensorCore",
     "Klas_GEMM_TensorCore2D", "Klas_GEMM_TensorCore2D_To", "Klas_SPMM",
     "Klas_Softmax", "Klas_LogSoftmax", "Klas_RowSoftmax", "Klas_RowScale", "Klas_HReduce", "Klas_AtomicReduce",
-    "Kuiper_Example_Fused_GEMM",
+    "Kuiper_Example_Fused_GEMM", "Kuiper_GraphDist",
 ]
 
 
@@ -59,12 +59,13 @@ def build_ref_cpu(ref_root: Path, force: bool = False) -> Path:
     out = REF_DIR / "libklas_ref_cpu.so"
     wrap = ORACLE_DIR / "ref_wrap" / "ref_cpu.cu"
     wrap2 = ORACLE_DIR / "ref_wrap" / "ref_softmax.cu"
-    if not force and _newer(out, wrap, wrap2):
+    wrap3 = ORACLE_DIR / "ref_wrap" / "ref_csr.cu"
+    if not force and _newer(out, wrap, wrap2, wrap3):
         return out
     REF_DIR.mkdir(exist_ok=True)
     _run(["nvcc", "-O3", "-std=c++17", *ARCH, "-Xcompiler", "-fPIC", "-shared",
           "-I", ref_root / "include", "-I", ref_root / "test", "-I", ref_root / "dist",
-          "-o", out, wrap, wrap2, ref_root / "dist" / "Kuiper_Example_Sparse_MM.cu"])
+          "-o", out, wrap, wrap2, wrap3, ref_root / "dist" / "Kuiper_Example_Sparse_MM.cu"])
     return out
 
 
@@ -92,14 +93,14 @@ def build_ref_gpu(ref_root: Path, force: bool = False) -> Path:
     names = {}
     for line in _run(["nm", "-D", "--defined-only", out]).splitlines():
         parts = line.split()
-        if len(parts) == 3 and parts[1] == "T" and ("Klas_" in parts[2] or "Kuiper_Example_Fused_GEMM" in parts[2]):
+        if len(parts) == 3 and parts[1] == "T" and any(t in parts[2] for t in ("Klas_", "Kuiper_Example_Fused_GEMM", "Kuiper_GraphDist")):
             demangled = _run(["c++filt", parts[2]]).strip()
             names[demangled.split("(")[0]] = parts[2]
     (REF_DIR / "symbols.json").write_text(json.dumps(names, indent=0, sort_keys=True))
     return out
 
 
-HOT_PATH_DRIVER_GLOBS = ("Test_Klas_GEMM_*.cu", "Test_Klas_SPMM__*.cu", "Test_Klas_Softmax__*.cu",
+HOT_PATH_DRIVER_GLOBS = ("Test_Kuiper_GraphDist.cu", "Test_Klas_GEMM_*.cu", "Test_Klas_SPMM__*.cu", "Test_Klas_Softmax__*.cu",
                          "Test_Klas_LogSoftmax__*.cu", "Test_Klas_HReduce__*.cu", "Test_Klas_AtomicReduce__*.cu")
 
 

@@ -389,6 +389,55 @@ void klas_oracle_map16(const uint16_t *in, uint16_t *out, size_t n, int bf16, in
     }
 }
 
+/* The (min,+) ring on 16-bit path lengths, 0 = no path, and the squaring step built on it:
+ * dist/Kuiper_GraphDist.cu:9-24 (add_, mult) and :26-45 (b[i][j] = add_(b[i][j], sum_k ...)),
+ * generalised to C = add(C, A (x) B) with A m x k, B k x n. */
+static uint16_t dist_add(uint16_t x, uint16_t y) { return (x == 0 || (y != 0 && y < x)) ? y : x; }
+static uint16_t dist_mult(uint16_t x, uint16_t y) { return (x == 0 || y == 0) ? 0 : (uint16_t)((uint32_t)x + (uint32_t)y); }
+
+void klas_oracle_minplus_u16(size_t m, size_t n, size_t k, const uint16_t *A, const uint16_t *B, uint16_t *C)
+{
+#pragma omp parallel for
+    for (size_t i = 0; i < m; ++i)
+        for (size_t j = 0; j < n; ++j) {
+            uint16_t sum = 0;
+            for (size_t kk = 0; kk < k; ++kk) sum = dist_add(sum, dist_mult(A[i * k + kk], B[kk * n + j]));
+            C[i * n + j] = dist_add(C[i * n + j], sum);
+        }
+}
+
+/* Dense -> CSR as the drivers build it on the host (test/spmm_common.c.inc:107-137): entries != 0
+ * in row-major scan order.  `as_float` selects the float comparison (-0.0 == 0, NaN != 0) on the
+ * same 32-bit words.  elems / col_ind may be NULL to count only; returns nnz. */
+uint32_t klas_oracle_sparsify32(const uint32_t *M, size_t rows, size_t cols, int as_float, uint32_t *row_off,
+                                uint32_t *elems, uint32_t *col_ind)
+{
+    uint32_t idx = 0;
+    row_off[0] = 0;
+    for (size_t i = 0; i < rows; ++i) {
+        for (size_t j = 0; j < cols; ++j) {
+            const uint32_t w = M[i * cols + j];
+            int nz;
+            if (as_float) {
+                float f;
+                memcpy(&f, &w, 4);
+                nz = f != 0.0f;
+            } else {
+                nz = w != 0;
+            }
+            if (nz) {
+                if (elems) {
+                    elems[idx] = w;
+                    col_ind[idx] = (uint32_t)j;
+                }
+                idx++;
+            }
+        }
+        row_off[i + 1] = idx;
+    }
+    return idx;
+}
+
 int klas_oracle_max_threads(void)
 {
 #ifdef _OPENMP

@@ -65,6 +65,41 @@ class Oracle:
             self.lib.klas_oracle_softmax_f64(rows[r].ctypes.data, o2[r].ctypes.data, rows.shape[1], int(log))
         return out
 
+    def minplus_u16(self, A: np.ndarray, B: np.ndarray, C: np.ndarray) -> np.ndarray:
+        """C' = add(C, A (min,+) B) on uint16 path lengths with 0 = no path; returns a new array."""
+        A, B = np.ascontiguousarray(A, dtype=np.uint16), np.ascontiguousarray(B, dtype=np.uint16)
+        out = np.array(C, dtype=np.uint16, order="C", copy=True)
+        m, k = A.shape
+        k2, n = B.shape
+        assert k == k2 and out.shape == (m, n)
+        self.lib.klas_oracle_minplus_u16.argtypes = [_sz, _sz, _sz, _vp, _vp, _vp]
+        self.lib.klas_oracle_minplus_u16(m, n, k, _p(A), _p(B), _p(out))
+        return out
+
+    def sparsify(self, M: np.ndarray):
+        """(row_off, elems, col_ind) of a dense float32 / uint32 matrix, entries != 0 in scan order."""
+        M = np.ascontiguousarray(M)
+        assert M.dtype in (np.float32, np.uint32) and M.ndim == 2
+        rows, cols = M.shape
+        words = M.view(np.uint32)
+        row_off = np.empty(rows + 1, dtype=np.uint32)
+        fn = self.lib.klas_oracle_sparsify32
+        fn.argtypes = [_vp, _sz, _sz, _int, _vp, _vp, _vp]
+        fn.restype = C.c_uint32
+        nnz = fn(_p(words), rows, cols, int(M.dtype == np.float32), _p(row_off), None, None)
+        elems = np.empty(nnz, dtype=np.uint32)
+        col_ind = np.empty(nnz, dtype=np.uint32)
+        if nnz:
+            fn(_p(words), rows, cols, int(M.dtype == np.float32), _p(row_off), _p(elems), _p(col_ind))
+        return row_off, elems.view(M.dtype), col_ind
+
+    @staticmethod
+    def row_order(row_off: np.ndarray) -> np.ndarray:
+        """Rows by decreasing length, equal lengths by increasing row (a stable sort; the drivers'
+        std::sort, test/spmm_common.c.inc:139-157, leaves ties open)."""
+        lens = np.diff(row_off.astype(np.int64))
+        return np.argsort(-lens, kind="stable").astype(np.uint32)
+
     def map16(self, bits: np.ndarray, kind: str, op: int) -> np.ndarray:
         """Element-wise operand map (0 id, 1 sqrt, 2 abs, 3 square, 4 relu, 5 neg) on bf16 / f16 bit
         patterns: evaluated in float, rounded once back to the 16-bit type."""
@@ -234,6 +269,26 @@ class RefCpu:
         fn = self.lib.ref_cpu_logsoftmax if log else self.lib.ref_cpu_softmax
         fn.argtypes = [_vp, _vp, _int]
         fn(_p(x), _p(out), x.size)
+        return out
+
+    def sparsify(self, M: np.ndarray):
+        """The drivers' sparsify_f32 / sparsify_u32: (row_off, elems, col_ind)."""
+        M = np.ascontiguousarray(M)
+        rows, cols = M.shape
+        fn = self.lib.ref_sparsify_f32 if M.dtype == np.float32 else self.lib.ref_sparsify_u32
+        fn.argtypes = [_vp, _int, _int, _vp, _vp, _vp]
+        fn.restype = C.c_uint32
+        row_off = np.empty(rows + 1, dtype=np.uint32)
+        nnz = fn(_p(M), rows, cols, _p(row_off), None, None)
+        elems, col_ind = np.empty(nnz, dtype=M.dtype), np.empty(nnz, dtype=np.uint32)
+        fn(_p(M), rows, cols, _p(row_off), _p(elems) if nnz else None, _p(col_ind) if nnz else None)
+        return row_off, elems, col_ind
+
+    def mk_row_indices(self, row_off: np.ndarray) -> np.ndarray:
+        row_off = np.ascontiguousarray(row_off, dtype=np.uint32)
+        out = np.empty(row_off.size - 1, dtype=np.uint32)
+        self.lib.ref_mk_row_indices.argtypes = [_int, _vp, _vp]
+        self.lib.ref_mk_row_indices(out.size, _p(row_off), _p(out))
         return out
 
     def mmsd_u32_rr(self, rows, shared, cols, elems, col_ind, row_off, B) -> np.ndarray:

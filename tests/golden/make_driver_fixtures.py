@@ -15,7 +15,7 @@ REPO = HERE.parent.parent
 ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
 
 expected = {}
-for pat in ("Test_Klas_GEMM_*.output.expected", "Test_Klas_SPMM__*.output.expected",
+for pat in ("Test_Kuiper_GraphDist.output.expected", "Test_Klas_GEMM_*.output.expected", "Test_Klas_SPMM__*.output.expected",
             "Test_Klas_Softmax__*.output.expected", "Test_Klas_LogSoftmax__*.output.expected",
             "Test_Klas_HReduce__*.output.expected", "Test_Klas_AtomicReduce__*.output.expected"):
     for f in sorted((ref_root / "test").glob(pat)):

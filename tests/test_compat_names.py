@@ -23,7 +23,7 @@ def exported(path):
 
 def test_every_reference_symbol_is_exported(compat):
     want = set((GOLD / "klas_symbols.txt").read_text().split())
-    assert len(want) == 596
+    assert len(want) == 598
     got = set()
     for obj in sorted(compat.COMPAT_OUT.glob("K*.o")):
         got |= exported(obj)
@@ -37,7 +37,7 @@ def test_one_object_per_reference_header(compat):
                      "Klas_GEMM_Naive1", "Klas_GEMM_Naive2", "Klas_GEMM_Naive3", "Klas_GEMM_TensorCore",
                      "Klas_GEMM_TensorCore2D", "Klas_GEMM_TensorCore2D_To", "Klas_SPMM", "Klas_Softmax",
                      "Klas_LogSoftmax", "Klas_RowSoftmax", "Klas_RowScale", "Klas_HReduce", "Klas_AtomicReduce",
-                     "Kuiper_Example_Fused_GEMM"}
+                     "Kuiper_Example_Fused_GEMM", "Kuiper_GraphDist"}
     for u in units:
         assert (REPO / "include" / "klas" / (u + ".h")).exists()
 
@@ -59,9 +59,9 @@ def test_python_mirror_knows_every_reference_name():
     from kuiper_b200 import klas
     names = [n.split("(")[0] for n in subprocess.run(["c++filt"], input=(GOLD / "klas_symbols.txt").read_text(),
                                                       capture_output=True, text=True, check=True).stdout.split("\n") if n]
-    assert len(names) == 596
+    assert len(names) == 598
     pats = [klas._RE_TILED, klas._RE_BT2D, klas._RE_NAIVE, klas._RE_NAIVE_B, klas._RE_TC2D, klas._RE_TC2D_TO,
-            klas._RE_TC1D, klas._RE_SPMM, klas._RE_SOFTMAX, klas._RE_ROWSOFTMAX, klas._RE_ROWSCALE, klas._RE_REDUCE, klas._RE_FUSED]
+            klas._RE_TC1D, klas._RE_SPMM, klas._RE_SOFTMAX, klas._RE_ROWSOFTMAX, klas._RE_ROWSCALE, klas._RE_REDUCE, klas._RE_FUSED, klas._RE_GRAPHDIST]
     for n in names:
         assert any(p.match(n) for p in pats), n
 

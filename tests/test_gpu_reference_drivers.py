@@ -26,7 +26,7 @@ def test_driver_prints_its_expected_output(name):
 
 
 def test_all_hot_path_drivers_are_covered():
-    assert len(EXPECTED) == 50   # 37 GEMM + 2 SpMM + 6 softmax / log-softmax + 5 reductions
+    assert len(EXPECTED) == 51   # 37 GEMM + 2 SpMM + 6 softmax / log-softmax + 5 reductions + graph distances
     if DRIVERS.exists():
         built = {p.stem for p in DRIVERS.glob("*.exe")}
         assert built == set(EXPECTED)

@@ -86,6 +86,26 @@ def test_fused_sqrt_gemm_against_the_reference_demo(ref):
         "flop": 2 * n ** 3}
 
 
+@pytest.mark.parametrize("top", [200, 65535])
+def test_graph_distance_step_bit_exact(ref, top):
+    """Kuiper_GraphDist_matmul_dist_gpu on random weights (top = 65535: sums wrap at 2^16 as in the reference)."""
+    n = 1026
+    u = synth.unit_uniform(31, 44, 0, n * n).reshape(n, n)
+    v = synth.integers_below_2_32(31, 45, 0, n * n).reshape(n, n) % top + 1
+    a = torch.where(u < 0.05, v, torch.zeros_like(v)).to(torch.int16).cuda()
+    mine, theirs = a.clone(), a.clone()
+    klas.call("Kuiper_GraphDist_matmul_dist_gpu", n, a, mine)
+    f = ref.fn("Kuiper_GraphDist_matmul_dist_gpu", [C.c_uint32, C.c_void_p, C.c_void_p])
+    f(n, a.data_ptr(), theirs.data_ptr())
+    torch.cuda.synchronize()
+    assert torch.equal(mine, theirs)
+    if top == 200:
+        TIMINGS["graphdist_1026"] = {
+            "ours_kernel_ms": event_ms(lambda: klas.minplus_u16(a, a, mine)),
+            "ref_call_ms": wall_ms(lambda: f(n, a.data_ptr(), theirs.data_ptr())),
+            "ring_ops": 2 * n ** 3}
+
+
 def test_u64_bit_exact(ref):
     n = 1024
     a, b = synth.gemm_u64(3, n, n, n, full_range=True, device="cuda")

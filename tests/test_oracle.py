@@ -146,6 +146,54 @@ def test_live_reference_softmax(oracle, refcpu):
     assert np.array_equal(oracle.softmax(x, log=True), refcpu.cpu_softmax(x, log=True))
 
 
+def test_minplus_squaring_reaches_all_path_lengths(oracle):
+    """The graph-distance driver's own check (test/Test_Kuiper_GraphDist.cu:55-95): on the path graph
+    0 -> 1 -> ... -> n-1, repeated squaring ends with dist[i][j] = j - i above the diagonal, 0 elsewhere."""
+    n = 70
+    m1 = np.zeros((n, n), dtype=np.uint16)
+    m1[np.arange(n - 1), np.arange(1, n)] = 1
+    m2 = m1.copy()
+    length = 1
+    while length < n:
+        m2 = oracle.minplus_u16(m1, m1, m2)
+        m1, m2 = m2, m1
+        length *= 2
+    want = np.triu(np.arange(n)[None, :] - np.arange(n)[:, None], 1).astype(np.uint16)
+    assert np.array_equal(m1, want)
+
+
+def test_minplus_ring_laws(oracle):
+    # 0 is absorbing for mult and neutral for add; x + y wraps at 2^16 as the reference's uint16 return does
+    a = np.array([[0, 5, 40000]], dtype=np.uint16)
+    b = np.array([[7], [0], [30000]], dtype=np.uint16)
+    assert oracle.minplus_u16(a, b, np.zeros((1, 1), np.uint16))[0, 0] == (40000 + 30000) % 65536
+    assert oracle.minplus_u16(a, b, np.array([[3]], np.uint16))[0, 0] == 3
+    assert oracle.minplus_u16(a[:, :2], b[:2], np.array([[9]], np.uint16))[0, 0] == 9
+
+
+def test_sparsify_and_row_order(oracle):
+    M = np.array([[0, 1.5, -0.0, 2], [0, 0, 0, 0], [3, 0, 0, np.nan], [1, 1, 1, 1]], dtype=np.float32)
+    row_off, elems, col_ind = oracle.sparsify(M)
+    assert row_off.tolist() == [0, 2, 2, 4, 8]
+    assert col_ind.tolist() == [1, 3, 0, 3, 0, 1, 2, 3]
+    assert elems[:3].tolist() == [1.5, 2.0, 3.0] and np.isnan(elems[3])
+    assert oracle.row_order(row_off).tolist() == [3, 0, 2, 1]      # longest first, ties by row
+
+
+def test_live_reference_sparsify(oracle, refcpu):
+    rng = np.random.default_rng(3)
+    for dtype in (np.float32, np.uint32):
+        M = (rng.integers(1, 99, size=(57, 83)) * (rng.random((57, 83)) < 0.2)).astype(dtype)
+        got, want = oracle.sparsify(M), refcpu.sparsify(M)
+        for g, w in zip(got, want):
+            assert np.array_equal(g, w)
+        # the reference's order is any permutation with non-increasing lengths; ours is one of them
+        lens = np.diff(want[0].astype(np.int64))
+        ref_order, our_order = refcpu.mk_row_indices(want[0]), oracle.row_order(want[0])
+        assert sorted(ref_order.tolist()) == list(range(57)) == sorted(our_order.tolist())
+        assert np.array_equal(lens[ref_order], lens[our_order])
+
+
 # ------------------------------------------------------------------ live checks against oracle/_ref
 @pytest.mark.parametrize("shape", [(7, 5, 3), (33, 65, 17), (128, 96, 64)])
 def test_live_reference_loops(oracle, refcpu, shape):
