@@ -485,7 +485,7 @@ def cpu_baseline_leg(workload_name):
 
 # --------------------------------------------------------------------------- main
 # DRAM traffic of one launch from an ncu capture of the same kernel (profiles/): bytes read + written.
-NCU_TRAFFIC = {"gemm_bf16": 1.150e9, "spmm": 1.141e9, "gemm_u64": 2.163e9, "gemm_f32": 8.4e6}
+NCU_TRAFFIC = {"gemm_bf16": 1.150e9, "spmm": 1.141e9, "gemm_u64": 2.163e9, "gemm_f32": 8.4e6, "softmax_f32": 3.18e9}
 
 
 def main():
