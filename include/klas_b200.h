@@ -277,8 +277,8 @@ int klas_b200_spmm_host(int dtype, uint32_t rows, uint32_t shared, uint32_t cols
 
 /*
  * Row-wise neighbours of the products (what sits either side of Q.K^T and P.V in an
- * attention block).  dtype KLAS_F16 / KLAS_F32 / KLAS_F64 unless said otherwise; fp16 data is
- * processed in fp32 and rounded once.
+ * attention block).  dtype KLAS_F16 / KLAS_F32 / KLAS_F64 unless said otherwise (softmax also
+ * KLAS_BF16); 16-bit data is processed in fp32 and rounded once.
  *
  * klas_b200_softmax: in place, a[r][c] = exp(a[r][c] - max_r) / sum_c exp(a[r][c] - max_r) for
  * every row of the row-major rows x cols matrix `a` (log_softmax != 0: a[r][c] - max_r - log(sum)).
@@ -315,6 +315,25 @@ int klas_b200_softmax_host(int dtype, int log_softmax, uint64_t rows, uint64_t c
  */
 #define KLAS_B200_SOFTMAX_STATIC_MAX_COLS 16777216ull   /* 1024 chunks of 16384 elements */
 int klas_b200_softmax_static(int dtype, int log_softmax, uint64_t cols, void *a, void *stream);
+
+/*
+ * Scaled dot-product attention in the three steps of the reference's naive kernel
+ * (src/lib/kernel/Kuiper.Kernel.SDPA.Naive.fst:390-470: batched GEMM, row softmax, batched GEMM),
+ * for `pages` = batch x heads independent heads:
+ *
+ *   S = scale * Q.K^T + bias      written over `bias_scores`
+ *   P = softmax of every row of S (in place)
+ *   O = P.V
+ *
+ * Q [pages][l][e], K [pages][s][e], V [pages][s][ev], bias_scores [pages][l][s], out [pages][l][ev],
+ * all row-major, contiguous, of one dtype (KLAS_F16 or KLAS_BF16) and 16-byte aligned; e, s and ev
+ * multiples of 8.  Products accumulate in fp32 on the tensor cores; S, P and O are rounded to
+ * `dtype` once each.  has_bias == 0: `bias_scores` is only the scratch for S (its contents on
+ * entry are ignored).  On return it holds P.  Three launches on `stream` (four without bias).
+ */
+int klas_b200_sdpa(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e, uint64_t ev,
+                   const void *Q, const void *K, const void *V, void *bias_scores, int has_bias,
+                   void *out, float scale, void *stream);
 
 /*
  * b[r][c] = scale[r] * b[r][c] for the m x n matrix b, row-major (col_major == 0) or

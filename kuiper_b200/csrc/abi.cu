@@ -199,6 +199,28 @@ int klas_b200_minplus_u16(uint32_t m, uint32_t n, uint32_t k, const uint16_t *A,
     return launch_minplus_u16(m, n, k, A, B, C, static_cast<cudaStream_t>(stream));
 }
 
+int klas_b200_sdpa(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e, uint64_t ev, const void *Q,
+                   const void *K, const void *V, void *bias_scores, int has_bias, void *out, float scale,
+                   void *stream) {
+    clear_error();
+    if (dtype != KLAS_F16 && dtype != KLAS_BF16) return fail(KLAS_ERR_INVALID, "sdpa: dtype must be KLAS_F16 or KLAS_BF16");
+    if (pages == 0 || l == 0 || ev == 0) return KLAS_OK;
+    if (s == 0) return fail(KLAS_ERR_INVALID, "sdpa: no keys (s == 0): the softmax of an empty row is undefined");
+    if (!Q || !K || !V || !bias_scores || !out) return fail(KLAS_ERR_INVALID, "sdpa: null pointer");
+    if (e % 8 || s % 8 || ev % 8)
+        return fail(KLAS_ERR_UNSUPPORTED, "sdpa: e (%llu), s (%llu) and ev (%llu) must be multiples of 8",
+                    (unsigned long long)e, (unsigned long long)s, (unsigned long long)ev);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!has_bias) KLAS_TRY_CUDA(cudaMemsetAsync(bias_scores, 0, size_t(pages) * l * s * 2, st));
+    // S = scale * Q.K^T + bias: K's rows are the columns of K^T, i.e. a column-major B operand
+    if (int rc = launch_gemm_umma(dtype, dtype, KLAS_B_COL_MAJOR, pages, l, e, s, Q, K, bias_scores, bias_scores, scale,
+                                  1.0f, nullptr, st))
+        return rc;
+    if (int rc = launch_softmax(dtype, 0, uint64_t(pages) * l, s, bias_scores, nullptr, 0, st)) return rc;
+    return launch_gemm_umma(dtype, dtype, KLAS_B_ROW_MAJOR, pages, l, s, ev, bias_scores, V, nullptr, out, 1.0f, 0.0f,
+                            nullptr, st);
+}
+
 int klas_b200_gemm_tc_status(int *site) {
     clear_error();
     int v = 0;

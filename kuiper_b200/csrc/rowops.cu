@@ -15,6 +15,7 @@
 // (block max -> subtract -> block sum of exp -> divide, one CTA for the reductions),
 // dist/Klas_LogSoftmax.cu, dist/Klas_RowSoftmax.cu:3-45, dist/Klas_RowScale.cu:3-30,
 // dist/Klas_HReduce.cu and dist/Klas_AtomicReduce.cu (one atomic per element).
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -40,6 +41,12 @@ struct Num<__half> {
     using Acc = float;
     static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
     static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
+};
+template <>
+struct Num<__nv_bfloat16> {
+    using Acc = float;
+    static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 down(float v) { return __float2bfloat16_rn(v); }
 };
 template <>
 struct Num<double> {
@@ -251,6 +258,53 @@ __global__ void __launch_bounds__(THREADS) row_softmax_kernel(T *a, uint64_t col
     cta_apply<T, LOG>(row, 0, cols, st.m, denom);   // second read of the row comes from L2
 }
 
+// Short rows: one warp per row, the whole row in registers (PACKS 16-byte packs per lane), so
+// the row is read once and written once and the reductions are shuffles.  Needs 16-byte
+// aligned rows (cols a multiple of the pack size, aligned base).
+template <typename T, bool LOG, int PACKS>
+__global__ void __launch_bounds__(THREADS) row_softmax_warp_kernel(T *a, uint64_t rows, uint32_t cols) {
+    using A = typename Num<T>::Acc;
+    constexpr int N = Pack<T>::N;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t row_id = uint64_t(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5);
+    if (row_id >= rows) return;
+    Pack<T> *row = reinterpret_cast<Pack<T> *>(a + row_id * cols);
+    const uint32_t packs = cols / N;
+    Pack<T> buf[PACKS];
+#pragma unroll
+    for (int u = 0; u < PACKS; ++u) {
+        const uint32_t i = lane + 32u * u;
+        if (i < packs) buf[u] = row[i];
+    }
+    MaxSum<A> st = ms_empty<A>();
+#pragma unroll
+    for (int u = 0; u < PACKS; ++u) {
+        if (lane + 32u * u < packs) {
+            A vals[N];
+#pragma unroll
+            for (int j = 0; j < N; ++j) vals[j] = A(Num<T>::up(buf[u].v[j]));
+            ms_fold(st, vals);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        MaxSum<A> o;
+        o.m = __shfl_xor_sync(0xffffffffu, st.m, off);
+        o.s = __shfl_xor_sync(0xffffffffu, st.s, off);
+        st = ms_merge(st, o);
+    }
+    const A denom = LOG ? flog(st.s) : A(1) / st.s;
+#pragma unroll
+    for (int u = 0; u < PACKS; ++u) {
+        const uint32_t i = lane + 32u * u;
+        if (i < packs) {
+#pragma unroll
+            for (int j = 0; j < N; ++j) buf[u].v[j] = finish<T, LOG>(buf[u].v[j], st.m, denom);
+            row[i] = buf[u];
+        }
+    }
+}
+
 // ---- row scaling: b[r][c] = scale[r] * b[r][c], b row- or column-major -------------------------
 template <typename T>
 __global__ void __launch_bounds__(THREADS) rowscale_kernel(const T *__restrict__ scale, T *b, uint64_t m,
@@ -348,6 +402,24 @@ static int softmax_t(int log_softmax, uint64_t rows, uint64_t cols, void *a, voi
     T *p = static_cast<T *>(a);
     if (rows > 1) {
         if (rows > 0x7fffffffull) return fail(KLAS_ERR_TOO_LARGE, "softmax: too many rows");
+        constexpr uint64_t N = Pack<T>::N;
+        if (cols % N == 0 && cols / N <= 32 * 8 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0) {
+            // warp per row, row held in registers: 2, 4 or 8 packs per lane
+            const uint64_t per_lane = (cols / N + 31) / 32;
+            const unsigned grid = unsigned((rows + THREADS / 32 - 1) / (THREADS / 32));
+#define KLAS_ROW_WARP(P)                                                                                   \
+    do {                                                                                                   \
+        if (log_softmax)                                                                                   \
+            row_softmax_warp_kernel<T, true, P><<<grid, THREADS, 0, s>>>(p, rows, uint32_t(cols));         \
+        else                                                                                               \
+            row_softmax_warp_kernel<T, false, P><<<grid, THREADS, 0, s>>>(p, rows, uint32_t(cols));        \
+    } while (0)
+            if (per_lane <= 2) KLAS_ROW_WARP(2);
+            else if (per_lane <= 4) KLAS_ROW_WARP(4);
+            else KLAS_ROW_WARP(8);
+#undef KLAS_ROW_WARP
+            return check_cuda(cudaGetLastError(), "row_softmax_warp_kernel launch");
+        }
         if (log_softmax)
             row_softmax_kernel<T, true><<<unsigned(rows), THREADS, 0, s>>>(p, cols);
         else
@@ -397,9 +469,10 @@ int launch_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, voi
         return fail(KLAS_ERR_INVALID, "softmax: scratch must be 16-byte aligned");
     switch (dtype) {
         case KLAS_F16: return rowops::softmax_t<__half>(log_softmax, rows, cols, a, scratch, stream);
+        case KLAS_BF16: return rowops::softmax_t<__nv_bfloat16>(log_softmax, rows, cols, a, scratch, stream);
         case KLAS_F32: return rowops::softmax_t<float>(log_softmax, rows, cols, a, scratch, stream);
         case KLAS_F64: return rowops::softmax_t<double>(log_softmax, rows, cols, a, scratch, stream);
-        default: return fail(KLAS_ERR_INVALID, "softmax: dtype must be F16, F32 or F64");
+        default: return fail(KLAS_ERR_INVALID, "softmax: dtype must be F16, BF16, F32 or F64");
     }
 }
 

@@ -119,6 +119,36 @@ def gemm(A: torch.Tensor, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
     return C_
 
 
+def sdpa(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
+         scale: Optional[float] = None, scores: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """softmax(scale * Q.K^T + bias).V per head.  Q [..., l, e], K [..., s, e], V [..., s, ev] (f16 or
+    bf16, contiguous, same leading dimensions); `bias` [..., l, s] is overwritten with the
+    probabilities; without it pass `scores` (same shape) as scratch or let one be allocated.
+    scale defaults to 1/sqrt(e)."""
+    if Q.dtype not in (torch.float16, torch.bfloat16) or K.dtype != Q.dtype or V.dtype != Q.dtype:
+        raise TypeError("sdpa needs f16 or bf16 tensors of one dtype")
+    lead = tuple(Q.shape[:-2])
+    l, e = Q.shape[-2:]
+    s, e2 = K.shape[-2:]
+    s2, ev = V.shape[-2:]
+    if tuple(K.shape[:-2]) != lead or tuple(V.shape[:-2]) != lead or e2 != e or s2 != s:
+        raise ValueError("shapes do not match: %s %s %s" % (tuple(Q.shape), tuple(K.shape), tuple(V.shape)))
+    pages = 1
+    for d in lead:
+        pages *= d
+    buf = bias if bias is not None else scores
+    if buf is None:
+        buf = torch.empty(lead + (l, s), dtype=Q.dtype, device=Q.device)
+    if tuple(buf.shape) != lead + (l, s) or buf.dtype != Q.dtype:
+        raise ValueError("bias / scores must have shape %s and dtype %s" % (lead + (l, s), Q.dtype))
+    out = torch.empty(lead + (l, ev), dtype=Q.dtype, device=Q.device)
+    with torch.cuda.device(Q.device):
+        check(_lib.load().klas_b200_sdpa(_code(Q), pages, l, s, e, ev, _dev(Q, "Q"), _dev(K, "K"), _dev(V, "V"),
+                                         _dev(buf, "bias"), int(bias is not None), _dev(out, "out"),
+                                         float(scale if scale is not None else e ** -0.5), _stream()))
+    return out
+
+
 def csr_from_dense(M: torch.Tensor) -> Csr:
     """CSR form (values != 0 in column order, offsets, longest-first row order) of a dense 2-D f32 or
     32-bit integer CUDA tensor, built on the device.  One 4-byte read-back (nnz) sizes the arrays."""
@@ -286,9 +316,9 @@ def spmm(A: Csr, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
 
 def softmax(a: torch.Tensor, *, log: bool = False) -> torch.Tensor:
     """In-place softmax (log-softmax with log=True) of a vector, or of every row of a row-major
-    matrix; f16 / f32 / f64.  Returns `a`."""
-    if a.dtype not in (torch.float16, torch.float32, torch.float64) or a.dim() not in (1, 2):
-        raise TypeError("softmax needs a 1-D or 2-D f16/f32/f64 tensor")
+    matrix; f16 / bf16 / f32 / f64.  Returns `a`."""
+    if a.dtype not in (torch.float16, torch.bfloat16, torch.float32, torch.float64) or a.dim() not in (1, 2):
+        raise TypeError("softmax needs a 1-D or 2-D f16/bf16/f32/f64 tensor")
     rows, cols = (1, a.shape[0]) if a.dim() == 1 else a.shape
     lib = _lib.load()
     with torch.cuda.device(a.device):

@@ -10,9 +10,9 @@ pytestmark = pytest.mark.gpu
 
 # |got - want| bounds.  Softmax outputs lie in [0, 1]; the f32 kernels evaluate expf / logf
 # (a few ulp) and sum in f32 over at most ~1e6 terms in a tree of partial sums.
-TOL_SOFTMAX = {torch.float64: 1e-13, torch.float32: 2e-6, torch.float16: 1e-3}
+TOL_SOFTMAX = {torch.float64: 1e-13, torch.float32: 2e-6, torch.float16: 1e-3, torch.bfloat16: 8e-3}
 # log-softmax values reach a few tens in magnitude (f16 spacing there is 2^-5): absolute bounds.
-TOL_LOGSOFTMAX = {torch.float64: 1e-11, torch.float32: 2e-5, torch.float16: 3.2e-2}
+TOL_LOGSOFTMAX = {torch.float64: 1e-11, torch.float32: 2e-5, torch.float16: 3.2e-2, torch.bfloat16: 0.26}
 
 
 def values(seed, *shape, dtype=torch.float32, spread=4.0):
@@ -34,8 +34,10 @@ def test_vector_softmax(oracle, dtype, n, log):
         assert abs(got.sum() - 1.0) <= 1e-4
 
 
-@pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.float16])
-@pytest.mark.parametrize("rows,cols", [(1, 33), (5, 1), (64, 1000), (300, 257), (7, 70000)])
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(1, 33), (5, 1), (64, 1000), (300, 257), (7, 70000),
+                                       # rows held in registers by one warp: 1 to 8 packs per lane, ragged last pack
+                                       (3, 8), (1000, 64), (77, 256), (515, 1024), (33, 2048), (9, 1016), (2, 4096)])
 @pytest.mark.parametrize("log", [False, True])
 def test_row_softmax(oracle, dtype, rows, cols, log):
     x = values(rows + cols, rows, cols, dtype=dtype)
