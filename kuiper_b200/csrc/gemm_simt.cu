@@ -27,6 +27,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 #include "klas_internal.h"
@@ -34,6 +35,9 @@
 namespace klas {
 namespace simt {
 
+#ifndef KLAS_SIMT_BK8
+#define KLAS_SIMT_BK8 8   // K depth of the large tile of the 8-byte types
+#endif
 constexpr int THREADS = 256;
 constexpr int TX = 16;  // threads along N
 constexpr int TY = 16;  // threads along M
@@ -155,8 +159,10 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
     constexpr int B_PER_THREAD = (B_VECS + THREADS - 1) / THREADS;
     static_assert(BK % VEC == 0 && BN % VEC == 0, "tile not vectorisable");
 
-    __shared__ __align__(16) T As[2][BK][BM + PAD];  // transposed: [k][m]
-    __shared__ __align__(16) T Bs[2][BK][BN + PAD];
+    // Dynamic shared memory: the deepest tiles need a little more than the 48 KiB static limit.
+    extern __shared__ __align__(16) unsigned char simt_smem[];
+    T(*As)[BK][BM + PAD] = reinterpret_cast<T(*)[BK][BM + PAD]>(simt_smem);  // transposed: [k][m]
+    T(*Bs)[BK][BN + PAD] = reinterpret_cast<T(*)[BK][BN + PAD]>(simt_smem + sizeof(T) * 2 * BK * (BM + PAD));
 
     const int tid = threadIdx.x;
     const int tx = tid % TX;
@@ -362,6 +368,24 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
     }
 }
 
+template <typename S, typename T, int BM, int BN, int BK, bool FAST, bool HOOKS>
+static int launch_kernel(const Args<T> &a, unsigned blocks, cudaStream_t stream) {
+    constexpr int PAD = 16 / sizeof(T);
+    constexpr size_t SMEM = sizeof(T) * 2 * BK * (BM + PAD + BN + PAD);
+    if constexpr (SMEM > 48 * 1024) {
+        static bool configured[64] = {};
+        int dev = 0;
+        KLAS_TRY_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !configured[dev]) {
+            KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_simt_kernel<S, T, BM, BN, BK, FAST, HOOKS>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
+            if (dev >= 0 && dev < 64) configured[dev] = true;
+        }
+    }
+    gemm_simt_kernel<S, T, BM, BN, BK, FAST, HOOKS><<<blocks, THREADS, SMEM, stream>>>(a);
+    return check_cuda(cudaGetLastError(), "gemm_simt_kernel launch");
+}
+
 template <typename S, typename T, int BM, int BN, int BK>
 static int launch_cfg(const Problem &q, T alpha, T beta, int scaled, const void *A, const void *B, void *C,
                       cudaStream_t stream) {
@@ -396,18 +420,12 @@ static int launch_cfg(const Problem &q, T alpha, T beta, int scaled, const void 
                         reinterpret_cast<uintptr_t>(C)) & 15u) == 0;
     if constexpr (sizeof(S) == sizeof(T)) {
         if (fast) {
-            if (q.hooks)
-                gemm_simt_kernel<S, T, BM, BN, BK, true, true><<<unsigned(blocks), THREADS, 0, stream>>>(a);
-            else
-                gemm_simt_kernel<S, T, BM, BN, BK, true><<<unsigned(blocks), THREADS, 0, stream>>>(a);
-            return check_cuda(cudaGetLastError(), "gemm_simt_kernel launch");
+            if (q.hooks) return launch_kernel<S, T, BM, BN, BK, true, true>(a, unsigned(blocks), stream);
+            return launch_kernel<S, T, BM, BN, BK, true, false>(a, unsigned(blocks), stream);
         }
     }
-    if (q.hooks)
-        gemm_simt_kernel<S, T, BM, BN, BK, false, true><<<unsigned(blocks), THREADS, 0, stream>>>(a);
-    else
-        gemm_simt_kernel<S, T, BM, BN, BK, false><<<unsigned(blocks), THREADS, 0, stream>>>(a);
-    return check_cuda(cudaGetLastError(), "gemm_simt_kernel launch");
+    if (q.hooks) return launch_kernel<S, T, BM, BN, BK, false, true>(a, unsigned(blocks), stream);
+    return launch_kernel<S, T, BM, BN, BK, false, false>(a, unsigned(blocks), stream);
 }
 
 template <typename S, typename T>
@@ -425,7 +443,7 @@ static int launch_type(const Problem &q, T alpha, T beta, int scaled, const void
         return launch_cfg<S, T, 64, 64, 16>(q, alpha, beta, scaled, A, B, C, stream);
     } else {
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
-        if (big_tiles >= uint64_t(sm_count)) return launch_cfg<S, T, 128, 64, 8>(q, alpha, beta, scaled, A, B, C, stream);
+        if (big_tiles >= uint64_t(sm_count)) return launch_cfg<S, T, 128, 64, KLAS_SIMT_BK8>(q, alpha, beta, scaled, A, B, C, stream);
         return launch_cfg<S, T, 64, 32, 8>(q, alpha, beta, scaled, A, B, C, stream);
     }
 }
@@ -440,10 +458,19 @@ static int dispatch(int dtype, const Problem &q, const void *alpha, const void *
             return launch_type<float, float>(q, scaled ? *static_cast<const float *>(alpha) : 1.0f,
                                              scaled ? *static_cast<const float *>(beta) : 0.0f, scaled, A, B, C,
                                              info.sm_count, stream);
-        case KLAS_F64:
+        case KLAS_F64: {
+            // Plain contiguous products go to the FP64 tensor-core kernel (KLAS_F64_MODE=simt keeps
+            // them here); strided pages and the element-wise hooks stay on this kernel.
+            const char *mode = getenv("KLAS_F64_MODE");
+            const bool contiguous = q.lda == q.k && q.ldb == q.n && q.ldc == q.n && q.sa == q.m * q.k &&
+                                    q.sb == q.k * q.n && q.sc == q.m * q.n;
+            if (!q.hooks && contiguous && !(mode && !strcmp(mode, "simt")))
+                return launch_gemm_dmma(q.batch, q.m, q.n, q.k, static_cast<const double *>(alpha),
+                                        static_cast<const double *>(beta), A, B, C, stream);
             return launch_type<double, double>(q, scaled ? *static_cast<const double *>(alpha) : 1.0,
                                                scaled ? *static_cast<const double *>(beta) : 0.0, scaled, A, B, C,
                                                info.sm_count, stream);
+        }
         case KLAS_U32:
             return launch_type<uint32_t, uint32_t>(q, scaled ? *static_cast<const uint32_t *>(alpha) : 1u,
                                                    scaled ? *static_cast<const uint32_t *>(beta) : 0u, scaled, A, B, C,

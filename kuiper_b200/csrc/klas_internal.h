@@ -55,6 +55,9 @@ int launch_gemm_simt(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t
                      const void *alpha, const void *beta, const void *A, const void *B, void *C,
                      cudaStream_t stream);
 
+int launch_gemm_dmma(uint32_t batch, uint64_t m, uint64_t n, uint64_t k, const double *alpha, const double *beta,
+                     const void *A, const void *B, void *C, cudaStream_t stream);
+
 int launch_gemm_simt_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, uint64_t k, const void *alpha,
                              const void *beta, const void *A, uint64_t lda, uint64_t stride_a, const void *B,
                              uint64_t ldb, uint64_t stride_b, void *C, uint64_t ldc, uint64_t stride_c, int map_a,

@@ -28,8 +28,34 @@ def test_f32_matmul(oracle, m, n, k):
     assert rel_err_componentwise(Cg.cpu().numpy(), acc, scale) <= TOL_F32
 
 
+@pytest.fixture(params=["tensor", "simt"])
+def f64_mode(request, monkeypatch):
+    """fp64 products run on the FP64 tensor-core kernel by default and on the CUDA-core kernel on request."""
+    if request.param == "simt":
+        monkeypatch.setenv("KLAS_F64_MODE", "simt")
+    else:
+        monkeypatch.delenv("KLAS_F64_MODE", raising=False)
+    return request.param
+
+
+@pytest.mark.parametrize("m,n,k,batch,layout", [(256, 128, 64, 1, "rrr"), (100, 36, 52, 1, "rrr"), (129, 67, 33, 3, "rrr"),
+                                               (384, 192, 160, 2, "rrr"), (70, 130, 45, 1, "ccc"), (1, 1, 1, 1, "rrr"),
+                                               (8, 8, 0, 1, "rrr")])
+def test_f64_alpha_beta_batched_layouts(oracle, f64_mode, m, n, k, batch, layout):
+    shape = lambda r, c: ((batch,) if batch > 1 else ()) + ((r, c) if layout == "rrr" else (c, r))
+    gen = lambda seed, r, c: (synth.uniform(seed, 61, 0, batch * r * c, -1, 1, dtype=torch.float64).reshape(shape(r, c))).cuda()
+    A, B, C0 = gen(1, m, max(k, 0)), gen(2, max(k, 0), n), gen(3, m, n)
+    t = (lambda x: x) if layout == "rrr" else (lambda x: x.transpose(-1, -2))
+    acc = t(A).cpu() @ t(B).cpu() if k else torch.zeros(((batch,) if batch > 1 else ()) + (m, n), dtype=torch.float64)
+    bound = (t(A).abs().cpu() @ t(B).abs().cpu() if k else torch.zeros_like(acc)) * 0.7 + 0.3 * t(C0).abs().cpu() + 1e-300
+    got = klas.gemm(A, B, C0.clone(), alpha=0.7, beta=-0.3, layout=layout)
+    assert float(((t(got).cpu() - (0.7 * acc - 0.3 * t(C0).cpu())).abs() / bound).max()) <= TOL_F64
+    got = klas.gemm(A, B, layout=layout)
+    assert float(((t(got).cpu() - acc).abs() / (bound + 1e-300)).max()) <= TOL_F64
+
+
 @pytest.mark.parametrize("m,n,k", SHAPES[1:])
-def test_f64_matmul(oracle, m, n, k):
+def test_f64_matmul(oracle, f64_mode, m, n, k):
     A, B = synth.gemm_f32(5, m, n, k, device="cuda")
     A, B = A.double() + 1e-9, B.double() - 1e-9
     Cg = klas.gemm(A, B)
