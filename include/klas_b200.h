@@ -76,7 +76,8 @@ typedef enum klas_comb_e {
     KLAS_COMB_MAX = 2,    /* max(c, acc) */
     KLAS_COMB_MIN = 3,    /* min(c, acc) */
     KLAS_COMB_MUL = 4,    /* c * acc */
-    KLAS_COMB_RELU = 5    /* max(acc, 0) (C not read) */
+    KLAS_COMB_RELU = 5,   /* max(acc, 0) (C not read) */
+    KLAS_COMB_SCALED = 6  /* alpha * acc (C not read) */
 } klas_comb;
 
 /* Last error message of the calling thread ("" if none). Never NULL. */
@@ -168,7 +169,7 @@ int klas_b200_gemm_tc(int in_dtype, int out_dtype, int b_major, uint32_t batch,
  * copy from global memory and the tensor-core instruction, by dedicated warps: no mapped copy
  * of A or B is ever written to global memory.  comb (klas_comb) runs in the epilogue on the
  * fp32 accumulator.  C is required for AXPBY / MAX / MIN / MUL and ignored otherwise; alpha and
- * beta matter for AXPBY only.  Everything else as klas_b200_gemm_tc (which is the case
+ * beta matter for AXPBY (alpha also for SCALED) only.  Everything else as klas_b200_gemm_tc (which is the case
  * map_a = map_b = KLAS_MAP_ID, comb = C ? AXPBY : NEW).
  *
  * Replaces: the fused tensor-core kernels the reference generates from
@@ -329,7 +330,7 @@ int klas_b200_softmax_static(int dtype, int log_softmax, uint64_t cols, void *a,
  * all row-major, contiguous, of one dtype (KLAS_F16 or KLAS_BF16) and 16-byte aligned; e, s and ev
  * multiples of 8.  Products accumulate in fp32 on the tensor cores; S, P and O are rounded to
  * `dtype` once each.  has_bias == 0: `bias_scores` is only the scratch for S (its contents on
- * entry are ignored).  On return it holds P.  Three launches on `stream` (four without bias).
+ * entry are ignored).  On return it holds P.  Three launches on `stream`.
  */
 int klas_b200_sdpa(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e, uint64_t ev,
                    const void *Q, const void *K, const void *V, void *bias_scores, int has_bias,

@@ -13,7 +13,7 @@ F32, F64, U32, U64, BF16, F16 = range(6)
 RRR, CCC = 0, 1
 B_ROW_MAJOR, B_COL_MAJOR = 0, 1
 MAP_ID, MAP_SQRT, MAP_ABS, MAP_SQUARE, MAP_RELU, MAP_NEG = range(6)
-COMB_NEW, COMB_AXPBY, COMB_MAX, COMB_MIN, COMB_MUL, COMB_RELU = range(6)
+COMB_NEW, COMB_AXPBY, COMB_MAX, COMB_MIN, COMB_MUL, COMB_RELU, COMB_SCALED = range(7)
 
 _u32, _u64, _vp, _int, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int, C.c_float
 

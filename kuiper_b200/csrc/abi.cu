@@ -2,6 +2,7 @@
 // plus the small amount of per-thread / per-device state behind them.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -91,8 +92,10 @@ int umma_wait_probe(uint32_t limit_ms, int *gave_up, cudaStream_t stream);
 // Streams and events of the chunked host-buffer calls, one set per device, created on first use.
 struct HostPipe {
     static constexpr int MAX_CHUNKS = 8;
+    static constexpr int GRID_2D = 16;                  // row blocks of A = column blocks of B in the 2-D schedule
+    static constexpr int EVENTS = 2 * GRID_2D + 2;      // which loads and computes 2 x GRID_2D pieces
     cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
-    cudaEvent_t loaded[MAX_CHUNKS + 1] = {}, computed[MAX_CHUNKS + 1] = {};
+    cudaEvent_t loaded[EVENTS] = {}, computed[EVENTS] = {};
     bool ready = false;
 };
 static HostPipe g_pipes[MAX_DEVICES];
@@ -107,7 +110,7 @@ static int host_pipe(HostPipe **out) {
         KLAS_TRY_CUDA(cudaStreamCreateWithFlags(&h.in, cudaStreamNonBlocking));
         KLAS_TRY_CUDA(cudaStreamCreateWithFlags(&h.compute, cudaStreamNonBlocking));
         KLAS_TRY_CUDA(cudaStreamCreateWithFlags(&h.out, cudaStreamNonBlocking));
-        for (int i = 0; i <= HostPipe::MAX_CHUNKS; ++i) {
+        for (int i = 0; i < HostPipe::EVENTS; ++i) {
             KLAS_TRY_CUDA(cudaEventCreateWithFlags(&h.loaded[i], cudaEventDisableTiming));
             KLAS_TRY_CUDA(cudaEventCreateWithFlags(&h.computed[i], cudaEventDisableTiming));
         }
@@ -211,10 +214,10 @@ int klas_b200_sdpa(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e
         return fail(KLAS_ERR_UNSUPPORTED, "sdpa: e (%llu), s (%llu) and ev (%llu) must be multiples of 8",
                     (unsigned long long)e, (unsigned long long)s, (unsigned long long)ev);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (!has_bias) KLAS_TRY_CUDA(cudaMemsetAsync(bias_scores, 0, size_t(pages) * l * s * 2, st));
-    // S = scale * Q.K^T + bias: K's rows are the columns of K^T, i.e. a column-major B operand
-    if (int rc = launch_gemm_umma(dtype, dtype, KLAS_B_COL_MAJOR, pages, l, e, s, Q, K, bias_scores, bias_scores, scale,
-                                  1.0f, nullptr, st))
+    // S = scale * Q.K^T (+ bias): K's rows are the columns of K^T, i.e. a column-major B operand
+    if (int rc = launch_gemm_umma_fused(dtype, dtype, KLAS_B_COL_MAJOR, pages, l, e, s, Q, K, has_bias ? bias_scores : nullptr,
+                                        bias_scores, scale, 1.0f, KLAS_MAP_ID, KLAS_MAP_ID,
+                                        has_bias ? KLAS_COMB_AXPBY : KLAS_COMB_SCALED, nullptr, st))
         return rc;
     if (int rc = launch_softmax(dtype, 0, uint64_t(pages) * l, s, bias_scores, nullptr, 0, st)) return rc;
     return launch_gemm_umma(dtype, dtype, KLAS_B_ROW_MAJOR, pages, l, s, ev, bias_scores, V, nullptr, out, 1.0f, 0.0f,
@@ -266,6 +269,82 @@ int klas_b200_gemm_host(int dtype, int layout, uint32_t batch, uint64_t m, uint6
     return KLAS_OK;
 }
 
+// One large product D = A.B from host buffers, scheduled so that the device->host copy of D
+// overlaps the host->device copies of A and B from early on.  A is cut into G row blocks and B
+// into G column blocks; they are sent alternately (A_0, B_0, A_1, B_1, ...) and after every
+// arrival the part of D that has just become computable is multiplied and sent back:
+//   after A_t:  D[rows of A_t][columns of B_0 .. B_(t-1)]
+//   after B_t:  D[rows of A_0 .. A_t][columns of B_t]
+// so after 2(t+1) of the 2G input pieces (t+1)^2 of the G^2 output tiles are on their way.
+// With one block of rows per chunk instead (the other schedule below), no output can leave
+// before all of B has arrived, and a call costs bytes(B) + bytes(D) over the link instead of
+// about max(bytes in, bytes out).  (How far that goes is limited by the product itself: after a
+// fraction f of the input only f^2 of the output can exist, so the outbound copy starves early.)
+static int gemm_tc_host_2d(HostPipe *hp, int in_dtype, int out_dtype, int b_major, uint64_t rows, uint64_t shared,
+                           uint64_t cols, const void *A, const void *B, void *D, void *dA, void *dB, void *dD) {
+    const size_t is = dtype_size(in_dtype), os = dtype_size(out_dtype);
+    uint64_t G = 4;   // measured best at 8192^3 bf16 -> f32: 7.54 ms (4), 7.79 (8), 7.77 (16), 8.36 (2)
+    if (const char *g = getenv("KLAS_HOST_GRID")) {   // developer override: 1 .. GRID_2D, 0 = row blocks only
+        const int v = atoi(g);
+        if (v >= 1 && v <= HostPipe::GRID_2D) G = uint64_t(v);
+    }
+    const uint64_t rc = ((rows + G - 1) / G + 511) / 512 * 512;   // rows per block of A
+    const uint64_t cc = ((cols + G - 1) / G + 255) / 256 * 256;   // columns per block of B
+    const bool col_major = b_major == KLAS_B_COL_MAJOR;
+    char *out_dev = static_cast<char *>(dD);   // output blocks are laid one after another here
+    int n_loaded = 0, n_computed = 0;
+    // one product of `m` rows of A from row r0 with `n` columns of B from column c0, then its copy home
+    auto product = [&](uint64_t r0, uint64_t m, uint64_t c0, uint64_t n, cudaEvent_t after) -> int {
+        if (m == 0 || n == 0) return KLAS_OK;
+        KLAS_TRY_CUDA(cudaStreamWaitEvent(hp->compute, after, 0));
+        const char *a_dev = static_cast<const char *>(dA) + r0 * shared * is;
+        const char *b_dev = static_cast<const char *>(dB) + c0 * shared * is;   // block c0 starts here in both layouts
+        if (int rc2 = launch_gemm_umma(in_dtype, out_dtype, b_major, 1, m, shared, n, a_dev, b_dev, nullptr, out_dev, 1.0f,
+                                       0.0f, nullptr, hp->compute))
+            return rc2;
+        cudaEvent_t done = hp->computed[n_computed++ % HostPipe::EVENTS];   // waits are enqueued right after each record, so reuse is safe
+        KLAS_TRY_CUDA(cudaEventRecord(done, hp->compute));
+        KLAS_TRY_CUDA(cudaStreamWaitEvent(hp->out, done, 0));
+        KLAS_TRY_CUDA(cudaMemcpy2DAsync(static_cast<char *>(D) + (r0 * cols + c0) * os, cols * os, out_dev, n * os, n * os, m,
+                                        cudaMemcpyDeviceToHost, hp->out));
+        out_dev += m * n * os;
+        return KLAS_OK;
+    };
+    for (uint64_t t = 0; t < G; ++t) {
+        const uint64_t r0 = t * rc < rows ? t * rc : rows, r1 = r0 + rc < rows ? r0 + rc : rows;
+        const uint64_t c0 = t * cc < cols ? t * cc : cols, c1 = c0 + cc < cols ? c0 + cc : cols;
+        // A_t
+        if (r1 > r0 && shared)
+            KLAS_TRY_CUDA(cudaMemcpyAsync(static_cast<char *>(dA) + r0 * shared * is, static_cast<const char *>(A) + r0 * shared * is,
+                                          (r1 - r0) * shared * is, cudaMemcpyHostToDevice, hp->in));
+        cudaEvent_t a_in = hp->loaded[n_loaded++];
+        KLAS_TRY_CUDA(cudaEventRecord(a_in, hp->in));
+        if (col_major) {
+            // columns [0, c0) of B are one contiguous operand (rows of the stored cols x shared matrix)
+            if (int rc2 = product(r0, r1 - r0, 0, c0, a_in)) return rc2;
+        } else {
+            for (uint64_t j = 0; j < t && j * cc < cols; ++j)   // row-major B: every column block is its own shared x cc operand
+                if (int rc2 = product(r0, r1 - r0, j * cc, (j + 1) * cc < cols ? cc : cols - j * cc, a_in)) return rc2;
+        }
+        // B_t
+        if (c1 > c0 && shared) {
+            char *b_dst = static_cast<char *>(dB) + c0 * shared * is;
+            if (col_major)
+                KLAS_TRY_CUDA(cudaMemcpyAsync(b_dst, static_cast<const char *>(B) + c0 * shared * is, (c1 - c0) * shared * is,
+                                              cudaMemcpyHostToDevice, hp->in));
+            else   // gather the column block into a contiguous shared x (c1 - c0) matrix
+                KLAS_TRY_CUDA(cudaMemcpy2DAsync(b_dst, (c1 - c0) * is, static_cast<const char *>(B) + c0 * is, cols * is,
+                                                (c1 - c0) * is, shared, cudaMemcpyHostToDevice, hp->in));
+        }
+        cudaEvent_t b_in = hp->loaded[n_loaded++];
+        KLAS_TRY_CUDA(cudaEventRecord(b_in, hp->in));
+        if (int rc2 = product(0, r1, c0, c1 - c0, b_in)) return rc2;
+    }
+    KLAS_TRY_CUDA(cudaStreamSynchronize(hp->out));
+    KLAS_TRY_CUDA(cudaStreamSynchronize(hp->in));
+    return klas_b200_gemm_tc_status(nullptr);
+}
+
 int klas_b200_gemm_tc_host(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
                            uint64_t shared, uint64_t cols, const void *A, const void *B,
                            const void *C, void *D, float alpha, float beta) {
@@ -285,6 +364,10 @@ int klas_b200_gemm_tc_host(int in_dtype, int out_dtype, int b_major, uint32_t ba
     if (C)
         if (int rc = workspace_reserve(2, d_bytes, &dC)) return rc;
     if (int rc = workspace_reserve(3, d_bytes, &dD)) return rc;
+    if (batch == 1 && !C && rows >= 4096 && cols >= 4096 && shared % 8 == 0 && cols % 8 == 0 &&
+        (b_major == KLAS_B_COL_MAJOR || b_major == KLAS_B_ROW_MAJOR) && A && B &&
+        !(getenv("KLAS_HOST_GRID") && atoi(getenv("KLAS_HOST_GRID")) == 0))
+        return gemm_tc_host_2d(hp, in_dtype, out_dtype, b_major, rows, shared, cols, A, B, D, dA, dB, dD);
 
     // The work is cut into chunks -- row blocks of A/C/D for one matrix, groups of pages for a
     // batch -- that flow through three streams: host->device copies, kernels, device->host

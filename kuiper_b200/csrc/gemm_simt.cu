@@ -134,6 +134,7 @@ __device__ __forceinline__ T comb_val(T old, T acc, T alpha, T beta, int comb) {
         case KLAS_COMB_MIN: return old < acc ? old : acc;
         case KLAS_COMB_MUL: return old * acc;
         case KLAS_COMB_RELU: return acc > T(0) ? acc : T(0);
+        case KLAS_COMB_SCALED: return alpha * acc;
         default: return beta * old + alpha * acc;
     }
 }
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
                 T *cp = reinterpret_cast<T *>(C) + r * a.ldc + c;
                 if (HOOKS && a.comb != KLAS_COMB_AXPBY) {
                     Vec<T, VEC> old{};
-                    if (a.comb != KLAS_COMB_NEW && a.comb != KLAS_COMB_RELU) old = *reinterpret_cast<const Vec<T, VEC> *>(cp);
+                    if (a.comb != KLAS_COMB_NEW && a.comb != KLAS_COMB_RELU && a.comb != KLAS_COMB_SCALED) old = *reinterpret_cast<const Vec<T, VEC> *>(cp);
 #pragma unroll
                     for (int e = 0; e < VEC; ++e)
                         out.v[e] = comb_val<T>(old.v[e], acc_at(i, g * VEC + e), a.alpha, a.beta, a.comb);
@@ -354,7 +355,7 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
                             S *cp = C + r * a.ldc + c + e;
                             T val = acc_at(i, g * VEC + e);
                             if (HOOKS && a.comb != KLAS_COMB_AXPBY) {
-                                const T old = (a.comb != KLAS_COMB_NEW && a.comb != KLAS_COMB_RELU) ? Conv<S, T>::load(*cp) : T(0);
+                                const T old = (a.comb != KLAS_COMB_NEW && a.comb != KLAS_COMB_RELU && a.comb != KLAS_COMB_SCALED) ? Conv<S, T>::load(*cp) : T(0);
                                 val = comb_val<T>(old, val, a.alpha, a.beta, a.comb);
                             } else if (a.scaled) {
                                 val = a.beta * Conv<S, T>::load(*cp) + a.alpha * val;
@@ -534,9 +535,10 @@ int launch_gemm_simt_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, 
                              int map_b, int comb, cudaStream_t stream) {
     if (map_a < KLAS_MAP_ID || map_a > KLAS_MAP_NEG || map_b < KLAS_MAP_ID || map_b > KLAS_MAP_NEG)
         return fail(KLAS_ERR_INVALID, "gemm_strided: unknown operand map (%d, %d)", map_a, map_b);
-    if (comb < KLAS_COMB_NEW || comb > KLAS_COMB_RELU) return fail(KLAS_ERR_INVALID, "gemm_strided: unknown combine rule %d", comb);
+    if (comb < KLAS_COMB_NEW || comb > KLAS_COMB_SCALED) return fail(KLAS_ERR_INVALID, "gemm_strided: unknown combine rule %d", comb);
     if (comb == KLAS_COMB_AXPBY && (!alpha || !beta))
         return fail(KLAS_ERR_INVALID, "gemm_strided: the axpby rule needs alpha and beta");
+    if (comb == KLAS_COMB_SCALED && !alpha) return fail(KLAS_ERR_INVALID, "gemm_strided: the scaled rule needs alpha");
     if ((dtype == KLAS_U32 || dtype == KLAS_U64) && (map_a == KLAS_MAP_SQRT || map_b == KLAS_MAP_SQRT))
         return fail(KLAS_ERR_UNSUPPORTED, "gemm_strided: sqrt is not defined on the wrapping integer types");
     if (m == 0 || n == 0 || batch == 0) return KLAS_OK;
@@ -559,8 +561,11 @@ int launch_gemm_simt_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, 
     q.map_b = map_b;
     q.comb = comb;
     q.hooks = map_a != KLAS_MAP_ID || map_b != KLAS_MAP_ID || (comb != KLAS_COMB_AXPBY && comb != KLAS_COMB_NEW);
-    const bool scaled = comb == KLAS_COMB_AXPBY;
-    return simt::dispatch(dtype, q, scaled ? alpha : nullptr, scaled ? beta : nullptr, A, B, C, stream);
+    // alpha / beta reach the kernel through the "scaled" arguments; SCALED needs alpha only
+    static const double zero_words[1] = {0.0};   // 8 zero bytes: beta = 0 in every dtype
+    const bool scaled = comb == KLAS_COMB_AXPBY || comb == KLAS_COMB_SCALED;
+    const void *beta_arg = comb == KLAS_COMB_SCALED ? static_cast<const void *>(zero_words) : beta;
+    return simt::dispatch(dtype, q, scaled ? alpha : nullptr, scaled ? beta_arg : nullptr, A, B, C, stream);
 }
 
 }  // namespace klas

@@ -356,7 +356,7 @@ __device__ __forceinline__ float comb_f32(float old, float acc, float alpha, flo
 template <typename OutT, uint32_t COMB>
 __device__ __forceinline__ void store_row_chunk_t(const uint32_t (&acc)[32], OutT *drow,
                                                   const OutT *crow, float alpha, float beta,
-                                                  uint32_t ncols_left, bool relu) {
+                                                  uint32_t ncols_left, bool relu, float plain_scale) {
     constexpr uint32_t VEC = 16 / sizeof(OutT);  // elements per 16-byte access
 #pragma unroll
     for (uint32_t v0 = 0; v0 < 32; v0 += VEC) {
@@ -374,7 +374,7 @@ __device__ __forceinline__ void store_row_chunk_t(const uint32_t (&acc)[32], Out
             } else {
 #pragma unroll
                 for (uint32_t j = 0; j < VEC; ++j) {
-                    const float a = __uint_as_float(acc[v0 + j]);
+                    const float a = __uint_as_float(acc[v0 + j]) * plain_scale;
                     out.e[j] = OutTraits<OutT>::from_f32(relu ? fmaxf(a, 0.0f) : a);
                 }
             }
@@ -387,11 +387,12 @@ template <typename OutT>
 __device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT *drow, const OutT *crow,
                                                 float alpha, float beta, uint32_t ncols_left, uint32_t comb) {
     switch (comb) {
-        case KLAS_COMB_MAX: store_row_chunk_t<OutT, KLAS_COMB_MAX>(acc, drow, crow, alpha, beta, ncols_left, false); break;
-        case KLAS_COMB_MIN: store_row_chunk_t<OutT, KLAS_COMB_MIN>(acc, drow, crow, alpha, beta, ncols_left, false); break;
-        case KLAS_COMB_MUL: store_row_chunk_t<OutT, KLAS_COMB_MUL>(acc, drow, crow, alpha, beta, ncols_left, false); break;
+        case KLAS_COMB_MAX: store_row_chunk_t<OutT, KLAS_COMB_MAX>(acc, drow, crow, alpha, beta, ncols_left, false, 1.0f); break;
+        case KLAS_COMB_MIN: store_row_chunk_t<OutT, KLAS_COMB_MIN>(acc, drow, crow, alpha, beta, ncols_left, false, 1.0f); break;
+        case KLAS_COMB_MUL: store_row_chunk_t<OutT, KLAS_COMB_MUL>(acc, drow, crow, alpha, beta, ncols_left, false, 1.0f); break;
         default:
-            store_row_chunk_t<OutT, KLAS_COMB_AXPBY>(acc, drow, crow, alpha, beta, ncols_left, comb == KLAS_COMB_RELU);
+            store_row_chunk_t<OutT, KLAS_COMB_AXPBY>(acc, drow, crow, alpha, beta, ncols_left, comb == KLAS_COMB_RELU,
+                                                     comb == KLAS_COMB_SCALED ? alpha : 1.0f);
             break;
     }
 }
@@ -957,6 +958,7 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
         const uint32_t tempty_cta0 = ptx::map_to_cta(tempty_bar, 0);
         const uint32_t taddr0 = tmem_base + ((quad * 32u) << 16) + h * BN;
         const bool relu = p.comb == KLAS_COMB_RELU;
+        const float plain_scale = p.comb == KLAS_COMB_SCALED ? p.alpha : 1.0f;   // x * 1.0f is exact
         uint32_t tile_phase = 0;
         bool ok = true;
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
@@ -995,7 +997,7 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
                     } pk;
 #pragma unroll
                     for (uint32_t e = 0; e < 16 / sizeof(OutT); ++e) {
-                        const float a = __uint_as_float(v[j * (16 / sizeof(OutT)) + e]);
+                        const float a = __uint_as_float(v[j * (16 / sizeof(OutT)) + e]) * plain_scale;
                         pk.e[e] = OutTraits<OutT>::from_f32(relu ? fmaxf(a, 0.0f) : a);
                     }
                     const uint32_t piece = (sub * PIECES + j) ^ (lane & 7u);
@@ -1256,8 +1258,8 @@ int launch_gemm_umma_fused(int in_dtype, int out_dtype, int b_major, uint32_t ba
     using namespace umma;
     if (map_a < KLAS_MAP_ID || map_a > KLAS_MAP_NEG || map_b < KLAS_MAP_ID || map_b > KLAS_MAP_NEG)
         return fail(KLAS_ERR_INVALID, "gemm_tc: unknown operand map (%d, %d)", map_a, map_b);
-    if (comb < KLAS_COMB_NEW || comb > KLAS_COMB_RELU) return fail(KLAS_ERR_INVALID, "gemm_tc: unknown combine rule %d", comb);
-    const bool reads_c = comb != KLAS_COMB_NEW && comb != KLAS_COMB_RELU;
+    if (comb < KLAS_COMB_NEW || comb > KLAS_COMB_SCALED) return fail(KLAS_ERR_INVALID, "gemm_tc: unknown combine rule %d", comb);
+    const bool reads_c = comb != KLAS_COMB_NEW && comb != KLAS_COMB_RELU && comb != KLAS_COMB_SCALED;
     if (reads_c && !C && rows && cols && batch) return fail(KLAS_ERR_INVALID, "gemm_tc: this combine rule needs C");
     if (!reads_c) C = nullptr;
     const bool xform = (map_a != KLAS_MAP_ID || map_b != KLAS_MAP_ID) && shared > 0;

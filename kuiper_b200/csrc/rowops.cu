@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "klas_internal.h"
 
@@ -67,7 +68,11 @@ struct Num<uint64_t> {
     static __device__ __forceinline__ uint64_t down(uint64_t v) { return v; }
 };
 
-__device__ __forceinline__ float fexp(float x) { return expf(x); }
+// f32 exponential as 2^(x log2 e) on the special-function unit: 2 ulp plus the rounding of the
+// product, i.e. a relative error below 1e-6 wherever exp(x) is not negligible (the arguments
+// here are x - max <= 0).  expf's extra range reduction would triple the instruction count of
+// kernels that are otherwise bandwidth-bound on 16-bit data.
+__device__ __forceinline__ float fexp(float x) { return exp2f(x * 1.4426950408889634f); }
 __device__ __forceinline__ double fexp(double x) { return exp(x); }
 __device__ __forceinline__ float flog(float x) { return logf(x); }
 __device__ __forceinline__ double flog(double x) { return log(x); }
@@ -258,51 +263,134 @@ __global__ void __launch_bounds__(THREADS) row_softmax_kernel(T *a, uint64_t col
     cta_apply<T, LOG>(row, 0, cols, st.m, denom);   // second read of the row comes from L2
 }
 
-// Short rows: one warp per row, the whole row in registers (PACKS 16-byte packs per lane), so
-// the row is read once and written once and the reductions are shuffles.  Needs 16-byte
-// aligned rows (cols a multiple of the pack size, aligned base).
+// Rows that fit in registers (one warp or one CTA per row, PACKS 16-byte packs per thread) are
+// read once and written once, and need ONE exponential per element: the maximum first (a
+// compare per element), then e = exp(x - max) kept in registers while it is summed, then e / sum.
+// For f32 arithmetic exp(x - max) is ex2(x * log2 e - max * log2 e), one fused multiply-add and
+// one special-function instruction; the rounding of max * log2 e scales every e of the row by
+// the same factor, which cancels in e / sum.  `reduce_max` / `reduce_sum` combine the partial
+// results of the threads that share the row.
+template <typename T, bool LOG, int PACKS, typename RMax, typename RSum>
+__device__ __forceinline__ void row_in_registers(Pack<T> *row, uint32_t packs, uint32_t first, uint32_t step,
+                                                 RMax reduce_max, RSum reduce_sum) {
+    using A = typename Num<T>::Acc;
+    constexpr int N = Pack<T>::N;
+    A e[PACKS][N];
+    A m = A(-INFINITY);
+#pragma unroll
+    for (int u = 0; u < PACKS; ++u) {
+        const uint32_t i = first + step * u;
+        if (i < packs) {
+            const Pack<T> in = row[i];
+#pragma unroll
+            for (int j = 0; j < N; ++j) {
+                e[u][j] = A(Num<T>::up(in.v[j]));
+                m = e[u][j] > m ? e[u][j] : m;
+            }
+        }
+    }
+    m = reduce_max(m);
+    A sum = A(0);
+    if constexpr (std::is_same<A, float>::value) {
+        constexpr float L = 1.4426950408889634f;
+        const float nml = -m * L;
+#pragma unroll
+        for (int u = 0; u < PACKS; ++u) {
+            if (first + step * u < packs) {
+#pragma unroll
+                for (int j = 0; j < N; ++j) {
+                    float p;
+                    // LOG keeps the common factor (it does not cancel in log(sum)): subtract first
+                    const float arg = LOG ? (e[u][j] - m) * L : fmaf(e[u][j], L, nml);
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(arg));
+                    sum += p;
+                    if (!LOG) e[u][j] = p;
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < PACKS; ++u) {
+            if (first + step * u < packs) {
+#pragma unroll
+                for (int j = 0; j < N; ++j) {
+                    const A p = fexp(e[u][j] - m);
+                    sum += p;
+                    if (!LOG) e[u][j] = p;
+                }
+            }
+        }
+    }
+    sum = reduce_sum(sum);
+    const A k = LOG ? m + flog(sum) : A(1) / sum;
+#pragma unroll
+    for (int u = 0; u < PACKS; ++u) {
+        const uint32_t i = first + step * u;
+        if (i < packs) {
+            Pack<T> out;
+#pragma unroll
+            for (int j = 0; j < N; ++j) out.v[j] = Num<T>::down(LOG ? e[u][j] - k : e[u][j] * k);
+            row[i] = out;
+        }
+    }
+}
+
+// Short rows: one warp per row; the reductions are shuffles.  Needs 16-byte aligned rows (cols a
+// multiple of the pack size, aligned base).
 template <typename T, bool LOG, int PACKS>
 __global__ void __launch_bounds__(THREADS) row_softmax_warp_kernel(T *a, uint64_t rows, uint32_t cols) {
     using A = typename Num<T>::Acc;
-    constexpr int N = Pack<T>::N;
-    const uint32_t lane = threadIdx.x & 31u;
     const uint64_t row_id = uint64_t(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5);
     if (row_id >= rows) return;
-    Pack<T> *row = reinterpret_cast<Pack<T> *>(a + row_id * cols);
-    const uint32_t packs = cols / N;
-    Pack<T> buf[PACKS];
+    auto warp_max = [](A v) {
 #pragma unroll
-    for (int u = 0; u < PACKS; ++u) {
-        const uint32_t i = lane + 32u * u;
-        if (i < packs) buf[u] = row[i];
-    }
-    MaxSum<A> st = ms_empty<A>();
-#pragma unroll
-    for (int u = 0; u < PACKS; ++u) {
-        if (lane + 32u * u < packs) {
-            A vals[N];
-#pragma unroll
-            for (int j = 0; j < N; ++j) vals[j] = A(Num<T>::up(buf[u].v[j]));
-            ms_fold(st, vals);
+        for (int off = 16; off > 0; off >>= 1) {
+            const A o = __shfl_xor_sync(0xffffffffu, v, off);
+            v = o > v ? o : v;
         }
-    }
+        return v;
+    };
+    auto warp_sum = [](A v) {
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        MaxSum<A> o;
-        o.m = __shfl_xor_sync(0xffffffffu, st.m, off);
-        o.s = __shfl_xor_sync(0xffffffffu, st.s, off);
-        st = ms_merge(st, o);
-    }
-    const A denom = LOG ? flog(st.s) : A(1) / st.s;
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        return v;
+    };
+    row_in_registers<T, LOG, PACKS>(reinterpret_cast<Pack<T> *>(a + row_id * cols), cols / Pack<T>::N,
+                                    threadIdx.x & 31u, 32u, warp_max, warp_sum);
+}
+
+// Medium rows: one CTA per row; the partial results meet in shared memory.
+template <typename T, bool LOG, int PACKS>
+__global__ void __launch_bounds__(THREADS) row_softmax_cta_kernel(T *a, uint64_t rows, uint32_t cols) {
+    using A = typename Num<T>::Acc;
+    __shared__ A part[2][THREADS / 32];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    auto cta_max = [&](A v) {
 #pragma unroll
-    for (int u = 0; u < PACKS; ++u) {
-        const uint32_t i = lane + 32u * u;
-        if (i < packs) {
-#pragma unroll
-            for (int j = 0; j < N; ++j) buf[u].v[j] = finish<T, LOG>(buf[u].v[j], st.m, denom);
-            row[i] = buf[u];
+        for (int off = 16; off > 0; off >>= 1) {
+            const A o = __shfl_xor_sync(0xffffffffu, v, off);
+            v = o > v ? o : v;
         }
-    }
+        if (lane == 0) part[0][warp] = v;
+        __syncthreads();
+        A r = part[0][0];
+#pragma unroll
+        for (int w = 1; w < THREADS / 32; ++w) r = part[0][w] > r ? part[0][w] : r;
+        return r;
+    };
+    auto cta_sum = [&](A v) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) part[1][warp] = v;
+        __syncthreads();
+        A r = A(0);
+#pragma unroll
+        for (int w = 0; w < THREADS / 32; ++w) r += part[1][w];   // same order in every thread
+        return r;
+    };
+    if (blockIdx.x < rows)
+        row_in_registers<T, LOG, PACKS>(reinterpret_cast<Pack<T> *>(a + uint64_t(blockIdx.x) * cols), cols / Pack<T>::N,
+                                        threadIdx.x, uint32_t(THREADS), cta_max, cta_sum);
 }
 
 // ---- row scaling: b[r][c] = scale[r] * b[r][c], b row- or column-major -------------------------
@@ -403,10 +491,11 @@ static int softmax_t(int log_softmax, uint64_t rows, uint64_t cols, void *a, voi
     if (rows > 1) {
         if (rows > 0x7fffffffull) return fail(KLAS_ERR_TOO_LARGE, "softmax: too many rows");
         constexpr uint64_t N = Pack<T>::N;
-        if (cols % N == 0 && cols / N <= 32 * 8 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0) {
-            // warp per row, row held in registers: 2, 4 or 8 packs per lane
+        if (cols % N == 0 && cols / N <= 32 * 4 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0) {
+            // warp per row, row held in registers: 2 or 4 packs per lane (more costs occupancy: measured slower)
             const uint64_t per_lane = (cols / N + 31) / 32;
-            const unsigned grid = unsigned((rows + THREADS / 32 - 1) / (THREADS / 32));
+            const uint64_t ctas = (rows + THREADS / 32 - 1) / (THREADS / 32);
+            const unsigned grid = unsigned(ctas);
 #define KLAS_ROW_WARP(P)                                                                                   \
     do {                                                                                                   \
         if (log_softmax)                                                                                   \
@@ -415,10 +504,26 @@ static int softmax_t(int log_softmax, uint64_t rows, uint64_t cols, void *a, voi
             row_softmax_warp_kernel<T, false, P><<<grid, THREADS, 0, s>>>(p, rows, uint32_t(cols));        \
     } while (0)
             if (per_lane <= 2) KLAS_ROW_WARP(2);
-            else if (per_lane <= 4) KLAS_ROW_WARP(4);
-            else KLAS_ROW_WARP(8);
+            else KLAS_ROW_WARP(4);
 #undef KLAS_ROW_WARP
             return check_cuda(cudaGetLastError(), "row_softmax_warp_kernel launch");
+        }
+        if (cols % N == 0 && cols / N <= uint64_t(THREADS) * 8 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0) {
+            // CTA per row, row held in registers: 2, 4 or 8 packs per thread
+            const uint64_t per_thread = (cols / N + THREADS - 1) / THREADS;
+            const unsigned grid = unsigned(rows);
+#define KLAS_ROW_CTA(P)                                                                                    \
+    do {                                                                                                   \
+        if (log_softmax)                                                                                   \
+            row_softmax_cta_kernel<T, true, P><<<grid, THREADS, 0, s>>>(p, rows, uint32_t(cols));          \
+        else                                                                                               \
+            row_softmax_cta_kernel<T, false, P><<<grid, THREADS, 0, s>>>(p, rows, uint32_t(cols));         \
+    } while (0)
+            if (per_thread <= 2) KLAS_ROW_CTA(2);
+            else if (per_thread <= 4) KLAS_ROW_CTA(4);
+            else KLAS_ROW_CTA(8);
+#undef KLAS_ROW_CTA
+            return check_cuda(cudaGetLastError(), "row_softmax_cta_kernel launch");
         }
         if (log_softmax)
             row_softmax_kernel<T, true><<<unsigned(rows), THREADS, 0, s>>>(p, cols);

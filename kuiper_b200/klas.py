@@ -229,7 +229,7 @@ def gemm_strided(A: torch.Tensor, B: torch.Tensor, C_: torch.Tensor, *, alpha=No
 _MAPS = {None: _lib.MAP_ID, "id": _lib.MAP_ID, "sqrt": _lib.MAP_SQRT, "abs": _lib.MAP_ABS,
          "square": _lib.MAP_SQUARE, "relu": _lib.MAP_RELU, "neg": _lib.MAP_NEG}
 _COMBS = {"new": _lib.COMB_NEW, "axpby": _lib.COMB_AXPBY, "max": _lib.COMB_MAX, "min": _lib.COMB_MIN,
-          "mul": _lib.COMB_MUL, "relu": _lib.COMB_RELU}
+          "mul": _lib.COMB_MUL, "relu": _lib.COMB_RELU, "scaled": _lib.COMB_SCALED}
 
 
 def gemm_tc(A: torch.Tensor, B: torch.Tensor, *, out_dtype=torch.float32, b_col_major: bool = False,
@@ -241,7 +241,7 @@ def gemm_tc(A: torch.Tensor, B: torch.Tensor, *, out_dtype=torch.float32, b_col_
     `b_col_major`.  Returns D (allocated when not given; pass D=C_ to accumulate in place).
 
     Fused hooks: `map_a` / `map_b` in {"sqrt", "abs", "square", "relu", "neg"} are applied to the
-    operands inside the kernel; `comb` in {"new", "axpby", "max", "min", "mul", "relu"} says how
+    operands inside the kernel; `comb` in {"new", "axpby", "max", "min", "mul", "relu", "scaled"} says how
     the product meets C_ (default: "axpby" with C_, "new" without)."""
     if A.dtype not in (torch.bfloat16, torch.float16) or B.dtype != A.dtype:
         raise TypeError("A and B must both be bf16 or both be f16")

@@ -80,7 +80,7 @@ def test_f16_sqrt_a_is_the_reference_demo(oracle, rows, shared, cols):
     assert rel_err_componentwise(D.double().cpu().numpy(), demo.numpy(), demo_scale) <= 2 ** -10
 
 
-@pytest.mark.parametrize("comb", ["max", "min", "mul", "relu", "axpby", "new"])
+@pytest.mark.parametrize("comb", ["max", "min", "mul", "relu", "axpby", "new", "scaled"])
 @pytest.mark.parametrize("rows,shared,cols", [(192, 80, 328), (1024, 256, 512)])
 def test_combine_rules(oracle, comb, rows, shared, cols):
     A, Bm = synth.gemm_bf16(13, rows, cols, shared, b_col_major=False, device="cuda")
@@ -88,12 +88,15 @@ def test_combine_rules(oracle, comb, rows, shared, cols):
     acc, scale = tc_reference(oracle, A.cpu(), Bm.cpu(), False)
     c = C.double().cpu().numpy()
     want = {"max": np.maximum(c, acc), "min": np.minimum(c, acc), "mul": c * acc, "relu": np.maximum(acc, 0),
-            "axpby": 0.5 * acc - 2.0 * c, "new": acc}[comb]
+            "axpby": 0.5 * acc - 2.0 * c, "new": acc, "scaled": 0.5 * acc}[comb]
     bound = {"mul": scale * np.abs(c), "axpby": 0.5 * scale + 2.0 * np.abs(c)}.get(comb, scale + (np.abs(c) if comb in ("max", "min") else 0))
     D = klas.gemm_tc(A, Bm, out_dtype=torch.float32, C_=C, D=torch.empty_like(C), alpha=0.5, beta=-2.0, comb=comb)
     torch.cuda.synchronize()
     assert rel_err_componentwise(D.cpu().numpy(), want, bound) <= 1e-5
-    if comb in ("new", "relu"):
+    if comb in ("new", "relu", "scaled"):
+        if comb == "scaled":
+            assert klas.gemm_tc(A, Bm, out_dtype=torch.float32, alpha=0.5, comb=comb).equal(D)
+            return
         assert klas.gemm_tc(A, Bm, out_dtype=torch.float32, comb=comb).equal(D)   # C is not read
 
 

@@ -27,7 +27,7 @@ def want_f64(A, B, C, map_a, map_b, comb, alpha, beta):
     acc = a @ b
     scale = a.abs() @ b.abs()
     out = {"new": acc, "axpby": alpha * acc + beta * c, "max": torch.maximum(c, acc), "min": torch.minimum(c, acc),
-           "mul": c * acc, "relu": torch.clamp(acc, min=0)}[comb]
+           "mul": c * acc, "relu": torch.clamp(acc, min=0), "scaled": alpha * acc}[comb]
     bound = {"axpby": abs(alpha) * scale + abs(beta) * c.abs(), "mul": scale * c.abs()}.get(comb, scale + c.abs())
     return out, bound
 
@@ -40,14 +40,15 @@ def want_f64(A, B, C, map_a, map_b, comb, alpha, beta):
     (1, 130, 40, 300, 304, 40, 44),
 ])
 @pytest.mark.parametrize("map_a,map_b,comb", [(None, None, "new"), ("sqrt", "abs", "axpby"), ("square", "neg", "max"),
-                                              ("relu", None, "mul"), (None, "relu", "relu"), ("abs", "abs", "min")])
+                                              ("relu", None, "mul"), (None, "relu", "relu"), ("abs", "abs", "min"), (None, None, "scaled")])
 def test_float_pages(dtype, tol, batch, m, n, k, lda, ldb, ldc, map_a, map_b, comb):
     A, _ = padded(1, batch, m, k, lda, 8, dtype, positive=map_a == "sqrt")
     B, _ = padded(2, batch, k, n, ldb, 4, dtype)
     C, cflat = padded(3, batch, m, n, ldc, 12, dtype)
     before = cflat.clone()
     want, bound = want_f64(A, B, C, map_a, map_b, comb, 0.75, -1.5)
-    klas.gemm_strided(A, B, C, alpha=0.75 if comb == "axpby" else None, beta=-1.5 if comb == "axpby" else None,
+    klas.gemm_strided(A, B, C, alpha=0.75 if comb in ("axpby", "scaled") else None,
+                      beta=-1.5 if comb == "axpby" else 0.0 if comb == "scaled" else None,
                       map_a=map_a, map_b=map_b, comb=comb)
     torch.cuda.synchronize()
     err = ((C.double().cpu() - want).abs() / bound.clamp(min=1e-300)).max()

@@ -27,6 +27,24 @@ def test_gemm_tc_host_row_chunks(rows, shared, cols, with_c):
         assert torch.equal(hD, want)
 
 
+@pytest.mark.parametrize("rows,shared,cols", [(4096, 256, 4096), (4608, 136, 4360), (8192, 64, 4104)])
+@pytest.mark.parametrize("b_col_major", [True, False])
+def test_gemm_tc_host_two_dimensional_schedule(rows, shared, cols, b_col_major):
+    """Large single products without C are sent as alternating row blocks of A and column blocks of B, each
+    arrival followed by the products it completes; every element is still one ascending-k accumulation, so
+    the result equals the device entry point's bit for bit."""
+    A, Bm = synth.gemm_bf16(6, rows, cols, shared, b_col_major=b_col_major)
+    want = klas.gemm_tc(A.cuda(), Bm.cuda(), b_col_major=b_col_major).cpu()
+    hA, hB, hD = A.pin_memory(), Bm.pin_memory(), torch.empty((rows, cols)).pin_memory()
+    lib = _lib.load()
+    for _ in range(2):
+        hD.fill_(-1)
+        _lib.check(lib.klas_b200_gemm_tc_host(_lib.BF16, _lib.F32, _lib.B_COL_MAJOR if b_col_major else _lib.B_ROW_MAJOR,
+                                              1, rows, shared, cols, hA.data_ptr(), hB.data_ptr(), None, hD.data_ptr(),
+                                              1.0, 0.0))
+        assert torch.equal(hD, want)
+
+
 def test_gemm_tc_host_batched_pages():
     batch, m, n, k = 11, 128, 136, 72
     A, B = synth.gemm_f16_batched(2, batch, m, n, k)

@@ -37,7 +37,9 @@ def test_vector_softmax(oracle, dtype, n, log):
 @pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("rows,cols", [(1, 33), (5, 1), (64, 1000), (300, 257), (7, 70000),
                                        # rows held in registers by one warp: 1 to 8 packs per lane, ragged last pack
-                                       (3, 8), (1000, 64), (77, 256), (515, 1024), (33, 2048), (9, 1016), (2, 4096)])
+                                       (3, 8), (1000, 64), (77, 256), (515, 1024), (33, 2048), (9, 1016), (2, 4096),
+                                       # rows held in registers by one CTA (2 to 8 packs per thread), then beyond that
+                                       (5, 8192), (3, 16384), (2, 12296), (2, 32768), (2, 70008)])
 @pytest.mark.parametrize("log", [False, True])
 def test_row_softmax(oracle, dtype, rows, cols, log):
     x = values(rows + cols, rows, cols, dtype=dtype)

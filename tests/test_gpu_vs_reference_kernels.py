@@ -106,6 +106,46 @@ def test_graph_distance_step_bit_exact(ref, top):
             "ring_ops": 2 * n ** 3}
 
 
+def test_row_wise_neighbours_against_the_reference_kernels(ref):
+    """Vector softmax, row softmax, row scale and sum: same inputs through both libraries."""
+    n = 1 << 22
+    x = (synth.normal(41, 11, 0, n, dtype=torch.float32, device="cuda") * 4.0)
+    mine, theirs = x.clone(), x.clone()
+    klas.softmax(mine)
+    f = ref.fn("Klas_Softmax_softmax_gpu_f32", [C.c_uint32, C.c_void_p])
+    f(n, theirs.data_ptr())
+    torch.cuda.synchronize()
+    # the reference sums 4M exponentials in f32, one long chain per thread: its own denominator is only good to ~1e-5
+    assert float((mine - theirs).abs().max()) <= 2e-5 * float(theirs.max())
+    TIMINGS["softmax_f32_4M"] = {"ours_kernel_ms": event_ms(lambda: klas.softmax(mine)),
+                                 "ref_call_ms": wall_ms(lambda: f(n, theirs.data_ptr())), "elements": n}
+
+    rows, cols = 4096, 1024
+    m = synth.normal(42, 11, 0, rows * cols, dtype=torch.float32, device="cuda").reshape(rows, cols) * 3.0
+    mine, theirs = m.clone(), m.clone()
+    klas.softmax(mine)
+    g = ref.fn("Klas_RowSoftmax_row_softmax_rm_f32", [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p])
+    g(rows, cols, 256, theirs.data_ptr())
+    torch.cuda.synchronize()
+    assert float((mine - theirs).abs().max()) <= 2e-6
+    TIMINGS["row_softmax_f32_4096x1024"] = {"ours_kernel_ms": event_ms(lambda: klas.softmax(mine)),
+                                            "ref_call_ms": wall_ms(lambda: g(rows, cols, 256, theirs.data_ptr()))}
+
+    sc = synth.normal(43, 11, 0, rows, dtype=torch.float32, device="cuda")
+    mine, theirs = m.clone(), m.clone()
+    klas.rowscale(sc, mine)
+    h = ref.fn("Klas_RowScale_rowscale_f32_rowmajor", [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p])
+    h(rows, cols, sc.data_ptr(), theirs.data_ptr())
+    torch.cuda.synchronize()
+    assert torch.equal(mine, theirs)
+
+    r = ref.fn("Klas_HReduce_reduce_f32_plus", [C.c_uint32, C.c_uint32, C.c_void_p])
+    r.restype = C.c_float
+    total_ref = r(256, n, x.data_ptr())
+    total = klas.reduce_sum(x).item()
+    assert abs(total - total_ref) <= 2e-6 * float(x.abs().sum())
+
+
 def test_u64_bit_exact(ref):
     n = 1024
     a, b = synth.gemm_u64(3, n, n, n, full_range=True, device="cuda")
