@@ -337,6 +337,19 @@ int klas_b200_sdpa(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e
                    void *out, float scale, void *stream);
 
 /*
+ * The same attention in ONE kernel that never writes the scores to global memory (running row
+ * maximum and sum, as in the reference's Kuiper.Kernel.FlashAttention,
+ * src/lib/kernel/Kuiper.Kernel.FlashAttention.fst): O = softmax(scale * Q.K^T).V per head, no
+ * bias.  Q [pages][l][e], K [pages][s][e], V [pages][s][e], out [pages][l][e], row-major,
+ * contiguous, 16-byte aligned, dtype KLAS_F16 or KLAS_BF16; e = 64 or 128 (other head
+ * dimensions: KLAS_ERR_UNSUPPORTED, use klas_b200_sdpa).  Any l and s >= 1.  fp32 accumulation and
+ * fp32 softmax statistics; probabilities are rounded to `dtype` before they multiply V.  A
+ * bounded device-side wait that gives up is reported by klas_b200_gemm_tc_status().
+ */
+int klas_b200_sdpa_fused(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e,
+                         const void *Q, const void *K, const void *V, void *out, float scale, void *stream);
+
+/*
  * b[r][c] = scale[r] * b[r][c] for the m x n matrix b, row-major (col_major == 0) or
  * column-major.  Replaces: Klas_RowScale_rowscale_*_{rowmajor,colmajor} (dist/Klas_RowScale.h:7-23).
  */

@@ -33,6 +33,7 @@ SIGNATURES = {
     "klas_b200_csr_row_order": (_int, [_u32, _vp, _vp, _vp, C.c_size_t, _vp]),
     "klas_b200_minplus_u16": (_int, [_u32, _u32, _u32, _vp, _vp, _vp, _vp]),
     "klas_b200_sdpa": (_int, [_int, _u32, _u64, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _int, _vp, _f32, _vp]),
+    "klas_b200_sdpa_fused": (_int, [_int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _f32, _vp]),
     "klas_b200_gemm_tc_fused": (_int, [_int, _int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp,
                                         _f32, _f32, _int, _int, _int, _vp, _vp]),
     "klas_b200_gemm_tc_status": (_int, [C.POINTER(_int)]),

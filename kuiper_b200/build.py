@@ -19,7 +19,7 @@ LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libklas_b200.so"
 INCLUDE_DIR = REPO_DIR / "include"
 
-SOURCES = ["abi.cu", "gemm_umma.cu", "gemm_simt.cu", "spmm.cu", "rowops.cu", "minplus.cu", "csr_build.cu", "gemm_dmma.cu"]
+SOURCES = ["abi.cu", "gemm_umma.cu", "gemm_simt.cu", "spmm.cu", "rowops.cu", "minplus.cu", "csr_build.cu", "gemm_dmma.cu", "attention.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -224,6 +224,12 @@ int klas_b200_sdpa(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e
                             nullptr, st);
 }
 
+int klas_b200_sdpa_fused(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e, const void *Q, const void *K,
+                         const void *V, void *out, float scale, void *stream) {
+    clear_error();
+    return launch_sdpa_fused(dtype, pages, l, s, e, Q, K, V, out, scale, static_cast<cudaStream_t>(stream));
+}
+
 int klas_b200_gemm_tc_status(int *site) {
     clear_error();
     int v = 0;

@@ -1,0 +1,418 @@
+// Fused scaled-dot-product attention for sm_100a:  O = softmax(scale * Q.K^T) . V  per head,
+// without ever writing the score matrix to global memory.
+//
+// One CTA owns 128 query rows of one head and walks the keys 128 at a time:
+//   warp 0      TMA producer: Q once, then K and V tiles through a two-stage ring;
+//   warp 1      owns tensor memory and issues the MMAs from one thread: S_j = Q.K_j^T into one of
+//               two 128-column score buffers (so S_(j+1) is being multiplied while the softmax
+//               warps work on S_j), and O_j = P_j.V_j into a third region;
+//   warps 2-5   one thread per query row (= one TMEM lane): read the row of S_j twice (maximum,
+//               then exponentials), keep the running maximum m and sum l, write P_j = exp(S_j - m)
+//               as a 16-bit, 128-byte-swizzled A operand into shared memory, and fold the finished
+//               O_(j-1) into a register accumulator rescaled to the new maximum.
+// K is a K-major B operand (its rows are the columns of K^T), V an MN-major one, P a K-major A
+// operand: the three layouts the GEMM kernel uses, with the same descriptors.
+// Exponentials are ex2 of a pre-scaled argument (scale * log2 e folded into one multiply).
+// All hand-offs are mbarriers with bounded waits; a wait that gives up raises the library's
+// tensor-core status word and every role drains.
+//
+// Takes over the work of the reference's attention kernels, which exist in its F* sources only:
+// src/lib/kernel/Kuiper.Kernel.SDPA.Naive.fst:390-470 (GEMM, row softmax, GEMM through global
+// memory) and src/lib/kernel/Kuiper.Kernel.FlashAttention.fst (one thread block per query tile,
+// running maximum and sum per row).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "klas_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace klas {
+namespace fa {
+
+constexpr uint32_t BM = 128;          // query rows per CTA (= TMEM lanes)
+constexpr uint32_t BN = 128;          // keys per step
+constexpr uint32_t THREADS = 192;
+constexpr uint32_t STAGES = 2;
+constexpr uint32_t ATOM_BYTES = 128 * 128;   // 128 rows x one 128-byte swizzle row
+constexpr uint32_t TMEM_COLS = 512;          // S0 at 0, S1 at 128, O at 256
+constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
+
+enum : int { SITE_FA = 0x200 };
+
+template <uint32_t E>
+struct Cfg {
+    static constexpr uint32_t ATOMS = E / 64;             // swizzle atoms along the head dimension
+    static constexpr uint32_t TILE_BYTES = ATOMS * ATOM_BYTES;   // a 128 x E tile of Q, K or V
+    static constexpr uint32_t P_BYTES = 2 * ATOM_BYTES;   // 128 x 128 probabilities
+    static constexpr uint32_t SMEM = TILE_BYTES * (1 + 2 * STAGES) + P_BYTES + 256 + 1024;
+};
+
+struct Params {
+    void *out;
+    uint32_t L, S, pages, num_kv;
+    float scale_log2;      // scale * log2(e)
+    uint32_t idesc_qk, idesc_pv;
+    uint32_t bf16;
+    int *status;           // the library's tensor-core status word
+};
+
+struct Ctl {
+    volatile int *abort_flag;
+    int *status;
+};
+
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const Ctl &ctl, int site, uint32_t backoff_ns = 0) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if (backoff_ns) __nanosleep(backoff_ns);
+        if ((++spins & 0x3F) == 0) {
+            if (*ctl.abort_flag != 0) return false;
+            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *ctl.abort_flag = 1;
+                if (ctl.status) atomicCAS(ctl.status, 0, SITE_FA | site);
+                __threadfence();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, bool bf16) {
+    if (bf16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&v);
+    }
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+template <uint32_t E>
+__global__ void __launch_bounds__(THREADS, 1)
+    sdpa_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const Params p) {
+    using C = Cfg<E>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t *smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    const uint32_t q_base = smem_base;
+    auto k_base = [&](uint32_t s) { return smem_base + C::TILE_BYTES * (1 + s); };
+    auto v_base = [&](uint32_t s) { return smem_base + C::TILE_BYTES * (1 + STAGES + s); };
+    const uint32_t p_base = smem_base + C::TILE_BYTES * (1 + 2 * STAGES);
+    const uint32_t bar_base = p_base + C::P_BYTES;
+    uint8_t *bar_region = smem + C::TILE_BYTES * (1 + 2 * STAGES) + C::P_BYTES;
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_full, o_full
+    const uint32_t q_full = bar_base;
+    auto k_full = [&](uint32_t s) { return bar_base + 8u * (1 + s); };
+    auto k_empty = [&](uint32_t s) { return bar_base + 8u * (3 + s); };
+    auto v_full = [&](uint32_t s) { return bar_base + 8u * (5 + s); };
+    auto v_empty = [&](uint32_t s) { return bar_base + 8u * (7 + s); };
+    auto s_full = [&](uint32_t b) { return bar_base + 8u * (9 + b); };
+    auto s_free = [&](uint32_t b) { return bar_base + 8u * (11 + b); };
+    const uint32_t p_full = bar_base + 8u * 13;
+    const uint32_t o_full = bar_base + 8u * 14;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_region + 8u * 15);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tiles_q = (p.L + BM - 1) / BM;
+    const uint32_t page = blockIdx.x / tiles_q;
+    const uint32_t q0 = (blockIdx.x % tiles_q) * BM;
+    const Ctl ctl{abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(q_full, 1);
+        for (uint32_t s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(k_full(s), 1);
+            ptx::mbar_init(k_empty(s), 1);
+            ptx::mbar_init(v_full(s), 1);
+            ptx::mbar_init(v_empty(s), 1);
+            ptx::mbar_init(s_full(s), 1);
+            ptx::mbar_init(s_free(s), 4);   // one arrival per softmax warp
+        }
+        ptx::mbar_init(p_full, 4);
+        ptx::mbar_init(o_full, 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tm_q);
+        ptx::prefetch_tensormap(&tm_k);
+        ptx::prefetch_tensormap(&tm_v);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (one thread)
+        if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(q_full, C::TILE_BYTES);
+            for (uint32_t a = 0; a < C::ATOMS; ++a)
+                ptx::tma_load_3d(q_base + a * ATOM_BYTES, &tm_q, q_full, int32_t(a * 64), int32_t(q0), int32_t(page));
+            bool ok = true;
+            for (uint32_t j = 0; ok && j < p.num_kv; ++j) {
+                const uint32_t st = j % STAGES, ph = (j / STAGES) & 1u;
+                ok = bounded_wait(k_empty(st), ph ^ 1u, ctl, 0x11, 64);
+                if (!ok) break;
+                ptx::mbar_arrive_expect_tx(k_full(st), C::TILE_BYTES);
+                for (uint32_t a = 0; a < C::ATOMS; ++a)
+                    ptx::tma_load_3d(k_base(st) + a * ATOM_BYTES, &tm_k, k_full(st), int32_t(a * 64), int32_t(j * BN), int32_t(page));
+                ok = bounded_wait(v_empty(st), ph ^ 1u, ctl, 0x12, 64);
+                if (!ok) break;
+                ptx::mbar_arrive_expect_tx(v_full(st), C::TILE_BYTES);
+                for (uint32_t a = 0; a < C::ATOMS; ++a)
+                    ptx::tma_load_3d(v_base(st) + a * ATOM_BYTES, &tm_v, v_full(st), int32_t(a * 64), int32_t(j * BN), int32_t(page));
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (one thread)
+        if (lane == 0) {
+            const uint64_t kmajor = ptx::umma_desc_base_sw128(16, 1024);
+            const uint64_t mnmajor = ptx::umma_desc_base_sw128(ATOM_BYTES, 1024);   // next 64 columns: one slab further
+            // S_j = Q.K_j^T: E / 16 steps; step kk reads 16 head-dimension elements (32 bytes) of atom kk / 4
+            auto issue_qk = [&](uint32_t j) {
+                const uint32_t st = j % STAGES;
+#pragma unroll
+                for (uint32_t kk = 0; kk < E / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * ATOM_BYTES + (kk % 4) * 32u;
+                    ptx::umma_f16_ss(tmem_base + (j & 1u) * BN, ptx::umma_desc_at(kmajor, q_base + off),
+                                     ptx::umma_desc_at(kmajor, k_base(st) + off), p.idesc_qk, kk != 0 ? 1u : 0u);
+                }
+                ptx::umma_commit(k_empty(st));
+                ptx::umma_commit(s_full(j & 1u));
+            };
+            bool ok = bounded_wait(q_full, 0, ctl, 0x21);
+            if (ok && p.num_kv > 0) {
+                ok = bounded_wait(k_full(0), 0, ctl, 0x22);
+                if (ok) issue_qk(0);
+            }
+            for (uint32_t j = 0; ok && j < p.num_kv; ++j) {
+                const uint32_t st = j % STAGES, ph = (j / STAGES) & 1u;
+                if (j + 1 < p.num_kv) {
+                    // the other score buffer was last used by tile j - 1
+                    if (j >= 1) {
+                        ok = bounded_wait(s_free((j + 1) & 1u), ((j - 1) / 2) & 1u, ctl, 0x23);
+                        if (!ok) break;
+                        ptx::tc_fence_after_sync();
+                    }
+                    ok = bounded_wait(k_full((j + 1) % STAGES), ((j + 1) / STAGES) & 1u, ctl, 0x24);
+                    if (!ok) break;
+                    issue_qk(j + 1);
+                }
+                ok = bounded_wait(p_full, j & 1u, ctl, 0x25);
+                if (!ok) break;
+                ok = bounded_wait(v_full(st), ph, ctl, 0x26);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                // O_j = P_j.V_j: 8 steps of 16 keys; P is K-major (two atoms of 64 keys), V MN-major (16 key rows = 2048 bytes)
+#pragma unroll
+                for (uint32_t kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t p_off = (kk / 4) * ATOM_BYTES + (kk % 4) * 32u;
+                    ptx::umma_f16_ss(tmem_base + 2 * BN, ptx::umma_desc_at(kmajor, p_base + p_off),
+                                     ptx::umma_desc_at(mnmajor, v_base(st) + kk * 2048u), p.idesc_pv, kk != 0 ? 1u : 0u);
+                }
+                ptx::umma_commit(v_empty(st));
+                ptx::umma_commit(o_full);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ softmax, one thread per query row
+        const uint32_t quad = warp & 3u;
+        const uint32_t r = quad * 32u + lane;                     // row of the tile = TMEM lane
+        const uint32_t lane_addr = (quad * 32u) << 16;
+        const bool bf16 = p.bf16 != 0;
+        float m = -INFINITY, l = 0.0f;
+        float o[E];
+#pragma unroll
+        for (uint32_t i = 0; i < E; ++i) o[i] = 0.0f;
+        bool ok = true;
+        // adds the finished O tile to the register accumulator
+        auto take_o = [&]() {
+#pragma unroll
+            for (uint32_t c = 0; c < E / 32; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(tmem_base + lane_addr + 2 * BN + c * 32u, v);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (uint32_t i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(v[i]);
+            }
+        };
+        for (uint32_t j = 0; ok && j < p.num_kv; ++j) {
+            const uint32_t sb = j & 1u;
+            ok = lane != 0 || bounded_wait(s_full(sb), (j / 2) & 1u, ctl, 0x31, 32);
+            ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t s_addr = tmem_base + lane_addr + sb * BN;
+            const uint32_t valid = p.S - j * BN;                  // keys of this tile that exist (>= 128: all)
+            // pass 1: the row maximum of the scaled scores
+            float mx = -INFINITY;
+#pragma unroll
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(s_addr + c * 32u, v);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (uint32_t i = 0; i < 32; ++i) {
+                    const float x = (c * 32 + i < valid) ? __uint_as_float(v[i]) * p.scale_log2 : -INFINITY;
+                    mx = fmaxf(mx, x);
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            const float alpha = ex2(m - m_new);                   // 0 on the first tile (m = -inf)
+            // the previous tile's P.V must be done before P is overwritten; fold it in at the old scale
+            if (j > 0) {
+                ok = lane != 0 || bounded_wait(o_full, (j - 1) & 1u, ctl, 0x32, 32);
+                ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                take_o();
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < E; ++i) o[i] *= alpha;
+            l *= alpha;
+            // pass 2: exponentials, row sum, P as a swizzled 16-bit A operand
+#pragma unroll
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(s_addr + c * 32u, v);
+                ptx::tmem_ld_wait();
+                float e[32];
+#pragma unroll
+                for (uint32_t i = 0; i < 32; ++i) {
+                    e[i] = (c * 32 + i < valid) ? ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_new)) : 0.0f;
+                    l += e[i];
+                }
+#pragma unroll
+                for (uint32_t q = 0; q < 4; ++q) {                 // four 16-byte pieces of 8 keys
+                    uint32_t w[4];
+#pragma unroll
+                    for (uint32_t h = 0; h < 4; ++h) w[h] = pack16(e[q * 8 + 2 * h], e[q * 8 + 2 * h + 1], bf16);
+                    const uint32_t piece = c * 4 + q;               // 0..15 along the keys
+                    const uint32_t addr = p_base + (piece / 8) * ATOM_BYTES + r * 128u + (((piece % 8) ^ (r & 7u)) * 16u);
+                    ptx::sts128(addr, w);
+                }
+            }
+            m = m_new;
+            // this score buffer may be multiplied into again; P is ready for the tensor core
+            ptx::tc_fence_before_sync();
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::mbar_arrive(s_free(sb));
+                ptx::mbar_arrive(p_full);
+            }
+        }
+        if (ok && p.num_kv > 0) {
+            ok = lane != 0 || bounded_wait(o_full, (p.num_kv - 1) & 1u, ctl, 0x33, 32);
+            ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+            if (ok) {
+                ptx::tc_fence_after_sync();
+                take_o();
+            }
+        }
+        if (ok && q0 + r < p.L) {
+            const float inv = p.num_kv > 0 ? 1.0f / l : 0.0f;
+            uint32_t *dst = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.out) + (size_t(page) * p.L + q0 + r) * E * 2);
+#pragma unroll
+            for (uint32_t i = 0; i < E / 8; ++i) {
+                uint4 w;
+                w.x = pack16(o[8 * i + 0] * inv, o[8 * i + 1] * inv, bf16);
+                w.y = pack16(o[8 * i + 2] * inv, o[8 * i + 3] * inv, bf16);
+                w.z = pack16(o[8 * i + 4] * inv, o[8 * i + 5] * inv, bf16);
+                w.w = pack16(o[8 * i + 6] * inv, o[8 * i + 7] * inv, bf16);
+                reinterpret_cast<uint4 *>(dst)[i] = w;
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        if (*abort_flag != 0) {
+            for (int i = 0; i < 256; ++i) __nanosleep(1000);   // let copies and MMAs in flight land
+        }
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace fa
+
+int umma_status_address(int **out);
+int make_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t inner, uint64_t outer, uint64_t batch,
+                       uint32_t box_inner, uint32_t box_outer);
+
+template <uint32_t E>
+static int launch_sdpa_e(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const fa::Params &p,
+                         unsigned grid, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    KLAS_TRY_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        KLAS_TRY_CUDA(cudaFuncSetAttribute(fa::sdpa_fused_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           int(fa::Cfg<E>::SMEM)));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    fa::sdpa_fused_kernel<E><<<grid, fa::THREADS, fa::Cfg<E>::SMEM, stream>>>(tq, tk, tv, p);
+    return check_cuda(cudaGetLastError(), "sdpa_fused_kernel launch");
+}
+
+int launch_sdpa_fused(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e, const void *Q, const void *K,
+                      const void *V, void *out, float scale, cudaStream_t stream) {
+    if (dtype != KLAS_F16 && dtype != KLAS_BF16) return fail(KLAS_ERR_INVALID, "sdpa_fused: dtype must be KLAS_F16 or KLAS_BF16");
+    if (e != 64 && e != 128) return fail(KLAS_ERR_UNSUPPORTED, "sdpa_fused: head dimension %llu (64 and 128 are built)", (unsigned long long)e);
+    if (pages == 0 || l == 0) return KLAS_OK;
+    if (s == 0) return fail(KLAS_ERR_INVALID, "sdpa_fused: no keys (s == 0)");
+    if (!Q || !K || !V || !out) return fail(KLAS_ERR_INVALID, "sdpa_fused: null pointer");
+    if ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V) |
+         reinterpret_cast<uintptr_t>(out)) & 15u)
+        return fail(KLAS_ERR_INVALID, "sdpa_fused: Q, K, V and out must be 16-byte aligned");
+    if (l > 0x7fffffffull || s > 0x7fffffffull) return fail(KLAS_ERR_TOO_LARGE, "sdpa_fused: dimension beyond 2^31-1");
+    DeviceInfo info;
+    if (int rc = device_info(&info)) return rc;
+    if (info.cc_major != 10) return fail(KLAS_ERR_UNSUPPORTED, "sdpa_fused needs an sm_100 device");
+    const uint64_t tiles_q = (l + fa::BM - 1) / fa::BM;
+    if (tiles_q * pages > 0x7fffffffull) return fail(KLAS_ERR_TOO_LARGE, "sdpa_fused: too many query tiles for one grid");
+    fa::Params p{};
+    p.out = out;
+    p.L = uint32_t(l);
+    p.S = uint32_t(s);
+    p.pages = pages;
+    p.num_kv = uint32_t((s + fa::BN - 1) / fa::BN);
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.bf16 = dtype == KLAS_BF16 ? 1u : 0u;
+    p.idesc_qk = ptx::umma_idesc_f16(dtype == KLAS_BF16, false, false, fa::BM, fa::BN);
+    p.idesc_pv = ptx::umma_idesc_f16(dtype == KLAS_BF16, false, true, fa::BM, uint32_t(e));
+    if (int rc = umma_status_address(&p.status)) return rc;
+    CUtensorMap tq{}, tk{}, tv{};
+    if (int rc = make_tensor_map_3d(&tq, dtype, Q, e, l, pages, 64, fa::BM)) return rc;
+    if (int rc = make_tensor_map_3d(&tk, dtype, K, e, s, pages, 64, fa::BN)) return rc;
+    if (int rc = make_tensor_map_3d(&tv, dtype, V, e, s, pages, 64, fa::BN)) return rc;
+    const unsigned grid = unsigned(tiles_q * pages);
+    return e == 64 ? launch_sdpa_e<64>(tq, tk, tv, p, grid, stream) : launch_sdpa_e<128>(tq, tk, tv, p, grid, stream);
+}
+
+}  // namespace klas

@@ -1233,6 +1233,20 @@ int umma_wait_probe(uint32_t limit_ms, int *gave_up, cudaStream_t stream) {
     return check_cuda(cudaGetLastError(), "wait_probe_kernel launch");
 }
 
+// Device address of the status word, for other kernels of the library that use bounded waits.
+int umma_status_address(int **out) {
+    void *ptr = nullptr;
+    KLAS_TRY_CUDA(cudaGetSymbolAddress(&ptr, umma::g_umma_status));
+    *out = static_cast<int *>(ptr);
+    return KLAS_OK;
+}
+
+// 3-D tiled tensor map with 128-byte swizzle (see umma::make_map), for the attention kernel.
+int make_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t inner, uint64_t outer, uint64_t batch,
+                       uint32_t box_inner, uint32_t box_outer) {
+    return umma::make_map(map, dtype, base, inner, outer, batch, box_inner, box_outer);
+}
+
 int umma_read_status(int *value) {
     return check_cuda(cudaMemcpyFromSymbol(value, umma::g_umma_status, sizeof(int)),
                       "cudaMemcpyFromSymbol(status)");

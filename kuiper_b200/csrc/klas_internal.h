@@ -76,6 +76,9 @@ int launch_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32
                 const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
                 const uint32_t *row_indices, const void *B, void *C, cudaStream_t stream);
 
+int launch_sdpa_fused(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e, const void *Q, const void *K,
+                      const void *V, void *out, float scale, cudaStream_t stream);
+
 int launch_minplus_u16(uint32_t m, uint32_t n, uint32_t k, const uint16_t *A, const uint16_t *B, uint16_t *C,
                        cudaStream_t stream);
 

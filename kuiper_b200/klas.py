@@ -119,6 +119,27 @@ def gemm(A: torch.Tensor, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
     return C_
 
 
+def sdpa_fused(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, scale: Optional[float] = None) -> torch.Tensor:
+    """softmax(scale * Q.K^T).V per head in one kernel (scores never leave the chip).  Q [..., l, e],
+    K [..., s, e], V [..., s, e], f16 or bf16, contiguous, e = 64 or 128.  scale defaults to 1/sqrt(e)."""
+    if Q.dtype not in (torch.float16, torch.bfloat16) or K.dtype != Q.dtype or V.dtype != Q.dtype:
+        raise TypeError("sdpa_fused needs f16 or bf16 tensors of one dtype")
+    lead = tuple(Q.shape[:-2])
+    l, e = Q.shape[-2:]
+    s = K.shape[-2]
+    if tuple(K.shape) != lead + (s, e) or tuple(V.shape) != lead + (s, e):
+        raise ValueError("shapes do not match: %s %s %s" % (tuple(Q.shape), tuple(K.shape), tuple(V.shape)))
+    pages = 1
+    for d in lead:
+        pages *= d
+    out = torch.empty_like(Q)
+    with torch.cuda.device(Q.device):
+        check(_lib.load().klas_b200_sdpa_fused(_code(Q), pages, l, s, e, _dev(Q, "Q"), _dev(K, "K"), _dev(V, "V"),
+                                               _dev(out, "out"), float(scale if scale is not None else e ** -0.5),
+                                               _stream()))
+    return out
+
+
 def sdpa(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
          scale: Optional[float] = None, scores: Optional[torch.Tensor] = None) -> torch.Tensor:
     """softmax(scale * Q.K^T + bias).V per head.  Q [..., l, e], K [..., s, e], V [..., s, ev] (f16 or

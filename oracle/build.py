@@ -130,7 +130,34 @@ def build_ref_drivers(ref_root: Path, force: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
         exes = list(ex.map(one, srcs))
+    build_ref_tuning_drivers(ref_root, force)
     return out_dir if exes else out_dir
+
+
+# The reference's tuning drivers (test/Tune_*.cu) take the entry point to time as -Dstem=<name>
+# (tuning/tune_b2d.sh, tune_tc2d.sh, tune_spmm.sh); one representative stem each is enough to show
+# that they build and run against this library unchanged.
+TUNING_DRIVERS = {
+    "Tune_Klas_GEMM_BlockTiling2D": ("Klas_GEMM_BlockTiling2D", "Klas_GEMM_BlockTiling2D_g_gemm_f32_128x128x32_8x8"),
+    "Tune_Klas_GEMM_TensorCore2D": ("Klas_GEMM_TensorCore2D", "Klas_GEMM_TensorCore2D_g_gemm_f16_f16_128x128x32_16x16x16_2x2"),
+    "Tune_Klas_SPMM": ("Klas_SPMM", "Klas_SPMM_g_spmm_f32_16x16x16"),
+}
+
+
+def build_ref_tuning_drivers(ref_root: Path, force: bool = False) -> Path:
+    from kuiper_b200 import build as lib_build
+    out_dir = REF_DIR / "tune"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    inc = REPO_DIR / "include"
+    for name, (unit, stem) in TUNING_DRIVERS.items():
+        src, exe = ref_root / "test" / (name + ".cu"), out_dir / (name + ".exe")
+        if not src.exists() or (not force and exe.exists() and exe.stat().st_mtime >= lib_build.COMPAT_LIB.stat().st_mtime):
+            continue
+        _run(["nvcc", "-O3", *ARCH, "-DKUIPER_CFG_TENSORCORES=1", "-Dstem=" + stem, "-Dtile_sizes=", "-Dtc_tile_sizes=",
+              "-Dregch_sizes=", "-Det_lbl=", "-I", inc / "klas", "-I", ref_root / "test", "-o", exe, src,
+              lib_build.COMPAT_OUT / (unit + ".o"), "-L", lib_build.LIB_DIR, "-lklas_b200",
+              "-Xlinker", "-rpath=$ORIGIN/../../../kuiper_b200/lib"])
+    return out_dir
 
 
 def main(argv=None) -> int:

@@ -30,3 +30,19 @@ def test_all_hot_path_drivers_are_covered():
     if DRIVERS.exists():
         built = {p.stem for p in DRIVERS.glob("*.exe")}
         assert built == set(EXPECTED)
+
+
+@pytest.mark.parametrize("name,args,stem", [
+    ("Tune_Klas_GEMM_BlockTiling2D", ["3", "1024", "1024", "1024", "1"], "Klas_GEMM_BlockTiling2D_g_gemm_f32_128x128x32_8x8"),
+    ("Tune_Klas_GEMM_TensorCore2D", ["3", "1024", "1024", "1024", "1"], "Klas_GEMM_TensorCore2D_g_gemm_f16_f16_128x128x32_16x16x16_2x2"),
+    ("Tune_Klas_SPMM", ["3", "2048", "2048", "512", "5"], "Klas_SPMM_g_spmm_f32_16x16x16"),
+])
+def test_tuning_driver_runs_unchanged(name, args, stem):
+    """The reference's tuning harness (test/Tune_*.cu, compiled with -Dstem=<entry point> as tuning/*.sh do)
+    against this library: exits 0 and reports a timing line for the entry point."""
+    exe = REPO / "oracle" / "_ref" / "tune" / (name + ".exe")
+    if not exe.exists():
+        pytest.skip("tuning driver not built (the reference tree was not available at build time)")
+    r = subprocess.run([str(exe)] + args, capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, (r.stdout[-1000:], r.stderr[-1000:])
+    assert ">> RES" in r.stderr + r.stdout and stem in r.stderr + r.stdout

@@ -46,6 +46,42 @@ def test_matches_float64_attention(dtype, tol, lead, l, s, e, ev, with_bias):
         assert float((buf.double().cpu().sum(-1) - 1).abs().max()) <= 64 * tol
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 2e-3), (torch.bfloat16, 1.6e-2)])
+@pytest.mark.parametrize("lead,l,s,e", [((1,), 128, 128, 64), ((1,), 128, 128, 128), ((2, 3), 200, 264, 128), ((4,), 1024, 1024, 128),
+                                        ((1, 2), 77, 2056, 64), ((1,), 64, 4096, 64), ((2,), 130, 1, 64), ((1,), 1, 300, 128),
+                                        ((3,), 384, 129, 128)])
+def test_fused_kernel_matches_float64_attention(dtype, tol, lead, l, s, e):
+    """One kernel, scores never in global memory: against plain float64 attention (no intermediate roundings)."""
+    Q, K, V = (tensor(10 + i, *lead, r, e, dtype=dtype) for i, r in enumerate([l, s, s]))
+    scale = e ** -0.5
+    S = scale * (Q.double() @ K.double().transpose(-1, -2))
+    P = torch.softmax(S, dim=-1)
+    want = P @ V.double()
+    out = klas.sdpa_fused(Q.cuda(), K.cuda(), V.cuda(), scale=scale)
+    torch.cuda.synchronize()
+    assert klas.gemm_tc_status() == 0
+    bound = (P @ V.double().abs()).clamp(min=1e-30)
+    err = float(((out.double().cpu() - want).abs() / bound).max())
+    assert err <= tol, err
+
+
+def test_fused_kernel_with_a_peaked_distribution():
+    # large scores: the running maximum moves from tile to tile and old sums are rescaled
+    dtype = torch.float16
+    Q, K, V = tensor(20, 2, 256, 64, dtype=dtype, spread=3.0), tensor(21, 2, 1000, 64, dtype=dtype, spread=3.0), tensor(22, 2, 1000, 64, dtype=dtype)
+    P = torch.softmax(1.0 * (Q.double() @ K.double().transpose(-1, -2)), dim=-1)
+    want = P @ V.double()
+    out = klas.sdpa_fused(Q.cuda(), K.cuda(), V.cuda(), scale=1.0)
+    bound = (P @ V.double().abs()).clamp(min=1e-30)
+    assert float(((out.double().cpu() - want).abs() / bound).max()) <= 2e-3
+
+
+def test_fused_kernel_rejects_other_head_dimensions():
+    Q = torch.zeros((1, 8, 96), dtype=torch.float16, device="cuda")
+    with pytest.raises(klas.KlasError):
+        klas.sdpa_fused(Q, Q, Q)
+
+
 def test_probabilities_ignore_masked_keys():
     dtype = torch.float16
     Q, K, V = tensor(1, 2, 64, 64, dtype=dtype), tensor(2, 2, 256, 64, dtype=dtype), tensor(3, 2, 256, 64, dtype=dtype)
