@@ -6,10 +6,14 @@
 //   warp 1      owns tensor memory and issues the MMAs from one thread: S_j = Q.K_j^T into one of
 //               two 128-column score buffers (so S_(j+1) is being multiplied while the softmax
 //               warps work on S_j), and O_j = P_j.V_j into a third region;
-//   warps 2-5   one thread per query row (= one TMEM lane): read the row of S_j twice (maximum,
-//               then exponentials), keep the running maximum m and sum l, write P_j = exp(S_j - m)
-//               as a 16-bit, 128-byte-swizzled A operand into shared memory, and fold the finished
-//               O_(j-1) into a register accumulator rescaled to the new maximum.
+//   warps 2-9   two threads per query row (= TMEM lane), one for keys 0-63 of the tile and columns
+//               0 .. E/2 of O, one for the other halves: read their part of the row of S_j twice
+//               (maximum, then exponentials), exchange the partial maxima through shared memory,
+//               keep the running maximum m and a partial sum l, write P_j = exp(S_j - m) as a 16-bit,
+//               128-byte-swizzled A operand into shared memory, and fold the finished O_(j-1) into a
+//               register accumulator rescaled to the new maximum.  (With one thread per row the four
+//               warps -- one per scheduler, nothing to hide latency with -- took three times as long
+//               per tile as the tensor core.)
 // K is a K-major B operand (its rows are the columns of K^T), V an MN-major one, P a K-major A
 // operand: the three layouts the GEMM kernel uses, with the same descriptors.
 // Exponentials are ex2 of a pre-scaled argument (scale * log2 e folded into one multiply).
@@ -33,7 +37,8 @@ namespace fa {
 
 constexpr uint32_t BM = 128;          // query rows per CTA (= TMEM lanes)
 constexpr uint32_t BN = 128;          // keys per step
-constexpr uint32_t THREADS = 192;
+constexpr uint32_t SOFTMAX_WARPS = 8;
+constexpr uint32_t THREADS = (2 + SOFTMAX_WARPS) * 32;
 constexpr uint32_t STAGES = 2;
 constexpr uint32_t ATOM_BYTES = 128 * 128;   // 128 rows x one 128-byte swizzle row
 constexpr uint32_t TMEM_COLS = 512;          // S0 at 0, S1 at 128, O at 256
@@ -46,7 +51,10 @@ struct Cfg {
     static constexpr uint32_t ATOMS = E / 64;             // swizzle atoms along the head dimension
     static constexpr uint32_t TILE_BYTES = ATOMS * ATOM_BYTES;   // a 128 x E tile of Q, K or V
     static constexpr uint32_t P_BYTES = 2 * ATOM_BYTES;   // 128 x 128 probabilities
-    static constexpr uint32_t SMEM = TILE_BYTES * (1 + 2 * STAGES) + P_BYTES + 256 + 1024;
+    // (value, tag) words the two threads of a row exchange: partial maxima [tile parity][key half][row],
+    // then the partial sums [key half][row]
+    static constexpr uint32_t XCHG_BYTES = (2 * 2 * BM + 2 * BM) * 8;
+    static constexpr uint32_t SMEM = TILE_BYTES * (1 + 2 * STAGES) + P_BYTES + XCHG_BYTES + 256 + 1024;
 };
 
 struct Params {
@@ -111,8 +119,11 @@ __global__ void __launch_bounds__(THREADS, 1)
     auto k_base = [&](uint32_t s) { return smem_base + C::TILE_BYTES * (1 + s); };
     auto v_base = [&](uint32_t s) { return smem_base + C::TILE_BYTES * (1 + STAGES + s); };
     const uint32_t p_base = smem_base + C::TILE_BYTES * (1 + 2 * STAGES);
-    const uint32_t bar_base = p_base + C::P_BYTES;
-    uint8_t *bar_region = smem + C::TILE_BYTES * (1 + 2 * STAGES) + C::P_BYTES;
+    volatile unsigned long long *xchg =
+        reinterpret_cast<volatile unsigned long long *>(smem + C::TILE_BYTES * (1 + 2 * STAGES) + C::P_BYTES);
+    for (uint32_t i = threadIdx.x; i < C::XCHG_BYTES / 8; i += THREADS) xchg[i] = 0ull;   // tag 0 = nothing yet
+    const uint32_t bar_base = p_base + C::P_BYTES + C::XCHG_BYTES;
+    uint8_t *bar_region = smem + C::TILE_BYTES * (1 + 2 * STAGES) + C::P_BYTES + C::XCHG_BYTES;
     // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_full, o_full
     const uint32_t q_full = bar_base;
     auto k_full = [&](uint32_t s) { return bar_base + 8u * (1 + s); };
@@ -140,9 +151,9 @@ __global__ void __launch_bounds__(THREADS, 1)
             ptx::mbar_init(v_full(s), 1);
             ptx::mbar_init(v_empty(s), 1);
             ptx::mbar_init(s_full(s), 1);
-            ptx::mbar_init(s_free(s), 4);   // one arrival per softmax warp
+            ptx::mbar_init(s_free(s), SOFTMAX_WARPS);   // one arrival per softmax warp
         }
-        ptx::mbar_init(p_full, 4);
+        ptx::mbar_init(p_full, SOFTMAX_WARPS);
         ptx::mbar_init(o_full, 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -237,22 +248,46 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ softmax, one thread per query row
+        // ------------------------------------------------------------ softmax, two threads per query row
         const uint32_t quad = warp & 3u;
+        const uint32_t half = (warp - 2u) >> 2;                   // 0: keys 0-63, O columns [0, E/2); 1: the rest
         const uint32_t r = quad * 32u + lane;                     // row of the tile = TMEM lane
         const uint32_t lane_addr = (quad * 32u) << 16;
         const bool bf16 = p.bf16 != 0;
+        constexpr uint32_t EH = E / 2;                            // O columns per thread
         float m = -INFINITY, l = 0.0f;
-        float o[E];
+        float o[EH];
 #pragma unroll
-        for (uint32_t i = 0; i < E; ++i) o[i] = 0.0f;
+        for (uint32_t i = 0; i < EH; ++i) o[i] = 0.0f;
         bool ok = true;
-        // adds the finished O tile to the register accumulator
+        // The two threads of a row trade a float through shared memory: each publishes (value, tag)
+        // in its slot and polls the partner's slot for the same tag -- a bounded wait like all the
+        // others (a hardware barrier between the two warps could not be left if the partner gave up).
+        auto trade = [&](volatile unsigned long long *mine, volatile unsigned long long *theirs, float value, uint32_t tag,
+                         float &got) -> bool {
+            *mine = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(value);
+            for (uint32_t spins = 0;; ++spins) {
+                const unsigned long long w = *theirs;
+                if (uint32_t(w >> 32) == tag) {
+                    got = __uint_as_float(uint32_t(w));
+                    return true;
+                }
+                if ((spins & 0x3F) == 0x3F) {
+                    if (*ctl.abort_flag != 0) return false;
+                    if (spins > (1u << 24)) {
+                        *ctl.abort_flag = 1;
+                        if (ctl.status) atomicCAS(ctl.status, 0, SITE_FA | 0x34);
+                        return false;
+                    }
+                }
+            }
+        };
+        // adds this thread's columns of the finished O tile to the register accumulator
         auto take_o = [&]() {
 #pragma unroll
-            for (uint32_t c = 0; c < E / 32; ++c) {
+            for (uint32_t c = 0; c < EH / 32; ++c) {
                 uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(tmem_base + lane_addr + 2 * BN + c * 32u, v);
+                ptx::tmem_ld_32x32b_x32(tmem_base + lane_addr + 2 * BN + half * EH + c * 32u, v);
                 ptx::tmem_ld_wait();
 #pragma unroll
                 for (uint32_t i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(v[i]);
@@ -264,22 +299,31 @@ __global__ void __launch_bounds__(THREADS, 1)
             ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
             if (!ok) break;
             ptx::tc_fence_after_sync();
-            const uint32_t s_addr = tmem_base + lane_addr + sb * BN;
-            const uint32_t valid = p.S - j * BN;                  // keys of this tile that exist (>= 128: all)
-            // pass 1: the row maximum of the scaled scores
+            const uint32_t s_addr = tmem_base + lane_addr + sb * BN + half * 64u;
+            const uint32_t left = p.S - j * BN;                                   // keys that exist from this tile on
+            const uint32_t valid = left > half * 64u ? left - half * 64u : 0u;   // ... among this thread's 64
+            const bool full = valid >= 64u;
+            // pass 1: maximum of the raw scores (the scale is positive, so it commutes with max)
             float mx = -INFINITY;
 #pragma unroll
-            for (uint32_t c = 0; c < BN / 32; ++c) {
+            for (uint32_t c = 0; c < 2; ++c) {
                 uint32_t v[32];
                 ptx::tmem_ld_32x32b_x32(s_addr + c * 32u, v);
                 ptx::tmem_ld_wait();
+                if (full) {
 #pragma unroll
-                for (uint32_t i = 0; i < 32; ++i) {
-                    const float x = (c * 32 + i < valid) ? __uint_as_float(v[i]) * p.scale_log2 : -INFINITY;
-                    mx = fmaxf(mx, x);
+                    for (uint32_t i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                } else {
+#pragma unroll
+                    for (uint32_t i = 0; i < 32; ++i) mx = fmaxf(mx, (c * 32 + i < valid) ? __uint_as_float(v[i]) : -INFINITY);
                 }
             }
-            const float m_new = fmaxf(m, mx);
+            float other_mx;
+            ok = trade(xchg + (sb * 2 + half) * BM + r, xchg + (sb * 2 + (half ^ 1u)) * BM + r, mx, j + 1, other_mx);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            mx = fmaxf(mx, other_mx);
+            const float m_new = fmaxf(m, mx * p.scale_log2);
             const float alpha = ex2(m - m_new);                   // 0 on the first tile (m = -inf)
             // the previous tile's P.V must be done before P is overwritten; fold it in at the old scale
             if (j > 0) {
@@ -290,18 +334,19 @@ __global__ void __launch_bounds__(THREADS, 1)
                 take_o();
             }
 #pragma unroll
-            for (uint32_t i = 0; i < E; ++i) o[i] *= alpha;
+            for (uint32_t i = 0; i < EH; ++i) o[i] *= alpha;
             l *= alpha;
             // pass 2: exponentials, row sum, P as a swizzled 16-bit A operand
 #pragma unroll
-            for (uint32_t c = 0; c < BN / 32; ++c) {
+            for (uint32_t c = 0; c < 2; ++c) {
                 uint32_t v[32];
                 ptx::tmem_ld_32x32b_x32(s_addr + c * 32u, v);
                 ptx::tmem_ld_wait();
                 float e[32];
 #pragma unroll
                 for (uint32_t i = 0; i < 32; ++i) {
-                    e[i] = (c * 32 + i < valid) ? ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_new)) : 0.0f;
+                    const float x = ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_new));
+                    e[i] = (full || c * 32 + i < valid) ? x : 0.0f;
                     l += e[i];
                 }
 #pragma unroll
@@ -309,8 +354,8 @@ __global__ void __launch_bounds__(THREADS, 1)
                     uint32_t w[4];
 #pragma unroll
                     for (uint32_t h = 0; h < 4; ++h) w[h] = pack16(e[q * 8 + 2 * h], e[q * 8 + 2 * h + 1], bf16);
-                    const uint32_t piece = c * 4 + q;               // 0..15 along the keys
-                    const uint32_t addr = p_base + (piece / 8) * ATOM_BYTES + r * 128u + (((piece % 8) ^ (r & 7u)) * 16u);
+                    const uint32_t piece = c * 4 + q;               // 0..7 inside this thread's atom of 64 keys
+                    const uint32_t addr = p_base + half * ATOM_BYTES + r * 128u + ((piece ^ (r & 7u)) * 16u);
                     ptx::sts128(addr, w);
                 }
             }
@@ -332,11 +377,18 @@ __global__ void __launch_bounds__(THREADS, 1)
                 take_o();
             }
         }
+        if (ok) {
+            // the row sum is the sum of the two partial sums (both at the final maximum)
+            float other_l;
+            ok = trade(xchg + (4 + half) * BM + r, xchg + (4 + (half ^ 1u)) * BM + r, l, 1u, other_l);
+            l += other_l;
+        }
         if (ok && q0 + r < p.L) {
             const float inv = p.num_kv > 0 ? 1.0f / l : 0.0f;
-            uint32_t *dst = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.out) + (size_t(page) * p.L + q0 + r) * E * 2);
+            uint32_t *dst = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.out) +
+                                                         ((size_t(page) * p.L + q0 + r) * E + half * EH) * 2);
 #pragma unroll
-            for (uint32_t i = 0; i < E / 8; ++i) {
+            for (uint32_t i = 0; i < EH / 8; ++i) {
                 uint4 w;
                 w.x = pack16(o[8 * i + 0] * inv, o[8 * i + 1] * inv, bf16);
                 w.y = pack16(o[8 * i + 2] * inv, o[8 * i + 3] * inv, bf16);
