@@ -342,7 +342,7 @@ int klas_b200_sdpa(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e
  * src/lib/kernel/Kuiper.Kernel.FlashAttention.fst): O = softmax(scale * Q.K^T).V per head, no
  * bias.  Q [pages][l][e], K [pages][s][e], V [pages][s][e], out [pages][l][e], row-major,
  * contiguous, 16-byte aligned, dtype KLAS_F16 or KLAS_BF16; e = 64 or 128 (other head
- * dimensions: KLAS_ERR_UNSUPPORTED, use klas_b200_sdpa).  Any l and s >= 1.  fp32 accumulation and
+ * dimensions: KLAS_ERR_UNSUPPORTED, use klas_b200_sdpa).  Any l and s >= 1; scale > 0.  fp32 accumulation and
  * fp32 softmax statistics; probabilities are rounded to `dtype` before they multiply V.  A
  * bounded device-side wait that gives up is reported by klas_b200_gemm_tc_status().
  */

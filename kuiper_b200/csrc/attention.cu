@@ -9,9 +9,10 @@
 //   warps 2-9   two threads per query row (= TMEM lane), one for keys 0-63 of the tile and columns
 //               0 .. E/2 of O, one for the other halves: read their part of the row of S_j twice
 //               (maximum, then exponentials), exchange the partial maxima through shared memory,
-//               keep the running maximum m and a partial sum l, write P_j = exp(S_j - m) as a 16-bit,
-//               128-byte-swizzled A operand into shared memory, and fold the finished O_(j-1) into a
-//               register accumulator rescaled to the new maximum.  (With one thread per row the four
+//               keep a reference point m and a partial sum l, write P_j = exp(S_j - m) as a 16-bit,
+//               128-byte-swizzled A operand into shared memory.  O accumulates in tensor memory across
+//               the tiles; m follows the running maximum only in steps of 2^8 or more, and only then
+//               are O (tcgen05.ld / st) and l rescaled.  (With one thread per row the four
 //               warps -- one per scheduler, nothing to hide latency with -- took three times as long
 //               per tile as the tensor core.)
 // K is a K-major B operand (its rows are the columns of K^T), V an MN-major one, P a K-major A
@@ -235,12 +236,12 @@ __global__ void __launch_bounds__(THREADS, 1)
                 ok = bounded_wait(v_full(st), ph, ctl, 0x26);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-                // O_j = P_j.V_j: 8 steps of 16 keys; P is K-major (two atoms of 64 keys), V MN-major (16 key rows = 2048 bytes)
+                // O += P_j.V_j: 8 steps of 16 keys; P is K-major (two atoms of 64 keys), V MN-major (16 key rows = 2048 bytes)
 #pragma unroll
                 for (uint32_t kk = 0; kk < BN / 16; ++kk) {
                     const uint32_t p_off = (kk / 4) * ATOM_BYTES + (kk % 4) * 32u;
                     ptx::umma_f16_ss(tmem_base + 2 * BN, ptx::umma_desc_at(kmajor, p_base + p_off),
-                                     ptx::umma_desc_at(mnmajor, v_base(st) + kk * 2048u), p.idesc_pv, kk != 0 ? 1u : 0u);
+                                     ptx::umma_desc_at(mnmajor, v_base(st) + kk * 2048u), p.idesc_pv, (j | kk) != 0 ? 1u : 0u);
                 }
                 ptx::umma_commit(v_empty(st));
                 ptx::umma_commit(o_full);
@@ -255,10 +256,8 @@ __global__ void __launch_bounds__(THREADS, 1)
         const uint32_t lane_addr = (quad * 32u) << 16;
         const bool bf16 = p.bf16 != 0;
         constexpr uint32_t EH = E / 2;                            // O columns per thread
+        const uint32_t o_addr = tmem_base + lane_addr + 2 * BN + half * EH;
         float m = -INFINITY, l = 0.0f;
-        float o[EH];
-#pragma unroll
-        for (uint32_t i = 0; i < EH; ++i) o[i] = 0.0f;
         bool ok = true;
         // The two threads of a row trade a float through shared memory: each publishes (value, tag)
         // in its slot and polls the partner's slot for the same tag -- a bounded wait like all the
@@ -282,16 +281,12 @@ __global__ void __launch_bounds__(THREADS, 1)
                 }
             }
         };
-        // adds this thread's columns of the finished O tile to the register accumulator
-        auto take_o = [&]() {
-#pragma unroll
-            for (uint32_t c = 0; c < EH / 32; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(tmem_base + lane_addr + 2 * BN + half * EH + c * 32u, v);
-                ptx::tmem_ld_wait();
-#pragma unroll
-                for (uint32_t i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(v[i]);
-            }
+        // waits (once per tile) until P.V of tile `tile` has completed: O is up to date, P may be rewritten
+        auto wait_pv = [&](uint32_t tile, int site) -> bool {
+            bool w = lane != 0 || bounded_wait(o_full, tile & 1u, ctl, site, 32);
+            w = __shfl_sync(0xffffffffu, int(w), 0) != 0;
+            if (w) ptx::tc_fence_after_sync();
+            return w;
         };
         for (uint32_t j = 0; ok && j < p.num_kv; ++j) {
             const uint32_t sb = j & 1u;
@@ -302,99 +297,116 @@ __global__ void __launch_bounds__(THREADS, 1)
             const uint32_t s_addr = tmem_base + lane_addr + sb * BN + half * 64u;
             const uint32_t left = p.S - j * BN;                                   // keys that exist from this tile on
             const uint32_t valid = left > half * 64u ? left - half * 64u : 0u;   // ... among this thread's 64
-            const bool full = valid >= 64u;
-            // pass 1: maximum of the raw scores (the scale is positive, so it commutes with max)
-            float mx = -INFINITY;
+            // This thread's 64 scores, read once (both loads in flight together) and kept in registers.
+            uint32_t sv[2][32];
+            ptx::tmem_ld_32x32b_x32(s_addr, sv[0]);
+            ptx::tmem_ld_32x32b_x32(s_addr + 32u, sv[1]);
+            ptx::tmem_ld_wait();
+            if (valid < 64u) {
 #pragma unroll
-            for (uint32_t c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(s_addr + c * 32u, v);
-                ptx::tmem_ld_wait();
-                if (full) {
+                for (uint32_t c = 0; c < 2; ++c)
 #pragma unroll
-                    for (uint32_t i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                } else {
-#pragma unroll
-                    for (uint32_t i = 0; i < 32; ++i) mx = fmaxf(mx, (c * 32 + i < valid) ? __uint_as_float(v[i]) : -INFINITY);
-                }
+                    for (uint32_t i = 0; i < 32; ++i)
+                        if (c * 32 + i >= valid) sv[c][i] = 0xff800000u;   // -inf: exp gives 0, max ignores it
             }
+            // the score buffer may be multiplied into again
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(s_free(sb));
+            // maximum of the raw scores (the scale is positive, so it commutes with max); four chains
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (uint32_t c = 0; c < 2; ++c)
+#pragma unroll
+                for (uint32_t i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             float other_mx;
             ok = trade(xchg + (sb * 2 + half) * BM + r, xchg + (sb * 2 + (half ^ 1u)) * BM + r, mx, j + 1, other_mx);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            mx = fmaxf(mx, other_mx);
-            const float m_new = fmaxf(m, mx * p.scale_log2);
-            const float alpha = ex2(m - m_new);                   // 0 on the first tile (m = -inf)
-            // the previous tile's P.V must be done before P is overwritten; fold it in at the old scale
-            if (j > 0) {
-                ok = lane != 0 || bounded_wait(o_full, (j - 1) & 1u, ctl, 0x32, 32);
-                ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
-                if (!ok) break;
-                ptx::tc_fence_after_sync();
-                take_o();
-            }
+            const float m_cand = fmaxf(m, fmaxf(mx, other_mx) * p.scale_log2);
+            // The reference point m only has to keep exp2(x - m) in range, so it is moved (and the sums
+            // so far rescaled) only when the maximum has grown by more than 2^8; until then P.V simply
+            // keeps accumulating into the same O in tensor memory and nobody has to touch it.
+            const bool move = m_cand - m > 8.0f;                  // true on the first tile (m = -inf)
+            bool pv_done = j == 0;
+            if (__any_sync(0xffffffffu, move)) {
+                const float alpha = move ? ex2(m - m_cand) : 1.0f;
+                if (move) m = m_cand;
+                l *= alpha;
+                if (j > 0) {
+                    ok = wait_pv(j - 1, 0x32);
+                    if (!ok) break;
+                    pv_done = true;
 #pragma unroll
-            for (uint32_t i = 0; i < EH; ++i) o[i] *= alpha;
-            l *= alpha;
-            // pass 2: exponentials, row sum, P as a swizzled 16-bit A operand
+                    for (uint32_t c = 0; c < EH / 32; ++c) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32b_x32(o_addr + c * 32u, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        ptx::tmem_st_32x32b_x32(o_addr + c * 32u, v);
+                    }
+                    ptx::tmem_st_wait();
+                    ptx::tc_fence_before_sync();
+                }
+            }
+            // exponentials and row sum (four chains); P packed to 16 bits in registers
+            uint32_t pw[8][4];
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (uint32_t c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(s_addr + c * 32u, v);
-                ptx::tmem_ld_wait();
                 float e[32];
 #pragma unroll
                 for (uint32_t i = 0; i < 32; ++i) {
-                    const float x = ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_new));
-                    e[i] = (full || c * 32 + i < valid) ? x : 0.0f;
-                    l += e[i];
+                    e[i] = ex2(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -m));
+                    l4[i & 3] += e[i];
                 }
 #pragma unroll
-                for (uint32_t q = 0; q < 4; ++q) {                 // four 16-byte pieces of 8 keys
-                    uint32_t w[4];
+                for (uint32_t q = 0; q < 4; ++q)
 #pragma unroll
-                    for (uint32_t h = 0; h < 4; ++h) w[h] = pack16(e[q * 8 + 2 * h], e[q * 8 + 2 * h + 1], bf16);
-                    const uint32_t piece = c * 4 + q;               // 0..7 inside this thread's atom of 64 keys
-                    const uint32_t addr = p_base + half * ATOM_BYTES + r * 128u + ((piece ^ (r & 7u)) * 16u);
-                    ptx::sts128(addr, w);
-                }
+                    for (uint32_t h = 0; h < 4; ++h) pw[c * 4 + q][h] = pack16(e[q * 8 + 2 * h], e[q * 8 + 2 * h + 1], bf16);
             }
-            m = m_new;
-            // this score buffer may be multiplied into again; P is ready for the tensor core
-            ptx::tc_fence_before_sync();
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            // P of the previous tile must have been consumed before it is overwritten
+            if (!pv_done) {
+                ok = wait_pv(j - 1, 0x35);
+                if (!ok) break;
+            }
+#pragma unroll
+            for (uint32_t piece = 0; piece < 8; ++piece)          // eight 16-byte pieces of 8 keys, swizzled A operand
+                ptx::sts128(p_base + half * ATOM_BYTES + r * 128u + ((piece ^ (r & 7u)) * 16u), pw[piece]);
             ptx::fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                ptx::mbar_arrive(s_free(sb));
-                ptx::mbar_arrive(p_full);
-            }
+            if (lane == 0) ptx::mbar_arrive(p_full);
         }
-        if (ok && p.num_kv > 0) {
-            ok = lane != 0 || bounded_wait(o_full, (p.num_kv - 1) & 1u, ctl, 0x33, 32);
-            ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
-            if (ok) {
-                ptx::tc_fence_after_sync();
-                take_o();
-            }
-        }
+        if (ok && p.num_kv > 0) ok = wait_pv(p.num_kv - 1, 0x33);
         if (ok) {
-            // the row sum is the sum of the two partial sums (both at the final maximum)
+            // the row sum is the sum of the two partial sums (both relative to the same m)
             float other_l;
             ok = trade(xchg + (4 + half) * BM + r, xchg + (4 + (half ^ 1u)) * BM + r, l, 1u, other_l);
             l += other_l;
         }
-        if (ok && q0 + r < p.L) {
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
             const float inv = p.num_kv > 0 ? 1.0f / l : 0.0f;
-            uint32_t *dst = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.out) +
-                                                         ((size_t(page) * p.L + q0 + r) * E + half * EH) * 2);
+            uint8_t *dst = static_cast<uint8_t *>(p.out) + ((size_t(page) * p.L + q0 + r) * E + half * EH) * 2;
 #pragma unroll
-            for (uint32_t i = 0; i < EH / 8; ++i) {
-                uint4 w;
-                w.x = pack16(o[8 * i + 0] * inv, o[8 * i + 1] * inv, bf16);
-                w.y = pack16(o[8 * i + 2] * inv, o[8 * i + 3] * inv, bf16);
-                w.z = pack16(o[8 * i + 4] * inv, o[8 * i + 5] * inv, bf16);
-                w.w = pack16(o[8 * i + 6] * inv, o[8 * i + 7] * inv, bf16);
-                reinterpret_cast<uint4 *>(dst)[i] = w;
+            for (uint32_t c = 0; c < EH / 32; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(o_addr + c * 32u, v);
+                ptx::tmem_ld_wait();
+                if (q0 + r < p.L) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        uint4 w;
+                        w.x = pack16(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv, bf16);
+                        w.y = pack16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv, bf16);
+                        w.z = pack16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv, bf16);
+                        w.w = pack16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv, bf16);
+                        reinterpret_cast<uint4 *>(dst + c * 64)[i] = w;
+                    }
+                }
             }
         }
     }
@@ -438,6 +450,7 @@ int launch_sdpa_fused(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_
     if (e != 64 && e != 128) return fail(KLAS_ERR_UNSUPPORTED, "sdpa_fused: head dimension %llu (64 and 128 are built)", (unsigned long long)e);
     if (pages == 0 || l == 0) return KLAS_OK;
     if (s == 0) return fail(KLAS_ERR_INVALID, "sdpa_fused: no keys (s == 0)");
+    if (!(scale > 0.0f) || !(scale < 3.0e38f)) return fail(KLAS_ERR_INVALID, "sdpa_fused: scale must be positive and finite");
     if (!Q || !K || !V || !out) return fail(KLAS_ERR_INVALID, "sdpa_fused: null pointer");
     if ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V) |
          reinterpret_cast<uintptr_t>(out)) & 15u)
