@@ -3,18 +3,23 @@
 //
 // One CTA owns 128 query rows of one head and walks the keys 128 at a time:
 //   warp 0      TMA producer: Q once, then K and V tiles through a two-stage ring;
-//   warp 1      owns tensor memory and issues the MMAs from one thread: S_j = Q.K_j^T into one of
-//               two 128-column score buffers (so S_(j+1) is being multiplied while the softmax
-//               warps work on S_j), and O_j = P_j.V_j into a third region;
-//   warps 2-9   two threads per query row (= TMEM lane), one for keys 0-63 of the tile and columns
+//   warp 1      owns tensor memory; one thread issues S_j = Q.K_j^T into one of two 128-column score
+//               buffers (so S_(j+1) is being multiplied while the softmax warps work on S_j);
+//   warp 2      one thread issues O += P_j.V_j into a third region of tensor memory;
+//   warps 3-10  two threads per query row (= TMEM lane), one for keys 0-63 of the tile and columns
 //               0 .. E/2 of O, one for the other halves: read their part of the row of S_j twice
 //               (maximum, then exponentials), exchange the partial maxima through shared memory,
 //               keep a reference point m and a partial sum l, write P_j = exp(S_j - m) as a 16-bit,
 //               128-byte-swizzled A operand into shared memory.  O accumulates in tensor memory across
 //               the tiles; m follows the running maximum only in steps of 2^8 or more, and only then
-//               are O (tcgen05.ld / st) and l rescaled.  (With one thread per row the four
-//               warps -- one per scheduler, nothing to hide latency with -- took three times as long
-//               per tile as the tensor core.)
+//               are O (tcgen05.ld / st) and l rescaled.
+// Where a tile's time goes (cycle counters of one softmax warp, -DKLAS_FA_PROFILE): of ~2950 cycles
+// per 128 x 128 tile at E = 128, 1340 are the exponentials -- the special-function unit's rate for
+// the two warps of a scheduler, 2 x 64 x 8 cycles -- and the rest is the serial chain around them
+// (wait for S and load it 540, maximum 200, exchange 300, wait for the previous P.V 275, store and
+// publish P 290); the tensor core needs 1024.  One thread per row took 3950 cycles, four per row
+// gained nothing over two, and issuing the two products from one thread or from two made no
+// difference: what is left is to run the exponentials of one tile under the bookkeeping of the next.
 // K is a K-major B operand (its rows are the columns of K^T), V an MN-major one, P a K-major A
 // operand: the three layouts the GEMM kernel uses, with the same descriptors.
 // Exponentials are ex2 of a pre-scaled argument (scale * log2 e folded into one multiply).
@@ -39,13 +44,24 @@ namespace fa {
 constexpr uint32_t BM = 128;          // query rows per CTA (= TMEM lanes)
 constexpr uint32_t BN = 128;          // keys per step
 constexpr uint32_t SOFTMAX_WARPS = 8;
-constexpr uint32_t THREADS = (2 + SOFTMAX_WARPS) * 32;
+constexpr uint32_t FIRST_SOFTMAX_WARP = 3;    // warp 0 producer, warp 1 Q.K^T issuer, warp 2 P.V issuer
+constexpr uint32_t THREADS = (FIRST_SOFTMAX_WARP + SOFTMAX_WARPS) * 32;
 constexpr uint32_t STAGES = 2;
 constexpr uint32_t ATOM_BYTES = 128 * 128;   // 128 rows x one 128-byte swizzle row
 constexpr uint32_t TMEM_COLS = 512;          // S0 at 0, S1 at 128, O at 256
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
 enum : int { SITE_FA = 0x200 };
+
+#ifdef KLAS_FA_PROFILE
+// Developer build only: cycles one softmax warp of CTA 0 spends in each phase of a tile.
+__device__ unsigned long long g_fa_prof[8];
+#define FA_T(n) const long long fa_t##n = clock64()
+#define FA_ACC(slot, a, b) fa_acc[slot] += (unsigned long long)(fa_t##b - fa_t##a)
+#else
+#define FA_T(n)
+#define FA_ACC(slot, a, b)
+#endif
 
 template <uint32_t E>
 struct Cfg {
@@ -197,13 +213,22 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (one thread)
+        // ------------------------------------------------------------ Q.K^T issuer (one thread)
+        // The two products are issued by two threads: one thread spends ~60 cycles per MMA and ~150 per
+        // commit, and sixteen N = 128 MMAs plus four commits per tile cost more than the MMAs take.
         if (lane == 0) {
             const uint64_t kmajor = ptx::umma_desc_base_sw128(16, 1024);
-            const uint64_t mnmajor = ptx::umma_desc_base_sw128(ATOM_BYTES, 1024);   // next 64 columns: one slab further
-            // S_j = Q.K_j^T: E / 16 steps; step kk reads 16 head-dimension elements (32 bytes) of atom kk / 4
-            auto issue_qk = [&](uint32_t j) {
+            bool ok = bounded_wait(q_full, 0, ctl, 0x21);
+            for (uint32_t j = 0; ok && j < p.num_kv; ++j) {
                 const uint32_t st = j % STAGES;
+                if (j >= 2) {   // this score buffer was last used by tile j - 2
+                    ok = bounded_wait(s_free(j & 1u), ((j - 2) / 2) & 1u, ctl, 0x23);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                }
+                ok = bounded_wait(k_full(st), (j / STAGES) & 1u, ctl, 0x24);
+                if (!ok) break;
+                // S_j = Q.K_j^T: E / 16 steps; step kk reads 16 head-dimension elements (32 bytes) of atom kk / 4
 #pragma unroll
                 for (uint32_t kk = 0; kk < E / 16; ++kk) {
                     const uint32_t off = (kk / 4) * ATOM_BYTES + (kk % 4) * 32u;
@@ -212,28 +237,20 @@ __global__ void __launch_bounds__(THREADS, 1)
                 }
                 ptx::umma_commit(k_empty(st));
                 ptx::umma_commit(s_full(j & 1u));
-            };
-            bool ok = bounded_wait(q_full, 0, ctl, 0x21);
-            if (ok && p.num_kv > 0) {
-                ok = bounded_wait(k_full(0), 0, ctl, 0x22);
-                if (ok) issue_qk(0);
             }
+        }
+        __syncwarp();
+    } else if (warp == 2) {
+        // ------------------------------------------------------------ P.V issuer (one thread)
+        if (lane == 0) {
+            const uint64_t kmajor = ptx::umma_desc_base_sw128(16, 1024);
+            const uint64_t mnmajor = ptx::umma_desc_base_sw128(ATOM_BYTES, 1024);   // next 64 columns: one slab further
+            bool ok = true;
             for (uint32_t j = 0; ok && j < p.num_kv; ++j) {
-                const uint32_t st = j % STAGES, ph = (j / STAGES) & 1u;
-                if (j + 1 < p.num_kv) {
-                    // the other score buffer was last used by tile j - 1
-                    if (j >= 1) {
-                        ok = bounded_wait(s_free((j + 1) & 1u), ((j - 1) / 2) & 1u, ctl, 0x23);
-                        if (!ok) break;
-                        ptx::tc_fence_after_sync();
-                    }
-                    ok = bounded_wait(k_full((j + 1) % STAGES), ((j + 1) / STAGES) & 1u, ctl, 0x24);
-                    if (!ok) break;
-                    issue_qk(j + 1);
-                }
+                const uint32_t st = j % STAGES;
                 ok = bounded_wait(p_full, j & 1u, ctl, 0x25);
                 if (!ok) break;
-                ok = bounded_wait(v_full(st), ph, ctl, 0x26);
+                ok = bounded_wait(v_full(st), (j / STAGES) & 1u, ctl, 0x26);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 // O += P_j.V_j: 8 steps of 16 keys; P is K-major (two atoms of 64 keys), V MN-major (16 key rows = 2048 bytes)
@@ -251,7 +268,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     } else {
         // ------------------------------------------------------------ softmax, two threads per query row
         const uint32_t quad = warp & 3u;
-        const uint32_t half = (warp - 2u) >> 2;                   // 0: keys 0-63, O columns [0, E/2); 1: the rest
+        const uint32_t half = (warp - FIRST_SOFTMAX_WARP) >> 2;   // 0: keys 0-63, O columns [0, E/2); 1: the rest
         const uint32_t r = quad * 32u + lane;                     // row of the tile = TMEM lane
         const uint32_t lane_addr = (quad * 32u) << 16;
         const bool bf16 = p.bf16 != 0;
@@ -288,8 +305,12 @@ __global__ void __launch_bounds__(THREADS, 1)
             if (w) ptx::tc_fence_after_sync();
             return w;
         };
+#ifdef KLAS_FA_PROFILE
+        unsigned long long fa_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
         for (uint32_t j = 0; ok && j < p.num_kv; ++j) {
             const uint32_t sb = j & 1u;
+            FA_T(0);
             ok = lane != 0 || bounded_wait(s_full(sb), (j / 2) & 1u, ctl, 0x31, 32);
             ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
             if (!ok) break;
@@ -302,6 +323,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             ptx::tmem_ld_32x32b_x32(s_addr, sv[0]);
             ptx::tmem_ld_32x32b_x32(s_addr + 32u, sv[1]);
             ptx::tmem_ld_wait();
+            FA_T(1);
             if (valid < 64u) {
 #pragma unroll
                 for (uint32_t c = 0; c < 2; ++c)
@@ -321,9 +343,11 @@ __global__ void __launch_bounds__(THREADS, 1)
                 for (uint32_t i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             float other_mx;
+            FA_T(2);
             ok = trade(xchg + (sb * 2 + half) * BM + r, xchg + (sb * 2 + (half ^ 1u)) * BM + r, mx, j + 1, other_mx);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            FA_T(3);
             const float m_cand = fmaxf(m, fmaxf(mx, other_mx) * p.scale_log2);
             // The reference point m only has to keep exp2(x - m) in range, so it is moved (and the sums
             // so far rescaled) only when the maximum has grown by more than 2^8; until then P.V simply
@@ -369,17 +393,32 @@ __global__ void __launch_bounds__(THREADS, 1)
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             // P of the previous tile must have been consumed before it is overwritten
+            FA_T(4);
             if (!pv_done) {
                 ok = wait_pv(j - 1, 0x35);
                 if (!ok) break;
             }
+            FA_T(5);
 #pragma unroll
             for (uint32_t piece = 0; piece < 8; ++piece)          // eight 16-byte pieces of 8 keys, swizzled A operand
                 ptx::sts128(p_base + half * ATOM_BYTES + r * 128u + ((piece ^ (r & 7u)) * 16u), pw[piece]);
+            FA_T(6);
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(p_full);
+            FA_T(7);
+            FA_ACC(0, 0, 1);   // wait for S + load
+            FA_ACC(1, 1, 2);   // mask, release, max
+            FA_ACC(2, 2, 3);   // trade
+            FA_ACC(3, 3, 4);   // rescale decision, exponentials, packing
+            FA_ACC(4, 4, 5);   // wait for the previous P.V
+            FA_ACC(5, 5, 6);   // stores of P
+            FA_ACC(6, 6, 7);   // fence + arrive
         }
+#ifdef KLAS_FA_PROFILE
+        if (blockIdx.x == 0 && warp == FIRST_SOFTMAX_WARP && lane == 0)
+            for (int i = 0; i < 8; ++i) g_fa_prof[i] = fa_acc[i];
+#endif
         if (ok && p.num_kv > 0) ok = wait_pv(p.num_kv - 1, 0x33);
         if (ok) {
             // the row sum is the sum of the two partial sums (both relative to the same m)
@@ -424,6 +463,12 @@ __global__ void __launch_bounds__(THREADS, 1)
 }
 
 }  // namespace fa
+
+#ifdef KLAS_FA_PROFILE
+extern "C" int klas_dev_read_fa_profile(unsigned long long *out) {
+    return cudaMemcpyFromSymbol(out, fa::g_fa_prof, sizeof(unsigned long long) * 8) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int umma_status_address(int **out);
 int make_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t inner, uint64_t outer, uint64_t batch,
