@@ -144,10 +144,12 @@ def sdpa(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, bias: Optional[torch
          scale: Optional[float] = None, scores: Optional[torch.Tensor] = None) -> torch.Tensor:
     """softmax(scale * Q.K^T + bias).V per head.  Q [..., l, e], K [..., s, e], V [..., s, ev] (f16 or
     bf16, contiguous, same leading dimensions); `bias` [..., l, s] is overwritten with the
-    probabilities; without it pass `scores` (same shape) as scratch or let one be allocated.
-    scale defaults to 1/sqrt(e)."""
+    probabilities; without it pass `scores` (same shape) to receive them.  With neither, and a head
+    dimension of 64 or 128, the fused kernel runs instead (`sdpa_fused`).  scale defaults to 1/sqrt(e)."""
     if Q.dtype not in (torch.float16, torch.bfloat16) or K.dtype != Q.dtype or V.dtype != Q.dtype:
         raise TypeError("sdpa needs f16 or bf16 tensors of one dtype")
+    if bias is None and scores is None and Q.shape[-1] in (64, 128) and V.shape[-1] == Q.shape[-1]:
+        return sdpa_fused(Q, K, V, scale=scale)      # nobody asked for the probabilities: one kernel, scores on chip
     lead = tuple(Q.shape[:-2])
     l, e = Q.shape[-2:]
     s, e2 = K.shape[-2:]

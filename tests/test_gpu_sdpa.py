@@ -36,7 +36,8 @@ def test_matches_float64_attention(dtype, tol, lead, l, s, e, ev, with_bias):
     scale = e ** -0.5
     want, P = attention_f64(Q, K, V, bias, scale, dtype)
     buf = bias.cuda().clone() if with_bias else None
-    out = klas.sdpa(Q.cuda(), K.cuda(), V.cuda(), buf, scale=scale)
+    scratch = None if with_bias else torch.empty(lead + (l, s), dtype=dtype, device="cuda")   # keeps the three-step path
+    out = klas.sdpa(Q.cuda(), K.cuda(), V.cuda(), buf, scale=scale, scores=scratch)
     torch.cuda.synchronize()
     # output rows are convex combinations of V's rows: errors are measured against sum_j P_ij |V_jc|
     bound = (P @ V.double().abs()).clamp(min=1e-30)
