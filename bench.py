@@ -358,7 +358,55 @@ class Softmax(Workload):
         return float(self._host[0])
 
 
+class Attention(Workload):
+    name, metric, unit, dtype, bound = "attention_f16", "attention_tflops", "TFLOP/s", "f16", "tensor"
+    e2e_api = "pinned host copies around klas_b200_sdpa_fused (C ABI, device pointers)"
+    L = S = 2048
+    E = 128
+
+    def __init__(self, rank, world, device, heads=256):
+        import torch
+        from kuiper_b200 import synth
+        self.torch = torch
+        self.heads = heads
+        n = heads * self.L * self.E
+        mk = lambda stream: synth.normal(6 + rank, stream, 0, n, dtype=torch.float16, device=device).reshape(heads, self.L, self.E)
+        self.Q, self.K, self.V = mk(31), mk(32), mk(33)
+        self.out = torch.empty_like(self.Q)
+        torch.cuda.empty_cache()
+        self.algorithmic_bytes = 4 * n * 2
+        self.config = {"workload": "fused attention softmax(Q.K^T / sqrt(e)).V, f16, %d heads per GPU, l = s = %d, e = %d, N(0,1) values, seed 6+rank"
+                                   % (heads, self.L, self.E),
+                       "sharding": "heads, no collective", "cache": "%d MiB of Q, K, V, O" % (4 * n * 2 >> 20)}
+        self.h2d, self.d2h = 3 * n * 2, n * 2
+        self._host = None
+
+    def per_step_units(self):
+        return 4.0 * self.heads * self.L * self.S * self.E
+
+    def launch(self):
+        from kuiper_b200 import _lib
+        _lib.check(_lib.load().klas_b200_sdpa_fused(_lib.F16, self.heads, self.L, self.S, self.E, self.Q.data_ptr(), self.K.data_ptr(),
+                                                    self.V.data_ptr(), self.out.data_ptr(), self.E ** -0.5,
+                                                    self.torch.cuda.current_stream().cuda_stream))
+
+    def e2e_step(self):
+        # no host-buffer entry point for attention: pinned copies around the device call
+        if self._host is None:
+            self._host = tuple(t.cpu().pin_memory() for t in (self.Q, self.K, self.V, self.out))
+        hq, hk, hv, ho = self._host
+        self.Q.copy_(hq, non_blocking=True)
+        self.K.copy_(hk, non_blocking=True)
+        self.V.copy_(hv, non_blocking=True)
+        self.launch()
+        ho.copy_(self.out, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+        return float(ho[0, 0, 0])
+
+
 def make_workload(name, rank, world, device, args=None):
+    if name == "attention_f16":
+        return Attention(rank, world, device, args.attention_heads if args else 256)
     if name == "softmax_f32":
         return Softmax(rank, world, device, args.softmax_log2n if args else 28)
     if name == "gemm_bf16":
@@ -498,6 +546,8 @@ def main():
     ap.add_argument("--workload", default="gemm_bf16")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--attention-heads", type=int, default=256,
+                    help="attention_f16 only: heads per GPU (256 is the bench size; fewer for profiler captures)")
     ap.add_argument("--softmax-log2n", type=int, default=28,
                     help="softmax_f32 only: log2 of the vector length (28 is the bench size; smaller for profiler captures)")
     args = ap.parse_args()
@@ -601,11 +651,11 @@ def main():
                     "kernel_ms": per_launch_ms, **extra}
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": warm, "ms_per_step": per_launch_ms, "higher_is_better": True, "scaling": "weak" if wl.name in ("gemm_bf16", "softmax_f32") else "strong",
+            "warmup": warm, "ms_per_step": per_launch_ms, "higher_is_better": True, "scaling": "weak" if wl.name in ("gemm_bf16", "softmax_f32", "attention_f16") else "strong",
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
             "clocks": sampler.summary(),
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
-                    "steps": args.e2e_steps, "api": "klas_b200_*_host (C ABI, pinned host buffers)"},
+                    "steps": args.e2e_steps, "api": getattr(wl, "e2e_api", "klas_b200_*_host (C ABI, pinned host buffers)")},
             "gpu_launches": args.steps * wl.launches_per_step,
             "roofline": roofline,
         }

@@ -19,7 +19,12 @@
 // (wait for S and load it 540, maximum 200, exchange 300, wait for the previous P.V 275, store and
 // publish P 290); the tensor core needs 1024.  One thread per row took 3950 cycles, four per row
 // gained nothing over two, and issuing the two products from one thread or from two made no
-// difference: what is left is to run the exponentials of one tile under the bookkeeping of the next.
+// difference.  Also tried and measured no better: two independent streams of tiles per CTA (even /
+// odd tiles, each with its own scores, P, O, producer and issuing thread, combined at the end, the
+// second started half a period late), and a single optimistic pass per tile with the inherited
+// reference point.  The warps are bound by instruction issue, not by the special-function unit:
+// every instruction per score costs the two warps of a scheduler two cycles per key, so the next
+// step is fewer instructions per score (packed 16-bit arithmetic), not more overlap.
 // K is a K-major B operand (its rows are the columns of K^T), V an MN-major one, P a K-major A
 // operand: the three layouts the GEMM kernel uses, with the same descriptors.
 // Exponentials are ex2 of a pre-scaled argument (scale * log2 e folded into one multiply).
