@@ -1,6 +1,7 @@
 """Same seeded inputs through this library and through the reference's own kernels (dist/Klas_*.cu
 compiled for sm_100a, oracle/_ref): results must agree -- bit for bit for integers, within the
-float tolerances otherwise -- and the timings of both go to gpurun_out/ref_kernel_timings.json."""
+float tolerances otherwise -- and the timings of both are written to ref_kernel_timings.json in the
+run's output folder."""
 import ctypes as C
 import json
 import time
