@@ -34,7 +34,9 @@ def test_all_hot_path_drivers_are_covered():
 
 @pytest.mark.parametrize("name,args,stem", [
     ("Tune_Klas_GEMM_BlockTiling2D", ["3", "1024", "1024", "1024", "1"], "Klas_GEMM_BlockTiling2D_g_gemm_f32_128x128x32_8x8"),
-    ("Tune_Klas_GEMM_TensorCore2D", ["3", "1024", "1024", "1024", "1"], "Klas_GEMM_TensorCore2D_g_gemm_f16_f16_128x128x32_16x16x16_2x2"),
+    # check flag 0, as tuning/tune_tc2d.sh runs it: this driver's own gold applies alpha = 0.7, which the
+    # alpha-free TensorCore2D entry points do not take
+    ("Tune_Klas_GEMM_TensorCore2D", ["3", "1024", "1024", "1024", "0"], "Klas_GEMM_TensorCore2D_g_gemm_f16_f16_128x128x32_16x16x16_2x2"),
     ("Tune_Klas_SPMM", ["3", "2048", "2048", "512", "5"], "Klas_SPMM_g_spmm_f32_16x16x16"),
 ])
 def test_tuning_driver_runs_unchanged(name, args, stem):
