@@ -184,6 +184,31 @@ int klas_b200_gemm_tc_fused(int in_dtype, int out_dtype, int b_major, uint32_t b
                             int *status_word, void *stream);
 
 /*
+ * klas_b200_gemm_tc_fused on operands that are windows of larger arrays: rows of A, B and C / D
+ * are lda, ldb, ldd elements apart and consecutive pages stride_a, stride_b, stride_d elements
+ * apart (0 = packed: the row length, resp. rows x the row stride).  C, where the combine rule
+ * reads it, has D's strides.  The last dimension of every operand stays contiguous.  With
+ * KLAS_B_COL_MAJOR the "rows" of B are its `cols` stored rows of `shared` elements.  The strides
+ * go into the tensor maps of the TMA copies, so a window costs nothing over a packed operand.
+ * Requires every stride to be a multiple of 8 elements (16-byte steps for the 16-bit operands)
+ * and not shorter than the row it steps over, besides what klas_b200_gemm_tc requires.
+ * A page stride of 0 cannot share one matrix between pages on this path (a tensor map has no
+ * zero stride); use klas_b200_gemm_strided, or one call per page, for that.
+ *
+ * Replaces: the strided row-major A and B that the reference's tensor-core kernel accepts in
+ * its sources (`strided_row_major lA / lB`, row stride a multiple of the copy vector:
+ * src/lib/kernel/gemm/Kuiper.Kernel.GEMM.TensorCore2D.fsti:29-36), which its exported entries
+ * instantiate with packed rows only (dist/Klas_GEMM_TensorCore2D.h:8-1220).
+ */
+int klas_b200_gemm_tc_strided(int in_dtype, int out_dtype, int b_major, uint32_t batch,
+                              uint64_t rows, uint64_t shared, uint64_t cols,
+                              const void *A, uint64_t lda, uint64_t stride_a,
+                              const void *B, uint64_t ldb, uint64_t stride_b,
+                              const void *C, void *D, uint64_t ldd, uint64_t stride_d,
+                              float alpha, float beta, int map_a, int map_b, int comb,
+                              int *status_word, void *stream);
+
+/*
  * Reads (and then clears) the current device's tensor-core status word.
  * Returns KLAS_OK and *site = 0 when no bounded wait has given up since the
  * last call; otherwise KLAS_ERR_TIMEOUT and *site = the code of the first wait

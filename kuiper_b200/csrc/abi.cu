@@ -177,6 +177,17 @@ int klas_b200_gemm_tc_fused(int in_dtype, int out_dtype, int b_major, uint32_t b
                                   map_a, map_b, comb, status_word, static_cast<cudaStream_t>(stream));
 }
 
+int klas_b200_gemm_tc_strided(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                              uint64_t shared, uint64_t cols, const void *A, uint64_t lda, uint64_t stride_a,
+                              const void *B, uint64_t ldb, uint64_t stride_b, const void *C, void *D, uint64_t ldd,
+                              uint64_t stride_d, float alpha, float beta, int map_a, int map_b, int comb,
+                              int *status_word, void *stream) {
+    clear_error();
+    const TcStrides st{lda, stride_a, ldb, stride_b, ldd, stride_d};
+    return launch_gemm_umma_strided(in_dtype, out_dtype, b_major, batch, rows, shared, cols, A, B, C, D, st, alpha, beta,
+                                    map_a, map_b, comb, status_word, static_cast<cudaStream_t>(stream));
+}
+
 int klas_b200_csr_count(int dtype, uint32_t rows, uint32_t cols, const void *dense, uint32_t *row_off, void *stream) {
     clear_error();
     return launch_csr_count(dtype, rows, cols, dense, row_off, static_cast<cudaStream_t>(stream));

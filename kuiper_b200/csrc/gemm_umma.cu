@@ -102,6 +102,7 @@ struct Params {
     const void *C;
     void *D;
     uint32_t M, N, K, batch;
+    uint64_t ldd, sd;      // C / D: elements between rows, elements between pages
     uint32_t tiles_m, tiles_n, num_tiles, num_kb;
     float alpha, beta;
     uint32_t idesc;
@@ -649,7 +650,7 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
             }
             const uint32_t row = tm * S::TILE_M + cta_rank * BM + quad * 32u + lane;
             const uint32_t col0 = tn * BN;
-            const size_t row_off = (size_t(b) * p.M + row) * size_t(p.N);
+            const size_t row_off = size_t(b) * p.sd + size_t(row) * p.ldd;
 #pragma unroll 1
             for (uint32_t c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
@@ -973,7 +974,7 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
             }
             const uint32_t row0 = tm * TILE_M + cta_rank * A_ROWS + h * BM + quad * 32u;
             const uint32_t row = row0 + lane;
-            const size_t row_off = (size_t(b) * p.M + row) * size_t(p.N);
+            const size_t row_off = size_t(b) * p.sd + size_t(row) * p.ldd;
 
             // Converts one chunk and either stores it directly (alpha/beta path, C read with plain
             // loads) or transposes it through shared memory so that global stores are coalesced:
@@ -1021,7 +1022,7 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
                                      : "r"(addr)
                                      : "memory");
                         if (row0 + r < p.M && gcol < p.N)
-                            *reinterpret_cast<uint4 *>(D + (size_t(b) * p.M + row0 + r) * size_t(p.N) + gcol) = val;
+                            *reinterpret_cast<uint4 *>(D + size_t(b) * p.sd + size_t(row0 + r) * p.ldd + gcol) = val;
                     }
                     __syncwarp();   // the buffer may be overwritten by the next block
                 }
@@ -1113,13 +1114,17 @@ static EncodeTiledFn encode_fn() {
 
 // 3-D map over `batch` row-major pages of `outer` x `inner` elements of `elt` bytes,
 // box = box_inner x box_outer x 1, 128-byte swizzle, zero fill outside (loads) / clipping (stores).
+// `row_stride` / `page_stride` (elements; 0 = contiguous) place rows and pages further apart.
 static int make_map(CUtensorMap *map, int dtype, const void *base, uint64_t inner, uint64_t outer,
-                    uint64_t batch, uint32_t box_inner, uint32_t box_outer) {
+                    uint64_t batch, uint32_t box_inner, uint32_t box_outer, uint64_t row_stride = 0,
+                    uint64_t page_stride = 0) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(KLAS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const uint64_t elt = dtype_size(dtype);
+    if (row_stride == 0) row_stride = inner;
+    if (page_stride == 0) page_stride = row_stride * outer;
     const cuuint64_t dims[3] = {inner, outer, batch};
-    const cuuint64_t strides[2] = {inner * elt, inner * outer * elt};
+    const cuuint64_t strides[2] = {row_stride * elt, page_stride * elt};
     const cuuint32_t box[3] = {box_inner, box_outer, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = dtype == KLAS_BF16   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -1133,11 +1138,6 @@ static int make_map(CUtensorMap *map, int dtype, const void *base, uint64_t inne
                     int(rc), (unsigned long long)inner, (unsigned long long)outer,
                     (unsigned long long)batch);
     return KLAS_OK;
-}
-
-static int make_map_16bit(CUtensorMap *map, int dtype, const void *base, uint64_t inner,
-                          uint64_t outer, uint64_t batch, uint32_t box_inner, uint32_t box_outer) {
-    return make_map(map, dtype, base, inner, outer, batch, box_inner, box_outer);
 }
 
 template <typename OutT, bool XFORM>
@@ -1269,7 +1269,25 @@ int launch_gemm_umma_fused(int in_dtype, int out_dtype, int b_major, uint32_t ba
                            uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
                            void *D, float alpha, float beta, int map_a, int map_b, int comb,
                            int *status_word, cudaStream_t stream) {
+    TcStrides st{};   // all zero: contiguous
+    return launch_gemm_umma_strided(in_dtype, out_dtype, b_major, batch, rows, shared, cols, A, B, C, D, st, alpha, beta,
+                                    map_a, map_b, comb, status_word, stream);
+}
+
+int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                             uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
+                             void *D, const TcStrides &st, float alpha, float beta, int map_a, int map_b, int comb,
+                             int *status_word, cudaStream_t stream) {
     using namespace umma;
+    // rows of A are `shared` long; rows of B `cols` (row-major) or `shared` (column-major) long
+    const uint64_t b_inner = b_major == KLAS_B_ROW_MAJOR ? cols : shared, b_outer = b_major == KLAS_B_ROW_MAJOR ? shared : cols;
+    const uint64_t lda = st.lda ? st.lda : shared, ldb = st.ldb ? st.ldb : b_inner, ldd = st.ldd ? st.ldd : cols;
+    const uint64_t sa = st.stride_a ? st.stride_a : lda * rows, sb = st.stride_b ? st.stride_b : ldb * b_outer,
+                   sd = st.stride_d ? st.stride_d : ldd * rows;
+    if (lda < shared || ldb < b_inner || ldd < cols) return fail(KLAS_ERR_INVALID, "gemm_tc: a row stride is shorter than the row");
+    if ((lda | ldb | ldd | sa | sb | sd) % 8 != 0)
+        return fail(KLAS_ERR_UNSUPPORTED, "gemm_tc: row and page strides must be multiples of 8 elements");
+    if (batch > 1 && sd < (rows - 1) * ldd + cols) return fail(KLAS_ERR_INVALID, "gemm_tc: pages of D overlap");
     if (map_a < KLAS_MAP_ID || map_a > KLAS_MAP_NEG || map_b < KLAS_MAP_ID || map_b > KLAS_MAP_NEG)
         return fail(KLAS_ERR_INVALID, "gemm_tc: unknown operand map (%d, %d)", map_a, map_b);
     if (comb < KLAS_COMB_NEW || comb > KLAS_COMB_SCALED) return fail(KLAS_ERR_INVALID, "gemm_tc: unknown combine rule %d", comb);
@@ -1328,6 +1346,8 @@ int launch_gemm_umma_fused(int in_dtype, int out_dtype, int b_major, uint32_t ba
         if (wide_tiles > 0xffffffffull) return fail(KLAS_ERR_TOO_LARGE, "gemm_tc: too many tiles");
         p.num_tiles = uint32_t(wide_tiles);
         p.num_kb = uint32_t((shared + BK - 1) / BK);
+        p.ldd = ldd;
+        p.sd = sd;
         p.alpha = alpha;
         p.beta = beta;
         p.b_row_major = (b_major == KLAS_B_ROW_MAJOR) ? 1u : 0u;
@@ -1344,11 +1364,11 @@ int launch_gemm_umma_fused(int in_dtype, int out_dtype, int b_major, uint32_t ba
         }
         CUtensorMap ta{}, tb{};
         if (shared > 0) {
-            if (int rc = make_map(&ta, in_dtype, A, shared, rows, batch, BK, wide::A_ROWS)) return rc;
+            if (int rc = make_map(&ta, in_dtype, A, shared, rows, batch, BK, wide::A_ROWS, lda, sa)) return rc;
             if (p.b_row_major) {
-                if (int rc = make_map(&tb, in_dtype, B, cols, shared, batch, 64, BK)) return rc;
+                if (int rc = make_map(&tb, in_dtype, B, cols, shared, batch, 64, BK, ldb, sb)) return rc;
             } else {
-                if (int rc = make_map(&tb, in_dtype, B, shared, cols, batch, BK, wide::B_COLS)) return rc;
+                if (int rc = make_map(&tb, in_dtype, B, shared, cols, batch, BK, wide::B_COLS, ldb, sb)) return rc;
             }
         }
         const uint64_t groups = wide_tiles < uint64_t(info.sm_count / 2) ? wide_tiles : uint64_t(info.sm_count / 2);
@@ -1370,6 +1390,8 @@ int launch_gemm_umma_fused(int in_dtype, int out_dtype, int b_major, uint32_t ba
     if (num_tiles > 0xffffffffull) return fail(KLAS_ERR_TOO_LARGE, "gemm_tc: too many tiles");
     p.num_tiles = uint32_t(num_tiles);
     p.num_kb = uint32_t((shared + BK - 1) / BK);
+    p.ldd = ldd;
+    p.sd = sd;
     p.alpha = alpha;
     p.beta = beta;
     p.b_row_major = (b_major == KLAS_B_ROW_MAJOR) ? 1u : 0u;
@@ -1388,11 +1410,11 @@ int launch_gemm_umma_fused(int in_dtype, int out_dtype, int b_major, uint32_t ba
     const uint32_t b_cols = pair ? Shape<true>::B_COLS : Shape<false>::B_COLS;
     CUtensorMap ta{}, tb{};
     if (shared > 0) {
-        if (int rc = make_map_16bit(&ta, in_dtype, A, shared, rows, batch, BK, BM)) return rc;
+        if (int rc = make_map(&ta, in_dtype, A, shared, rows, batch, BK, BM, lda, sa)) return rc;
         if (p.b_row_major) {
-            if (int rc = make_map_16bit(&tb, in_dtype, B, cols, shared, batch, 64, BK)) return rc;
+            if (int rc = make_map(&tb, in_dtype, B, cols, shared, batch, 64, BK, ldb, sb)) return rc;
         } else {
-            if (int rc = make_map_16bit(&tb, in_dtype, B, shared, cols, batch, BK, b_cols)) return rc;
+            if (int rc = make_map(&tb, in_dtype, B, shared, cols, batch, BK, b_cols, ldb, sb)) return rc;
         }
     }
     if (pair) {

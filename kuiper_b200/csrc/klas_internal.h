@@ -72,6 +72,15 @@ int launch_gemm_umma_fused(int in_dtype, int out_dtype, int b_major, uint32_t ba
                            void *D, float alpha, float beta, int map_a, int map_b, int comb,
                            int *status_word, cudaStream_t stream);
 
+// Row and page strides (elements) of a tensor-core GEMM; 0 = contiguous.  C shares D's.
+struct TcStrides {
+    uint64_t lda, stride_a, ldb, stride_b, ldd, stride_d;
+};
+int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                             uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
+                             void *D, const TcStrides &st, float alpha, float beta, int map_a, int map_b, int comb,
+                             int *status_word, cudaStream_t stream);
+
 int launch_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32_t nnz,
                 const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
                 const uint32_t *row_indices, const void *B, void *C, cudaStream_t stream);

@@ -305,6 +305,51 @@ def gemm_tc(A: torch.Tensor, B: torch.Tensor, *, out_dtype=torch.float32, b_col_
     return D
 
 
+def gemm_tc_strided(A: torch.Tensor, B: torch.Tensor, D: torch.Tensor, *, b_col_major: bool = False,
+                    C_: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
+                    map_a: Optional[str] = None, map_b: Optional[str] = None,
+                    comb: Optional[str] = None) -> torch.Tensor:
+    """Tensor-core GEMM on tensor VIEWS (windows of larger arrays): A [batch,] rows x shared, B [batch,]
+    shared x cols (cols x shared when `b_col_major`), D [batch,] rows x cols, last dimension contiguous;
+    row and page strides come from the views and must be multiples of 8 elements.  C_, when given,
+    must have D's strides (pass C_=D to accumulate in place).  Hooks as in gemm_tc.  Returns D."""
+    if A.dtype not in (torch.bfloat16, torch.float16) or B.dtype != A.dtype:
+        raise TypeError("A and B must both be bf16 or both be f16")
+    if A.dim() == 2:
+        A, B, D3 = A[None], B[None], D[None]
+        C3 = None if C_ is None else C_[None]
+    else:
+        D3, C3 = D, C_
+    batch, rows, shared = A.shape
+    cols, k2 = (B.shape[1], B.shape[2]) if b_col_major else (B.shape[2], B.shape[1])
+    if k2 != shared or B.shape[0] != batch or tuple(D3.shape) != (batch, rows, cols):
+        raise ValueError("shapes do not match: %s %s %s" % (tuple(A.shape), tuple(B.shape), tuple(D3.shape)))
+    for t, name in ((A, "A"), (B, "B"), (D3, "D")) + (((C3, "C"),) if C3 is not None else ()):
+        if not t.is_cuda:
+            raise ValueError("%s must be a CUDA tensor" % name)
+        if t.shape[2] > 1 and t.stride(2) != 1:
+            raise ValueError("%s: the last dimension must be contiguous" % name)
+        if batch > 1 and t.stride(0) == 0:
+            raise ValueError("%s: pages that share one matrix (stride 0) are not served on this path" % name)
+    if C3 is not None and (C3.dtype != D3.dtype or tuple(C3.shape) != tuple(D3.shape) or
+                           (rows > 1 and C3.stride(1) != D3.stride(1)) or (batch > 1 and C3.stride(0) != D3.stride(0))):
+        raise ValueError("C must have D's dtype, shape and strides")
+    try:
+        ma, mb = _MAPS[map_a], _MAPS[map_b]
+        cb = _COMBS[comb] if comb is not None else (_lib.COMB_AXPBY if C_ is not None else _lib.COMB_NEW)
+    except KeyError as e:
+        raise ValueError("unknown map or combine rule %s" % e) from None
+    page = (lambda t: t.stride(0) if batch > 1 else 0)
+    row = (lambda t: t.stride(1) if t.shape[1] > 1 else 0)
+    with torch.cuda.device(A.device):
+        check(_lib.load().klas_b200_gemm_tc_strided(
+            _code(A), _DTYPES[D3.dtype], _lib.B_COL_MAJOR if b_col_major else _lib.B_ROW_MAJOR, batch, rows, shared, cols,
+            A.data_ptr(), row(A), page(A), B.data_ptr(), row(B), page(B),
+            C3.data_ptr() if C3 is not None else None, D3.data_ptr(), row(D3), page(D3),
+            float(alpha), float(beta), ma, mb, cb, None, _stream()))
+    return D
+
+
 def gemm_tc_status() -> int:
     """Raises KlasError(ERR_TIMEOUT) if a bounded device-side wait of the tensor-core kernel
     gave up since the last call (synchronises the device); returns 0 otherwise."""
