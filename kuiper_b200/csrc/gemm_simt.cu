@@ -165,9 +165,16 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
     T(*As)[BK][BM + PAD] = reinterpret_cast<T(*)[BK][BM + PAD]>(simt_smem);  // transposed: [k][m]
     T(*Bs)[BK][BN + PAD] = reinterpret_cast<T(*)[BK][BN + PAD]>(simt_smem + sizeof(T) * 2 * BK * (BM + PAD));
 
+    constexpr bool PACKED = IsF32<T>::value;   // f32: accumulate column pairs with fma.rn.f32x2
     const int tid = threadIdx.x;
-    const int tx = tid % TX;
-    const int ty = tid / TX;
+    // Integer and fp64 tiles: a warp covers 4 x 8 thread tiles and each half-warp 2 x 8, so a
+    // half-warp's 16-byte reads of a k-row touch 32 bytes of A and 128 bytes of B, one
+    // shared-memory wavefront each (16 threads in a row touch 256 bytes of B: two wavefronts per
+    // half-warp; measured 3 % slower for u32).  The packed f32 loop measured 1-2 % faster on
+    // the plain 2 x 16 arrangement, which it keeps.
+    static_assert(TX == 16 && TY == 16 && THREADS == 256, "warp layout assumes a 16 x 16 thread grid");
+    const int tx = PACKED ? tid % TX : ((tid >> 5) & 1) * 8 + (tid & 7);
+    const int ty = PACKED ? tid / TX : (tid >> 6) * 4 + ((tid >> 3) & 3);
 
     const uint64_t per_batch = a.tiles_m * a.tiles_n;
     const uint64_t bidx = blockIdx.x / per_batch;
@@ -179,7 +186,6 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
     const S *__restrict__ B = static_cast<const S *>(a.B) + bidx * a.sb;
     S *C = static_cast<S *>(a.C) + bidx * a.sc;
 
-    constexpr bool PACKED = IsF32<T>::value;   // f32: accumulate column pairs with fma.rn.f32x2
     T acc[PACKED ? 1 : TM][PACKED ? 1 : TN];
     unsigned long long acc2[PACKED ? TM : 1][PACKED ? TN / 2 : 1];
 #pragma unroll
@@ -277,15 +283,35 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
         const int buf = int(kb & 1);
         const bool more = kb + 1 < num_kb;
         if (more) load_global((kb + 1) * BK);
-#pragma unroll
-        for (int k = 0; k < BK; ++k) {
-            Vec<T, VEC> av[GM], bv[GN];
+        // The packed f32 loop reads the operands of step k + 1 before the multiply-adds of step k
+        // (in program order: it is fully unrolled); without that hint the compiler's schedule left
+        // the FP32 pipe idle 30 % of the time (50.7 -> 58 TFLOP/s at 4096^3).  The other types
+        // measured no better with it.
+        Vec<T, VEC> avq[2][GM], bvq[2][GN];
+        auto load_frag = [&](int slot, int k) {
 #pragma unroll
             for (int g = 0; g < GM; ++g)
-                av[g] = *reinterpret_cast<const Vec<T, VEC> *>(&As[buf][k][g * (BM / GM) + ty * VEC]);
+                avq[slot][g] = *reinterpret_cast<const Vec<T, VEC> *>(&As[buf][k][g * (BM / GM) + ty * VEC]);
 #pragma unroll
             for (int g = 0; g < GN; ++g)
-                bv[g] = *reinterpret_cast<const Vec<T, VEC> *>(&Bs[buf][k][g * (BN / GN) + tx * VEC]);
+                bvq[slot][g] = *reinterpret_cast<const Vec<T, VEC> *>(&Bs[buf][k][g * (BN / GN) + tx * VEC]);
+        };
+        if constexpr (PACKED) load_frag(0, 0);
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            Vec<T, VEC> avk[GM], bvk[GN];
+            if constexpr (PACKED) {
+                if (k + 1 < BK) load_frag((k + 1) & 1, k + 1);
+            } else {
+#pragma unroll
+                for (int g = 0; g < GM; ++g)
+                    avk[g] = *reinterpret_cast<const Vec<T, VEC> *>(&As[buf][k][g * (BM / GM) + ty * VEC]);
+#pragma unroll
+                for (int g = 0; g < GN; ++g)
+                    bvk[g] = *reinterpret_cast<const Vec<T, VEC> *>(&Bs[buf][k][g * (BN / GN) + tx * VEC]);
+            }
+            Vec<T, VEC>(&av)[GM] = PACKED ? avq[k & 1] : avk;
+            Vec<T, VEC>(&bv)[GN] = PACKED ? bvq[k & 1] : bvk;
             if constexpr (PACKED) {
                 unsigned long long bp[TN / 2];
 #pragma unroll
@@ -434,14 +460,18 @@ static int launch_type(const Problem &q, T alpha, T beta, int scaled, const void
                        int sm_count, cudaStream_t stream) {
     const uint64_t m = q.m, n = q.n, batch = q.batch;
     if constexpr (sizeof(T) == 4) {
-        // Large tiles once they fill the machine; small ones otherwise.
+        // 128 x 128 tiles from 0.6 tiles per SM on (a part-filled single wave of large tiles beat
+        // two waves of smaller ones: 51 against 41 TFLOP/s at 1536^3, 35 against 31 at 1280^3; at
+        // 1024^3, 64 tiles, the 128 x 64 tile wins 33 to 22), 128 x 64 from 0.8 per SM, else 64 x 64.
+        // The two smaller tiles walk K in steps of 32: they run one wave with few warps per SM,
+        // where a barrier per step costs more (+6 % at 1024^3).
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 127) / 128) * batch;
         const uint64_t mid_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
-        int pick = big_tiles >= uint64_t(sm_count) ? 2 : (mid_tiles * 10 >= uint64_t(sm_count) * 8 ? 1 : 0);
+        int pick = big_tiles * 10 >= uint64_t(sm_count) * 6 ? 2 : (mid_tiles * 10 >= uint64_t(sm_count) * 8 ? 1 : 0);
         if (const char *t = getenv("KLAS_SIMT_TILE")) pick = atoi(t);
         if (pick == 2) return launch_cfg<S, T, 128, 128, 16>(q, alpha, beta, scaled, A, B, C, stream);
-        if (pick == 1) return launch_cfg<S, T, 128, 64, 16>(q, alpha, beta, scaled, A, B, C, stream);
-        return launch_cfg<S, T, 64, 64, 16>(q, alpha, beta, scaled, A, B, C, stream);
+        if (pick == 1) return launch_cfg<S, T, 128, 64, 32>(q, alpha, beta, scaled, A, B, C, stream);
+        return launch_cfg<S, T, 64, 64, 32>(q, alpha, beta, scaled, A, B, C, stream);
     } else {
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
         if (big_tiles >= uint64_t(sm_count)) return launch_cfg<S, T, 128, 64, KLAS_SIMT_BK8>(q, alpha, beta, scaled, A, B, C, stream);
