@@ -273,16 +273,25 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
     };
 
     const uint64_t num_kb = (a.K + BK - 1) / BK;
+    // Tile kb + 1 travels global -> registers -> shared memory while tile kb is multiplied.  EARLY:
+    // its global reads are issued just before the barrier that ends step kb - 1 (they cannot be
+    // scheduled past it) and its shared-memory stores come at the end of step kb, a whole step
+    // between issue and use wherever the compiler puts the rest.  That is what the tiles that run
+    // with few warps per SM need (f32 1024^3: 32.7 -> 36.1 TFLOP/s; fp64 4096^3 20.8 -> 23.1;
+    // u64 +3 %).  The 128 x 128 tiles of the 4-byte types, two CTAs per SM, measured 4 % faster
+    // with the reads at the top of step kb instead, and keep that.
+    constexpr bool EARLY = sizeof(T) == 8 || BM * BN < 128 * 128;
     if (num_kb > 0) {
         load_global(0);
         store_shared(0);
+        if (EARLY && num_kb > 1) load_global(BK);
     }
     __syncthreads();
 
     for (uint64_t kb = 0; kb < num_kb; ++kb) {
         const int buf = int(kb & 1);
         const bool more = kb + 1 < num_kb;
-        if (more) load_global((kb + 1) * BK);
+        if (!EARLY && more) load_global((kb + 1) * BK);
         // The packed f32 loop reads the operands of step k + 1 before the multiply-adds of step k
         // (in program order: it is fully unrolled); without that hint the compiler's schedule left
         // the FP32 pipe idle 30 % of the time (50.7 -> 58 TFLOP/s at 4096^3).  The other types
@@ -333,6 +342,7 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
             }
         }
         if (more) store_shared(buf ^ 1);
+        if (EARLY && kb + 2 < num_kb) load_global((kb + 2) * BK);
         __syncthreads();
     }
 
