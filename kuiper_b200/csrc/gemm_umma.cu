@@ -1320,14 +1320,27 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
         return fail(KLAS_ERR_UNSUPPORTED, "gemm_tc needs an sm_100 device (found sm_%d%d)",
                     info.cc_major, info.cc_minor);
 
-    // Tile shape: "wide" (512 x 256 per CTA pair) once such tiles fill the machine, CTA pairs with
-    // 256 x 256 tiles below that, single CTAs (128 x 256) for small problems.
+    // Tile shape: single CTAs with 128 x 256 tiles, CTA pairs with 256 x 256 tiles, or "wide" CTA
+    // pairs with 512 x 256 tiles, whichever a wave count x tile cost estimate makes fastest.  The
+    // kernels are persistent with a static round-robin of tiles, so a launch takes
+    // ceil(tiles / slots) rounds; per round a wide tile costs twice a 256 x 256 one, less what it
+    // saves by sharing operands (relative rates measured at 8192^3: wide 1408, pair 1160, single
+    // 1144 TFLOP/s).  Examples the estimate gets right where "wide once it fills the machine"
+    // did not: 3072^3 (72 wide tiles, one round: 1324 against 1120 TFLOP/s for two rounds of pairs),
+    // 3584 x 3072 (84 wide tiles would take two rounds; pairs: 1049 against 910), 2048^2 (one
+    // round of 128 single tiles: 720 against 488 for 32 wide tiles on 74 pairs).
     // KLAS_TC_MODE=single|pair|wide overrides the choice.
     const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
+    const uint64_t pair_tiles = ((rows + 2 * BM - 1) / (2 * BM)) * ((cols + BN - 1) / BN) * batch;
     const uint64_t wide_tiles = ((rows + wide::TILE_M - 1) / wide::TILE_M) * ((cols + BN - 1) / BN) * batch;
     const bool can_pair = info.sm_count >= 2;
-    bool pair = can_pair && rows > BM && single_tiles >= uint64_t(info.sm_count) && !xform;
-    bool use_wide = can_pair && wide_tiles >= uint64_t(info.sm_count / 2);
+    const uint64_t sms = uint64_t(info.sm_count), pairs = uint64_t(info.sm_count / 2);
+    const double cost_single = double((single_tiles + sms - 1) / sms);
+    const bool pair_ok = can_pair && rows > BM && single_tiles >= sms && !xform;   // the pair tile has no mapped form
+    const double cost_pair = pair_ok ? double((pair_tiles + pairs - 1) / pairs) * (1144.0 / 1160.0) : 1e30;
+    const double cost_wide = can_pair ? double((wide_tiles + pairs - 1) / pairs) * 2.0 * (1144.0 / 1408.0) : 1e30;
+    bool use_wide = can_pair && cost_wide < cost_single && cost_wide <= cost_pair;
+    bool pair = pair_ok && !use_wide && cost_pair <= cost_single;
     if (const char *mode = getenv("KLAS_TC_MODE")) {
         if (!strcmp(mode, "single")) pair = use_wide = false;
         else if (!strcmp(mode, "pair")) { pair = can_pair && !xform; use_wide = false; }
