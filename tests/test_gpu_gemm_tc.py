@@ -165,3 +165,32 @@ def test_zero_inner_dimension():
     D = torch.full((64, 64), 7.0, device="cuda")
     klas.gemm_tc(A, B, D=D)
     assert bool((D == 0).all())
+
+
+@pytest.mark.parametrize("rows,cols,expect", [
+    (2048, 2048, "one round of single tiles"), (2560, 2048, "40 wide tiles, one round"),
+    (3072, 3072, "72 wide tiles, one round"), (3584, 3072, "84 wide tiles would take two rounds: pairs"),
+    (3000, 2056, "ragged edges")])
+def test_tile_choice_does_not_change_results(oracle, rows, cols, expect, monkeypatch, tc_mode):
+    """The library picks single, pair or wide tiles from the shape.  Every element is accumulated
+    over k in the same order whatever the tile, so the three kernels and the library's own choice
+    must agree bit for bit; a sample of rows is checked against the oracle."""
+    if tc_mode != "auto":
+        return   # the modes are set below; one pass is enough
+    shared = 192
+    A, Bt = synth.gemm_bf16(31, rows, cols, shared, b_col_major=True, device="cuda")
+    results = {}
+    for mode in ("auto", "single", "pair", "wide"):
+        if mode == "auto":
+            monkeypatch.delenv("KLAS_TC_MODE", raising=False)
+        else:
+            monkeypatch.setenv("KLAS_TC_MODE", mode)
+        results[mode] = klas.gemm_tc(A, Bt, out_dtype=torch.float32, b_col_major=True)
+    torch.cuda.synchronize()
+    assert klas.gemm_tc_status() == 0
+    for mode in ("single", "pair", "wide"):
+        assert torch.equal(results["auto"], results[mode]), "%s differs (%s)" % (mode, expect)
+    pick = torch.arange(0, rows, 97, device="cuda")
+    acc, scale = tc_reference(oracle, A[pick].cpu(), Bt.cpu(), True)
+    err = rel_err_componentwise(results["auto"][pick].cpu().numpy(), acc, scale)
+    assert err <= 1e-5, "relative error %.3e" % err
