@@ -24,7 +24,10 @@
 // second started half a period late), and a single optimistic pass per tile with the inherited
 // reference point.  The warps are bound by instruction issue, not by the special-function unit:
 // every instruction per score costs the two warps of a scheduler two cycles per key, so the next
-// step is fewer instructions per score (packed 16-bit arithmetic), not more overlap.
+// step is fewer instructions per score, not more overlap.  (One try at that, also measured: for f16,
+// rounding the exponent's argument to f16 and taking two exponentials per special-function operation,
+// with the row sum added pairwise in f16 first -- 5.75 instead of 7 instructions per pair of scores
+// -- ran 5 % slower, 666 against 700 TFLOP/s at 256 heads of 2048 x 128; not kept.)
 // K is a K-major B operand (its rows are the columns of K^T), V an MN-major one, P a K-major A
 // operand: the three layouts the GEMM kernel uses, with the same descriptors.
 // Exponentials are ex2 of a pre-scaled argument (scale * log2 e folded into one multiply).
