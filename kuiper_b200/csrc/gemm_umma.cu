@@ -104,6 +104,7 @@ struct Params {
     uint32_t M, N, K, batch;
     uint64_t ldd, sd;      // C / D: elements between rows, elements between pages
     uint32_t tiles_m, tiles_n, num_tiles, num_kb;
+    uint32_t tile_n;       // columns per tile of the single-CTA kernel: 256, or 128 for small outputs
     float alpha, beta;
     uint32_t idesc;
     uint32_t b_row_major;  // 1: B is K x N (N contiguous) -> MN-major operand
@@ -485,7 +486,8 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
             uint32_t b, tm, tn;
             decode_tile(t, p, b, tm, tn);
             const int32_t a_row = int32_t(tm * S::TILE_M + cta_rank * BM);
-            const int32_t b_col = int32_t(tn * BN + cta_rank * S::B_COLS);
+            const uint32_t tile_n = PAIR ? BN : p.tile_n;
+            const int32_t b_col = int32_t(tn * tile_n + cta_rank * S::B_COLS);
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 if (stage % S::RELEASE_GROUP == 0) {
                     // stages are handed back in groups; the group's last stage carries the barrier
@@ -512,11 +514,10 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
                             ptx::tma_load_3d_pair(b_dst, &tm_b, bar, k0, b_col, int32_t(b));
                         }
                     } else {
-                        ptx::mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+                        ptx::mbar_arrive_expect_tx(full_bar(stage), A_STAGE_BYTES + tile_n * BK * 2u);
                         ptx::tma_load_3d(a_dst, &tm_a, full_bar(stage), k0, a_row, int32_t(b));
                         if (p.b_row_major) {
-#pragma unroll
-                            for (uint32_t j = 0; j < S::B_COLS / 64; ++j)
+                            for (uint32_t j = 0; j < tile_n / 64; ++j)
                                 ptx::tma_load_3d(b_dst + j * B_CHUNK_BYTES, &tm_b, full_bar(stage),
                                                  b_col + int32_t(j * 64), k0, int32_t(b));
                         } else {
@@ -617,7 +618,7 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 if (turn == xw)
                     ok = xform_stage(p, full_bar(stage), phase, ctl, SITE_XFORM_FULL, smem_base + stage * STAGE_BYTES,
-                                     A_STAGE_BYTES, S::B_STAGE_BYTES, xfull_bar(stage), lane);
+                                     A_STAGE_BYTES, PAIR ? S::B_STAGE_BYTES : p.tile_n * BK * 2u, xfull_bar(stage), lane);
                 if (!ok) break;
                 if (++turn == XFORM_WARPS) turn = 0;
                 if (++stage == STAGES) {
@@ -649,10 +650,11 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
                 ptx::tc_fence_after_sync();
             }
             const uint32_t row = tm * S::TILE_M + cta_rank * BM + quad * 32u + lane;
-            const uint32_t col0 = tn * BN;
+            const uint32_t tile_n = PAIR ? BN : p.tile_n;
+            const uint32_t col0 = tn * tile_n;
             const size_t row_off = size_t(b) * p.sd + size_t(row) * p.ldd;
 #pragma unroll 1
-            for (uint32_t c = 0; c < BN / 32; ++c) {
+            for (uint32_t c = 0; c < tile_n / 32; ++c) {
                 uint32_t v[32];
                 if (p.num_kb > 0) {
                     ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + acc * BN + c * 32u, v);
@@ -1341,10 +1343,16 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     const double cost_wide = can_pair ? double((wide_tiles + pairs - 1) / pairs) * 2.0 * (1144.0 / 1408.0) : 1e30;
     bool use_wide = can_pair && cost_wide < cost_single && cost_wide <= cost_pair;
     bool pair = pair_ok && !use_wide && cost_pair <= cost_single;
+    // Small outputs: the single-CTA kernel with 128-column tiles puts twice as many CTAs to work
+    // (1024^2: 64 tiles instead of 32 on 148 SMs); a narrow tile costs a little more than half a
+    // full one (the A operand is read from shared memory once per 128 instead of 256 columns).
+    const uint64_t narrow_tiles = ((rows + BM - 1) / BM) * ((cols + 127) / 128) * batch;
+    bool narrow = !use_wide && !pair && double((narrow_tiles + sms - 1) / sms) * 0.55 < cost_single;
     if (const char *mode = getenv("KLAS_TC_MODE")) {
-        if (!strcmp(mode, "single")) pair = use_wide = false;
-        else if (!strcmp(mode, "pair")) { pair = can_pair && !xform; use_wide = false; }
-        else if (!strcmp(mode, "wide")) use_wide = can_pair;
+        if (!strcmp(mode, "single")) pair = use_wide = narrow = false;
+        else if (!strcmp(mode, "narrow")) { pair = use_wide = false; narrow = true; }
+        else if (!strcmp(mode, "pair")) { pair = can_pair && !xform; use_wide = false; narrow = narrow && !pair; }
+        else if (!strcmp(mode, "wide")) { use_wide = can_pair; narrow = narrow && !use_wide; }
     }
     if (use_wide) {
         Params p{};
@@ -1397,8 +1405,9 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     p.N = uint32_t(cols);
     p.K = uint32_t(shared);
     p.batch = batch;
+    p.tile_n = (narrow && !pair) ? 128u : BN;
     p.tiles_m = uint32_t((rows + tile_m - 1) / tile_m);
-    p.tiles_n = uint32_t((cols + BN - 1) / BN);
+    p.tiles_n = uint32_t((cols + p.tile_n - 1) / p.tile_n);
     const uint64_t num_tiles = uint64_t(p.tiles_m) * p.tiles_n * batch;
     if (num_tiles > 0xffffffffull) return fail(KLAS_ERR_TOO_LARGE, "gemm_tc: too many tiles");
     p.num_tiles = uint32_t(num_tiles);
@@ -1408,7 +1417,7 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     p.alpha = alpha;
     p.beta = beta;
     p.b_row_major = (b_major == KLAS_B_ROW_MAJOR) ? 1u : 0u;
-    p.idesc = ptx::umma_idesc_f16(in_dtype == KLAS_BF16, false, p.b_row_major != 0, tile_m, BN);
+    p.idesc = ptx::umma_idesc_f16(in_dtype == KLAS_BF16, false, p.b_row_major != 0, tile_m, p.tile_n);
     p.status = status_word;
     p.in_bf16 = in_dtype == KLAS_BF16 ? 1u : 0u;
     p.map_a = uint32_t(map_a);
@@ -1420,7 +1429,7 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
         if (v >= 1 && v <= 1024) p.raster_group = uint32_t(v);
     }
 
-    const uint32_t b_cols = pair ? Shape<true>::B_COLS : Shape<false>::B_COLS;
+    const uint32_t b_cols = pair ? Shape<true>::B_COLS : p.tile_n;
     CUtensorMap ta{}, tb{};
     if (shared > 0) {
         if (int rc = make_map(&ta, in_dtype, A, shared, rows, batch, BK, BM, lda, sa)) return rc;

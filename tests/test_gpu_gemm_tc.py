@@ -13,9 +13,10 @@ TOL_BF16_F32 = 2e-3   # bf16 x bf16 -> f32, relative to fp64, component-wise sca
 TOL_F16_F16 = 1e-2    # f16 x f16 -> f16
 
 
-@pytest.fixture(autouse=True, params=["single", "pair", "wide", "auto"])
+@pytest.fixture(autouse=True, params=["single", "narrow", "pair", "wide", "auto"])
 def tc_mode(request, monkeypatch):
-    """Every test runs with the single-CTA tiles, the CTA-pair tiles, the wide pair tiles and the library's own choice."""
+    """Every test runs with the single-CTA tiles (256 and 128 columns wide), the CTA-pair tiles, the wide pair
+    tiles and the library's own choice."""
     if request.param == "auto":
         monkeypatch.delenv("KLAS_TC_MODE", raising=False)
     else:
@@ -170,7 +171,7 @@ def test_zero_inner_dimension():
 @pytest.mark.parametrize("rows,cols,expect", [
     (2048, 2048, "one round of single tiles"), (2560, 2048, "40 wide tiles, one round"),
     (3072, 3072, "72 wide tiles, one round"), (3584, 3072, "84 wide tiles would take two rounds: pairs"),
-    (3000, 2056, "ragged edges")])
+    (3000, 2056, "ragged edges"), (1024, 1024, "64 narrow tiles instead of 32"), (1536, 1480, "narrow, ragged")])
 def test_tile_choice_does_not_change_results(oracle, rows, cols, expect, monkeypatch, tc_mode):
     """The library picks single, pair or wide tiles from the shape.  Every element is accumulated
     over k in the same order whatever the tile, so the three kernels and the library's own choice
@@ -180,7 +181,7 @@ def test_tile_choice_does_not_change_results(oracle, rows, cols, expect, monkeyp
     shared = 192
     A, Bt = synth.gemm_bf16(31, rows, cols, shared, b_col_major=True, device="cuda")
     results = {}
-    for mode in ("auto", "single", "pair", "wide"):
+    for mode in ("auto", "single", "narrow", "pair", "wide"):
         if mode == "auto":
             monkeypatch.delenv("KLAS_TC_MODE", raising=False)
         else:
@@ -188,7 +189,7 @@ def test_tile_choice_does_not_change_results(oracle, rows, cols, expect, monkeyp
         results[mode] = klas.gemm_tc(A, Bt, out_dtype=torch.float32, b_col_major=True)
     torch.cuda.synchronize()
     assert klas.gemm_tc_status() == 0
-    for mode in ("single", "pair", "wide"):
+    for mode in ("single", "narrow", "pair", "wide"):
         assert torch.equal(results["auto"], results[mode]), "%s differs (%s)" % (mode, expect)
     pick = torch.arange(0, rows, 97, device="cuda")
     acc, scale = tc_reference(oracle, A[pick].cpu(), Bt.cpu(), True)
