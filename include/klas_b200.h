@@ -234,15 +234,33 @@ int klas_b200_debug_wait_probe(uint32_t limit_ms, int *gave_up, void *stream);
  * CSR x dense:  C[rows x cols] = CSR(A)[rows x shared] . B[shared x cols],
  * B and C row-major, dtype KLAS_F32 or KLAS_U32 (wrapping).  Each row's
  * products are summed in CSR order starting from 0.  Every row of C is
- * overwritten (all-zero rows included).  `row_indices` (a permutation of
- * 0..rows-1 giving the order in which rows are scheduled) may be NULL.
+ * overwritten (all-zero rows included).  `row_indices` (in the reference a permutation of
+ * 0..rows-1 giving the order in which rows are scheduled) may be NULL and is not read: work is
+ * cut into ranges of equal size (rows + nonzeros) instead.
  * CSR: row_off[0] == 0, monotone, row_off[rows] == nnz, columns < shared.
+ * A row with more than max(1024, (rows + nnz) / (4 * resident warps)) nonzeros is summed in
+ * pieces that are added to C atomically: for such rows the f32 result is within the tolerance
+ * but the order of the pieces, hence the last bits, may change from call to call.  All other
+ * rows are summed in CSR order and repeat bit for bit.
  *
  * Replaces: Klas_SPMM_spmm_{f32,u32}, Klas_SPMM_g_spmm_f32_* (dist/Klas_SPMM.h:15-673).
  */
 int klas_b200_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32_t nnz,
                    const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
                    const uint32_t *row_indices, const void *B, void *C, void *stream);
+
+/*
+ * Measurement aid for klas_b200_spmm (f32, cols % 4 == 0): issues exactly the reads of B that the
+ * SpMM kernel issues for a matrix with these column indices -- for every nonzero and every slab
+ * of 128 columns one 512-byte piece of row col_ind[i] of B (shared x cols, row-major) -- and
+ * nothing else: no values, no products, no C.  Its duration is the time the memory system needs
+ * to deliver the gathers, the ceiling a bench reports the SpMM kernel against (with random
+ * columns the gathers, nnz * 4 * cols bytes from L2 to the SMs, outweigh the bytes DRAM moves by
+ * more than an order of magnitude).  Writes nothing.
+ * No counterpart in the reference.
+ */
+int klas_b200_spmm_gather_probe(uint32_t shared, uint32_t cols, uint32_t nnz, const uint32_t *col_ind,
+                                const void *B, void *stream);
 
 /*
  * Building the CSR operand of klas_b200_spmm on the device, from a dense row-major rows x cols

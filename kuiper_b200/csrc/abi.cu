@@ -230,7 +230,7 @@ int klas_b200_sdpa(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e
                                         bias_scores, scale, 1.0f, KLAS_MAP_ID, KLAS_MAP_ID,
                                         has_bias ? KLAS_COMB_AXPBY : KLAS_COMB_SCALED, nullptr, st))
         return rc;
-    if (int rc = launch_softmax(dtype, 0, uint64_t(pages) * l, s, bias_scores, nullptr, 0, st)) return rc;
+    if (int rc = launch_softmax_rows(dtype, 0, uint64_t(pages) * l, s, bias_scores, st)) return rc;
     return launch_gemm_umma(dtype, dtype, KLAS_B_ROW_MAJOR, pages, l, s, ev, bias_scores, V, nullptr, out, 1.0f, 0.0f,
                             nullptr, st);
 }
@@ -263,6 +263,13 @@ int klas_b200_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uin
     clear_error();
     return launch_spmm(dtype, rows, shared, cols, nnz, elems, col_ind, row_off, row_indices, B, C,
                        static_cast<cudaStream_t>(stream));
+}
+
+int klas_b200_spmm_gather_probe(uint32_t shared, uint32_t cols, uint32_t nnz, const uint32_t *col_ind, const void *B,
+                                void *stream) {
+    clear_error();
+    return launch_spmm_gather_probe(shared, cols, nnz, col_ind, static_cast<const float *>(B),
+                                    static_cast<cudaStream_t>(stream));
 }
 
 int klas_b200_gemm_host(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t n, uint64_t k,

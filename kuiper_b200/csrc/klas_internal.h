@@ -85,6 +85,10 @@ int launch_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32
                 const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
                 const uint32_t *row_indices, const void *B, void *C, cudaStream_t stream);
 
+// The gathers of the SpMM kernel alone (no values, products or stores): the rate ceiling it is measured against.
+int launch_spmm_gather_probe(uint32_t shared, uint32_t cols, uint32_t nnz, const uint32_t *col_ind, const float *B,
+                             cudaStream_t stream);
+
 int launch_sdpa_fused(int dtype, uint32_t pages, uint64_t l, uint64_t s, uint64_t e, const void *Q, const void *K,
                       const void *V, void *out, float scale, cudaStream_t stream);
 
@@ -102,6 +106,7 @@ size_t softmax_scratch_bytes(uint64_t rows, uint64_t cols);
 size_t reduce_scratch_bytes(uint64_t n);
 int launch_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a, void *scratch,
                    size_t scratch_bytes, cudaStream_t stream);
+int launch_softmax_rows(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a, cudaStream_t stream);
 int launch_rowscale(int dtype, int col_major, uint64_t m, uint64_t n, const void *scale, void *b,
                     cudaStream_t stream);
 int launch_reduce_sum(int dtype, uint64_t n, const void *a, void *out, void *scratch, size_t scratch_bytes,

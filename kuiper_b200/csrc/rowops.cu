@@ -486,9 +486,10 @@ static uint32_t reduce_blocks(uint64_t n) {
 }
 
 template <typename T>
-static int softmax_t(int log_softmax, uint64_t rows, uint64_t cols, void *a, void *scratch, cudaStream_t s) {
+static int softmax_t(int log_softmax, uint64_t rows, uint64_t cols, void *a, void *scratch, cudaStream_t s,
+                     bool as_rows = false) {
     T *p = static_cast<T *>(a);
-    if (rows > 1) {
+    if (rows > 1 || as_rows) {   // as_rows: a single row takes the row kernels too (no scratch)
         if (rows > 0x7fffffffull) return fail(KLAS_ERR_TOO_LARGE, "softmax: too many rows");
         constexpr uint64_t N = Pack<T>::N;
         if (cols % N == 0 && cols / N <= 32 * 4 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0) {
@@ -577,6 +578,20 @@ int launch_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, voi
         case KLAS_BF16: return rowops::softmax_t<__nv_bfloat16>(log_softmax, rows, cols, a, scratch, stream);
         case KLAS_F32: return rowops::softmax_t<float>(log_softmax, rows, cols, a, scratch, stream);
         case KLAS_F64: return rowops::softmax_t<double>(log_softmax, rows, cols, a, scratch, stream);
+        default: return fail(KLAS_ERR_INVALID, "softmax: dtype must be F16, BF16, F32 or F64");
+    }
+}
+
+// Softmax of every row with the row kernels whatever `rows` is: a one-row matrix (one query of one
+// head in attention) must not fall into the chunked vector path, which needs scratch.
+int launch_softmax_rows(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return KLAS_OK;
+    if (!a) return fail(KLAS_ERR_INVALID, "softmax: null data pointer");
+    switch (dtype) {
+        case KLAS_F16: return rowops::softmax_t<__half>(log_softmax, rows, cols, a, nullptr, stream, true);
+        case KLAS_BF16: return rowops::softmax_t<__nv_bfloat16>(log_softmax, rows, cols, a, nullptr, stream, true);
+        case KLAS_F32: return rowops::softmax_t<float>(log_softmax, rows, cols, a, nullptr, stream, true);
+        case KLAS_F64: return rowops::softmax_t<double>(log_softmax, rows, cols, a, nullptr, stream, true);
         default: return fail(KLAS_ERR_INVALID, "softmax: dtype must be F16, BF16, F32 or F64");
     }
 }

@@ -80,8 +80,13 @@ def gemm(A: torch.Tensor, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
     if B.dtype != A.dtype:
         raise TypeError("A and B dtypes differ")
     batch = 1
+    if A.dim() not in (2, 3) or B.dim() != A.dim():
+        raise ValueError("A and B must both be 2-D, or both 3-D with one page count (A %s, B %s); a matrix shared "
+                         "by all pages goes through gemm_strided with a page stride of 0" % (tuple(A.shape), tuple(B.shape)))
     if A.dim() == 3:
         batch = A.shape[0]
+        if B.shape[0] != batch:
+            raise ValueError("A has %d pages, B %d" % (batch, B.shape[0]))
         a2, b2 = A.shape[1:], B.shape[1:]
     else:
         a2, b2 = A.shape, B.shape
@@ -268,6 +273,9 @@ def gemm_tc(A: torch.Tensor, B: torch.Tensor, *, out_dtype=torch.float32, b_col_
     the product meets C_ (default: "axpby" with C_, "new" without)."""
     if A.dtype not in (torch.bfloat16, torch.float16) or B.dtype != A.dtype:
         raise TypeError("A and B must both be bf16 or both be f16")
+    if A.dim() not in (2, 3) or B.dim() != A.dim() or (A.dim() == 3 and B.shape[0] != A.shape[0]):
+        raise ValueError("A and B must both be 2-D, or both 3-D with one page count (A %s, B %s); the kernel reads one "
+                         "page of B per page of A" % (tuple(A.shape), tuple(B.shape)))
     batch = A.shape[0] if A.dim() == 3 else 1
     rows, shared = A.shape[-2:]
     if b_col_major:
@@ -380,6 +388,20 @@ def spmm(A: Csr, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
                                  _dev(A.row_off, "row_off"), ri, _dev(B, "B"), _dev(C_, "C"),
                                  _stream()))
     return C_
+
+
+def spmm_gather_probe(A: Csr, B: torch.Tensor) -> None:
+    """Issues the reads of B that spmm(A, B) issues (f32, cols % 4 == 0) and nothing else; time it
+    to get the gather-rate ceiling of that product."""
+    if B.dtype != torch.float32 or A.elems.dtype != torch.float32:
+        raise TypeError("spmm_gather_probe needs f32 operands")
+    shared, cols = B.shape
+    if shared != A.shared:
+        raise ValueError("B has %d rows, the CSR matrix %d columns" % (shared, A.shared))
+    lib = _lib.load()
+    with torch.cuda.device(B.device):
+        check(lib.klas_b200_spmm_gather_probe(shared, cols, A.nnz, _dev(A.col_ind, "col_ind") if A.nnz else None,
+                                              _dev(B, "B"), _stream()))
 
 
 def softmax(a: torch.Tensor, *, log: bool = False) -> torch.Tensor:

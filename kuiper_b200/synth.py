@@ -242,6 +242,69 @@ def csr_poisson(seed: int, rows: int, shared: int, mean_nnz: float, row0: int = 
     return Csr(nrows, shared, elems, col_ind, row_off32, longest_first(row_off32))
 
 
+def power_law_counts(rows: int, shared: int, mean_nnz: float, alpha: float = 0.8, device="cpu") -> torch.Tensor:
+    """Row lengths proportional to 1 / rank^alpha, scaled to the given mean and capped at `shared`:
+    a few very long rows and a long tail of short ones (the shape of the reference's non-uniform
+    SpMM bench, bench/sputnik-bench/spmm_bench.cu:136-154, with row i of rank i + 1)."""
+    w = torch.arange(1, rows + 1, dtype=torch.float64, device=device) ** (-alpha)
+    cnt = torch.floor(w * (mean_nnz * rows / float(w.sum()))).to(torch.int64)
+    return torch.clamp(cnt, min=0, max=shared)
+
+
+def csr_from_counts(seed: int, cnt: torch.Tensor, shared: int, device="cpu", value_kind: str = "f32",
+                    dense_from: int = 1024) -> Csr:
+    """CSR matrix with the given number of nonzeros per row: distinct sorted columns, uniform over
+    [0, shared), values uniform [-1,1) (f32) or [1, 100) (u32).  Short rows (up to `dense_from`
+    nonzeros and few enough that repeated draws rarely collide) are drawn together, with redraws on
+    collisions; each other row takes the `cnt` smallest of `shared` hashed keys, one row at a time."""
+    cnt = cnt.to(torch.int64).to(device)
+    nrows = int(cnt.numel())
+    if int(cnt.max()) > shared:
+        raise ValueError("a row cannot have more distinct columns than the matrix")
+    row_off = torch.zeros(nrows + 1, dtype=torch.int64, device=device)
+    row_off[1:] = torch.cumsum(cnt, 0)
+    nnz = int(row_off[-1])
+    col_ind = torch.empty(nnz, dtype=torch.int32, device=device)
+    is_short = (cnt <= dense_from) & (cnt * cnt <= shared)   # few collisions expected per draw
+    short = torch.nonzero(is_short).flatten()
+    maxc = int(cnt[short].max()) if short.numel() else 0
+    if maxc > 0:
+        j = torch.arange(maxc, dtype=torch.int64, device=device)[None, :]
+        todo = short
+        attempt = 0
+        while todo.numel() > 0:
+            ctr = ((todo[:, None] * 64 + attempt) * 4096 + j).reshape(-1)
+            z = splitmix64(_stream_seed(seed, 3), ctr)
+            c = (_lsr(z, 11).to(torch.float64) * (1.0 / (1 << 53)) * shared).to(torch.int64)
+            c = torch.clamp(c, max=shared - 1).view(-1, maxc)
+            c = torch.where(j < cnt[todo][:, None], c, shared + j)
+            c = torch.sort(c, dim=1).values
+            dup = ((c[:, 1:] == c[:, :-1]) & (c[:, 1:] < shared)).any(dim=1)
+            good = todo[~dup]
+            cg = c[~dup]
+            valid = cg < shared
+            dest = (row_off[good][:, None] + j)[valid]
+            col_ind[dest] = cg[valid].to(torch.int32)
+            todo = todo[dup]
+            attempt += 1
+            if attempt >= 256:
+                raise RuntimeError("csr_from_counts: could not draw distinct columns")
+    allc = torch.arange(shared, dtype=torch.int64, device=device)
+    for r in torch.nonzero(~is_short).flatten().tolist():
+        keys = splitmix64(_stream_seed(seed, 3), r * shared + allc)
+        pick = torch.argsort(keys, stable=True)[:int(cnt[r])]
+        lo = int(row_off[r])
+        col_ind[lo:lo + int(cnt[r])] = torch.sort(pick).values.to(torch.int32)
+    z = splitmix64(_stream_seed(seed, 4), torch.arange(nnz, dtype=torch.int64, device=device))
+    u = _lsr(z, 11).to(torch.float64) * (1.0 / (1 << 53))
+    if value_kind == "f32":
+        elems = (-1.0 + 2.0 * u).to(torch.float32)
+    else:
+        elems = (1 + (u * 99).to(torch.int64)).to(torch.int32)
+    row_off32 = row_off.to(torch.int32)
+    return Csr(nrows, shared, elems, col_ind, row_off32, longest_first(row_off32))
+
+
 def spmm_dense_b(seed: int, shared: int, cols: int, device="cpu", value_kind: str = "f32"):
     """Dense right-hand side, uniform [-1,1) f32 (or u32 in [0, 100) as int32)."""
     if value_kind == "f32":

@@ -58,3 +58,21 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(ImportError):
         _lib.load()
+
+
+def test_wrappers_reject_mismatched_page_counts_before_any_launch():
+    """A 3-D A with a 2-D B, or operands with different page counts, would make the kernel read
+    pages of B that do not exist: the wrappers must raise on the host (no GPU is touched here)."""
+    import torch
+    from kuiper_b200 import klas
+    a3 = torch.zeros((4, 64, 32), dtype=torch.bfloat16)
+    b2 = torch.zeros((32, 64), dtype=torch.bfloat16)
+    b3 = torch.zeros((2, 32, 64), dtype=torch.bfloat16)
+    for bad in (b2, b3):
+        with pytest.raises(ValueError):
+            klas.gemm_tc(a3, bad)
+    f3 = torch.zeros((4, 8, 8))
+    with pytest.raises(ValueError):
+        klas.gemm(f3, torch.zeros((8, 8)))
+    with pytest.raises(ValueError):
+        klas.gemm(f3, torch.zeros((3, 8, 8)))

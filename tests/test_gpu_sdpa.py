@@ -28,7 +28,8 @@ def attention_f64(Q, K, V, bias, scale, dtype):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float16, 2e-3), (torch.bfloat16, 1.6e-2)])
 @pytest.mark.parametrize("lead,l,s,e,ev", [((1,), 128, 128, 64, 64), ((2, 3), 200, 264, 40, 72), ((4,), 1024, 1024, 128, 128),
-                                           ((1, 2), 77, 2056, 64, 32), ((1,), 64, 4096, 64, 64)])
+                                           ((1, 2), 77, 2056, 64, 32), ((1,), 64, 4096, 64, 64),
+                                           ((1,), 1, 304, 40, 40)])   # one query of one head: a one-row score matrix
 @pytest.mark.parametrize("with_bias", [True, False])
 def test_matches_float64_attention(dtype, tol, lead, l, s, e, ev, with_bias):
     Q, K, V = (tensor(i, *lead, r, c, dtype=dtype) for i, (r, c) in enumerate([(l, e), (s, e), (s, ev)]))

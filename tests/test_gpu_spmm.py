@@ -34,6 +34,65 @@ def test_f32_matches_oracle(oracle, rows, shared, cols, mean):
     assert rel_err_componentwise(got, want, scale) <= TOL_SPMM
 
 
+def _counts_case(oracle, cnt, shared, cols, seed=21, value_kind="f32"):
+    csr = synth.csr_from_counts(seed, cnt, shared, value_kind=value_kind)
+    B = synth.spmm_dense_b(seed, shared, cols, value_kind=value_kind)
+    got = klas.spmm(csr.to("cuda"), B.cuda()).cpu().numpy()
+    if value_kind == "f32":
+        want, scale = oracle.spmm_f32(csr.rows, cols, csr.elems.numpy(), csr.col_ind.numpy().view(np.uint32),
+                                      csr.row_off.numpy().view(np.uint32), B.numpy(), with_abs=True)
+        return rel_err_componentwise(got, want, scale)
+    want = oracle.spmm_u32(csr.rows, cols, csr.elems.numpy().view(np.uint32), csr.col_ind.numpy().view(np.uint32),
+                           csr.row_off.numpy().view(np.uint32), B.numpy().view(np.uint32))
+    return 0.0 if np.array_equal(got.view(np.uint32), want) else 1.0
+
+
+@pytest.mark.parametrize("cols", [256, 96, 10])
+def test_long_rows_are_cut_across_ranges(oracle, cols):
+    """Rows far longer than a work range (the kernel cuts rows of more than 1024 nonzeros at range
+    boundaries and adds the pieces to C): a power-law matrix whose first rows are dense, a matrix
+    that is one long row between runs of empty rows, and long rows back to back."""
+    shared = 20000
+    assert _counts_case(oracle, synth.power_law_counts(600, shared, 120.0), shared, cols) <= TOL_SPMM
+    cnt = torch.zeros(700, dtype=torch.int64)
+    cnt[350] = 15000
+    assert _counts_case(oracle, cnt, shared, cols) <= TOL_SPMM
+    cnt = torch.tensor([5000, 1025, 1024, 0, 0, 9000, 3, 20000, 20000, 1, 0, 2047, 64, 64, 64, 1100])
+    assert _counts_case(oracle, cnt, shared, cols) <= TOL_SPMM
+
+
+def test_long_rows_u32_bit_exact(oracle):
+    """Wrapping integer sums are exact whatever the order of the pieces."""
+    cnt = torch.tensor([7000, 0, 12000, 5, 1500, 0, 0, 2500, 64])
+    assert _counts_case(oracle, cnt, 12000, 136, value_kind="u32") == 0.0
+
+
+def test_runs_of_empty_rows_and_one_nonzero(oracle):
+    cnt = torch.zeros(5000, dtype=torch.int64)
+    cnt[4999] = 1
+    assert _counts_case(oracle, cnt, 64, 128) <= TOL_SPMM
+    cnt = torch.zeros(5000, dtype=torch.int64)
+    cnt[0] = 40
+    cnt[2500:2510] = 7
+    assert _counts_case(oracle, cnt, 64, 36) <= TOL_SPMM
+
+
+def test_short_rows_repeat_bit_for_bit():
+    """Rows that stay on one warp (every row here) are summed in CSR order: two calls agree exactly."""
+    csr = synth.csr_poisson(9, 5000, 9000, 64.0, device="cuda")
+    B = synth.spmm_dense_b(9, 9000, 256, device="cuda")
+    assert torch.equal(klas.spmm(csr, B), klas.spmm(csr, B))
+
+
+def test_gather_probe_runs_and_writes_nothing():
+    csr = synth.csr_poisson(9, 3000, 4000, 30.0, device="cuda")
+    B = synth.spmm_dense_b(9, 4000, 200, device="cuda")
+    keep = B.clone()
+    klas.spmm_gather_probe(csr, B)
+    torch.cuda.synchronize()
+    assert torch.equal(B, keep)
+
+
 def test_row_order_does_not_change_results(oracle):
     csr = synth.csr_poisson(6, 333, 777, 25.0)
     B = synth.spmm_dense_b(6, 777, 64)
