@@ -19,13 +19,27 @@ benchmark configurations; see kuiper_b200/synth.py):
 Shards need no data-path collective: every rank owns its rows (or pages) of A and C
 and a replica of B.
 
+Beside the timed region the line carries, all measured outside it:
+  check        sampled rows of this rank's result against an fp64 product of the same inputs; with
+               more than one rank also one gathered pass (NCCL all-gather of C) compared with the
+               rank-local blocks.
+  sustained    (1 GPU, default workload) the same launch back to back for 3 s, with the clocks seen.
+  configs      (1 GPU, default workload) a short run of each other benchmark configuration
+               (spmm, gemm_f16b, gemm_u64, gemm_f32) with its own roofline and parity bit.
+  comparisons  (1 GPU, default workload) the reference's own kernels compiled for sm_100a
+               (oracle/_ref), cuBLAS and cuSPARSE through torch, on the same inputs.
+`--no-extras` leaves the last three out (profiler captures, quick runs).
+
 `--impl reference` times the reference's own host gold loop (test/matmul_common.c.inc
-cpu_mul, compiled unmodified into oracle/_ref) on the host cores, one instance per
-hardware thread on disjoint row blocks of a bounded sample of the same workload.
+cpu_mul, compiled unmodified into oracle/_ref; the CSR loop of the oracle for spmm, which
+the reference has for u32 only) on the host cores, one instance per hardware thread on
+disjoint row blocks of a bounded sample of the same workload.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
+import hashlib
 import json
 import os
 import statistics
@@ -135,6 +149,9 @@ class Workload:
     def e2e_step(self):                        # C-ABI host-buffer call: H2D + kernel + D2H
         raise NotImplementedError
 
+    def check(self):                           # parity of the last launch's result, outside any timed region
+        return None
+
 
 class GemmBf16(Workload):
     name, metric, unit, dtype, bound = "gemm_bf16", "bf16_gemm_tflops", "TFLOP/s", "bf16", "tensor"
@@ -169,8 +186,18 @@ class GemmBf16(Workload):
         from kuiper_b200 import klas
         klas.gemm_tc(self.A, self.Bt, out_dtype=self.torch.float32, b_col_major=True, D=self.D)
 
-    def result_scalar(self):
-        return float(self.D[0, 0])
+    TOL = 2e-3          # bf16 x bf16 -> f32 against fp64, relative to (|A|.|B|)_ij
+
+    def check(self):
+        """64 rows of this rank's block of D against an fp64 product of the same seeded rows."""
+        t = self.torch
+        idx = t.arange(0, self.rows, max(1, self.rows // 64), device=self.A.device)[:64]
+        b64 = self.Bt.double()
+        want = self.A[idx].double() @ b64.t()
+        scale = self.A[idx].double().abs() @ b64.abs().t()
+        err = float(((self.D[idx].double() - want).abs() / scale.clamp_min(1e-300)).max())
+        return {"what": "64 rows of this rank's block against an fp64 product of the same inputs",
+                "rows": int(idx.numel()), "max_rel_err": err, "tol": self.TOL, "ok": err <= self.TOL}
 
     def e2e_step(self):
         from kuiper_b200 import _lib
@@ -218,6 +245,21 @@ class GemmF16Batched(Workload):
         from kuiper_b200 import klas
         klas.gemm_tc(self.A, self.B, out_dtype=self.torch.float16, D=self.D)
 
+    TOL = 1e-2
+
+    def check(self):
+        """16 rows of EVERY page against fp64 products of the same rows."""
+        t = self.torch
+        idx = t.arange(0, self.m, self.m // 16, device=self.A.device)[:16]
+        worst = 0.0
+        for pg in range(self.pages):
+            b64 = self.B[pg].double()
+            want = self.A[pg][idx].double() @ b64
+            scale = self.A[pg][idx].double().abs() @ b64.abs()
+            worst = max(worst, float(((self.D[pg][idx].double() - want).abs() / scale.clamp_min(1e-300)).max()))
+        return {"what": "16 rows of each of the %d pages against fp64 products" % self.pages, "rows": 16 * self.pages,
+                "max_rel_err": worst, "tol": self.TOL, "ok": worst <= self.TOL}
+
     def e2e_step(self):
         from kuiper_b200 import _lib
         if self._host is None:
@@ -264,6 +306,23 @@ class GemmSimt(Workload):
         from kuiper_b200 import klas
         klas.gemm(self.A, self.B, self.C)
 
+    def check(self):
+        t = self.torch
+        if self.kind == "u64":
+            # 8 rows, exact: int64 products and sums wrap mod 2^64 exactly as the kernel's do
+            idx = list(range(0, self.rows, max(1, self.rows // 8)))[:8]
+            bad = 0
+            for r in idx:
+                want = (self.A[r][:, None] * self.B).sum(0)
+                bad += int((want != self.C[r]).sum())
+            return {"what": "8 rows, bit for bit, against wrapping int64 arithmetic", "rows": len(idx),
+                    "mismatches": bad, "ok": bad == 0}
+        want = self.A.double() @ self.B.double()
+        scale = self.A.double().abs() @ self.B.double().abs()
+        err = float(((self.C.double() - want).abs() / scale.clamp_min(1e-300)).max())
+        return {"what": "the whole result against an fp64 product", "rows": self.rows, "max_rel_err": err,
+                "tol": 1e-5, "ok": err <= 1e-5}
+
     def e2e_step(self):
         from kuiper_b200 import _lib
         if self._host is None:
@@ -307,6 +366,24 @@ class Spmm(Workload):
         from kuiper_b200 import klas
         klas.spmm(self.csr, self.B, self.C)
 
+    def launch_gather_probe(self):
+        from kuiper_b200 import klas
+        klas.spmm_gather_probe(self.csr, self.B)
+
+    def check(self):
+        """64 rows against an fp64 gather-and-sum of the same rows."""
+        t = self.torch
+        ro = self.csr.row_off.long()
+        worst = 0.0
+        rows = list(range(0, self.rows, max(1, self.rows // 64)))[:64]
+        for r in rows:
+            lo, hi = int(ro[r]), int(ro[r + 1])
+            prod = self.csr.elems[lo:hi].double()[:, None] * self.B[self.csr.col_ind[lo:hi].long()].double()
+            want, scale = prod.sum(0), prod.abs().sum(0)
+            worst = max(worst, float(((self.C[r].double() - want).abs() / scale.clamp_min(1e-300)).max()))
+        return {"what": "64 rows against an fp64 sum of the same products", "rows": len(rows), "max_rel_err": worst,
+                "tol": 1e-5, "ok": worst <= 1e-5}
+
     def e2e_step(self):
         from kuiper_b200 import _lib
         if self._host is None:
@@ -333,7 +410,7 @@ class Softmax(Workload):
         need = _lib.load().klas_b200_softmax_scratch_bytes(1, self.N)
         self.scratch = torch.empty(need, dtype=torch.uint8, device=device)
         self.algorithmic_bytes = 3 * 4 * self.N          # two reads and one write of the vector
-        self.traffic = NCU_TRAFFIC["softmax_f32"] if log2n == 28 else None   # the capture is scaled to the bench size only
+        self.traffic_scaled = log2n == 28   # the DRAM-traffic capture is of the bench size only
         self.config = {"workload": "in-place softmax of one f32 vector of 2^%d elements per GPU, N(0,16) values, seed 5+rank; "
                                    "steps after the first run on the previous step's output (same traffic and instruction count)" % log2n,
                        "sharding": "one independent vector per GPU, no collective",
@@ -423,34 +500,78 @@ def make_workload(name, rank, world, device, args=None):
 
 
 # --------------------------------------------------------------------------- CPU legs
-def reference_cpu_gemm_bf16(seconds_target: float, threads: int):
-    """Times the reference's cpu_mul (bf16 in, f32 out, double accumulation; compiled unmodified
-    into oracle/_ref) -- or the oracle port when oracle/_ref is absent -- on a row sample of the
-    gemm_bf16 workload, one instance per thread on disjoint row blocks.
-    Returns (tflops, kind, cores, sample description, seconds)."""
+CPU_METRICS = {"gemm_bf16": ("bf16_gemm_tflops", "TFLOP/s", "bf16"), "gemm_f16b": ("f16_batched_gemm_tflops", "TFLOP/s", "f16"),
+               "gemm_u64": ("u64_gemm_tops", "Tops/s", "u64"), "gemm_f32": ("f32_gemm_tflops", "TFLOP/s", "f32"),
+               "spmm": ("spmm_compulsory_gbs", "GB/s", "f32")}
+
+
+def reference_cpu_leg(workload: str, threads: int):
+    """The reference's own host gold loop for `workload` (test/matmul_common.c.inc cpu_mul per element
+    type, compiled unmodified into oracle/_ref; the oracle port where oracle/_ref is absent, and for
+    spmm, whose f32 CSR loop the reference does not have) on a bounded sample of the workload: every
+    thread multiplies its own block of rows of A by all of B.
+    Returns (one_pass -> seconds, kind, sample description, units per pass)."""
     import numpy as np
     sys.path.insert(0, str(REPO / "oracle"))
     import build as oracle_build
     from oracle_api import Oracle, RefCpu, bf16_bits
-    wl = GemmBf16.__new__(GemmBf16)
-    rows_per_thread = 2
-    a, b = GemmBf16.cpu_inputs(wl, rows_per_thread * threads)
-    a_bits, b_bits = bf16_bits(a), bf16_bits(b)
-    if RefCpu.available():
-        ref = RefCpu()
-        kind = "reference"
-
-        def run_block(t):
-            blk = np.ascontiguousarray(a_bits[t * rows_per_thread:(t + 1) * rows_per_thread])
-            ref.cpu_mul("bf16_f32", blk, b_bits)
-    else:
+    from kuiper_b200 import synth
+    have_ref = RefCpu.available()
+    ref = RefCpu() if have_ref else None
+    if not have_ref or workload == "spmm":
         oracle_build.build_oracle()
-        orc = Oracle()
-        kind = "port"
+    orc = Oracle() if (not have_ref or workload == "spmm") else None
+    kind = "reference" if have_ref and workload != "spmm" else "port"
+
+    def gemm_leg(ref_kind, port_kind, a_np, b_np, rows_per_thread, units, sample):
+        def run_block(t):
+            blk = np.ascontiguousarray(a_np[t * rows_per_thread:(t + 1) * rows_per_thread])
+            if have_ref:
+                ref.cpu_mul(ref_kind, blk, b_np)
+            elif port_kind in ("u64",):
+                orc.gemm_int(blk, b_np)
+            else:
+                orc.gemm(blk, b_np, kind=port_kind, threads=1)
+        return run_block, units, sample
+
+    if workload == "gemm_bf16":
+        rpt = 2
+        a, b = synth.gemm_bf16(1, GemmBf16.ROWS_PER_GPU, GemmBf16.N, GemmBf16.K, row0=0, rows=rpt * threads, b_col_major=False)
+        run_block, units, sample = gemm_leg("bf16_f32", "bf16", bf16_bits(a), bf16_bits(b), rpt, 2.0 * rpt * threads * GemmBf16.N * GemmBf16.K,
+                                            "%d rows of A (%d per thread) x full 8192 x 8192 B per step" % (rpt * threads, rpt))
+    elif workload == "gemm_f16b":
+        rpt = 16
+        a, b = synth.gemm_f16_batched(2, 1, 2048, 2048, 2048)
+        a_np, b_np = a[0][:rpt * threads].contiguous().view(torch_int16()).numpy().view(np.uint16), b[0].view(torch_int16()).numpy().view(np.uint16)
+        run_block, units, sample = gemm_leg("f16_f16", "f16", a_np, b_np, rpt, 2.0 * min(rpt * threads, 2048) * 2048 * 2048,
+                                            "%d rows of page 0 (%d per thread) x its 2048 x 2048 B per step" % (min(rpt * threads, 2048), rpt))
+    elif workload == "gemm_u64":
+        rpt = 4
+        a, b = synth.gemm_u64(3, 4096, 4096, 4096, row0=0, rows=rpt * threads)
+        run_block, units, sample = gemm_leg("u64", "u64", a.numpy().view(np.uint64), b.numpy().view(np.uint64), rpt, 2.0 * rpt * threads * 4096 * 4096,
+                                            "%d rows of A (%d per thread) x full 4096 x 4096 B per step" % (rpt * threads, rpt))
+    elif workload == "gemm_f32":
+        rpt = max(1, min(64, 1024 // threads))
+        a, b = synth.gemm_f32(0, 1024, 1024, 1024, row0=0, rows=rpt * threads)
+        run_block, units, sample = gemm_leg("f32", "f32", a.numpy(), b.numpy(), rpt, 2.0 * rpt * threads * 1024 * 1024,
+                                            "%d rows of A (%d per thread) x full 1024 x 1024 B per step" % (rpt * threads, rpt))
+    elif workload == "spmm":
+        rpt = 256
+        nrows = rpt * threads
+        csr = synth.csr_poisson(4, Spmm.ROWS, Spmm.SHARED, 64.0, row0=0, nrows=nrows)
+        bmat = synth.spmm_dense_b(4, Spmm.SHARED, Spmm.COLS).numpy()
+        el, ci, ro = csr.elems.numpy(), csr.col_ind.numpy().view(np.uint32), csr.row_off.numpy().view(np.uint32)
 
         def run_block(t):
-            blk = np.ascontiguousarray(a_bits[t * rows_per_thread:(t + 1) * rows_per_thread])
-            orc.gemm(blk, b_bits, kind="bf16", threads=1)
+            lo, hi = int(ro[t * rpt]), int(ro[(t + 1) * rpt])
+            orc.spmm_f32(rpt, Spmm.COLS, el[lo:hi], ci[lo:hi], np.ascontiguousarray(ro[t * rpt:(t + 1) * rpt + 1] - ro[t * rpt]), bmat, threads=1)
+        nnz = int(ro[nrows])
+        # the GPU line's byte model, scaled to the sample: its nonzeros, row offsets and order, its rows of C,
+        # and its share (rows / all rows) of the one read of B
+        units = nnz * 8 + (2 * nrows + 1) * 4 + 4 * nrows * Spmm.COLS + 4 * Spmm.SHARED * Spmm.COLS * nrows / Spmm.ROWS
+        sample = "%d CSR rows (%d per thread, %d nonzeros) x full 131072 x 256 B per step; the oracle's f32 CSR loop (the reference has one for u32 only)" % (nrows, rpt, nnz)
+    else:
+        return None
 
     def one_pass():
         ts = [threading.Thread(target=run_block, args=(t,)) for t in range(threads)]
@@ -461,31 +582,38 @@ def reference_cpu_gemm_bf16(seconds_target: float, threads: int):
             t.join()
         return time.perf_counter() - t0
 
-    return one_pass, kind, rows_per_thread * threads, GemmBf16.cpu_units(wl, rows_per_thread * threads)
+    return one_pass, kind, sample, float(units)
+
+
+def torch_int16():
+    import torch
+    return torch.int16
 
 
 def run_reference_arm(args, rank, world):
     if rank != 0:
         return 0
-    if args.workload != "gemm_bf16":
-        print(json.dumps({"impl": "reference", "unavailable": "reference arm implemented for the gemm_bf16 headline workload only"}))
+    if args.workload not in CPU_METRICS:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference has no host loop for workload %s" % args.workload}))
         return 0
     threads = os.cpu_count() or 1
-    one_pass, kind, rows, units = reference_cpu_gemm_bf16(0, threads)
+    one_pass, kind, sample, units = reference_cpu_leg(args.workload, threads)
+    metric, unit, dtype = CPU_METRICS[args.workload]
+    scale = 1e12 if unit in ("TFLOP/s", "Tops/s") else 1e9
     for _ in range(max(args.warmup, 1)):
         one_pass()
     t = 0.0
     for _ in range(args.steps):
         t += one_pass()
-    value = units * args.steps / t / 1e12
-    sample = "%d rows of A (2 per thread) x full 8192 x 8192 B per step" % rows
+    value = units * args.steps / t / scale
+    describe = {"gemm_bf16": GemmBf16.describe(max(args.gpus, 1))}.get(args.workload, {"workload": args.workload})
     line = {
-        "impl": "reference", "metric": "bf16_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": dict(GemmBf16.describe(max(args.gpus, 1)), sample=sample, impl="host gold loop cpu_mul on a row sample"),
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
-        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "scaling": "weak" if args.workload == "gemm_bf16" else "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": dict(describe, sample=sample, impl="host gold loop on a row sample, one instance per hardware thread"),
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
@@ -518,25 +646,288 @@ def cpu_baseline_softmax():
             "sample": "%d x softmax of 2^24 elements in float64, single thread as written; bytes counted as 12 per element" % reps}
 
 
-def cpu_baseline_leg(workload_name):
-    """Single-threaded, as the reference's loop is written; ~10-20 s of CPU work."""
+def cpu_baseline_leg(workload_name, seconds=12.0):
+    """Single-threaded, as the reference's loop is written; about `seconds` of CPU work."""
     if workload_name == "softmax_f32":
         return cpu_baseline_softmax()
-    if workload_name != "gemm_bf16":
+    if workload_name not in CPU_METRICS:
         return None
-    one_pass, kind, rows, units = reference_cpu_gemm_bf16(0, 1)
+    one_pass, kind, sample, units = reference_cpu_leg(workload_name, 1)
+    unit = CPU_METRICS[workload_name][1]
+    scale = 1e12 if unit in ("TFLOP/s", "Tops/s") else 1e9
     t1 = one_pass()
-    reps = max(1, min(64, int(12.0 / max(t1, 1e-3))))
+    reps = max(1, min(64, int(seconds / max(t1, 1e-3))))
     t = sum(one_pass() for _ in range(reps))
-    return {"value": units * reps / t / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": kind,
-            "sample": "%d x (%d rows of A x full 8192 x 8192 B), single thread as written" % (reps, rows)}
+    return {"value": units * reps / t / scale, "unit": unit, "cores": 1, "kind": kind,
+            "sample": "%d x (%s), single thread as written" % (reps, sample)}
+
+
+# --------------------------------------------------------------------------- measurement helpers
+# DRAM traffic of one launch (dram__bytes_read.sum + dram__bytes_write.sum) from an ncu capture of
+# the same kernel on the same workload (the summaries are under profiles/).  Each figure is tied
+# to the SHA-256 of the kernel source it was captured from: when the source has changed since,
+# the figure is withheld (traffic null, with a note) instead of going stale silently.
+NCU_TRAFFIC = {
+    "gemm_bf16": (1.150e9, "kuiper_b200/csrc/gemm_umma.cu", "bbd8d21d02a71b67"),
+    "spmm": (1.141e9, "kuiper_b200/csrc/spmm.cu", "UNSET"),
+    "gemm_u64": (2.163e9, "kuiper_b200/csrc/gemm_simt.cu", "ec549630d00e7b32"),
+    "gemm_f32": (8.4e6, "kuiper_b200/csrc/gemm_simt.cu", "ec549630d00e7b32"),
+    "softmax_f32": (3.18e9, "kuiper_b200/csrc/rowops.cu", "UNSET"),
+}
+NOMINAL_BF16_TFLOPS = 2250.0     # dense bf16, vendor figure
+NOMINAL_HBM_GBS = 8000.0
+
+
+def ncu_traffic(name):
+    """(bytes or None, note) for workload `name`."""
+    if name not in NCU_TRAFFIC:
+        return None, "no capture"
+    nbytes, rel, digest = NCU_TRAFFIC[name]
+    src = REPO / rel
+    if not src.exists():
+        return None, "kernel source not found"
+    now = hashlib.sha256(src.read_bytes()).hexdigest()[:16]
+    if now != digest:
+        return None, "withheld: %s has changed since the capture (%s then, %s now)" % (rel, digest, now)
+    return nbytes, "ncu capture of this source (%s)" % digest
+
+
+def time_launches(torch, fn, steps, warm=3):
+    """Average device time of `fn` (ms) over `steps` back-to-back calls after `warm` untimed ones."""
+    for _ in range(warm):
+        fn()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(steps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / steps
+
+
+def roofline_of(wl, per_launch_ms, peaks, sm_mhz=None):
+    """The roofline block of one workload: algorithmic work of a launch over its device time,
+    against the measured peak (and, for the tensor-core and HBM bounds, the other denominators)."""
+    sec = per_launch_ms * 1e-3
+    out = {}
+    if wl.bound == "tensor":
+        achieved = wl.per_step_units() / sec / 1e12
+        peak, runit = peaks["bf16_tflops"], "TFLOP/s"
+        peak_note = "cuBLAS bf16 burst, of %s" % peaks["source"]
+        out["frac_burst"] = achieved / peaks["bf16_tflops"]
+        if peaks.get("bf16_tflops_sustained"):
+            out["frac_sustained"] = achieved / peaks["bf16_tflops_sustained"]
+        out["frac_nominal"] = achieved / NOMINAL_BF16_TFLOPS
+        out["denominators"] = {"burst_of_%s" % peaks["source"]: peaks["bf16_tflops"],
+                               "sustained_of_%s" % peaks["source"]: peaks.get("bf16_tflops_sustained"),
+                               "nominal_dense_bf16": NOMINAL_BF16_TFLOPS}
+    elif wl.bound == "hbm":
+        achieved = wl.algorithmic_bytes / sec / 1e9
+        peak, runit = peaks["hbm_gbs"], "GB/s"
+        peak_note = "stream copy, of %s" % peaks["source"]
+        out["frac_nominal"] = achieved / NOMINAL_HBM_GBS
+    else:
+        # CUDA-core GEMMs are issue-bound: reported against the nominal issue peak at max clock
+        achieved = wl.per_step_units() / sec / 1e12
+        if wl.name == "gemm_u64":
+            # a wrapping u64 multiply-add = one widening 32x32 multiply-add (2 issue slots of the
+            # 64-lane integer-multiply pipe) + two 32-bit ones: 4 slots per MAC, 2 ops per MAC
+            peak, runit = 2 * (64 / 4) * 148 * 1.965e9 / 1e12, "Tops/s"
+            peak_note = "64 integer-multiply lanes/clk/SM, 4 slots per u64 MAC, 148 SMs, 1965 MHz (nominal)"
+        else:
+            peak, runit = 2 * 128 * 148 * 1.965e9 / 1e12, "TFLOP/s"
+            peak_note = "2*128 lanes*148 SMs*1965 MHz FP32 issue peak (nominal)"
+    traffic, traffic_note = ncu_traffic(wl.name)
+    if getattr(wl, "traffic_scaled", True) is False:
+        traffic, traffic_note = None, "the capture is of the bench size only"
+    roof = {"bound": "tensor" if wl.bound == "tensor" else "hbm" if wl.bound == "hbm" else "issue",
+            "achieved": achieved, "peak": peak, "unit": runit, "frac": achieved / peak,
+            "traffic": traffic, "traffic_note": traffic_note, "peak_note": peak_note,
+            "algorithmic_bytes_per_launch": wl.algorithmic_bytes, "kernel_ms": per_launch_ms}
+    if sm_mhz:
+        roof["sm_mhz"] = sm_mhz
+    roof.update(out)
+    return roof
+
+
+def spmm_gather_block(torch, wl, per_launch_ms):
+    """What really bounds the SpMM kernel: with random columns every nonzero moves 4 * cols bytes of a
+    row of B from L2 to an SM whatever the schedule.  The ceiling is measured here, on the same
+    matrix: a kernel that issues exactly those reads and nothing else (klas_b200_spmm_gather_probe)."""
+    gather = wl.nnz * 4 * wl.COLS
+    probe_ms = time_launches(torch, wl.launch_gather_probe, 20)
+    return {"gather_bytes_per_launch": gather, "gather_achieved_gbs": gather / (per_launch_ms * 1e-3) / 1e9,
+            "gather_probe_ms": probe_ms, "gather_ceiling_gbs": gather / (probe_ms * 1e-3) / 1e9,
+            "frac_of_gather_ceiling": probe_ms / per_launch_ms,
+            "note": "compulsory DRAM bytes are 1/25 of the L2->SM gather volume at this size: the kernel is bound by "
+                    "the gather rate, measured by the probe (same index stream, same 512-byte reads, no values, "
+                    "products or stores)"}
+
+
+def sustained_leg(torch, wl, local, peaks, seconds=3.0):
+    """The headline launch back to back for `seconds` (the power cap settles within about a second):
+    what the kernel sustains, with the SM clock and throttle reasons seen while it ran."""
+    per = time_launches(torch, wl.launch, 10)
+    n = max(50, int(seconds * 1e3 / per))
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    torch.cuda.synchronize()
+    with sampler:
+        s.record()
+        for _ in range(n):
+            wl.launch()
+        e.record()
+        torch.cuda.synchronize()
+    ms = s.elapsed_time(e)
+    value = wl.per_step_units() * n / (ms * 1e-3) / 1e12
+    out = {"seconds": ms * 1e-3, "launches": n, "value": value, "unit": "TFLOP/s", "ms_per_launch": ms / n,
+           "clocks": sampler.summary(), "frac_nominal": value / NOMINAL_BF16_TFLOPS, "frac_burst": value / peaks["bf16_tflops"]}
+    if peaks.get("bf16_tflops_sustained"):
+        out["frac_sustained"] = value / peaks["bf16_tflops_sustained"]
+    return out
+
+
+def config_leg(torch, name, device, peaks, args):
+    """A short run (>= 20 launches) of one of the other benchmark configurations on this GPU: value,
+    roofline, parity of the result, and the host loop on a small sample."""
+    t0 = time.perf_counter()
+    wl = make_workload(name, 0, 1, device, args)
+    steps = 20 if name != "gemm_f32" else 200
+    per = time_launches(torch, wl.launch, steps)
+    scale = 1e12 if wl.unit in ("TFLOP/s", "Tops/s") else 1e9
+    out = {"metric": wl.metric, "value": wl.per_step_units() / (per * 1e-3) / scale, "unit": wl.unit, "steps": steps,
+           "ms_per_step": per, "config": wl.config, "roofline": roofline_of(wl, per, peaks), "parity": wl.check()}
+    if name == "spmm":
+        out["roofline"]["gather"] = spmm_gather_block(torch, wl, per)
+    wl.e2e_step()
+    t1 = time.perf_counter()
+    for _ in range(2):
+        wl.e2e_step()
+    torch.cuda.synchronize()
+    out["e2e"] = {"value": wl.per_step_units() * 2 / (time.perf_counter() - t1) / scale, "unit": wl.unit,
+                  "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "steps": 2}
+    if not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline_leg(name, seconds=2.0)
+    del wl
+    torch.cuda.empty_cache()
+    out["leg_seconds"] = time.perf_counter() - t0
+    return out
+
+
+class RefGpuLib:
+    """The reference's own extracted kernels compiled for sm_100a (oracle/_ref, built from the
+    FStarLang/kuiper tree by oracle/build.py).  Comparison rows only: nothing here is timed as ours."""
+
+    class SMatrixF32(ctypes.Structure):
+        _fields_ = [("nnz", ctypes.c_uint32), ("elems", ctypes.c_void_p), ("col_ind", ctypes.c_void_p), ("row_off", ctypes.c_void_p)]
+
+    def __init__(self):
+        d = REPO / "oracle" / "_ref"
+        self.lib = ctypes.CDLL(str(d / "libklas_ref_gpu.so"))
+        self.symbols = json.loads((d / "symbols.json").read_text())
+        ng = d / "libklas_ref_spmm_noguard.so"
+        self.noguard = ctypes.CDLL(str(ng)) if ng.exists() else None
+
+    @staticmethod
+    def available():
+        d = REPO / "oracle" / "_ref"
+        return (d / "libklas_ref_gpu.so").exists() and (d / "symbols.json").exists()
+
+    def gemm(self, name, m, k, n, A, B, Cc):
+        f = getattr(self.lib, self.symbols[name])
+        f.restype = None
+        f.argtypes = [ctypes.c_uint32] * 3 + [ctypes.c_void_p] * 3
+        f(m, k, n, A.data_ptr(), B.data_ptr(), Cc.data_ptr())
+
+    def spmm(self, name, rows, shared, cols, csr, B, Cc):
+        f = getattr(self.noguard, self.symbols[name])
+        f.restype = None
+        f.argtypes = [ctypes.c_uint32] * 3 + [self.SMatrixF32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        sm = self.SMatrixF32(csr.nnz, csr.elems.data_ptr(), csr.col_ind.data_ptr(), csr.row_off.data_ptr())
+        f(rows, shared, cols, sm, csr.row_indices.data_ptr(), B.data_ptr(), Cc.data_ptr())
+
+
+def wall_ms(torch, fn, reps):
+    """Per-call wall time of a blocking call (the reference's entry points create a stream, launch,
+    synchronise and destroy the stream: test/tensor_core_gemm_alpha_beta_1_driver.c.inc:139-149 times them so)."""
+    fn()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    return (time.perf_counter() - t0) / reps * 1e3
+
+
+def comparisons_leg(torch, device, ours_gemm_ms):
+    """Other implementations on the same GPU and the same seeded inputs.  GEMM: the reference's
+    TensorCore2D kernels (row-major B, as its API has it) -- all 72 bf16 -> f32 instances swept at
+    4096^3 as tuning/tune_tc2d.sh does, the fastest then timed at 8192^3 -- and cuBLAS with f32
+    output through torch.  SpMM: the reference's kernels with the size guard compiled out, cuSPARSE
+    through torch.sparse."""
+    from kuiper_b200 import klas, synth
+    out = {}
+    flop = 2.0 * 8192 ** 3
+    A, B = synth.gemm_bf16(1, 8192, 8192, 8192, b_col_major=False, device=device)
+    D = torch.empty((8192, 8192), dtype=torch.float32, device=device)
+    ours_rm = time_launches(torch, lambda: klas.gemm_tc(A, B, D=D), 20)
+    out["gemm_bf16_8192_row_major_b"] = {"ours_ms": ours_rm, "ours_tflops": flop / ours_rm / 1e9,
+                                         "ours_col_major_b_ms": ours_gemm_ms}
+    try:
+        f = lambda: torch.mm(A, B, out_dtype=torch.float32)
+        f()
+        what = "torch.mm(bf16, bf16, out_dtype=float32)"
+    except Exception:
+        f = lambda: torch.mm(A, B)
+        what = "torch.mm(bf16, bf16) with bf16 output (this torch has no f32-output form)"
+    ms = time_launches(torch, f, 20)
+    out["gemm_bf16_8192_row_major_b"]["cublas"] = {"ms": ms, "tflops": flop / ms / 1e9, "call": what}
+    if RefGpuLib.available():
+        ref = RefGpuLib()
+        n = 4096
+        a4, b4, d4 = A[:n, :n].contiguous(), B[:n, :n].contiguous(), torch.empty((n, n), dtype=torch.float32, device=device)
+        names = sorted(k for k in ref.symbols if k.startswith("Klas_GEMM_TensorCore2D_g_gemm_bf16_f32_"))
+        best = None
+        for nm in names:
+            t = wall_ms(torch, lambda: ref.gemm(nm, n, n, n, a4, b4, d4), 2)
+            if best is None or t < best[1]:
+                best = (nm, t)
+        t8 = wall_ms(torch, lambda: ref.gemm(best[0], 8192, 8192, 8192, A, B, D), 3)
+        out["gemm_bf16_8192_row_major_b"]["reference_kernel"] = {
+            "instance": best[0], "swept": len(names), "sweep": "per-call wall time at 4096^3, 2 calls each",
+            "ms_per_call_4096": best[1], "ms_per_call_8192": t8, "tflops_8192": flop / t8 / 1e9,
+            "note": "the reference's entry points are blocking (fresh stream, launch, sync, destroy); ours above is device time"}
+    del A, B, D
+    torch.cuda.empty_cache()
+
+    rows = shared = Spmm.ROWS
+    cols = Spmm.COLS
+    csr = synth.csr_poisson(4, rows, shared, 64.0, device=device)
+    Bd = synth.spmm_dense_b(4, shared, cols, device=device)
+    Cd = torch.empty((rows, cols), device=device)
+    sp = torch.sparse_csr_tensor(csr.row_off.long(), csr.col_ind.long(), csr.elems, size=(rows, shared))
+    ours = time_launches(torch, lambda: klas.spmm(csr, Bd, Cd), 20)
+    ms = time_launches(torch, lambda: torch.sparse.mm(sp, Bd), 10)
+    out["spmm_131072"] = {"ours_ms": ours, "cusparse": {"ms": ms, "call": "torch.sparse.mm(csr, dense)"}}
+    if RefGpuLib.available() and ref.noguard is not None:
+        theirs = torch.empty_like(Cd)
+        res = {}
+        for nm in ("Klas_SPMM_spmm_f32", "Klas_SPMM_g_spmm_f32_512x512x64"):
+            if nm in ref.symbols:
+                res[nm] = wall_ms(torch, lambda: ref.spmm(nm, rows, shared, cols, csr, Bd, theirs), 2)
+        klas.spmm(csr, Bd, Cd)
+        torch.cuda.synchronize()
+        out["spmm_131072"]["reference_kernel"] = {
+            "ms_per_call": res, "bit_equal_to_ours": bool(torch.equal(Cd, theirs)),
+            "note": "the reference's wrappers abort at rows, shared or cols >= 10000 (dist/Klas_SPMM.cu:196-198); this is a "
+                    "comparison copy with the guards compiled out (oracle/ref_wrap/ref_spmm_noguard.cu)"}
+    else:
+        out["spmm_131072"]["reference_kernel"] = "aborts by guard (rows >= 10000); comparison copy not built"
+    return out
 
 
 # --------------------------------------------------------------------------- main
-# DRAM traffic of one launch from an ncu capture of the same kernel (profiles/): bytes read + written.
-NCU_TRAFFIC = {"gemm_bf16": 1.150e9, "spmm": 1.141e9, "gemm_u64": 2.163e9, "gemm_f32": 8.4e6, "softmax_f32": 3.18e9}
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -545,6 +936,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm_bf16")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="leave out the sustained leg, the other configurations and the comparison rows")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--attention-heads", type=int, default=256,
                     help="attention_f16 only: heads per GPU (256 is the bench size; fewer for profiler captures)")
@@ -568,7 +961,7 @@ def main():
     os.dup2(2, 1)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    from kuiper_b200 import klas  # noqa: F401  (fails loudly if libklas_b200.so is missing)
+    from kuiper_b200 import klas, sharding  # noqa: F401  (fails loudly if libklas_b200.so is missing)
 
     wl = make_workload(args.workload, rank, world, device, args)
     warm = max(args.warmup, 3)
@@ -602,6 +995,39 @@ def main():
     value = float(units) * args.steps / (total_ms * 1e-3) / scale
     klas.gemm_tc_status()
 
+    # parity of what was just timed, outside the timed region: sampled rows of every rank's block ...
+    check = wl.check()
+    if check is not None and world > 1:
+        flags = torch.tensor([1.0 if check["ok"] else 0.0, check.get("max_rel_err", 0.0)], dtype=torch.float64, device=device)
+        worst = flags.clone()
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        check = dict(check, ok=bool(flags[0] > 0), max_rel_err=float(worst[1]), ranks=world,
+                     rows=check["rows"] * world)
+    # ... and, with several ranks, one pass with C assembled on every rank (NCCL all-gather over
+    # NVLink): each rank compares its own block of the gathered matrix bit for bit, and the other
+    # ranks' blocks through a checksum every rank computed of its local block.
+    if world > 1 and wl.name == "gemm_bf16" and check is not None:
+        ranks = sharding.Ranks(rank, world, local, device)
+        ranges = [(r * wl.rows, (r + 1) * wl.rows) for r in range(world)]
+        t0 = time.perf_counter()
+        full = sharding.gemm_tc_sharded(wl.A, wl.Bt, ranges, ranks, gather=True, out_dtype=torch.float32, b_col_major=True)
+        torch.cuda.synchronize()
+        gather_s = time.perf_counter() - t0
+        lo, hi = ranges[rank]
+        mine_ok = bool(torch.equal(full[lo:hi], wl.D))
+        sums = torch.zeros(world, dtype=torch.int64, device=device)
+        sums[rank] = wl.D.view(torch.int32).to(torch.int64).sum()
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+        got = torch.stack([full[a:b].view(torch.int32).to(torch.int64).sum() for a, b in ranges])
+        ok = torch.tensor([1.0 if (mine_ok and bool(torch.equal(got, sums))) else 0.0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        check.update(gather_ok=bool(ok[0] > 0), gathered_shape=list(full.shape), gather_pass_seconds=gather_s,
+                     gather="all_gather_into_tensor of the %d row blocks; own block compared bit for bit, the others by a "
+                            "64-bit sum of their bit patterns" % world)
+        del full
+        torch.cuda.empty_cache()
+
     # end to end through the host-buffer C ABI (pinned host memory, H2D + kernel + D2H per step)
     wl.e2e_step()
     barrier()
@@ -617,57 +1043,51 @@ def main():
     if rank == 0:
         peaks = load_peaks()
         per_launch_ms = total_ms / args.steps
-        if wl.bound == "tensor":
-            achieved = wl.per_step_units() / (per_launch_ms * 1e-3) / 1e12
-            peak, runit = peaks["bf16_tflops"], "TFLOP/s"
-            peak_note = "cuBLAS bf16 burst, of %s" % peaks["source"]
-        elif wl.bound == "hbm":
-            achieved = wl.algorithmic_bytes / (per_launch_ms * 1e-3) / 1e9
-            peak, runit = peaks["hbm_gbs"], "GB/s"
-            peak_note = "stream copy, of %s" % peaks["source"]
-        else:
-            # CUDA-core GEMMs are issue-bound: reported against the nominal issue peak at max clock
-            achieved = wl.per_step_units() / (per_launch_ms * 1e-3) / 1e12
-            if wl.name == "gemm_u64":
-                # a wrapping u64 multiply-add = one widening 32x32 multiply-add (2 issue slots of the
-                # 64-lane integer-multiply pipe) + two 32-bit ones: 4 slots per MAC, 2 ops per MAC
-                peak, runit = 2 * (64 / 4) * 148 * 1.965e9 / 1e12, "Tops/s"
-                peak_note = "64 integer-multiply lanes/clk/SM, 4 slots per u64 MAC, 148 SMs, 1965 MHz (nominal)"
-            else:
-                peak, runit = 2 * 128 * 148 * 1.965e9 / 1e12, "TFLOP/s"
-                peak_note = "2*128 lanes*148 SMs*1965 MHz FP32 issue peak (nominal)"
-        extra = {}
+        clocks = sampler.summary()
+        roofline = roofline_of(wl, per_launch_ms, peaks, clocks.get("sm_mhz"))
         if wl.name == "spmm":
-            # every nonzero moves 4*cols bytes of a random row of B through L2 whatever the schedule
-            gather = wl.nnz * (8 + 4 * wl.COLS) + 4 * wl.rows * wl.COLS + 8 * wl.rows
-            extra = {"l2_gather_bytes_per_launch": gather,
-                     "l2_gather_achieved_gbs": gather / (per_launch_ms * 1e-3) / 1e9,
-                     "l2_gather_note": "random 512-byte row segments of B; highest L2->SM rate measured on this GPU "
-                                       "(tensor-core GEMM, 128x256 tiles) is 15600 GB/s"}
-        roofline = {"bound": "tensor" if wl.bound == "tensor" else "hbm" if wl.bound == "hbm" else "issue",
-                    "achieved": achieved, "peak": peak, "unit": runit, "frac": achieved / peak,
-                    "traffic": getattr(wl, "traffic", NCU_TRAFFIC.get(wl.name)), "peak_note": peak_note,
-                    "algorithmic_bytes_per_launch": wl.algorithmic_bytes,
-                    "kernel_ms": per_launch_ms, **extra}
+            roofline["gather"] = spmm_gather_block(torch, wl, per_launch_ms)
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": per_launch_ms, "higher_is_better": True, "scaling": "weak" if wl.name in ("gemm_bf16", "softmax_f32", "attention_f16") else "strong",
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
-            "clocks": sampler.summary(),
+            "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                     "steps": args.e2e_steps, "api": getattr(wl, "e2e_api", "klas_b200_*_host (C ABI, pinned host buffers)")},
             "gpu_launches": args.steps * wl.launches_per_step,
             "roofline": roofline,
         }
+        if check is not None:
+            line["check"] = check
+        extras = world == 1 and wl.name == "gemm_bf16" and not args.no_extras
+        if extras:
+            line["sustained"] = sustained_leg(torch, wl, local, peaks)
         if not args.no_cpu_baseline and world == 1:
             cb = cpu_baseline_leg(wl.name)
             if cb:
                 line["cpu_baseline"] = cb
+        if extras:
+            ours_ms = per_launch_ms
+            del wl
+            torch.cuda.empty_cache()
+            klas.release_workspace()
+            line["configs"] = {}
+            for name in ("spmm", "gemm_f16b", "gemm_u64", "gemm_f32"):
+                try:
+                    line["configs"][name] = config_leg(torch, name, device, peaks, args)
+                except Exception as exc:     # one configuration failing must not lose the headline line
+                    line["configs"][name] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+                klas.release_workspace()
+            try:
+                line["comparisons"] = comparisons_leg(torch, device, ours_ms)
+            except Exception as exc:
+                line["comparisons"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
         sys.stdout.flush()
         os.dup2(real_stdout, 1)
         print(json.dumps(line), flush=True)
         os.dup2(2, 1)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 

@@ -358,6 +358,11 @@ def gemm_tc_strided(A: torch.Tensor, B: torch.Tensor, D: torch.Tensor, *, b_col_
     return D
 
 
+def release_workspace() -> None:
+    """Frees the device workspace that the host-buffer entry points keep on the current device."""
+    check(_lib.load().klas_b200_release_workspace())
+
+
 def gemm_tc_status() -> int:
     """Raises KlasError(ERR_TIMEOUT) if a bounded device-side wait of the tensor-core kernel
     gave up since the last call (synchronises the device); returns 0 otherwise."""

@@ -23,7 +23,8 @@ if str(REPO_DIR) not in sys.path:
     sys.path.insert(0, str(REPO_DIR))
 ORACLE_LIB = ORACLE_DIR / "libklas_oracle.so"
 REF_DIR = ORACLE_DIR / "_ref"
-DEFAULT_REF_ROOT = Path("/root/reference")
+# where the FStarLang/kuiper tree is mounted: KUIPER_REF_ROOT, or --ref-root on the command line
+DEFAULT_REF_ROOT = Path(os.environ.get("KUIPER_REF_ROOT", "/root/reference"))
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 REF_GPU_UNITS = [
@@ -100,6 +101,19 @@ def build_ref_gpu(ref_root: Path, force: bool = False) -> Path:
     return out
 
 
+def build_ref_spmm_noguard(ref_root: Path, force: bool = False) -> Path:
+    """The reference's SpMM unit with its `< 10000` size guards compiled out (oracle/ref_wrap/
+    ref_spmm_noguard.cu): lets the benchmark time the reference's own kernel at 131072^2."""
+    out = REF_DIR / "libklas_ref_spmm_noguard.so"
+    wrap = ORACLE_DIR / "ref_wrap" / "ref_spmm_noguard.cu"
+    if not force and _newer(out, wrap):
+        return out
+    REF_DIR.mkdir(exist_ok=True)
+    _run(["nvcc", "-O3", *ARCH, "-Xcompiler", "-fPIC", "-shared", "-I", ref_root / "include", "-I", ref_root / "dist",
+          "-o", out, wrap])
+    return out
+
+
 HOT_PATH_DRIVER_GLOBS = ("Test_Kuiper_GraphDist.cu", "Test_Klas_GEMM_*.cu", "Test_Klas_SPMM__*.cu", "Test_Klas_Softmax__*.cu",
                          "Test_Klas_LogSoftmax__*.cu", "Test_Klas_HReduce__*.cu", "Test_Klas_AtomicReduce__*.cu")
 
@@ -171,6 +185,7 @@ def main(argv=None) -> int:
         print(build_ref_cpu(a.ref_root, a.force))
         if not a.no_ref_gpu:
             print(build_ref_gpu(a.ref_root, a.force))
+            print(build_ref_spmm_noguard(a.ref_root, a.force))
         print(build_ref_drivers(a.ref_root, a.force))
     else:
         print("reference tree not mounted at %s: oracle/_ref not (re)built" % a.ref_root)
