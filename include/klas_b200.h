@@ -412,6 +412,36 @@ int klas_b200_reduce_sum(int dtype, uint64_t n, const void *a, void *result, voi
                          size_t scratch_bytes, void *stream);
 int klas_b200_reduce_sum_host(int dtype, uint64_t n, const void *a, void *result);
 
+/*
+ * Tuning / testing knobs.  The library picks tile shapes and schedules from the problem size;
+ * these process-wide overrides exist so that a test or a tuning run can force each variant and
+ * compare (every variant gives bit-identical results, which is what the tests check).  They are
+ * plain atomics read at launch time: set them while no other thread is launching.  The library
+ * never reads the environment.
+ *
+ *   KLAS_KNOB_TC_MODE    tensor-core tile: 0 library's choice (default), 1 single-CTA 128x256,
+ *                        2 single-CTA 128x128, 3 CTA pair 256x256, 4 wide pair 512x256
+ *   KLAS_KNOB_TC_RASTER  tile columns swept together: 0 default (8), else 1..1024
+ *   KLAS_KNOB_TC_SPLIT_K K slices per output tile of the single-CTA kernel: 0 library's choice, 1 none, 2..8
+ *   KLAS_KNOB_F64_MODE   0 library's choice, 1 keep fp64 products on the CUDA-core kernel
+ *   KLAS_KNOB_SIMT_TILE  CUDA-core tile of 4-byte types: -1 library's choice, 0 64x64, 1 128x64, 2 128x128
+ *   KLAS_KNOB_HOST_GRID  blocks per side of the 2-D schedule of klas_b200_gemm_tc_host: -1 default (4),
+ *                        0 row blocks only, 1..16
+ * Returns KLAS_ERR_INVALID for an unknown knob or a value outside its range.  klas_b200_debug_get
+ * returns the current value (INT32_MIN for an unknown knob).  No counterpart in the reference.
+ */
+typedef enum klas_knob_e {
+    KLAS_KNOB_TC_MODE = 0,
+    KLAS_KNOB_TC_RASTER = 1,
+    KLAS_KNOB_TC_SPLIT_K = 2,
+    KLAS_KNOB_F64_MODE = 3,
+    KLAS_KNOB_SIMT_TILE = 4,
+    KLAS_KNOB_HOST_GRID = 5,
+    KLAS_KNOB_COUNT = 6
+} klas_knob;
+int klas_b200_debug_set(int knob, int value);
+int klas_b200_debug_get(int knob);
+
 /* Frees the calling device's host-variant workspace. */
 int klas_b200_release_workspace(void);
 

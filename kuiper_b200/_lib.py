@@ -15,6 +15,8 @@ B_ROW_MAJOR, B_COL_MAJOR = 0, 1
 MAP_ID, MAP_SQRT, MAP_ABS, MAP_SQUARE, MAP_RELU, MAP_NEG = range(6)
 COMB_NEW, COMB_AXPBY, COMB_MAX, COMB_MIN, COMB_MUL, COMB_RELU, COMB_SCALED = range(7)
 
+KNOB_TC_MODE, KNOB_TC_RASTER, KNOB_TC_SPLIT_K, KNOB_F64_MODE, KNOB_SIMT_TILE, KNOB_HOST_GRID = range(6)
+
 _u32, _u64, _vp, _int, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int, C.c_float
 
 # name -> (restype, argtypes): every function declared in include/klas_b200.h
@@ -54,6 +56,8 @@ SIGNATURES = {
     "klas_b200_reduce_scratch_bytes": (C.c_size_t, [_u64]),
     "klas_b200_reduce_sum": (_int, [_int, _u64, _vp, _vp, _vp, C.c_size_t, _vp]),
     "klas_b200_reduce_sum_host": (_int, [_int, _u64, _vp, _vp]),
+    "klas_b200_debug_set": (_int, [_int, _int]),
+    "klas_b200_debug_get": (_int, [_int]),
     "klas_b200_release_workspace": (_int, []),
 }
 

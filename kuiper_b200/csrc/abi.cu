@@ -3,6 +3,8 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
+#include <climits>
 #include <cstring>
 #include <mutex>
 
@@ -21,6 +23,15 @@ int fail(int code, const char *fmt, ...) {
 }
 
 void clear_error() { tls_error[0] = '\0'; }
+
+// tuning knobs (klas_knob): defaults = the library's own choice
+static std::atomic<int> g_knobs[KLAS_KNOB_COUNT] = {{0}, {0}, {0}, {0}, {-1}, {-1}};
+struct KnobRange { int lo, hi; };
+static const KnobRange g_knob_range[KLAS_KNOB_COUNT] = {{0, 4}, {0, 1024}, {0, 8}, {0, 1}, {-1, 2}, {-1, 16}};
+
+int debug_knob(int knob) {
+    return knob >= 0 && knob < KLAS_KNOB_COUNT ? g_knobs[knob].load(std::memory_order_relaxed) : INT_MIN;
+}
 
 constexpr int MAX_DEVICES = 64;
 static std::mutex g_mutex;
@@ -308,10 +319,7 @@ static int gemm_tc_host_2d(HostPipe *hp, int in_dtype, int out_dtype, int b_majo
                            uint64_t cols, const void *A, const void *B, void *D, void *dA, void *dB, void *dD) {
     const size_t is = dtype_size(in_dtype), os = dtype_size(out_dtype);
     uint64_t G = 4;   // measured best at 8192^3 bf16 -> f32: 7.54 ms (4), 7.79 (8), 7.77 (16), 8.36 (2)
-    if (const char *g = getenv("KLAS_HOST_GRID")) {   // developer override: 1 .. GRID_2D, 0 = row blocks only
-        const int v = atoi(g);
-        if (v >= 1 && v <= HostPipe::GRID_2D) G = uint64_t(v);
-    }
+    if (const int v = debug_knob(KLAS_KNOB_HOST_GRID); v >= 1 && v <= HostPipe::GRID_2D) G = uint64_t(v);
     const uint64_t rc = ((rows + G - 1) / G + 511) / 512 * 512;   // rows per block of A
     const uint64_t cc = ((cols + G - 1) / G + 255) / 256 * 256;   // columns per block of B
     const bool col_major = b_major == KLAS_B_COL_MAJOR;
@@ -390,7 +398,7 @@ int klas_b200_gemm_tc_host(int in_dtype, int out_dtype, int b_major, uint32_t ba
     if (int rc = workspace_reserve(3, d_bytes, &dD)) return rc;
     if (batch == 1 && !C && rows >= 4096 && cols >= 4096 && shared % 8 == 0 && cols % 8 == 0 &&
         (b_major == KLAS_B_COL_MAJOR || b_major == KLAS_B_ROW_MAJOR) && A && B &&
-        !(getenv("KLAS_HOST_GRID") && atoi(getenv("KLAS_HOST_GRID")) == 0))
+        debug_knob(KLAS_KNOB_HOST_GRID) != 0)
         return gemm_tc_host_2d(hp, in_dtype, out_dtype, b_major, rows, shared, cols, A, B, D, dA, dB, dD);
 
     // The work is cut into chunks -- row blocks of A/C/D for one matrix, groups of pages for a
@@ -517,6 +525,18 @@ int klas_b200_reduce_sum_host(int dtype, uint64_t n, const void *a, void *result
     KLAS_TRY_CUDA(cudaStreamSynchronize(s));
     return KLAS_OK;
 }
+
+int klas_b200_debug_set(int knob, int value) {
+    clear_error();
+    if (knob < 0 || knob >= KLAS_KNOB_COUNT) return fail(KLAS_ERR_INVALID, "debug_set: unknown knob %d", knob);
+    if (value < g_knob_range[knob].lo || value > g_knob_range[knob].hi)
+        return fail(KLAS_ERR_INVALID, "debug_set: knob %d takes values %d..%d, got %d", knob, g_knob_range[knob].lo,
+                    g_knob_range[knob].hi, value);
+    g_knobs[knob].store(value, std::memory_order_relaxed);
+    return KLAS_OK;
+}
+
+int klas_b200_debug_get(int knob) { return debug_knob(knob); }
 
 int klas_b200_release_workspace(void) {
     clear_error();

@@ -478,7 +478,7 @@ static int launch_type(const Problem &q, T alpha, T beta, int scaled, const void
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 127) / 128) * batch;
         const uint64_t mid_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
         int pick = big_tiles * 10 >= uint64_t(sm_count) * 6 ? 2 : (mid_tiles * 10 >= uint64_t(sm_count) * 8 ? 1 : 0);
-        if (const char *t = getenv("KLAS_SIMT_TILE")) pick = atoi(t);
+        if (const int t = debug_knob(KLAS_KNOB_SIMT_TILE); t >= 0) pick = t;
         if (pick == 2) return launch_cfg<S, T, 128, 128, 16>(q, alpha, beta, scaled, A, B, C, stream);
         if (pick == 1) return launch_cfg<S, T, 128, 64, 32>(q, alpha, beta, scaled, A, B, C, stream);
         return launch_cfg<S, T, 64, 64, 32>(q, alpha, beta, scaled, A, B, C, stream);
@@ -500,12 +500,12 @@ static int dispatch(int dtype, const Problem &q, const void *alpha, const void *
                                              scaled ? *static_cast<const float *>(beta) : 0.0f, scaled, A, B, C,
                                              info.sm_count, stream);
         case KLAS_F64: {
-            // Plain contiguous products go to the FP64 tensor-core kernel (KLAS_F64_MODE=simt keeps
-            // them here); strided pages and the element-wise hooks stay on this kernel.
-            const char *mode = getenv("KLAS_F64_MODE");
+            // Plain contiguous products go to the FP64 tensor-core kernel (the KLAS_KNOB_F64_MODE knob
+            // keeps them here); strided pages and the element-wise hooks stay on this kernel.
+            const bool keep_simt = debug_knob(KLAS_KNOB_F64_MODE) == 1;
             const bool contiguous = q.lda == q.k && q.ldb == q.n && q.ldc == q.n && q.sa == q.m * q.k &&
                                     q.sb == q.k * q.n && q.sc == q.m * q.n;
-            if (!q.hooks && contiguous && !(mode && !strcmp(mode, "simt")))
+            if (!q.hooks && contiguous && !keep_simt)
                 return launch_gemm_dmma(q.batch, q.m, q.n, q.k, static_cast<const double *>(alpha),
                                         static_cast<const double *>(beta), A, B, C, stream);
             return launch_type<double, double>(q, scaled ? *static_cast<const double *>(alpha) : 1.0,

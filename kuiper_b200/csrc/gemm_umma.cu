@@ -1348,11 +1348,12 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     // full one (the A operand is read from shared memory once per 128 instead of 256 columns).
     const uint64_t narrow_tiles = ((rows + BM - 1) / BM) * ((cols + 127) / 128) * batch;
     bool narrow = !use_wide && !pair && double((narrow_tiles + sms - 1) / sms) * 0.55 < cost_single;
-    if (const char *mode = getenv("KLAS_TC_MODE")) {
-        if (!strcmp(mode, "single")) pair = use_wide = narrow = false;
-        else if (!strcmp(mode, "narrow")) { pair = use_wide = false; narrow = true; }
-        else if (!strcmp(mode, "pair")) { pair = can_pair && !xform; use_wide = false; narrow = narrow && !pair; }
-        else if (!strcmp(mode, "wide")) { use_wide = can_pair; narrow = narrow && !use_wide; }
+    switch (debug_knob(KLAS_KNOB_TC_MODE)) {   // a test or tuning run forcing one tile shape
+        case 1: pair = use_wide = narrow = false; break;
+        case 2: pair = use_wide = false; narrow = true; break;
+        case 3: pair = can_pair && !xform; use_wide = false; narrow = narrow && !pair; break;
+        case 4: use_wide = can_pair; narrow = narrow && !use_wide; break;
+        default: break;
     }
     if (use_wide) {
         Params p{};
@@ -1379,10 +1380,7 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
         p.map_b = uint32_t(map_b);
         p.comb = uint32_t(comb);
         p.raster_group = DEFAULT_RASTER_GROUP;
-        if (const char *rg = getenv("KLAS_TC_RASTER")) {
-            const int v = atoi(rg);
-            if (v >= 1 && v <= 1024) p.raster_group = uint32_t(v);
-        }
+        if (const int v = debug_knob(KLAS_KNOB_TC_RASTER); v >= 1) p.raster_group = uint32_t(v);
         CUtensorMap ta{}, tb{};
         if (shared > 0) {
             if (int rc = make_map(&ta, in_dtype, A, shared, rows, batch, BK, wide::A_ROWS, lda, sa)) return rc;
@@ -1424,10 +1422,7 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     p.map_b = uint32_t(map_b);
     p.comb = uint32_t(comb);
     p.raster_group = DEFAULT_RASTER_GROUP;
-    if (const char *rg = getenv("KLAS_TC_RASTER")) {
-        const int v = atoi(rg);
-        if (v >= 1 && v <= 1024) p.raster_group = uint32_t(v);
-    }
+    if (const int v = debug_knob(KLAS_KNOB_TC_RASTER); v >= 1) p.raster_group = uint32_t(v);
 
     const uint32_t b_cols = pair ? Shape<true>::B_COLS : p.tile_n;
     CUtensorMap ta{}, tb{};

@@ -46,6 +46,9 @@ struct DeviceInfo {
 // Properties of the current device, cached per device.
 int device_info(DeviceInfo *out);
 
+// Current value of a tuning knob (klas_knob of klas_b200.h); set by klas_b200_debug_set.
+int debug_knob(int knob);
+
 // Grow-only per-device scratch used by the *_host entry points.
 int workspace_reserve(int slot, size_t bytes, void **ptr);
 int workspace_release();

@@ -21,14 +21,12 @@ MAP_CODE = {None: 0, "sqrt": 1, "abs": 2, "square": 3, "relu": 4, "neg": 5}
 
 
 @pytest.fixture(autouse=True, params=["single", "narrow", "wide", "auto"])
-def tc_mode(request, monkeypatch):
+def tc_mode(request):
     """Single-CTA tiles, wide pair tiles, and the library's own choice (the 256 x 256 pair tiles
     carry no mapping warps and are never chosen for a mapped product)."""
-    if request.param == "auto":
-        monkeypatch.delenv("KLAS_TC_MODE", raising=False)
-    else:
-        monkeypatch.setenv("KLAS_TC_MODE", request.param)
+    klas.debug_set("tc_mode", request.param)
     yield request.param
+    klas.debug_set("tc_mode", "auto")
     assert klas.gemm_tc_status() == 0
 
 

@@ -29,13 +29,11 @@ def test_f32_matmul(oracle, m, n, k):
 
 
 @pytest.fixture(params=["tensor", "simt"])
-def f64_mode(request, monkeypatch):
+def f64_mode(request):
     """fp64 products run on the FP64 tensor-core kernel by default and on the CUDA-core kernel on request."""
-    if request.param == "simt":
-        monkeypatch.setenv("KLAS_F64_MODE", "simt")
-    else:
-        monkeypatch.delenv("KLAS_F64_MODE", raising=False)
-    return request.param
+    klas.debug_set("f64_mode", "simt" if request.param == "simt" else "auto")
+    yield request.param
+    klas.debug_set("f64_mode", "auto")
 
 
 @pytest.mark.parametrize("m,n,k,batch,layout", [(256, 128, 64, 1, "rrr"), (100, 36, 52, 1, "rrr"), (129, 67, 33, 3, "rrr"),

@@ -14,14 +14,12 @@ TOL_F16_F16 = 1e-2    # f16 x f16 -> f16
 
 
 @pytest.fixture(autouse=True, params=["single", "narrow", "pair", "wide", "auto"])
-def tc_mode(request, monkeypatch):
+def tc_mode(request):
     """Every test runs with the single-CTA tiles (256 and 128 columns wide), the CTA-pair tiles, the wide pair
     tiles and the library's own choice."""
-    if request.param == "auto":
-        monkeypatch.delenv("KLAS_TC_MODE", raising=False)
-    else:
-        monkeypatch.setenv("KLAS_TC_MODE", request.param)
+    klas.debug_set("tc_mode", request.param)
     yield request.param
+    klas.debug_set("tc_mode", "auto")
     assert klas.gemm_tc_status() == 0
 
 
@@ -172,7 +170,7 @@ def test_zero_inner_dimension():
     (2048, 2048, "one round of single tiles"), (2560, 2048, "40 wide tiles, one round"),
     (3072, 3072, "72 wide tiles, one round"), (3584, 3072, "84 wide tiles would take two rounds: pairs"),
     (3000, 2056, "ragged edges"), (1024, 1024, "64 narrow tiles instead of 32"), (1536, 1480, "narrow, ragged")])
-def test_tile_choice_does_not_change_results(oracle, rows, cols, expect, monkeypatch, tc_mode):
+def test_tile_choice_does_not_change_results(oracle, rows, cols, expect, tc_mode):
     """The library picks single, pair or wide tiles from the shape.  Every element is accumulated
     over k in the same order whatever the tile, so the three kernels and the library's own choice
     must agree bit for bit; a sample of rows is checked against the oracle."""
@@ -182,10 +180,7 @@ def test_tile_choice_does_not_change_results(oracle, rows, cols, expect, monkeyp
     A, Bt = synth.gemm_bf16(31, rows, cols, shared, b_col_major=True, device="cuda")
     results = {}
     for mode in ("auto", "single", "narrow", "pair", "wide"):
-        if mode == "auto":
-            monkeypatch.delenv("KLAS_TC_MODE", raising=False)
-        else:
-            monkeypatch.setenv("KLAS_TC_MODE", mode)
+        klas.debug_set("tc_mode", mode)
         results[mode] = klas.gemm_tc(A, Bt, out_dtype=torch.float32, b_col_major=True)
     torch.cuda.synchronize()
     assert klas.gemm_tc_status() == 0

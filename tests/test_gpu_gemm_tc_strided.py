@@ -16,12 +16,10 @@ TOL = {torch.float32: 1e-5, torch.float16: 1e-2, torch.bfloat16: 2e-2}
 
 
 @pytest.fixture(autouse=True, params=["single", "narrow", "wide", "auto"])
-def tc_mode(request, monkeypatch):
-    if request.param == "auto":
-        monkeypatch.delenv("KLAS_TC_MODE", raising=False)
-    else:
-        monkeypatch.setenv("KLAS_TC_MODE", request.param)
+def tc_mode(request):
+    klas.debug_set("tc_mode", request.param)
     yield request.param
+    klas.debug_set("tc_mode", "auto")
     assert klas.gemm_tc_status() == 0
 
 
