@@ -9,6 +9,10 @@
  *   KPR_KCALL(...)              kernel launch that is skipped for an empty grid   (kuiper.h:38-46)
  *   KPR_SHMEM(), KPR_SHMEM_AT   dynamic shared memory carving                     (kuiper.h:48-55)
  *   KPR_GPU_ALLOC, KPR_FRESH_STREAM, KPR_SHMEM_FITS, KRML_* host macros           (kuiper.h:85-143)
+ *   INFO()                      prints the sizes of the integer types                 (kuiper.h:111-123)
+ * and, as the reference's header does (kuiper.h:12-19), pulls in kuiper/atomics.h,
+ * kuiper/vectorops.h, kuiper/math.h and -- unless KUIPER_CFG_TENSORCORES is defined as 0 --
+ * kuiper/tensorcores.h from the directory beside it.
  */
 #ifndef KUIPER_H
 #define KUIPER_H 1
@@ -23,6 +27,13 @@
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
+
+#include "kuiper/atomics.h"
+#include "kuiper/vectorops.h"
+#include "kuiper/math.h"
+#if (!defined(KUIPER_CFG_TENSORCORES) || KUIPER_CFG_TENSORCORES)
+#include "kuiper/tensorcores.h"
+#endif
 
 /* Prints the standard failure banner and terminates; `how` selects exit(1) or abort(). */
 static inline void klas_shim_fail(const char *kind, const char *what, const char *func,
@@ -99,6 +110,21 @@ static inline cudaStream_t KPR_FRESH_STREAM(void)
     cudaStream_t s;
     __MUST(cudaStreamCreate(&s), "cudaStreamCreate", __func__, __FILE__, __LINE__);
     return s;
+}
+
+/* Sizes of the integer types on this host, one per line. */
+static inline void INFO(void)
+{
+#define KLAS_SHIM_SIZE(T) printf("sizeof(" #T ") = %zu\n", sizeof(T))
+    KLAS_SHIM_SIZE(short);
+    KLAS_SHIM_SIZE(int);
+    KLAS_SHIM_SIZE(long);
+    KLAS_SHIM_SIZE(long long);
+    KLAS_SHIM_SIZE(unsigned short);
+    KLAS_SHIM_SIZE(unsigned int);
+    KLAS_SHIM_SIZE(unsigned long);
+    KLAS_SHIM_SIZE(unsigned long long);
+#undef KLAS_SHIM_SIZE
 }
 
 #endif /* KUIPER_H */

@@ -220,6 +220,19 @@ int klas_b200_gemm_tc_strided(int in_dtype, int out_dtype, int b_major, uint32_t
 int klas_b200_gemm_tc_status(int *site);
 
 /*
+ * The same word without touching the device: the kernels also write the site code to a
+ * host-visible mirror (a 4-byte pinned, mapped allocation made once per device by the first
+ * tensor-core launch there -- make that launch outside any stream capture).  Returns 0 or the site
+ * code; it is exact once the launches of interest have been synchronised with, and costs a load.
+ * A blocking caller checks this after its synchronise and calls klas_b200_gemm_tc_status() only
+ * when it is non-zero (the reference-named wrappers do).  Asynchronous callers of
+ * klas_b200_gemm_tc / _fused / _strided / _sdpa_fused MUST look at one of the two after they
+ * synchronise: a wait that gave up leaves D undefined, and while the word is set later launches
+ * on the device drain at once.  No counterpart in the reference.
+ */
+int klas_b200_gemm_tc_status_peek(void);
+
+/*
  * Diagnostic: launches one warp that waits, with the same bounded wait the tensor-core
  * pipeline uses, on a barrier nothing will ever signal.  After `limit_ms` (1..1000) the wait
  * gives up, the device status word receives site 0x7F, `*gave_up` (optional device int) is set
@@ -303,7 +316,9 @@ int klas_b200_minplus_u16(uint32_t m, uint32_t n, uint32_t k, const uint16_t *A,
  * pointer (pinned memory makes the copies asynchronous and faster).  The call
  * stages inputs into a per-device workspace that grows on demand and is kept
  * until klas_b200_release_workspace(), runs the kernel, copies the result
- * back and returns after the result is in host memory.
+ * back and returns after the result is in host memory.  The workspace, streams and events are
+ * one set per device: calls from several host threads on the same device are serialised by the
+ * library (a per-device lock held for the whole call); calls on different devices run in parallel.
  */
 int klas_b200_gemm_host(int dtype, int layout, uint32_t batch,
                         uint64_t m, uint64_t n, uint64_t k,
@@ -355,7 +370,10 @@ int klas_b200_softmax_host(int dtype, int log_softmax, uint64_t rows, uint64_t c
  * current); make that first call outside any stream capture.  All calls on one device share the
  * array: calls that may overlap in time (several streams or threads) race on it and must be
  * serialised by the caller.  The array keeps the previous call's statistics; none of it needs
- * clearing, every entry read is written first by the same call.
+ * clearing, every entry read is written first by the same call.  The address looked up by the
+ * first call is kept per device ordinal for the life of the process: after cudaDeviceReset() (or
+ * anything else that destroys the device's primary context) it is stale and this entry point must
+ * not be called again in that process.
  */
 #define KLAS_B200_SOFTMAX_STATIC_MAX_COLS 16777216ull   /* 1024 chunks of 16384 elements */
 int klas_b200_softmax_static(int dtype, int log_softmax, uint64_t cols, void *a, void *stream);

@@ -41,6 +41,7 @@ SIGNATURES = {
     "klas_b200_gemm_tc_strided": (_int, [_int, _int, _int, _u32, _u64, _u64, _u64, _vp, _u64, _u64, _vp, _u64, _u64,
                                           _vp, _vp, _u64, _u64, _f32, _f32, _int, _int, _int, _vp, _vp]),
     "klas_b200_gemm_tc_status": (_int, [C.POINTER(_int)]),
+    "klas_b200_gemm_tc_status_peek": (_int, []),
     "klas_b200_debug_wait_probe": (_int, [_u32, _vp, _vp]),
     "klas_b200_spmm": (_int, [_int, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "klas_b200_spmm_gather_probe": (_int, [_u32, _u32, _u32, _vp, _vp, _vp]),

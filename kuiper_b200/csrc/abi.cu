@@ -97,6 +97,7 @@ int workspace_release() {
 }
 
 int umma_read_status(int *value);
+int umma_peek_status();
 int umma_clear_status();
 int umma_wait_probe(uint32_t limit_ms, int *gave_up, cudaStream_t stream);
 
@@ -110,6 +111,21 @@ struct HostPipe {
     bool ready = false;
 };
 static HostPipe g_pipes[MAX_DEVICES];
+
+// The host-buffer entry points share one workspace and one set of streams and events per device:
+// each holds this device's lock from start to finish, so calls from several host threads on one
+// device take turns instead of overwriting each other's staging buffers.
+static std::mutex g_host_call[MAX_DEVICES];
+struct HostCallLock {
+    std::unique_lock<std::mutex> lock;
+    int rc = KLAS_OK;
+    HostCallLock() {
+        int dev = 0;
+        rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+        if (rc == KLAS_OK && (dev < 0 || dev >= MAX_DEVICES)) rc = fail(KLAS_ERR_INVALID, "device index %d out of range", dev);
+        if (rc == KLAS_OK) lock = std::unique_lock<std::mutex>(g_host_call[dev]);
+    }
+};
 
 static int host_pipe(HostPipe **out) {
     int dev = 0;
@@ -262,6 +278,8 @@ int klas_b200_gemm_tc_status(int *site) {
     return fail(KLAS_ERR_TIMEOUT, "gemm_tc: a device-side wait gave up at site 0x%x", v);
 }
 
+int klas_b200_gemm_tc_status_peek(void) { return umma_peek_status(); }
+
 int klas_b200_debug_wait_probe(uint32_t limit_ms, int *gave_up, void *stream) {
     clear_error();
     if (limit_ms == 0 || limit_ms > 1000) return fail(KLAS_ERR_INVALID, "wait_probe: limit must be 1..1000 ms");
@@ -287,6 +305,8 @@ int klas_b200_gemm_host(int dtype, int layout, uint32_t batch, uint64_t m, uint6
                         const void *alpha, const void *beta, const void *A, const void *B,
                         void *C) {
     clear_error();
+    HostCallLock turn;
+    if (turn.rc) return turn.rc;
     const size_t es = dtype_size(dtype);
     if (es == 0) return fail(KLAS_ERR_INVALID, "gemm_host: bad dtype");
     const size_t a_bytes = size_t(batch) * m * k * es, b_bytes = size_t(batch) * k * n * es,
@@ -381,6 +401,8 @@ int klas_b200_gemm_tc_host(int in_dtype, int out_dtype, int b_major, uint32_t ba
                            uint64_t shared, uint64_t cols, const void *A, const void *B,
                            const void *C, void *D, float alpha, float beta) {
     clear_error();
+    HostCallLock turn;
+    if (turn.rc) return turn.rc;
     const size_t is = dtype_size(in_dtype), os = dtype_size(out_dtype);
     if (is == 0 || os == 0) return fail(KLAS_ERR_INVALID, "gemm_tc_host: bad dtype");
     const size_t a_bytes = size_t(batch) * rows * shared * is,
@@ -451,6 +473,8 @@ int klas_b200_spmm_host(int dtype, uint32_t rows, uint32_t shared, uint32_t cols
                         const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
                         const uint32_t *row_indices, const void *B, void *C) {
     clear_error();
+    HostCallLock turn;
+    if (turn.rc) return turn.rc;
     if (dtype != KLAS_F32 && dtype != KLAS_U32) return fail(KLAS_ERR_INVALID, "spmm_host: bad dtype");
     const size_t c_bytes = size_t(rows) * cols * 4;
     if (c_bytes == 0) return KLAS_OK;
@@ -482,6 +506,8 @@ int klas_b200_softmax(int dtype, int log_softmax, uint64_t rows, uint64_t cols, 
 
 int klas_b200_softmax_host(int dtype, int log_softmax, uint64_t rows, uint64_t cols, void *a) {
     clear_error();
+    HostCallLock turn;
+    if (turn.rc) return turn.rc;
     const size_t es = dtype_size(dtype), bytes = size_t(rows) * cols * es;
     if (es == 0) return fail(KLAS_ERR_INVALID, "softmax_host: bad dtype");
     if (bytes == 0) return KLAS_OK;
@@ -512,6 +538,8 @@ int klas_b200_reduce_sum(int dtype, uint64_t n, const void *a, void *result, voi
 
 int klas_b200_reduce_sum_host(int dtype, uint64_t n, const void *a, void *result) {
     clear_error();
+    HostCallLock turn;
+    if (turn.rc) return turn.rc;
     const size_t es = dtype_size(dtype);
     if (es == 0 || dtype == KLAS_BF16) return fail(KLAS_ERR_INVALID, "reduce_host: bad dtype");
     if (!result) return fail(KLAS_ERR_INVALID, "reduce_host: null result pointer");

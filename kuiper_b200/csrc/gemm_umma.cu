@@ -29,8 +29,10 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "klas_internal.h"
 #include "ptx_sm100.cuh"
@@ -81,6 +83,10 @@ struct Shape {
 
 // First failing wait of the most recent launches on this device (0 = none).
 __device__ int g_umma_status;
+// Host-visible mirror of the word (a mapped, pinned int; null until the first launch on the
+// device): a blocking caller that has just synchronised reads it with a plain load instead of
+// paying a device round trip per call.
+__device__ int *g_umma_host_flag;
 
 #ifdef KLAS_UMMA_PROFILE
 // Developer build only: per-CTA cycle counts of each role's waits.
@@ -159,6 +165,10 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
                 *ctl.abort_flag = 1;
                 atomicCAS(&g_umma_status, 0, site);
                 if (ctl.user_status) atomicCAS(ctl.user_status, 0, site);
+                if (int *hf = g_umma_host_flag) {
+                    *reinterpret_cast<volatile int *>(hf) = site;
+                    __threadfence_system();
+                }
                 __threadfence();
                 return false;
             }
@@ -1145,7 +1155,7 @@ static int make_map(CUtensorMap *map, int dtype, const void *base, uint64_t inne
 template <typename OutT, bool XFORM>
 static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
                              cudaStream_t stream) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -1173,7 +1183,7 @@ template <typename OutT, bool PAIR, bool XFORM>
 static int launch_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
                         cudaStream_t stream) {
     constexpr uint32_t SMEM = Shape<PAIR>::SMEM_BYTES;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -1230,7 +1240,10 @@ extern "C" int klas_dev_read_umma_profile(unsigned long long *out) {
 }
 #endif
 
+int umma_ensure_host_flag();
+
 int umma_wait_probe(uint32_t limit_ms, int *gave_up, cudaStream_t stream) {
+    if (int rc = umma_ensure_host_flag()) return rc;
     umma::wait_probe_kernel<<<1, 32, 0, stream>>>(uint64_t(limit_ms) * 1000000ull, nullptr, gave_up);
     return check_cuda(cudaGetLastError(), "wait_probe_kernel launch");
 }
@@ -1249,6 +1262,35 @@ int make_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t i
     return umma::make_map(map, dtype, base, inner, outer, batch, box_inner, box_outer);
 }
 
+// The host-visible mirror of the status word: one mapped int per device, created before the first
+// launch on that device and kept for the life of the process.
+static std::mutex g_flag_mutex;
+static volatile int *g_host_flags[64] = {};
+
+int umma_ensure_host_flag() {
+    int dev = 0;
+    KLAS_TRY_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return KLAS_OK;   // no mirror: callers fall back to the device word
+    std::lock_guard<std::mutex> lock(g_flag_mutex);
+    if (g_host_flags[dev]) return KLAS_OK;
+    int *h = nullptr, *d = nullptr;
+    KLAS_TRY_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&h), sizeof(int), cudaHostAllocMapped));
+    *h = 0;
+    KLAS_TRY_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&d), h, 0));
+    KLAS_TRY_CUDA(cudaMemcpyToSymbol(umma::g_umma_host_flag, &d, sizeof(d)));
+    g_host_flags[dev] = h;
+    return KLAS_OK;
+}
+
+// 0 when no bounded wait has given up on this device since the last clear, else its site code.
+// Exact only after the launches of interest have been synchronised with.
+int umma_peek_status() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    volatile int *h = g_host_flags[dev];
+    return h ? *h : 0;
+}
+
 int umma_read_status(int *value) {
     return check_cuda(cudaMemcpyFromSymbol(value, umma::g_umma_status, sizeof(int)),
                       "cudaMemcpyFromSymbol(status)");
@@ -1256,6 +1298,8 @@ int umma_read_status(int *value) {
 
 int umma_clear_status() {
     const int zero = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && g_host_flags[dev]) *g_host_flags[dev] = 0;
     return check_cuda(cudaMemcpyToSymbol(umma::g_umma_status, &zero, sizeof(int)),
                       "cudaMemcpyToSymbol(status)");
 }
@@ -1306,6 +1350,7 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     if (rows == 0 || cols == 0 || batch == 0) return KLAS_OK;
     if (!D || (shared > 0 && (!A || !B)))
         return fail(KLAS_ERR_INVALID, "gemm_tc: null matrix pointer");
+    if (int rc = umma_ensure_host_flag()) return rc;
     if (shared % 8 != 0 || cols % 8 != 0)
         return fail(KLAS_ERR_UNSUPPORTED,
                     "gemm_tc: shared (%llu) and cols (%llu) must be multiples of 8",

@@ -2,7 +2,7 @@
 only where the FStarLang/kuiper tree is mounted -- oracle/_ref/: the reference's own
 host loops, GPU kernels and test drivers compiled from where they lie.
 
-    python oracle/build.py [--ref-root /path/to/kuiper] [--no-ref-gpu] [--no-drivers]
+    KUIPER_REF_ROOT=/path/to/kuiper python oracle/build.py [--ref-root /path/to/kuiper] [--no-ref-gpu]
 
 Outputs are git-ignored build products; nothing here is part of the product library.
 """
@@ -23,8 +23,11 @@ if str(REPO_DIR) not in sys.path:
     sys.path.insert(0, str(REPO_DIR))
 ORACLE_LIB = ORACLE_DIR / "libklas_oracle.so"
 REF_DIR = ORACLE_DIR / "_ref"
-# where the FStarLang/kuiper tree is mounted: KUIPER_REF_ROOT, or --ref-root on the command line
-DEFAULT_REF_ROOT = Path(os.environ.get("KUIPER_REF_ROOT", "/root/reference"))
+def ref_root_from_env():
+    """Where the FStarLang/kuiper tree is mounted: the KUIPER_REF_ROOT environment variable (or pass
+    --ref-root on the command line).  None when it is not set or holds no dist/ directory."""
+    v = os.environ.get("KUIPER_REF_ROOT")
+    return Path(v) if v and (Path(v) / "dist").is_dir() else None
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 REF_GPU_UNITS = [
@@ -176,19 +179,20 @@ def build_ref_tuning_drivers(ref_root: Path, force: bool = False) -> Path:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref-root", type=Path, default=DEFAULT_REF_ROOT)
+    ap.add_argument("--ref-root", type=Path, default=ref_root_from_env(),
+                    help="the FStarLang/kuiper tree (default: $KUIPER_REF_ROOT)")
     ap.add_argument("--no-ref-gpu", action="store_true")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args(argv)
     print(build_oracle(a.force))
-    if (a.ref_root / "dist").is_dir():
+    if a.ref_root is not None and (a.ref_root / "dist").is_dir():
         print(build_ref_cpu(a.ref_root, a.force))
         if not a.no_ref_gpu:
             print(build_ref_gpu(a.ref_root, a.force))
             print(build_ref_spmm_noguard(a.ref_root, a.force))
         print(build_ref_drivers(a.ref_root, a.force))
     else:
-        print("reference tree not mounted at %s: oracle/_ref not (re)built" % a.ref_root)
+        print("reference tree not found (--ref-root / KUIPER_REF_ROOT): oracle/_ref not (re)built")
     return 0
 
 

@@ -75,3 +75,35 @@ def test_shim_header_serves_kuiper_h_users(tmp_path):
                    '  MUST(cudaStreamDestroy(s)); Kuiper_Sparse_Matrix_smatrix__float m; m.nnz = 0; return (int)m.nnz; }\n')
     subprocess.run(["nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", str(REPO / "include" / "klas"),
                     "-c", str(src), "-o", str(tmp_path / "t.o")], check=True)
+
+
+SHIM_USER = r"""
+#include <kuiper.h>
+__global__ void k(half *h, __nv_bfloat16 *b, float *f, double *d, uint32_t *u, uint64_t *w, float4 *v) {
+    h[0] = kpr_hfma(kpr_hsqrt(h[1]), kpr_htanh(h[2]), kpr_hpow(h[3], h[4]));
+    h[5] = kpr_hfabs(kpr_hexp2(kpr_hlog2(__hrcp(h[6]))));
+    b[0] = kpr_bf16fma(kpr_bf16add(b[1], b[2]), kpr_bf16mul(b[3], b[4]), kpr_bf16exp(kpr_bf16tanh(b[5])));
+    b[6] = kpr_bf16atan2(kpr_bf16div(b[1], b[2]), kpr_bf16sub(b[3], b[4]));
+    atomic_add_f32(f, 1.f); atomic_add_f64(d, 1.0); atomic_add_u32(u, 1u); atomic_add_u64(w, 1ull);
+    vec_memcpy(v, v + 1);
+    kpr_fragment(wmma::matrix_a, 16, 16, 16, half, wmma::row_major) fa;
+    kpr_fragment(wmma::accumulator, 16, 16, 16, float) acc;
+    wmma::fill_fragment(acc, 0.f);
+    KPR_LOAD_MAP(h, fa, 16, kpr_hsqrt(_kpr_in_v));
+    KPR_STORE_COMB(f, acc, 16, _kpr_old_v + 2.f * _kpr_new_v);
+}
+int main() { INFO(); half x = kpr_hsqrt(HLF_MAX); (void)x; MUST(cudaDeviceSynchronize()); return 0; }
+"""
+
+
+def test_runtime_shim_provides_the_sub_headers(tmp_path):
+    """<kuiper.h> of the reference pulls in kuiper/atomics.h, vectorops.h, math.h and tensorcores.h and
+    defines INFO() (include/kuiper.h:12-19,111-123): a translation unit that uses a name from each
+    must compile against this repository's include directory (nvcc cross-compiles without a GPU)."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    src = tmp_path / "shim_user.cu"
+    src.write_text(SHIM_USER)
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-I", str(REPO / "include" / "klas"),
+                    "-c", str(src), "-o", str(tmp_path / "shim_user.o")], check=True)

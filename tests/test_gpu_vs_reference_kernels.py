@@ -1,9 +1,10 @@
 """Same seeded inputs through this library and through the reference's own kernels (dist/Klas_*.cu
 compiled for sm_100a, oracle/_ref): results must agree -- bit for bit for integers, within the
-float tolerances otherwise -- and the timings of both are written to ref_kernel_timings.json in the
-run's output folder."""
+float tolerances otherwise.  The timings of both are written to the file named by the
+KLAS_TIMINGS_OUT environment variable, when it is set."""
 import ctypes as C
 import json
+import os
 import time
 from pathlib import Path
 
@@ -16,7 +17,6 @@ from ref_gpu import RefGpu
 
 pytestmark = pytest.mark.gpu
 
-OUT = Path(__file__).resolve().parent.parent / "gpurun_out"
 TIMINGS = {}
 
 
@@ -25,8 +25,10 @@ def ref():
     if not RefGpu.available():
         pytest.skip("oracle/_ref/libklas_ref_gpu.so not built")
     yield RefGpu()
-    OUT.mkdir(exist_ok=True)
-    (OUT / "ref_kernel_timings.json").write_text(json.dumps(TIMINGS, indent=1))
+    if os.environ.get("KLAS_TIMINGS_OUT"):
+        out = Path(os.environ["KLAS_TIMINGS_OUT"])
+        out.parent.mkdir(parents=True, exist_ok=True)
+        out.write_text(json.dumps(TIMINGS, indent=1))
 
 
 def wall_ms(fn, reps=3):
