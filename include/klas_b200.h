@@ -431,6 +431,65 @@ int klas_b200_reduce_sum(int dtype, uint64_t n, const void *a, void *result, voi
 int klas_b200_reduce_sum_host(int dtype, uint64_t n, const void *a, void *result);
 
 /*
+ * ---- Several GPUs of one node, one host thread --------------------------------------------------
+ *
+ * The products shard without any exchange of data: dense GEMM by row blocks of A and C with B
+ * replicated on every device, batched GEMM by pages, CSR x dense by CSR row ranges with B
+ * replicated.  A context holds one stream per device; a sharded call launches the single-GPU kernel
+ * on every device's stream with that device's shard pointers and returns (asynchronous, like the
+ * single-GPU entries); klas_b200_mg_synchronize waits for all devices and reports a tensor-core
+ * wait that gave up.  Pointer arrays have one entry per device of the context, in its order;
+ * every pointer is a device pointer on ITS device.  `bounds` arrays have count + 1 entries:
+ * device i owns rows (or pages) [bounds[i], bounds[i+1]) and its shard pointer addresses its
+ * first row; a device may own nothing.
+ *
+ * `gather` asks for the result assembled, by NCCL over NVLink on the same streams (loaded with
+ * dlopen when first needed; without an NCCL library a gather returns KLAS_ERR_UNSUPPORTED and
+ * everything else still works): KLAS_MG_NO_GATHER leaves the shards where they are (`full`
+ * ignored); KLAS_MG_GATHER_ALL fills full[i] on every device with all rows; KLAS_MG_GATHER_FIRST
+ * fills full[0] only.  Shards of unequal size are fine.
+ *
+ * No counterpart in the reference, which is single-GPU (dist/Klas_*.h run on the current device).
+ */
+typedef struct klas_mg_context_s klas_mg_context;
+typedef enum klas_mg_gather_e { KLAS_MG_NO_GATHER = 0, KLAS_MG_GATHER_ALL = 1, KLAS_MG_GATHER_FIRST = 2 } klas_mg_gather;
+
+int klas_b200_mg_create(const int *devices, int count, klas_mg_context **ctx);
+int klas_b200_mg_destroy(klas_mg_context *ctx);
+int klas_b200_mg_count(const klas_mg_context *ctx);
+void *klas_b200_mg_stream(const klas_mg_context *ctx, int index);   /* cudaStream_t of device `index`, for the caller's own copies */
+int klas_b200_mg_synchronize(klas_mg_context *ctx);
+
+/* Host-only partitioners.  Row blocks: `parts` contiguous blocks of [0, rows) whose boundaries are
+ * multiples of `align` (256 = the tensor-core tile height), as even as that allows.  CSR ranges:
+ * equal row counts, or (balance_nnz != 0, row_off a HOST array of rows + 1 offsets) boundaries by
+ * binary search on row_off so that every range holds about nnz / parts nonzeros. */
+int klas_b200_mg_row_blocks(uint64_t rows, int parts, uint64_t align, uint64_t *bounds);
+int klas_b200_mg_csr_row_ranges(const uint32_t *row_off, uint32_t rows, int parts, int balance_nnz, uint32_t *bounds);
+
+/* Copies `bytes` bytes from buffers[root] into every other device's buffer: the one-off replication of B. */
+int klas_b200_mg_broadcast(klas_mg_context *ctx, void *const *buffers, size_t bytes, int root);
+
+/* D_i = A_i . B on every device (klas_b200_gemm_tc with C = NULL); A_i = rows row_bounds[i] .. of A. */
+int klas_b200_mg_gemm_tc(klas_mg_context *ctx, int in_dtype, int out_dtype, int b_major, const uint64_t *row_bounds,
+                         uint64_t shared, uint64_t cols, const void *const *A_shards, const void *const *B_replicas,
+                         void *const *D_shards, int gather, void *const *D_full);
+/* Batched: device i multiplies its pages of A by its pages of B (nothing is replicated). */
+int klas_b200_mg_gemm_tc_batched(klas_mg_context *ctx, int in_dtype, int out_dtype, int b_major, const uint64_t *page_bounds,
+                                 uint64_t rows, uint64_t shared, uint64_t cols, const void *const *A_pages,
+                                 const void *const *B_pages, void *const *D_pages, int gather, void *const *D_full);
+/* CUDA-core GEMM C_i = A_i . B (klas_b200_gemm, row-major, alpha = beta = NULL). */
+int klas_b200_mg_gemm(klas_mg_context *ctx, int dtype, const uint64_t *row_bounds, uint64_t n, uint64_t k,
+                      const void *const *A_shards, const void *const *B_replicas, void *const *C_shards, int gather,
+                      void *const *C_full);
+/* CSR x dense on CSR row ranges: device i holds its rows' nonzeros (nnz[i], elems[i], col_ind[i]) and
+ * their row offsets REBASED to start at 0 (row_off[i], rows_i + 1 entries), and a replica of B. */
+int klas_b200_mg_spmm(klas_mg_context *ctx, int dtype, const uint32_t *row_bounds, uint32_t shared, uint32_t cols,
+                      const uint32_t *nnz, const void *const *elems, const uint32_t *const *col_ind,
+                      const uint32_t *const *row_off, const void *const *B_replicas, void *const *C_shards, int gather,
+                      void *const *C_full);
+
+/*
  * Tuning / testing knobs.  The library picks tile shapes and schedules from the problem size;
  * these process-wide overrides exist so that a test or a tuning run can force each variant and
  * compare (every variant gives bit-identical results, which is what the tests check).  They are

@@ -15,6 +15,7 @@ B_ROW_MAJOR, B_COL_MAJOR = 0, 1
 MAP_ID, MAP_SQRT, MAP_ABS, MAP_SQUARE, MAP_RELU, MAP_NEG = range(6)
 COMB_NEW, COMB_AXPBY, COMB_MAX, COMB_MIN, COMB_MUL, COMB_RELU, COMB_SCALED = range(7)
 
+MG_NO_GATHER, MG_GATHER_ALL, MG_GATHER_FIRST = range(3)
 KNOB_TC_MODE, KNOB_TC_RASTER, KNOB_TC_SPLIT_K, KNOB_F64_MODE, KNOB_SIMT_TILE, KNOB_HOST_GRID = range(6)
 
 _u32, _u64, _vp, _int, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int, C.c_float
@@ -57,6 +58,18 @@ SIGNATURES = {
     "klas_b200_reduce_scratch_bytes": (C.c_size_t, [_u64]),
     "klas_b200_reduce_sum": (_int, [_int, _u64, _vp, _vp, _vp, C.c_size_t, _vp]),
     "klas_b200_reduce_sum_host": (_int, [_int, _u64, _vp, _vp]),
+    "klas_b200_mg_create": (_int, [_vp, _int, _vp]),
+    "klas_b200_mg_destroy": (_int, [_vp]),
+    "klas_b200_mg_count": (_int, [_vp]),
+    "klas_b200_mg_stream": (_vp, [_vp, _int]),
+    "klas_b200_mg_synchronize": (_int, [_vp]),
+    "klas_b200_mg_row_blocks": (_int, [_u64, _int, _u64, _vp]),
+    "klas_b200_mg_csr_row_ranges": (_int, [_vp, _u32, _int, _int, _vp]),
+    "klas_b200_mg_broadcast": (_int, [_vp, _vp, C.c_size_t, _int]),
+    "klas_b200_mg_gemm_tc": (_int, [_vp, _int, _int, _int, _vp, _u64, _u64, _vp, _vp, _vp, _int, _vp]),
+    "klas_b200_mg_gemm_tc_batched": (_int, [_vp, _int, _int, _int, _vp, _u64, _u64, _u64, _vp, _vp, _vp, _int, _vp]),
+    "klas_b200_mg_gemm": (_int, [_vp, _int, _vp, _u64, _u64, _vp, _vp, _vp, _int, _vp]),
+    "klas_b200_mg_spmm": (_int, [_vp, _int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "klas_b200_debug_set": (_int, [_int, _int]),
     "klas_b200_debug_get": (_int, [_int]),
     "klas_b200_release_workspace": (_int, []),

@@ -19,7 +19,7 @@ LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libklas_b200.so"
 INCLUDE_DIR = REPO_DIR / "include"
 
-SOURCES = ["abi.cu", "gemm_umma.cu", "gemm_simt.cu", "spmm.cu", "rowops.cu", "minplus.cu", "csr_build.cu", "gemm_dmma.cu", "attention.cu"]
+SOURCES = ["abi.cu", "gemm_umma.cu", "gemm_simt.cu", "spmm.cu", "rowops.cu", "minplus.cu", "csr_build.cu", "gemm_dmma.cu", "attention.cu", "multi_gpu.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -65,7 +65,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         if p.returncode != 0:
             raise RuntimeError("nvcc failed: %s\n%s" % (" ".join(cmd), out))
     link = [nvcc_path(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
-            "-o", str(LIB_PATH), *map(str, objs)]
+            "-o", str(LIB_PATH), *map(str, objs), "-ldl"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed: %s\n%s" % (" ".join(link), r.stdout))

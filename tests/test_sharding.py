@@ -144,3 +144,33 @@ def test_two_ranks_on_gloo(tmp_path, oracle):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / ("ok%d" % r)).exists() for r in range(world))
+
+
+# --------------------------------------------------------------------------- the C partitioners
+def test_c_partitioners_match_the_python_ones():
+    """klas_b200_mg_row_blocks / klas_b200_mg_csr_row_ranges (host-only functions of the C ABI)
+    against sharding.row_blocks / csr_row_ranges: cover, disjoint, tile-aligned, nnz-balanced."""
+    import ctypes as C
+    from kuiper_b200 import _lib
+    lib = _lib.load()
+    for m, world, align in [(8192, 8, 256), (65536, 8, 512), (1000, 3, 128), (5, 4, 1), (0, 2, 16), (700, 4, 256)]:
+        out = (C.c_uint64 * (world + 1))()
+        assert lib.klas_b200_mg_row_blocks(m, world, align, out) == 0
+        want = sharding.row_blocks(m, world, align)
+        assert [(out[i], out[i + 1]) for i in range(world)] == want
+        assert all(out[i] % align == 0 for i in range(1, world) if out[i] < m)
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(0, 50, (997,), generator=g)
+    lens[100] = 5000                       # one heavy row
+    row_off = torch.zeros(998, dtype=torch.int64)
+    row_off[1:] = torch.cumsum(lens, 0)
+    ro32 = row_off.to(torch.int32).numpy().astype("uint32")
+    for world in (1, 2, 3, 8):
+        for balance in ("rows", "nnz"):
+            out = (C.c_uint32 * (world + 1))()
+            assert lib.klas_b200_mg_csr_row_ranges(ro32.ctypes.data, 997, world, int(balance == "nnz"), out) == 0
+            got = [(out[i], out[i + 1]) for i in range(world)]
+            sharding.check_partition(got, 997)
+            if balance == "nnz":
+                assert got == sharding.csr_row_ranges(row_off, world, "nnz")
+    assert lib.klas_b200_mg_row_blocks(10, 0, 1, None) == _lib.ERR_INVALID
