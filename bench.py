@@ -927,6 +927,97 @@ def comparisons_leg(torch, device, ours_gemm_ms):
     return out
 
 
+def pcie_probe(torch, device, seconds=0.5, mib=256):
+    """Host<->device copy rates of this rank, pinned memory: host->device alone, device->host alone,
+    both at once (GB/s; the third is the sum of the two directions).  Every rank of a job runs it
+    at the same time, so the figures include the contention for the host's memory and PCIe roots."""
+    n = mib << 20
+    h_in = torch.empty(n, dtype=torch.uint8).pin_memory()
+    h_out = torch.empty(n, dtype=torch.uint8).pin_memory()
+    d_in = torch.empty(n, dtype=torch.uint8, device=device)
+    d_out = torch.empty(n, dtype=torch.uint8, device=device)
+    s1, s2 = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def run(h2d, d2h):
+        reps, out = 1, 0.0
+        while True:
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                if h2d:
+                    with torch.cuda.stream(s1):
+                        d_in.copy_(h_in, non_blocking=True)
+                if d2h:
+                    with torch.cuda.stream(s2):
+                        h_out.copy_(d_out, non_blocking=True)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            out = (int(h2d) + int(d2h)) * n * reps / dt / 1e9
+            if dt >= seconds or reps >= 4096:
+                return out
+            reps = max(reps * 2, int(reps * seconds / max(dt, 1e-4)) + 1)
+
+    return {"h2d_gbs": run(True, False), "d2h_gbs": run(False, True), "both_gbs": run(True, True)}
+
+
+def run_mg_api(args):
+    """`--mg-api`: the headline workload through the multi-GPU entry points of the C ABI
+    (klas_b200_mg_*), ONE process and one host thread driving args.gpus devices -- what a C or C++
+    caller gets; no torch.distributed.  Timed as host wall-clock between two all-device
+    synchronisations, max over devices by construction."""
+    import torch
+    from kuiper_b200 import _lib, synth
+    lib = _lib.load()
+    n = args.gpus
+    if torch.cuda.device_count() < n:
+        raise SystemExit("--mg-api --gpus %d needs %d visible devices" % (n, n))
+    rows, N, K = GemmBf16.ROWS_PER_GPU, GemmBf16.N, GemmBf16.K
+    devs = (ctypes.c_int * n)(*range(n))
+    ctx = ctypes.c_void_p()
+    _lib.check(lib.klas_b200_mg_create(devs, n, ctypes.byref(ctx)))
+    A, B, D = [], [], []
+    for i in range(n):
+        dev = torch.device("cuda", i)
+        a, bt = synth.gemm_bf16(1, rows * n, N, K, row0=i * rows, rows=rows, b_col_major=True, device=dev)
+        A.append(a)
+        B.append(bt)
+        D.append(torch.empty((rows, N), dtype=torch.float32, device=dev))
+    bounds = (ctypes.c_uint64 * (n + 1))(*[i * rows for i in range(n + 1)])
+    pa = (ctypes.c_void_p * n)(*[t.data_ptr() for t in A])
+    pb = (ctypes.c_void_p * n)(*[t.data_ptr() for t in B])
+    pd = (ctypes.c_void_p * n)(*[t.data_ptr() for t in D])
+
+    def step(gather=_lib.MG_NO_GATHER, full=None):
+        _lib.check(lib.klas_b200_mg_gemm_tc(ctx, _lib.BF16, _lib.F32, _lib.B_COL_MAJOR, bounds, K, N, pa, pb, pd, gather, full))
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    _lib.check(lib.klas_b200_mg_synchronize(ctx))
+    sampler = ClockSampler(0)
+    with sampler:
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step()
+        _lib.check(lib.klas_b200_mg_synchronize(ctx))
+        dt = time.perf_counter() - t0
+    flop = 2.0 * rows * n * N * K
+    # one gathered pass, checked against the per-device blocks
+    fulls = [torch.empty((rows * n, N), dtype=torch.float32, device=torch.device("cuda", i)) for i in range(n)]
+    pf = (ctypes.c_void_p * n)(*[t.data_ptr() for t in fulls])
+    step(_lib.MG_GATHER_ALL, pf)
+    _lib.check(lib.klas_b200_mg_synchronize(ctx))
+    gather_ok = all(torch.equal(fulls[i][j * rows:(j + 1) * rows].cpu(), D[j].cpu()) for i in (0, n - 1) for j in range(n))
+    _lib.check(lib.klas_b200_mg_destroy(ctx))
+    line = {"metric": "bf16_gemm_tflops", "value": flop * args.steps / dt / 1e12, "unit": "TFLOP/s", "n_gpus": n,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(GemmBf16.describe(n), api="klas_b200_mg_gemm_tc: one process, one host thread, %d devices" % n,
+                           timing="host wall-clock between two all-device synchronisations"),
+            "clocks": sampler.summary(), "gpu_launches": args.steps * n, "check": {"gather_ok": bool(gather_ok)}}
+    print(json.dumps(line), flush=True)
+    return 0
+
+
 # --------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -938,6 +1029,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="leave out the sustained leg, the other configurations and the comparison rows")
+    ap.add_argument("--mg-api", action="store_true",
+                    help="gemm_bf16 through the multi-GPU C entry points: one process drives --gpus devices (no torchrun)")
+    ap.add_argument("--no-numa-bind", action="store_true",
+                    help="do not bind this rank's host thread and pinned buffers to the NUMA node of its GPU")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--attention-heads", type=int, default=256,
                     help="attention_f16 only: heads per GPU (256 is the bench size; fewer for profiler captures)")
@@ -947,6 +1042,8 @@ def main():
     rank, world, local = dist_env()
     if args.impl == "reference":
         return run_reference_arm(args, rank, world)
+    if args.mg_api:
+        return run_mg_api(args)
 
     import torch
     import torch.distributed as dist
@@ -961,7 +1058,11 @@ def main():
     os.dup2(2, 1)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    from kuiper_b200 import klas, sharding  # noqa: F401  (fails loudly if libklas_b200.so is missing)
+    from kuiper_b200 import _lib, klas, sharding  # noqa: F401  (fails loudly if libklas_b200.so is missing)
+    # host placement: this rank's thread and the pinned buffers it allocates go to the socket its GPU hangs off
+    numa = {"node": _lib.load().klas_b200_host_numa_node(), "bound": False}
+    if not args.no_numa_bind:
+        numa["bound"] = _lib.load().klas_b200_host_bind_near_device() == _lib.OK
 
     wl = make_workload(args.workload, rank, world, device, args)
     warm = max(args.warmup, 3)
@@ -1039,6 +1140,16 @@ def main():
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_value = float(units) * args.e2e_steps / float(e2e_s) / scale
+    # what the host links give every rank while all ranks copy at once
+    barrier()
+    probe = pcie_probe(torch, device)
+    mine = torch.tensor([probe["h2d_gbs"], probe["d2h_gbs"], probe["both_gbs"], float(numa["node"]), float(numa["bound"]),
+                         float(e2e_s)], dtype=torch.float64, device=device)
+    per_rank = [torch.zeros_like(mine) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(per_rank, mine)
+    else:
+        per_rank = [mine]
 
     if rank == 0:
         peaks = load_peaks()
@@ -1053,7 +1164,14 @@ def main():
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
-                    "steps": args.e2e_steps, "api": getattr(wl, "e2e_api", "klas_b200_*_host (C ABI, pinned host buffers)")},
+                    "steps": args.e2e_steps, "api": getattr(wl, "e2e_api", "klas_b200_*_host (C ABI, pinned host buffers)"),
+                    "ms_per_call_per_rank": [float(t[5]) / args.e2e_steps * 1e3 for t in per_rank],
+                    "h2d_gbs": [float(t[0]) for t in per_rank], "d2h_gbs": [float(t[1]) for t in per_rank],
+                    "both_gbs": [float(t[2]) for t in per_rank],
+                    "node_aggregate_gbs": {"h2d": sum(float(t[0]) for t in per_rank), "d2h": sum(float(t[1]) for t in per_rank),
+                                           "both": sum(float(t[2]) for t in per_rank)},
+                    "numa_node_per_rank": [int(t[3]) for t in per_rank], "numa_bound": [bool(t[4]) for t in per_rank],
+                    "copy_rates_note": "pinned 256 MiB copies, all ranks at once: host->device alone, device->host alone, both"},
             "gpu_launches": args.steps * wl.launches_per_step,
             "roofline": roofline,
         }

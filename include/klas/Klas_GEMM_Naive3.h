@@ -7,7 +7,7 @@
 #include "klas_signatures.h"
 
 #define KLAS_ENTRY(name, params, ...) void name params;
-KLAS_NAIVE3_TYPES(KLAS_NAIVE_ENTRIES, Naive3)
+KLAS_NAIVE3_TYPES(KLAS_NAIVE3_ENTRIES, Naive3)
 #undef KLAS_ENTRY
 
 #define Klas_GEMM_Naive3_H_DEFINED

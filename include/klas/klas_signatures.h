@@ -49,6 +49,9 @@
 
 /* ---- Naive3 (dist/Klas_GEMM_Naive3.h:8-41): compensated sums; bf16, f32, f64 --------------- */
 #define KLAS_NAIVE3_TYPES(X, F) X(F, bf16, __nv_bfloat16) X(F, f32, float) X(F, f64, double)
+#define KLAS_NAIVE3_ENTRIES(F, L, T)                                                                    \
+    KLAS_ENTRY(Klas_GEMM_##F##_g_matmul_##L##_rrr, (KLAS_MNK_ABC(T)), COMPENSATED, L, T, 0)            \
+    KLAS_ENTRY(Klas_GEMM_##F##_g_matmul_##L##_ccc, (KLAS_MNK_ABC(T)), COMPENSATED_CCC, L, T, 0)
 
 /* ---- BlockTiling2D (dist/Klas_GEMM_BlockTiling2D.h:8-1376): f32 and bf16 per tile instance - */
 #define KLAS_BT2D_INSTANCE(bm, bn, bk, tm, tn)                                                          \

@@ -103,13 +103,26 @@ int klas_b200_sm_count(void);
  * Replaces: Klas_GEMM_SHMem_g_{matmul,gemm}_* (dist/Klas_GEMM_SHMem.h:8-187),
  * Klas_GEMM_Tiled_* (dist/Klas_GEMM_Tiled.h), Klas_GEMM_BlockTiling1D_*
  * (dist/Klas_GEMM_BlockTiling1D.h:8-131), Klas_GEMM_BlockTiling2D_g_gemm_*
- * (dist/Klas_GEMM_BlockTiling2D.h:8-1376), Klas_GEMM_Naive{1,2}_*
- * (dist/Klas_GEMM_Naive1.h:8-65) and Klas_GEMM_Naive3_* (dist/Klas_GEMM_Naive3.h:8-41).
+ * (dist/Klas_GEMM_BlockTiling2D.h:8-1376) and Klas_GEMM_Naive{1,2}_* (dist/Klas_GEMM_Naive1.h:8-65).
  */
 int klas_b200_gemm(int dtype, int layout, uint32_t batch,
                    uint64_t m, uint64_t n, uint64_t k,
                    const void *alpha, const void *beta,
                    const void *A, const void *B, void *C, void *stream);
+
+/*
+ * C = A.B (one matrix, no alpha / beta) for callers that asked the reference for its compensated
+ * sums: Klas_GEMM_Naive3_* add each row-by-column sum with Kahan's correction in the element type
+ * (dist/Klas_GEMM_Naive3.cu:17-30).  KLAS_F32 is accumulated here in f64 -- the products of f32
+ * numbers are exact in f64 and the sum carries 29 more bits than a compensated f32 sum recovers --
+ * and rounded to f32 once; KLAS_BF16 is accumulated in f32 as in klas_b200_gemm (again more than
+ * bf16 compensation keeps).  KLAS_F64 takes the plain kernel: its sums are ordinary f64 sums in
+ * ascending k, WITHOUT compensation -- within the drivers' tolerance, but a cancellation-heavy
+ * sum loses the digits the reference's correction term would have kept.
+ * Replaces: Klas_GEMM_Naive3_g_matmul_{bf16,f32,f64}_{rrr,ccc} (dist/Klas_GEMM_Naive3.h:8-41).
+ */
+int klas_b200_gemm_compensated(int dtype, int layout, uint64_t m, uint64_t n, uint64_t k,
+                               const void *A, const void *B, void *C, void *stream);
 
 /*
  * General batched CUDA-core GEMM: `batch` row-major products
@@ -333,6 +346,23 @@ int klas_b200_gemm_tc_host(int in_dtype, int out_dtype, int b_major, uint32_t ba
 int klas_b200_spmm_host(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32_t nnz,
                         const void *elems, const uint32_t *col_ind, const uint32_t *row_off,
                         const uint32_t *row_indices, const void *B, void *C);
+
+/*
+ * Host placement for the host-buffer variants.  On a two-socket node a GPU reads and writes host
+ * memory at full PCIe rate only when the buffers live on the socket it hangs off; with eight
+ * ranks whose pinned buffers all sit on one socket the copies of half the GPUs cross the
+ * socket link and the node's aggregate rate collapses.
+ *   klas_b200_host_numa_node         NUMA node of the current device (from sysfs), -1 if unknown.
+ *   klas_b200_host_bind_near_device  restricts the CALLING THREAD to that node's CPUs and makes the
+ *                                    node the preferred one for memory it allocates from now on;
+ *                                    call it before allocating the pinned buffers.  Changes only
+ *                                    the calling thread's affinity and memory policy, nothing of the
+ *                                    GPU.  KLAS_ERR_UNSUPPORTED when the node is unknown or its CPUs
+ *                                    are not available to the process (nothing is changed then).
+ * No counterpart in the reference.
+ */
+int klas_b200_host_numa_node(void);
+int klas_b200_host_bind_near_device(void);
 
 /*
  * Row-wise neighbours of the products (what sits either side of Q.K^T and P.V in an

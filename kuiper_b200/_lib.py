@@ -26,6 +26,7 @@ SIGNATURES = {
     "klas_b200_version": (_int, []),
     "klas_b200_sm_count": (_int, []),
     "klas_b200_gemm": (_int, [_int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "klas_b200_gemm_compensated": (_int, [_int, _int, _u64, _u64, _u64, _vp, _vp, _vp, _vp]),
     "klas_b200_gemm_tc": (_int, [_int, _int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp,
                                   _f32, _f32, _vp, _vp]),
     "klas_b200_gemm_strided": (_int, [_int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _u64, _u64, _vp, _u64, _u64,
@@ -50,6 +51,8 @@ SIGNATURES = {
     "klas_b200_gemm_tc_host": (_int, [_int, _int, _int, _u32, _u64, _u64, _u64, _vp, _vp, _vp, _vp,
                                        _f32, _f32]),
     "klas_b200_spmm_host": (_int, [_int, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "klas_b200_host_numa_node": (_int, []),
+    "klas_b200_host_bind_near_device": (_int, []),
     "klas_b200_softmax_scratch_bytes": (C.c_size_t, [_u64, _u64]),
     "klas_b200_softmax": (_int, [_int, _int, _u64, _u64, _vp, _vp, C.c_size_t, _vp]),
     "klas_b200_softmax_host": (_int, [_int, _int, _u64, _u64, _vp]),

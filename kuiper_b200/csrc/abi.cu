@@ -3,6 +3,10 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <sched.h>
+#include <sys/syscall.h>
+#include <unistd.h>
+
 #include <atomic>
 #include <climits>
 #include <cstring>
@@ -176,6 +180,12 @@ int klas_b200_gemm(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t n
     clear_error();
     return launch_gemm_simt(dtype, layout, batch, m, n, k, alpha, beta, A, B, C,
                             static_cast<cudaStream_t>(stream));
+}
+
+int klas_b200_gemm_compensated(int dtype, int layout, uint64_t m, uint64_t n, uint64_t k, const void *A, const void *B,
+                               void *C, void *stream) {
+    clear_error();
+    return launch_gemm_simt_compensated(dtype, layout, m, n, k, A, B, C, static_cast<cudaStream_t>(stream));
 }
 
 int klas_b200_gemm_tc(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
@@ -551,6 +561,65 @@ int klas_b200_reduce_sum_host(int dtype, uint64_t n, const void *a, void *result
     if (int rc = launch_reduce_sum(dtype, n, a, dOut, dS, sb, s)) return rc;
     KLAS_TRY_CUDA(cudaMemcpyAsync(result, dOut, es, cudaMemcpyDeviceToHost, s));
     KLAS_TRY_CUDA(cudaStreamSynchronize(s));
+    return KLAS_OK;
+}
+
+// NUMA node the current device hangs off (sysfs of its PCI function), -1 when unknown.
+static int device_numa_node() {
+    int dev = 0;
+    char bus[32] = "";
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetPCIBusId(bus, sizeof bus, dev) != cudaSuccess) return -1;
+    for (char *c = bus; *c; ++c)
+        if (*c >= 'A' && *c <= 'F') *c = char(*c - 'A' + 'a');
+    char path[128];
+    snprintf(path, sizeof path, "/sys/bus/pci/devices/%s/numa_node", bus);
+    FILE *f = fopen(path, "r");
+    if (!f) return -1;
+    int node = -1;
+    if (fscanf(f, "%d", &node) != 1) node = -1;
+    fclose(f);
+    return node;
+}
+
+int klas_b200_host_numa_node(void) {
+    clear_error();
+    return device_numa_node();
+}
+
+int klas_b200_host_bind_near_device(void) {
+    clear_error();
+    const int node = device_numa_node();
+    if (node < 0) return fail(KLAS_ERR_UNSUPPORTED, "host_bind: the device's NUMA node is not known on this system");
+    char path[128];
+    snprintf(path, sizeof path, "/sys/devices/system/node/node%d/cpulist", node);
+    FILE *f = fopen(path, "r");
+    if (!f) return fail(KLAS_ERR_UNSUPPORTED, "host_bind: cannot read %s", path);
+    cpu_set_t want, allowed, both;
+    CPU_ZERO(&want);
+    int lo = 0, hi = 0;
+    for (;;) {   // "0-15,64-79"
+        if (fscanf(f, "%d", &lo) != 1) break;
+        hi = lo;
+        int ch = fgetc(f);
+        if (ch == '-') {
+            if (fscanf(f, "%d", &hi) != 1) break;
+            ch = fgetc(f);
+        }
+        for (int c = lo; c <= hi && c < CPU_SETSIZE; ++c) CPU_SET(c, &want);
+        if (ch != ',') break;
+    }
+    fclose(f);
+    if (sched_getaffinity(0, sizeof allowed, &allowed) != 0) return fail(KLAS_ERR_UNSUPPORTED, "host_bind: sched_getaffinity failed");
+    CPU_AND(&both, &want, &allowed);
+    if (CPU_COUNT(&both) == 0) return fail(KLAS_ERR_UNSUPPORTED, "host_bind: none of node %d's CPUs is available to this process", node);
+    if (sched_setaffinity(0, sizeof both, &both) != 0) return fail(KLAS_ERR_UNSUPPORTED, "host_bind: sched_setaffinity failed");
+    // memory allocated from now on (pinned buffers included) is taken from that node when it has room
+    unsigned long mask[16] = {};
+    if (node < int(sizeof mask * 8)) {
+        mask[node / (8 * sizeof(unsigned long))] |= 1ul << (node % (8 * sizeof(unsigned long)));
+        const long MPOL_PREFERRED = 1;
+        syscall(SYS_set_mempolicy, MPOL_PREFERRED, mask, sizeof mask * 8);   // best effort: affinity alone already gives local first touch
+    }
     return KLAS_OK;
 }
 

@@ -4,4 +4,4 @@
 #undef KLAS_ENTRY
 #include "compat_common.h"
 
-KLAS_NAIVE3_TYPES(KLAS_NAIVE_ENTRIES, Naive3)
+KLAS_NAIVE3_TYPES(KLAS_NAIVE3_ENTRIES, Naive3)

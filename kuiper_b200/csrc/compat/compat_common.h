@@ -55,6 +55,12 @@ static inline void finish(int status, const char *entry, bool tensor_core) {
 #define KLAS_BODY_MATMUL_CCC(NAME, L, T, TILE) \
     klas_compat::finish(klas_b200_gemm(KLAS_CODE_##L, KLAS_CCC, 1, m, n, k, NULL, NULL, gA, gB, gC, NULL), NAME, false);
 
+// Naive3: the reference's compensated sums (f32 accumulated in f64 here)
+#define KLAS_BODY_COMPENSATED(NAME, L, T, TILE) \
+    klas_compat::finish(klas_b200_gemm_compensated(KLAS_CODE_##L, KLAS_RRR, m, n, k, gA, gB, gC, NULL), NAME, false);
+#define KLAS_BODY_COMPENSATED_CCC(NAME, L, T, TILE) \
+    klas_compat::finish(klas_b200_gemm_compensated(KLAS_CODE_##L, KLAS_CCC, m, n, k, gA, gB, gC, NULL), NAME, false);
+
 #define KLAS_BODY_GEMM(NAME, L, T, TILE)                                                          \
     KLAS_TILE_GUARDS(TILE)                                                                        \
     klas_compat::finish(klas_b200_gemm(KLAS_CODE_##L, KLAS_RRR, 1, m, n, k, &alpha, &beta, gA, gB, gC, NULL), NAME, false);

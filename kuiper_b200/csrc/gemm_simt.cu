@@ -104,6 +104,7 @@ struct Problem {
     uint64_t lda, ldb, ldc, sa, sb, sc;
     int map_a, map_b, comb;
     bool hooks;   // any map or a combine rule other than overwrite / axpby
+    bool wide_acc = false;   // f32 storage, f64 arithmetic: the compensated-sum entry points
 };
 
 template <typename T>
@@ -496,6 +497,10 @@ static int dispatch(int dtype, const Problem &q, const void *alpha, const void *
     const int scaled = alpha != nullptr;
     switch (dtype) {
         case KLAS_F32:
+            if (q.wide_acc)   // exact products and an f64 sum, rounded once: at least what a compensated f32 sum keeps
+                return launch_type<float, double>(q, scaled ? double(*static_cast<const float *>(alpha)) : 1.0,
+                                                  scaled ? double(*static_cast<const float *>(beta)) : 0.0, scaled, A, B, C,
+                                                  info.sm_count, stream);
             return launch_type<float, float>(q, scaled ? *static_cast<const float *>(alpha) : 1.0f,
                                              scaled ? *static_cast<const float *>(beta) : 0.0f, scaled, A, B, C,
                                              info.sm_count, stream);
@@ -567,6 +572,38 @@ int launch_gemm_simt(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t
     q.comb = alpha ? KLAS_COMB_AXPBY : KLAS_COMB_NEW;
     q.hooks = false;
     return simt::dispatch(dtype, q, alpha, beta, A, B, C, stream);
+}
+
+int launch_gemm_simt_compensated(int dtype, int layout, uint64_t m, uint64_t n, uint64_t k, const void *A, const void *B,
+                                 void *C, cudaStream_t stream) {
+    if (dtype != KLAS_F32) return launch_gemm_simt(dtype, layout, 1, m, n, k, nullptr, nullptr, A, B, C, stream);
+    if (layout != KLAS_RRR && layout != KLAS_CCC) return fail(KLAS_ERR_INVALID, "gemm: bad layout");
+    if (m == 0 || n == 0) return KLAS_OK;
+    if (!C || (k > 0 && (!A || !B))) return fail(KLAS_ERR_INVALID, "gemm: null matrix pointer");
+    if (layout == KLAS_CCC) {
+        const void *t = A;
+        A = B;
+        B = t;
+        const uint64_t tm = m;
+        m = n;
+        n = tm;
+    }
+    simt::Problem q{};
+    q.batch = 1;
+    q.m = m;
+    q.n = n;
+    q.k = k;
+    q.lda = k;
+    q.ldb = n;
+    q.ldc = n;
+    q.sa = m * k;
+    q.sb = k * n;
+    q.sc = m * n;
+    q.map_a = q.map_b = KLAS_MAP_ID;
+    q.comb = KLAS_COMB_NEW;
+    q.hooks = false;
+    q.wide_acc = true;
+    return simt::dispatch(dtype, q, nullptr, nullptr, A, B, C, stream);
 }
 
 int launch_gemm_simt_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, uint64_t k, const void *alpha,

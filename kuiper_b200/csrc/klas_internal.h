@@ -58,6 +58,11 @@ int launch_gemm_simt(int dtype, int layout, uint32_t batch, uint64_t m, uint64_t
                      const void *alpha, const void *beta, const void *A, const void *B, void *C,
                      cudaStream_t stream);
 
+// C = A.B with a sum that keeps what a compensated (Kahan) sum in the element type keeps: f32 is
+// accumulated in f64; the other types take the plain kernel.
+int launch_gemm_simt_compensated(int dtype, int layout, uint64_t m, uint64_t n, uint64_t k, const void *A, const void *B,
+                                 void *C, cudaStream_t stream);
+
 int launch_gemm_dmma(uint32_t batch, uint64_t m, uint64_t n, uint64_t k, const double *alpha, const double *beta,
                      const void *A, const void *B, void *C, cudaStream_t stream);
 

@@ -124,6 +124,31 @@ def gemm(A: torch.Tensor, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *,
     return C_
 
 
+def gemm_compensated(A: torch.Tensor, B: torch.Tensor, C_: Optional[torch.Tensor] = None, *, layout: str = "rrr") -> torch.Tensor:
+    """C = A.B with the accuracy of the reference's compensated sums (Klas_GEMM_Naive3_*): f32 is
+    accumulated in f64 and rounded once; the other dtypes run as gemm.  2-D operands, layouts as gemm."""
+    if A.dim() != 2 or B.dim() != 2 or B.dtype != A.dtype:
+        raise ValueError("gemm_compensated takes two 2-D matrices of one dtype")
+    if layout == "rrr":
+        (m, k), (k2, n) = A.shape, B.shape
+        cshape = (m, n)
+    elif layout == "ccc":
+        (k, m), (n, k2) = A.shape, B.shape
+        cshape = (n, m)
+    else:
+        raise ValueError("layout must be 'rrr' or 'ccc'")
+    if k != k2:
+        raise ValueError("inner dimensions differ: %d vs %d" % (k, k2))
+    if C_ is None:
+        C_ = torch.empty(cshape, dtype=A.dtype, device=A.device)
+    elif tuple(C_.shape) != cshape or C_.dtype != A.dtype:
+        raise ValueError("C has the wrong shape or dtype")
+    with torch.cuda.device(A.device):
+        check(_lib.load().klas_b200_gemm_compensated(_code(A), _lib.RRR if layout == "rrr" else _lib.CCC, m, n, k,
+                                                     _dev(A, "A"), _dev(B, "B"), _dev(C_, "C"), _stream()))
+    return C_
+
+
 def sdpa_fused(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, scale: Optional[float] = None) -> torch.Tensor:
     """softmax(scale * Q.K^T).V per head in one kernel (scores never leave the chip).  Q [..., l, e],
     K [..., s, e], V [..., s, e], f16 or bf16, contiguous, e = 64 or 128.  scale defaults to 1/sqrt(e)."""
@@ -539,13 +564,14 @@ def call(name: str, *args):
         return None
     m_ = _RE_NAIVE.match(name)
     if m_:
-        _, dt, lay = m_.groups()
+        which, dt, lay = m_.groups()
         m, n, k, A, B, Cc = args
         t = _TORCH_OF[dt]
+        mul = gemm_compensated if which == "3" else gemm   # Naive3: the reference's compensated sums
         if lay == "rrr":
-            gemm(_view(A, t, m, k), _view(B, t, k, n), _view(Cc, t, m, n))
+            mul(_view(A, t, m, k), _view(B, t, k, n), _view(Cc, t, m, n))
         else:
-            gemm(_view(A, t, k, m), _view(B, t, n, k), _view(Cc, t, n, m), layout="ccc")
+            mul(_view(A, t, k, m), _view(B, t, n, k), _view(Cc, t, n, m), layout="ccc")
         return None
     m_ = _RE_NAIVE_B.match(name)
     if m_:

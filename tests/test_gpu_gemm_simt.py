@@ -169,3 +169,24 @@ def test_guards_raise():
         klas.call("Klas_GEMM_BlockTiling2D_g_gemm_f32_128x128x32_8x8", 1.0, 0.0, 64, 64, 64, z, z, z)
     with pytest.raises(klas.KlasGuardError):
         klas.call("Klas_GEMM_BlockTiling1D_g_matmul_f32_tile32_rrr", 48, 64, 64, z, z, z)
+
+
+def test_compensated_f32_keeps_what_cancellation_destroys():
+    """Klas_GEMM_Naive3 adds with Kahan's correction (dist/Klas_GEMM_Naive3.cu:17-30).  Rows built to
+    cancel -- huge terms of both signs around small ones -- lose the small terms in a plain f32 sum;
+    the compensated entry point (f64 accumulation of the exact products) must return the correctly
+    rounded f32 result, under the reference's name as well."""
+    m, n, k = 65, 33, 4096
+    g = torch.Generator().manual_seed(11)
+    small = torch.rand((m, k), generator=g) + 0.5
+    big = torch.where(torch.arange(k) % 2 == 0, torch.tensor(3.0e7), torch.tensor(-3.0e7)).repeat(m, 1)
+    A = (small + big).float()                 # alternating +-3e7, each carrying a term of order 1
+    B = torch.ones((k, n))
+    want = (A.double() @ B.double()).float()  # exact in f64: the big terms cancel pair by pair
+    got = klas.gemm_compensated(A.cuda(), B.cuda()).cpu()
+    assert torch.equal(got, want)
+    named = torch.zeros((m, n), device="cuda")
+    klas.call("Klas_GEMM_Naive3_g_matmul_f32_rrr", m, n, k, A.cuda(), B.cuda(), named)
+    assert torch.equal(named.cpu(), want)
+    plain = klas.gemm(A.cuda(), B.cuda()).cpu()
+    assert float((plain - want).abs().max()) > 1.0     # the uncompensated f32 sum really does lose them
