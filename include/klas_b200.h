@@ -529,7 +529,8 @@ int klas_b200_mg_spmm(klas_mg_context *ctx, int dtype, const uint32_t *row_bound
  *   KLAS_KNOB_TC_MODE    tensor-core tile: 0 library's choice (default), 1 single-CTA 128x256,
  *                        2 single-CTA 128x128, 3 CTA pair 256x256, 4 wide pair 512x256
  *   KLAS_KNOB_TC_RASTER  tile columns swept together: 0 default (8), else 1..1024
- *   KLAS_KNOB_TC_SPLIT_K K slices per output tile of the single-CTA kernel: 0 library's choice, 1 none, 2..8
+ *   KLAS_KNOB_SIMT_SPLIT_K  CTAs per output tile along K in the CUDA-core kernel: 0 library's choice
+ *                        (two when one part-filled wave of tiles would leave each SM with one CTA), 1 never, 2 whenever legal
  *   KLAS_KNOB_F64_MODE   0 library's choice, 1 keep fp64 products on the CUDA-core kernel
  *   KLAS_KNOB_SIMT_TILE  CUDA-core tile of 4-byte types: -1 library's choice, 0 64x64, 1 128x64, 2 128x128
  *   KLAS_KNOB_HOST_GRID  blocks per side of the 2-D schedule of klas_b200_gemm_tc_host: -1 default (4),
@@ -540,7 +541,7 @@ int klas_b200_mg_spmm(klas_mg_context *ctx, int dtype, const uint32_t *row_bound
 typedef enum klas_knob_e {
     KLAS_KNOB_TC_MODE = 0,
     KLAS_KNOB_TC_RASTER = 1,
-    KLAS_KNOB_TC_SPLIT_K = 2,
+    KLAS_KNOB_SIMT_SPLIT_K = 2,
     KLAS_KNOB_F64_MODE = 3,
     KLAS_KNOB_SIMT_TILE = 4,
     KLAS_KNOB_HOST_GRID = 5,

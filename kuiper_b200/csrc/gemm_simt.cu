@@ -92,6 +92,8 @@ struct Args {
     uint64_t lda, ldb, ldc;   // row strides in elements
     uint64_t sa, sb, sc;      // page strides in elements
     uint64_t tiles_m, tiles_n;
+    uint64_t k_chunk;         // K range of one CTA: K, or half of it when two CTAs share a tile
+    uint32_t ksplits;         // CTAs per output tile along K: 1, or 2 (partial sums added atomically to a zeroed C)
     T alpha, beta;
     int scaled;  // 0: C = A.B   1: C = beta*C + alpha*A.B
     int map_a, map_b, comb;   // klas_map / klas_comb, read by the HOOKS instantiations only
@@ -140,6 +142,13 @@ __device__ __forceinline__ T comb_val(T old, T acc, T alpha, T beta, int comb) {
     }
 }
 
+__device__ __forceinline__ void atomic_add(float *p, float v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add(double *p, double v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add(uint32_t *p, uint32_t v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add(uint64_t *p, uint64_t v) {
+    atomicAdd(reinterpret_cast<unsigned long long *>(p), static_cast<unsigned long long>(v));
+}
+
 template <typename T, int N>
 struct alignas(16) Vec {
     T v[N];
@@ -177,9 +186,11 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
     const int tx = PACKED ? tid % TX : ((tid >> 5) & 1) * 8 + (tid & 7);
     const int ty = PACKED ? tid / TX : (tid >> 6) * 4 + ((tid >> 3) & 3);
 
-    const uint64_t per_batch = a.tiles_m * a.tiles_n;
+    const uint64_t per_batch = a.tiles_m * a.tiles_n * a.ksplits;
     const uint64_t bidx = blockIdx.x / per_batch;
-    const uint64_t rem = blockIdx.x - bidx * per_batch;
+    const uint64_t rem = (blockIdx.x - bidx * per_batch) / a.ksplits;
+    const uint64_t k_base = ((blockIdx.x - bidx * per_batch) % a.ksplits) * a.k_chunk;   // 0 unless K is split
+    const uint64_t k_len = a.K - k_base < a.k_chunk ? a.K - k_base : a.k_chunk;
     const uint64_t m0 = (rem / a.tiles_n) * BM;
     const uint64_t n0 = (rem % a.tiles_n) * BN;
 
@@ -209,7 +220,7 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
                 const int kv = (idx % (BK / VEC)) * VEC;
                 if constexpr (FAST) {
                     ra[i] = *reinterpret_cast<const Vec<T, VEC> *>(
-                        reinterpret_cast<const T *>(A) + (m0 + r) * a.lda + k0 + kv);
+                        reinterpret_cast<const T *>(A) + (m0 + r) * a.lda + k_base + k0 + kv);
                 } else {
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) {
@@ -233,7 +244,7 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
                 const int nv = (idx % (BN / VEC)) * VEC;
                 if constexpr (FAST) {
                     rb[i] = *reinterpret_cast<const Vec<T, VEC> *>(
-                        reinterpret_cast<const T *>(B) + (k0 + kr) * a.ldb + n0 + nv);
+                        reinterpret_cast<const T *>(B) + (k_base + k0 + kr) * a.ldb + n0 + nv);
                 } else {
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) {
@@ -273,7 +284,7 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
         }
     };
 
-    const uint64_t num_kb = (a.K + BK - 1) / BK;
+    const uint64_t num_kb = (k_len + BK - 1) / BK;   // k_len == K unless K is split (fast instantiations only)
     // Tile kb + 1 travels global -> registers -> shared memory while tile kb is multiplied.  EARLY:
     // its global reads are issued just before the barrier that ends step kb - 1 (they cannot be
     // scheduled past it) and its shared-memory stores come at the end of step kb, a whole step
@@ -382,6 +393,13 @@ __global__ void __launch_bounds__(THREADS, (BM * BN * sizeof(T) <= 64 * 64 * 4) 
                 } else {
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) out.v[e] = acc_at(i, g * VEC + e);
+                    if (a.ksplits > 1) {
+                        // two CTAs hold the two halves of this tile's sum: both add onto a zeroed C
+                        // (two addends: the result does not depend on which arrives first)
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) atomic_add(cp + e, out.v[e]);
+                        continue;
+                    }
                 }
                 *reinterpret_cast<Vec<T, VEC> *>(cp) = out;
             } else {
@@ -456,9 +474,27 @@ static int launch_cfg(const Problem &q, T alpha, T beta, int scaled, const void 
                       (q.lda | q.ldb | q.ldc | q.sa | q.sb | q.sc) % VEC == 0 &&
                       ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
                         reinterpret_cast<uintptr_t>(C)) & 15u) == 0;
+    a.ksplits = 1;
+    a.k_chunk = q.k;
     if constexpr (sizeof(S) == sizeof(T)) {
         if (fast) {
             if (q.hooks) return launch_kernel<S, T, BM, BN, BK, true, true>(a, unsigned(blocks), stream);
+            // One part-filled wave of tiles (f32 1024^3: 128 tiles of 128 x 64 on 148 SMs, eight warps
+            // per SM): two CTAs per tile, each summing half of K, put sixteen warps on an SM and hide
+            // the shared-memory latency the single CTA cannot.  The halves are added atomically onto
+            // a zeroed C -- two addends, so the result does not depend on their order; it differs
+            // from the unsplit sum by one rounding (integers: not at all).
+            DeviceInfo info;
+            if (int rc = device_info(&info)) return rc;
+            const int knob = debug_knob(KLAS_KNOB_SIMT_SPLIT_K);
+            const bool can_split = !scaled && q.comb == KLAS_COMB_NEW && q.batch == 1 && q.k % (2 * BK) == 0 && q.k >= 8 * BK;
+            const bool want_split = knob == 2 || (knob == 0 && blocks <= uint64_t(info.sm_count) && q.k >= 512);
+            if (can_split && want_split) {
+                a.ksplits = 2;
+                a.k_chunk = q.k / 2;
+                KLAS_TRY_CUDA(cudaMemset2DAsync(C, q.ldc * sizeof(T), 0, q.n * sizeof(T), q.m, stream));
+                return launch_kernel<S, T, BM, BN, BK, true, false>(a, unsigned(blocks * 2), stream);
+            }
             return launch_kernel<S, T, BM, BN, BK, true, false>(a, unsigned(blocks), stream);
         }
     }

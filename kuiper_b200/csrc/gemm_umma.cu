@@ -88,21 +88,6 @@ __device__ int g_umma_status;
 // paying a device round trip per call.
 __device__ int *g_umma_host_flag;
 
-#ifdef KLAS_UMMA_PROFILE
-// Developer build only: per-CTA cycle counts of each role's waits.
-// [cta][0] producer waiting for a free stage, [1] MMA waiting for data, [2] MMA waiting for a
-// free accumulator, [3] epilogue waiting for an accumulator, [4] whole kernel, [5] epilogue busy.
-__device__ unsigned long long g_umma_prof[1024][8];
-#define KLAS_PROF_DECL unsigned long long prof_acc0 = 0, prof_acc1 = 0, prof_acc2 = 0, prof_mma0 = 0, prof_mma3 = 0
-#define KLAS_PROF_BEGIN const long long prof_t0 = clock64()
-#define KLAS_PROF_END(acc) acc += (unsigned long long)(clock64() - prof_t0)
-#define KLAS_PROF_STORE(slot, acc) if (lane == 0 && blockIdx.x < 1024) g_umma_prof[blockIdx.x][slot] = acc
-#else
-#define KLAS_PROF_DECL
-#define KLAS_PROF_BEGIN
-#define KLAS_PROF_END(acc)
-#define KLAS_PROF_STORE(slot, acc)
-#endif
 
 struct Params {
     const void *C;
@@ -314,11 +299,7 @@ __device__ __forceinline__ void xform_dispatch(uint32_t op, uint32_t addr, uint3
 // the pair's even CTA).
 __device__ __forceinline__ bool xform_stage(const Params &p, uint32_t full_bar, uint32_t parity, const Ctl &ctl,
                                             int site, uint32_t a_addr, uint32_t a_bytes, uint32_t b_bytes,
-                                            uint32_t xfull_bar_cluster, uint32_t lane,
-                                            [[maybe_unused]] unsigned long long *prof = nullptr) {
-#ifdef KLAS_UMMA_PROFILE
-    const long long prof_t0 = clock64();
-#endif
+                                            uint32_t xfull_bar_cluster, uint32_t lane) {
     bool ok = lane != 0 || bounded_wait(full_bar, parity, ctl, site, WAIT_LIMIT_NS, 32);
     ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
     if (!ok) return false;
@@ -326,9 +307,6 @@ __device__ __forceinline__ bool xform_stage(const Params &p, uint32_t full_bar, 
     // this warp's own arrival below), which orders the copies' writes before its reads.
     for (uint32_t i = 0; i < 1024 && !ptx::mbar_try_wait(full_bar, parity); ++i) {
     }
-#ifdef KLAS_UMMA_PROFILE
-    const long long prof_t1 = clock64();
-#endif
     if (p.in_bf16) {
         xform_dispatch<true>(p.map_a, a_addr, a_bytes, lane);
         xform_dispatch<true>(p.map_b, a_addr + a_bytes, b_bytes, lane);
@@ -336,19 +314,9 @@ __device__ __forceinline__ bool xform_stage(const Params &p, uint32_t full_bar, 
         xform_dispatch<false>(p.map_a, a_addr, a_bytes, lane);
         xform_dispatch<false>(p.map_b, a_addr + a_bytes, b_bytes, lane);
     }
-#ifdef KLAS_UMMA_PROFILE
-    const long long prof_t2 = clock64();
-#endif
     ptx::fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive_cluster(xfull_bar_cluster);
-#ifdef KLAS_UMMA_PROFILE
-    if (prof) {
-        prof[0] += (unsigned long long)(prof_t1 - prof_t0);
-        prof[1] += (unsigned long long)(prof_t2 - prof_t1);
-        prof[2] += (unsigned long long)(clock64() - prof_t2);
-    }
-#endif
     return true;
 }
 
@@ -491,7 +459,6 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
         uint32_t stage = 0, phase = 0;
         bool ok = lane == 0;
         [[maybe_unused]] const uint32_t full_bars_cta0 = PAIR ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);
-        KLAS_PROF_DECL;
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             uint32_t b, tm, tn;
             decode_tile(t, p, b, tm, tn);
@@ -501,9 +468,7 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 if (stage % S::RELEASE_GROUP == 0) {
                     // stages are handed back in groups; the group's last stage carries the barrier
-                    KLAS_PROF_BEGIN;
                     ok = bounded_wait(empty_bar(stage + S::RELEASE_GROUP - 1), phase ^ 1u, ctl, SITE_PRODUCER_EMPTY, WAIT_LIMIT_NS, 64);
-                    KLAS_PROF_END(prof_acc0);
                     if (!ok) break;
                 }
                 {
@@ -541,7 +506,6 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
                 }
             }
         }
-        KLAS_PROF_STORE(0, prof_acc0);
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -555,25 +519,17 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
         uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
         bool ok = lane == 0;   // one thread runs the whole loop
         const bool issuer = cta_rank == 0;
-        KLAS_PROF_DECL;
         for (uint32_t t = group; issuer && ok && p.num_kb > 0 && t < p.num_tiles; t += num_groups) {
             {
-                KLAS_PROF_BEGIN;
                 ok = bounded_wait(tempty_bar(acc), acc_phase ^ 1u, ctl, SITE_MMA_TMEM_EMPTY);
-                KLAS_PROF_END(prof_acc2);
             }
             if (!ok) break;
             ptx::tc_fence_after_sync();   // orders the epilogue's TMEM reads before these MMAs' writes
             const uint32_t d_tmem = tmem_base + acc * BN;
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-                KLAS_PROF_BEGIN;
                 ok = bounded_wait(XFORM ? xfull_bar(stage) : full_bar(stage), phase, ctl, SITE_MMA_FULL);
-                KLAS_PROF_END(prof_acc0);
                 if (!ok) break;
                 {
-#ifdef KLAS_UMMA_PROFILE
-                    const long long prof_i0 = clock64();
-#endif
                     const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
                     const uint32_t b_addr = a_addr + A_STAGE_BYTES;
 #pragma unroll
@@ -585,10 +541,6 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
                             ptx::umma_f16_ss_pair(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
                         else
                             ptx::umma_f16_ss(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
-#ifdef KLAS_UMMA_PROFILE
-                        if (kk == 0) prof_mma0 += (unsigned long long)(clock64() - prof_i0);
-                        if (kk == 3) prof_mma3 = prof_mma3 - (unsigned long long)prof_i0 + (unsigned long long)clock64();
-#endif
                     }
                     // free the shared-memory stage (in both CTAs) once these MMAs retire
                     if constexpr (PAIR) {
@@ -599,9 +551,6 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
                         ptx::umma_commit(empty_bar(stage));
                         if (kb + 1 == p.num_kb) ptx::umma_commit(tfull_bar(acc));
                     }
-#ifdef KLAS_UMMA_PROFILE
-                    prof_acc1 += (unsigned long long)(clock64() - prof_i0);
-#endif
                 }
                 if (++stage == STAGES) {
                     stage = 0;
@@ -614,11 +563,6 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
             }
         }
         __syncwarp();
-        KLAS_PROF_STORE(1, prof_acc0);
-        KLAS_PROF_STORE(2, prof_acc2);
-        KLAS_PROF_STORE(6, prof_acc1);
-        KLAS_PROF_STORE(7, prof_mma0);
-        KLAS_PROF_STORE(4, prof_mma3);
     } else if (XFORM && warp >= 2 + NUM_EPI_WARPS) {
         // ------------------------------------------------------------ operand maps
         const uint32_t xw = warp - (2 + NUM_EPI_WARPS);
@@ -644,17 +588,11 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
         const OutT *const C = static_cast<const OutT *>(p.C);
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
-        KLAS_PROF_DECL;
-#ifdef KLAS_UMMA_PROFILE
-        const long long prof_start = clock64();
-#endif
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             uint32_t b, tm, tn;
             decode_tile(t, p, b, tm, tn);
             if (p.num_kb > 0) {
-                KLAS_PROF_BEGIN;
                 ok = lane != 0 || bounded_wait(tfull_bar(acc), acc_phase, ctl, SITE_EPI_TMEM_FULL, WAIT_LIMIT_NS, 128);
-                KLAS_PROF_END(prof_acc0);
                 ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;   // lane 0 polls, the warp follows
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
@@ -695,12 +633,6 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
                 }
             }
         }
-#ifdef KLAS_UMMA_PROFILE
-        if (warp == 2) {
-            KLAS_PROF_STORE(3, prof_acc0);
-            KLAS_PROF_STORE(5, (unsigned long long)(clock64() - prof_start));
-        }
-#endif
     }
 
     // ---------------------------------------------------------------- teardown
@@ -872,27 +804,19 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
         const uint32_t b_kstep = p.b_row_major ? UMMA_K * 128u : UMMA_K * 2u;
         uint32_t stage = 0, phase = 0, tile_phase = 0;
         bool ok = lane == 0 && cta_rank == 0;
-        KLAS_PROF_DECL;
-#ifdef KLAS_UMMA_PROFILE
-        const long long prof_start = clock64();
-#endif
         for (uint32_t t = group; ok && p.num_kb > 0 && t < p.num_tiles; t += num_groups) {
             // both CTAs' epilogues must have drained the previous tile's accumulators
             {
-                KLAS_PROF_BEGIN;
                 ok = bounded_wait(tempty_bar, tile_phase ^ 1u, ctl, SITE_WIDE | SITE_MMA_TMEM_EMPTY);
-                KLAS_PROF_END(prof_acc2);
             }
             if (!ok) break;
             ptx::tc_fence_after_sync();
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 {
-                    KLAS_PROF_BEGIN;
                     if constexpr (XFORM)
                         ok = bounded_wait<true>(xfull_bar(stage), phase, ctl, SITE_WIDE | SITE_MMA_FULL);
                     else
                         ok = bounded_wait(full_bar(stage), phase, ctl, SITE_WIDE | SITE_MMA_FULL);
-                    KLAS_PROF_END(prof_acc0);
                 }
                 if (!ok) break;
                 const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
@@ -918,13 +842,6 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
             }
             tile_phase ^= 1u;
         }
-#ifdef KLAS_UMMA_PROFILE
-        if (lane == 0 && cta_rank == 0 && blockIdx.x < 1024) {
-            g_umma_prof[blockIdx.x][1] = prof_acc0;
-            g_umma_prof[blockIdx.x][2] = prof_acc2;
-            g_umma_prof[blockIdx.x][5] = (unsigned long long)(clock64() - prof_start);
-        }
-#endif
         __syncwarp();
     } else if (XFORM && warp >= 2 + EPI_WARPS) {
         // ------------------------------------------------------------ operand maps (4 warps per CTA)
@@ -932,12 +849,11 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
         const uint32_t xfull_cta0 = ptx::map_to_cta(xfull_bar(0), 0);
         uint32_t stage = 0, phase = 0, turn = 0;
         bool ok = true;
-        unsigned long long xprof[3] = {0, 0, 0};
         for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 if (turn == xw)
                     ok = xform_stage(p, full_bar(stage), phase, ctl, SITE_WIDE | SITE_XFORM_FULL,
-                                     smem_base + stage * STAGE_BYTES, A_BYTES, B_BYTES, xfull_cta0 + 8u * stage, lane, xprof);
+                                     smem_base + stage * STAGE_BYTES, A_BYTES, B_BYTES, xfull_cta0 + 8u * stage, lane);
                 if (!ok) break;
                 if (++turn == XFORM_WARPS) turn = 0;
                 if (++stage == STAGES) {
@@ -946,13 +862,6 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
                 }
             }
         }
-#ifdef KLAS_UMMA_PROFILE
-        if (xw == 0 && lane == 0 && blockIdx.x < 1024) {
-            g_umma_prof[blockIdx.x][3] = xprof[0];
-            g_umma_prof[blockIdx.x][4] = xprof[1];
-            g_umma_prof[blockIdx.x][6] = xprof[2];
-        }
-#endif
     } else {
         // ------------------------------------------------------------ epilogue (8 warps)
         // Warps 2-5 drain accumulator half 0, warps 6-9 half 1; within a group warp w owns the
@@ -1229,16 +1138,6 @@ static int launch_wide_mode(int out_dtype, const CUtensorMap &ta, const CUtensor
 
 }  // namespace umma
 
-#ifdef KLAS_UMMA_PROFILE
-extern "C" int klas_dev_zero_umma_profile() {
-    void *ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, umma::g_umma_prof) != cudaSuccess) return 1;
-    return cudaMemset(ptr, 0, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? 0 : 1;
-}
-extern "C" int klas_dev_read_umma_profile(unsigned long long *out) {
-    return cudaMemcpyFromSymbol(out, umma::g_umma_prof, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 int umma_ensure_host_flag();
 

@@ -190,3 +190,32 @@ def test_compensated_f32_keeps_what_cancellation_destroys():
     assert torch.equal(named.cpu(), want)
     plain = klas.gemm(A.cuda(), B.cuda()).cpu()
     assert float((plain - want).abs().max()) > 1.0     # the uncompensated f32 sum really does lose them
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (512, 384, 2048), (128, 64, 512)])
+def test_two_ctas_per_tile_along_k(oracle, m, n, k):
+    """One part-filled wave of tiles is run with two CTAs per tile, each summing half of K and adding
+    its half onto a zeroed C.  Against the oracle (f32, 1e-5), equal from call to call (two addends:
+    no order dependence), and for wrapping integers bit-equal to the unsplit kernel."""
+    A, B = synth.gemm_f32(0, m, n, k, device="cuda")
+    try:
+        klas.debug_set("simt_split_k", 1)
+        whole = klas.gemm(A, B)
+        klas.debug_set("simt_split_k", 2)
+        split1 = klas.gemm(A, B)
+        split2 = klas.gemm(A, B, torch.full((m, n), 7.0, device="cuda"))   # whatever C held before is gone
+        klas.debug_set("simt_split_k", "auto")
+        auto = klas.gemm(A, B)
+        ua, ub = synth.gemm_u64(3, m, n, k, full_range=True, device="cuda")
+        klas.debug_set("simt_split_k", 1)
+        uw = klas.gemm(ua, ub)
+        klas.debug_set("simt_split_k", 2)
+        us = klas.gemm(ua, ub)
+    finally:
+        klas.debug_set("simt_split_k", "auto")
+    acc = oracle.acc(A.cpu().numpy(), B.cpu().numpy())
+    scale = oracle.absacc(A.cpu().numpy(), B.cpu().numpy())
+    for got in (whole, split1, auto):
+        assert rel_err_componentwise(got.cpu().numpy(), acc, scale) <= TOL_F32
+    assert torch.equal(split1, split2)
+    assert torch.equal(uw, us)
