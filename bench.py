@@ -221,6 +221,28 @@ class GemmBf16(Workload):
         return 2.0 * rows * self.N * self.K
 
 
+class CublasBf16(GemmBf16):
+    """COMPARISON ONLY: the headline product through cuBLAS (torch.mm with f32 output) on the same
+    inputs, so that a profiler can capture the vendor kernel with the same command line.  Nothing of
+    this library runs in its launch; its line reports gpu_launches = 0."""
+    name, metric = "cublas_bf16", "cublas_bf16_gemm_tflops_comparison_only"
+    launches_per_step = 0
+
+    def launch(self):
+        t = self.torch
+        try:
+            self.D = t.mm(self.A, self.Bt.t(), out_dtype=t.float32)
+        except TypeError:
+            self.D = t.mm(self.A, self.Bt.t()).float()
+
+    def e2e_step(self):
+        hA, hB = self.A.cpu().pin_memory(), self.Bt.cpu().pin_memory()
+        self.A.copy_(hA, non_blocking=True)
+        self.Bt.copy_(hB, non_blocking=True)
+        self.launch()
+        return float(self.D.cpu()[0, 0])
+
+
 class GemmF16Batched(Workload):
     name, metric, unit, dtype, bound = "gemm_f16b", "f16_batched_gemm_tflops", "TFLOP/s", "f16", "tensor"
 
@@ -488,6 +510,8 @@ def make_workload(name, rank, world, device, args=None):
         return Softmax(rank, world, device, args.softmax_log2n if args else 28)
     if name == "gemm_bf16":
         return GemmBf16(rank, world, device)
+    if name == "cublas_bf16":
+        return CublasBf16(rank, world, device)
     if name == "gemm_f16b":
         return GemmF16Batched(rank, world, device)
     if name == "gemm_u64":
@@ -1033,6 +1057,8 @@ def main():
                     help="gemm_bf16 through the multi-GPU C entry points: one process drives --gpus devices (no torchrun)")
     ap.add_argument("--no-numa-bind", action="store_true",
                     help="do not bind this rank's host thread and pinned buffers to the NUMA node of its GPU")
+    ap.add_argument("--tc-mode", default="auto", choices=["auto", "single", "narrow", "pair", "wide"],
+                    help="force one tile shape of the tensor-core kernel (profiler captures of the variants)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--attention-heads", type=int, default=256,
                     help="attention_f16 only: heads per GPU (256 is the bench size; fewer for profiler captures)")
@@ -1064,6 +1090,8 @@ def main():
     if not args.no_numa_bind:
         numa["bound"] = _lib.load().klas_b200_host_bind_near_device() == _lib.OK
 
+    if args.tc_mode != "auto":
+        klas.debug_set("tc_mode", args.tc_mode)
     wl = make_workload(args.workload, rank, world, device, args)
     warm = max(args.warmup, 3)
     for _ in range(warm):

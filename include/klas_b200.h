@@ -533,6 +533,7 @@ int klas_b200_mg_spmm(klas_mg_context *ctx, int dtype, const uint32_t *row_bound
  *                        (two when one part-filled wave of tiles would leave each SM with one CTA), 1 never, 2 whenever legal
  *   KLAS_KNOB_F64_MODE   0 library's choice, 1 keep fp64 products on the CUDA-core kernel
  *   KLAS_KNOB_SIMT_TILE  CUDA-core tile of 4-byte types: -1 library's choice, 0 64x64, 1 128x64, 2 128x128
+ *   KLAS_KNOB_SPMM_SLAB  columns per slab of the SpMM kernel: 0 library's choice, 32, 64 or 128
  *   KLAS_KNOB_HOST_GRID  blocks per side of the 2-D schedule of klas_b200_gemm_tc_host: -1 default (4),
  *                        0 row blocks only, 1..16
  * Returns KLAS_ERR_INVALID for an unknown knob or a value outside its range.  klas_b200_debug_get
@@ -545,7 +546,8 @@ typedef enum klas_knob_e {
     KLAS_KNOB_F64_MODE = 3,
     KLAS_KNOB_SIMT_TILE = 4,
     KLAS_KNOB_HOST_GRID = 5,
-    KLAS_KNOB_COUNT = 6
+    KLAS_KNOB_SPMM_SLAB = 6,
+    KLAS_KNOB_COUNT = 7
 } klas_knob;
 int klas_b200_debug_set(int knob, int value);
 int klas_b200_debug_get(int knob);

@@ -29,9 +29,9 @@ int fail(int code, const char *fmt, ...) {
 void clear_error() { tls_error[0] = '\0'; }
 
 // tuning knobs (klas_knob): defaults = the library's own choice
-static std::atomic<int> g_knobs[KLAS_KNOB_COUNT] = {{0}, {0}, {0}, {0}, {-1}, {-1}};
+static std::atomic<int> g_knobs[KLAS_KNOB_COUNT] = {{0}, {0}, {0}, {0}, {-1}, {-1}, {0}};
 struct KnobRange { int lo, hi; };
-static const KnobRange g_knob_range[KLAS_KNOB_COUNT] = {{0, 4}, {0, 1024}, {0, 2}, {0, 1}, {-1, 2}, {-1, 16}};
+static const KnobRange g_knob_range[KLAS_KNOB_COUNT] = {{0, 4}, {0, 1024}, {0, 2}, {0, 1}, {-1, 2}, {-1, 16}, {0, 128}};
 
 int debug_knob(int knob) {
     return knob >= 0 && knob < KLAS_KNOB_COUNT ? g_knobs[knob].load(std::memory_order_relaxed) : INT_MIN;

@@ -107,6 +107,7 @@ struct Problem {
     int map_a, map_b, comb;
     bool hooks;   // any map or a combine rule other than overwrite / axpby
     bool wide_acc = false;   // f32 storage, f64 arithmetic: the compensated-sum entry points
+    bool split_k = false;    // the tile was chosen so that two CTAs per tile along K fill the machine
 };
 
 template <typename T>
@@ -479,16 +480,15 @@ static int launch_cfg(const Problem &q, T alpha, T beta, int scaled, const void 
     if constexpr (sizeof(S) == sizeof(T)) {
         if (fast) {
             if (q.hooks) return launch_kernel<S, T, BM, BN, BK, true, true>(a, unsigned(blocks), stream);
-            // One part-filled wave of tiles (f32 1024^3: 128 tiles of 128 x 64 on 148 SMs, eight warps
-            // per SM): two CTAs per tile, each summing half of K, put sixteen warps on an SM and hide
-            // the shared-memory latency the single CTA cannot.  The halves are added atomically onto
-            // a zeroed C -- two addends, so the result does not depend on their order; it differs
-            // from the unsplit sum by one rounding (integers: not at all).
+            // Fewer tiles than half the SMs (the caller picked the tile for this): two CTAs per tile,
+            // each summing half of K.  The halves are added atomically onto a zeroed C -- two addends,
+            // so the result does not depend on their order; it differs from the unsplit sum by one
+            // rounding (integers: not at all).
             DeviceInfo info;
             if (int rc = device_info(&info)) return rc;
             const int knob = debug_knob(KLAS_KNOB_SIMT_SPLIT_K);
             const bool can_split = !scaled && q.comb == KLAS_COMB_NEW && q.batch == 1 && q.k % (2 * BK) == 0 && q.k >= 8 * BK;
-            const bool want_split = knob == 2 || (knob == 0 && blocks <= uint64_t(info.sm_count) && q.k >= 512);
+            const bool want_split = knob == 2 || (knob == 0 && q.split_k && 2 * blocks <= uint64_t(info.sm_count));
             if (can_split && want_split) {
                 a.ksplits = 2;
                 a.k_chunk = q.k / 2;
@@ -515,10 +515,25 @@ static int launch_type(const Problem &q, T alpha, T beta, int scaled, const void
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 127) / 128) * batch;
         const uint64_t mid_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
         int pick = big_tiles * 10 >= uint64_t(sm_count) * 6 ? 2 : (mid_tiles * 10 >= uint64_t(sm_count) * 8 ? 1 : 0);
+        // A small output with a long K is better served by the larger tiles (8 x 8 per thread:
+        // fewer shared-memory bytes per multiply-add) run as two CTAs per tile along K than by
+        // small tiles: the smallest of the two larger tiles that still leaves room for the second
+        // CTA of every tile.  Measured, f32: 1024^3 59.6 -> 57.5 us, 1024 x 1024 x 4096 227 -> 195,
+        // 768 x 768 x 2048 77.8 -> 66.5.
+        Problem qs = q;
+        if (q.k >= 512 && q.batch == 1 && !q.hooks && !scaled && debug_knob(KLAS_KNOB_SIMT_SPLIT_K) != 1) {
+            if (2 * mid_tiles <= uint64_t(sm_count)) {
+                pick = 1;
+                qs.split_k = true;
+            } else if (2 * big_tiles <= uint64_t(sm_count)) {
+                pick = 2;
+                qs.split_k = true;
+            }
+        }
         if (const int t = debug_knob(KLAS_KNOB_SIMT_TILE); t >= 0) pick = t;
-        if (pick == 2) return launch_cfg<S, T, 128, 128, 16>(q, alpha, beta, scaled, A, B, C, stream);
-        if (pick == 1) return launch_cfg<S, T, 128, 64, 32>(q, alpha, beta, scaled, A, B, C, stream);
-        return launch_cfg<S, T, 64, 64, 32>(q, alpha, beta, scaled, A, B, C, stream);
+        if (pick == 2) return launch_cfg<S, T, 128, 128, 16>(qs, alpha, beta, scaled, A, B, C, stream);
+        if (pick == 1) return launch_cfg<S, T, 128, 64, 32>(qs, alpha, beta, scaled, A, B, C, stream);
+        return launch_cfg<S, T, 64, 64, 32>(qs, alpha, beta, scaled, A, B, C, stream);
     } else {
         const uint64_t big_tiles = ((m + 127) / 128) * ((n + 63) / 64) * batch;
         if (big_tiles >= uint64_t(sm_count)) return launch_cfg<S, T, 128, 64, KLAS_SIMT_BK8>(q, alpha, beta, scaled, A, B, C, stream);

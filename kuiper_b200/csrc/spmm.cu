@@ -58,7 +58,11 @@ constexpr int WARPS_PER_BLOCK = 8;
 #ifndef KLAS_SPMM_UNROLL
 #define KLAS_SPMM_UNROLL 8
 #endif
-constexpr int UNROLL = KLAS_SPMM_UNROLL;   // gathers in flight per lane
+constexpr int UNROLL = KLAS_SPMM_UNROLL;   // gathers in flight per lane (16-byte pieces; twice as many 8-byte ones)
+// gathers in flight per lane by piece size: 8 pieces of 16 bytes (slabs of 128 columns) or 16 of
+// 8 bytes (slabs of 64 columns: the same bytes in flight, a slab of B half as large)
+template <int VEC>
+constexpr int UNR = VEC == 2 ? 2 * UNROLL : UNROLL;
 #ifndef KLAS_SPMM_MIN_BLOCKS
 #define KLAS_SPMM_MIN_BLOCKS 4
 #endif
@@ -141,12 +145,16 @@ __device__ __forceinline__ void put_row(T *dst, const Pack<T, VEC> &acc, bool ad
         uint4 w;
         memcpy(&w, &acc, 16);
         __stcs(reinterpret_cast<uint4 *>(dst), w);
+    } else if constexpr (VEC == 2) {
+        uint2 w;
+        memcpy(&w, &acc, 8);
+        __stcs(reinterpret_cast<uint2 *>(dst), w);
     } else {
         __stcs(dst, acc.v[0]);
     }
 }
 
-// One 16-byte (VEC = 4) or 4-byte piece of row c of B: `Bbytes` points at this lane's columns of
+// One 16-byte (VEC = 4), 8-byte (VEC = 2) or 4-byte piece of row c of B: `Bbytes` points at this lane's columns of
 // row 0, rows are `row_bytes` apart (one multiply-add with a 64-bit addend forms the address).
 template <typename T, int VEC>
 __device__ __forceinline__ Pack<T, VEC> gather(const char *Bbytes, uint32_t c, uint32_t row_bytes) {
@@ -155,6 +163,9 @@ __device__ __forceinline__ Pack<T, VEC> gather(const char *Bbytes, uint32_t c, u
     if constexpr (VEC == 4) {
         const uint4 w = __ldg(reinterpret_cast<const uint4 *>(p));
         memcpy(&r, &w, 16);
+    } else if constexpr (VEC == 2) {
+        const uint2 w = __ldg(reinterpret_cast<const uint2 *>(p));
+        memcpy(&r, &w, 8);
     } else {
         r.v[0] = __ldg(reinterpret_cast<const T *>(p));
     }
@@ -200,30 +211,33 @@ __device__ __forceinline__ void flush_finished_rows(Stream<T, VEC> &st, const ui
 // does -- so the bulky row-end sequence exists once.  (Written out after each of the eight
 // products it took the kernel from under 70 to over 110 registers; moved out of line it put the
 // gathered pieces in local memory.)
+__device__ __forceinline__ uint32_t word_of(const uint4 &q, int i) { return i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w; }
+
 template <typename T, int VEC, bool FULL>
-__device__ __forceinline__ void batch(Stream<T, VEC> &st, uint32_t nb, const uint32_t *cols8, const T *vals8,
+__device__ __forceinline__ void batch(Stream<T, VEC> &st, uint32_t nb, const uint32_t *cols_n, const T *vals_n,
                                       const char *Bbytes, uint32_t row_bytes, const uint32_t *__restrict__ row_off,
                                       uint32_t rows, uint32_t cols, uint32_t *ends, T *Cc, bool active, uint32_t lane) {
-    static_assert(UNROLL == 8, "columns and values are read in two groups of four");
-    Pack<T, VEC> bv[UNROLL];
-    {
-        const uint4 c0 = *reinterpret_cast<const uint4 *>(cols8);
-        const uint4 c1 = *reinterpret_cast<const uint4 *>(cols8 + 4);
-        const uint32_t cs[UNROLL] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    constexpr int N = UNR<VEC>;
+    static_assert(N % 4 == 0, "columns and values are read back four at a time");
+    Pack<T, VEC> bv[N];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
-            if (FULL || uint32_t(u) < nb) bv[u] = gather<T, VEC>(Bbytes, cs[u], row_bytes);
+    for (int g = 0; g < N / 4; ++g) {
+        const uint4 c = *reinterpret_cast<const uint4 *>(cols_n + 4 * g);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (FULL || uint32_t(4 * g + q) < nb) bv[4 * g + q] = gather<T, VEC>(Bbytes, word_of(c, q), row_bytes);
     }
-    const uint4 v0 = *reinterpret_cast<const uint4 *>(vals8);
-    const uint4 v1 = *reinterpret_cast<const uint4 *>(vals8 + 4);
-    const T vs[UNROLL] = {bits_as<T>(v0.x), bits_as<T>(v0.y), bits_as<T>(v0.z), bits_as<T>(v0.w),
-                          bits_as<T>(v1.x), bits_as<T>(v1.y), bits_as<T>(v1.z), bits_as<T>(v1.w)};
-    if (FULL && st.rend - st.p > UNROLL) {   // no row ends inside this batch
+    if (FULL && st.rend - st.p > uint32_t(N)) {   // no row ends inside this batch
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
+        for (int g = 0; g < N / 4; ++g) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(vals_n + 4 * g);
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) st.acc.v[e] = mul_add<T>(vs[u], bv[u].v[e], st.acc.v[e]);
-        st.p += UNROLL;
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e)
+                    st.acc.v[e] = mul_add<T>(bits_as<T>(word_of(v, q)), bv[4 * g + q].v[e], st.acc.v[e]);
+        }
+        st.p += N;
         return;
     }
     uint32_t done = 0;
@@ -231,11 +245,16 @@ __device__ __forceinline__ void batch(Stream<T, VEC> &st, uint32_t nb, const uin
         const uint32_t left = nb - done, in_row = st.rend - st.p;
         const uint32_t seg = left < in_row ? left : in_row;   // nonzeros [done, done + seg) finish or stay inside the row
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
-            if (uint32_t(u) - done < seg) {
+        for (int g = 0; g < N / 4; ++g) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(vals_n + 4 * g);
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) st.acc.v[e] = mul_add<T>(vs[u], bv[u].v[e], st.acc.v[e]);
-            }
+            for (int q = 0; q < 4; ++q)
+                if (uint32_t(4 * g + q) - done < seg) {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e)
+                        st.acc.v[e] = mul_add<T>(bits_as<T>(word_of(v, q)), bv[4 * g + q].v[e], st.acc.v[e]);
+                }
+        }
         done += seg;
         st.p += seg;
         if (st.p == st.rend) flush_finished_rows<T, VEC>(st, row_off, rows, cols, ends, Cc, active, lane);
@@ -337,8 +356,8 @@ __global__ void __launch_bounds__(WARPS_PER_BLOCK * 32, MIN_BLOCKS) spmm_kernel(
             const uint32_t cnt = min(32u, pe - base);
             uint32_t j0 = 0;
 #pragma unroll 1
-            for (; j0 + UNROLL <= cnt; j0 += UNROLL)
-                batch<T, VEC, true>(st, UNROLL, my_cols + j0, my_vals + j0, Bbytes, row_bytes, row_off, a.rows, a.cols,
+            for (; j0 + UNR<VEC> <= cnt; j0 += UNR<VEC>)
+                batch<T, VEC, true>(st, UNR<VEC>, my_cols + j0, my_vals + j0, Bbytes, row_bytes, row_off, a.rows, a.cols,
                                     my_ends, Cc, active, lane);
             if (j0 < cnt)
                 batch<T, VEC, false>(st, cnt - j0, my_cols + j0, my_vals + j0, Bbytes, row_bytes, row_off, a.rows, a.cols,
@@ -370,43 +389,47 @@ __global__ void __launch_bounds__(256) zero_long_rows_kernel(const uint32_t *__r
 // the column-index stream once per slab of 128 columns and reads the 512-byte pieces of B's rows
 // in batches of eight.  No values, no products, no C.  What this reaches is the rate the memory
 // system delivers such gathers at, i.e. the ceiling the SpMM kernel is measured against.
+template <int VEC>
 __global__ void __launch_bounds__(WARPS_PER_BLOCK * 32, MIN_BLOCKS)
 gather_probe_kernel(const uint32_t *__restrict__ col_ind, uint32_t nnz, const float *__restrict__ B, uint32_t cols,
                     uint32_t slabs, uint32_t per_warp, uint32_t *sink) {
+    constexpr int N = UNR<VEC>;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warp = blockIdx.x * WARPS_PER_BLOCK + (threadIdx.x >> 5);
-    uint32_t x0 = 0, x1 = 0, x2 = 0, x3 = 0;
+    const uint32_t row_bytes = cols * 4u;
+    uint32_t x = 0;
     for (uint32_t slab = 0; slab < slabs; ++slab) {
         const uint64_t b64 = uint64_t(warp) * per_warp;
         const uint32_t begin = b64 < nnz ? uint32_t(b64) : nnz;
         const uint32_t end = nnz - begin < per_warp ? nnz : begin + per_warp;
-        const uint32_t col = slab * 128 + lane * 4;
-        const float *Bc = B + (col < cols ? col : 0);
+        const uint32_t col = slab * (32 * VEC) + lane * VEC;
+        const char *Bbytes = reinterpret_cast<const char *>(B + (col < cols ? col : 0));
         uint32_t nxt = begin + lane < end ? col_ind[begin + lane] : 0u;
         for (uint32_t base = begin; base < end; base += 32) {
             const uint32_t my_col = nxt;
             if (base + 32 + lane < end) nxt = col_ind[base + 32 + lane];
             const uint32_t cnt = min(32u, end - base);
 #pragma unroll
-            for (int j0 = 0; j0 < 32; j0 += UNROLL) {
+            for (int j0 = 0; j0 < 32; j0 += N) {
                 if (uint32_t(j0) < cnt) {
-                    uint4 bv[UNROLL];
+                    Pack<float, VEC> bv[N];
 #pragma unroll
-                    for (int u = 0; u < UNROLL; ++u) {
+                    for (int u = 0; u < N; ++u) {
                         const uint32_t c = __shfl_sync(0xffffffffu, my_col, j0 + u);
-                        bv[u] = make_uint4(0, 0, 0, 0);
-                        if (uint32_t(j0 + u) < cnt) bv[u] = __ldg(reinterpret_cast<const uint4 *>(Bc + size_t(c) * cols));
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) bv[u].v[e] = 0.f;
+                        if (uint32_t(j0 + u) < cnt) bv[u] = gather<float, VEC>(Bbytes, c, row_bytes);
                     }
 #pragma unroll
-                    for (int u = 0; u < UNROLL; ++u) {
-                        x0 ^= bv[u].x; x1 ^= bv[u].y; x2 ^= bv[u].z; x3 ^= bv[u].w;
-                    }
+                    for (int u = 0; u < N; ++u)
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) x ^= __float_as_uint(bv[u].v[e]) + uint32_t(e);
                 }
             }
         }
     }
     // keeps the loads alive; the comparison is not expected to hold
-    if (x0 == 0x12345678u && x1 == 0x9abcdef0u && x2 == 0x0fedcba9u && x3 == 0x87654321u && sink) *sink = warp;
+    if (x == 0x12345678u && sink) *sink = warp;
 }
 
 static int persistent_grid(const void *kernel, int *blocks) {
@@ -419,16 +442,34 @@ static int persistent_grid(const void *kernel, int *blocks) {
     return KLAS_OK;
 }
 
+// Elements per gathered piece: 4 (slabs of 128 columns), 2 (slabs of 64) or 1 (slabs of 32; any
+// cols and alignment).  Slabs of 128 move the fewest instructions per byte; once the part of B a
+// slab touches (shared x 512 bytes) no longer fits the half of L2 that data read by every SM can
+// use, slabs of 64 keep it resident at the price of streaming the CSR arrays twice as often.
+static int piece_elems(uint32_t shared, uint32_t cols, const void *B, const void *C) {
+    const uintptr_t both = reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C);
+    const bool can4 = cols % 4 == 0 && (both & 15u) == 0, can2 = cols % 2 == 0 && (both & 7u) == 0;
+    const int knob = debug_knob(KLAS_KNOB_SPMM_SLAB);
+    if (knob == 128 && can4) return 4;
+    if (knob == 64 && can2) return 2;
+    if (knob == 32) return 1;
+    if (!can4) return can2 && cols > 32 ? 2 : 1;
+    DeviceInfo info;
+    if (device_info(&info)) return 4;
+    const uint64_t slab_bytes = uint64_t(shared) * 512u;
+    return cols > 64 && slab_bytes > uint64_t(info.l2_bytes) * 3 / 8 ? 2 : 4;
+}
+
 template <typename T>
-static int launch_t(const Args &base, cudaStream_t stream) {
+static int launch_t(const Args &base, uint32_t shared, cudaStream_t stream) {
     Args a = base;
-    const bool vec4 = a.cols % 4 == 0 &&
-                      ((reinterpret_cast<uintptr_t>(a.B) | reinterpret_cast<uintptr_t>(a.C)) & 15u) == 0;
-    const uint32_t slab_cols = vec4 ? 128u : 32u;
+    const int vec = piece_elems(shared, a.cols, a.B, a.C);
+    const uint32_t slab_cols = 32u * uint32_t(vec);
     a.slabs = (a.cols + slab_cols - 1) / slab_cols;
     int blocks = 0;
-    if (int rc = persistent_grid(vec4 ? reinterpret_cast<const void *>(spmm_kernel<T, 4>)
-                                      : reinterpret_cast<const void *>(spmm_kernel<T, 1>), &blocks))
+    if (int rc = persistent_grid(vec == 4   ? reinterpret_cast<const void *>(spmm_kernel<T, 4>)
+                                 : vec == 2 ? reinterpret_cast<const void *>(spmm_kernel<T, 2>)
+                                            : reinterpret_cast<const void *>(spmm_kernel<T, 1>), &blocks))
         return rc;
     const uint64_t total = uint64_t(a.nnz) + a.rows;
     // about RANGES_PER_WARP ranges per resident warp and slab, but no range shorter than MIN_RANGE keys
@@ -450,8 +491,10 @@ static int launch_t(const Args &base, cudaStream_t stream) {
         zero_long_rows_kernel<T><<<zb, 256, 0, stream>>>(a.row_off, a.rows, a.cols, a.long_row, static_cast<T *>(a.C));
         KLAS_TRY_CUDA(cudaGetLastError());
     }
-    if (vec4)
+    if (vec == 4)
         spmm_kernel<T, 4><<<grid, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
+    else if (vec == 2)
+        spmm_kernel<T, 2><<<grid, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
     else
         spmm_kernel<T, 1><<<grid, WARPS_PER_BLOCK * 32, 0, stream>>>(a);
     return check_cuda(cudaGetLastError(), "spmm_kernel launch");
@@ -478,23 +521,26 @@ int launch_spmm(int dtype, uint32_t rows, uint32_t shared, uint32_t cols, uint32
     a.rows = rows;
     a.cols = cols;
     a.nnz = nnz;
-    (void)shared;
-    return dtype == KLAS_F32 ? spmm::launch_t<float>(a, stream) : spmm::launch_t<uint32_t>(a, stream);
+    return dtype == KLAS_F32 ? spmm::launch_t<float>(a, shared, stream) : spmm::launch_t<uint32_t>(a, shared, stream);
 }
 
 int launch_spmm_gather_probe(uint32_t shared, uint32_t cols, uint32_t nnz, const uint32_t *col_ind, const float *B,
                              cudaStream_t stream) {
     if (nnz == 0 || cols == 0) return KLAS_OK;
     if (!col_ind || !B) return fail(KLAS_ERR_INVALID, "gather_probe: null col_ind or B");
-    if (cols % 4 || (reinterpret_cast<uintptr_t>(B) & 15u))
-        return fail(KLAS_ERR_UNSUPPORTED, "gather_probe: cols must be a multiple of 4 and B 16-byte aligned");
-    (void)shared;
+    const int vec = spmm::piece_elems(shared, cols, B, B);   // the piece size klas_b200_spmm would use
+    if (vec == 1) return fail(KLAS_ERR_UNSUPPORTED, "gather_probe: cols must be even and B 8-byte aligned");
     int blocks = 0;
-    if (int rc = spmm::persistent_grid(reinterpret_cast<const void *>(spmm::gather_probe_kernel), &blocks)) return rc;
+    if (int rc = spmm::persistent_grid(vec == 4 ? reinterpret_cast<const void *>(spmm::gather_probe_kernel<4>)
+                                                : reinterpret_cast<const void *>(spmm::gather_probe_kernel<2>), &blocks))
+        return rc;
     const uint32_t warps = uint32_t(blocks) * spmm::WARPS_PER_BLOCK;
     const uint32_t per_warp = (nnz + warps - 1) / warps;
-    spmm::gather_probe_kernel<<<blocks, spmm::WARPS_PER_BLOCK * 32, 0, stream>>>(col_ind, nnz, B, cols, (cols + 127) / 128,
-                                                                               per_warp, nullptr);
+    const uint32_t slabs = (cols + 32u * vec - 1) / (32u * vec);
+    if (vec == 4)
+        spmm::gather_probe_kernel<4><<<blocks, spmm::WARPS_PER_BLOCK * 32, 0, stream>>>(col_ind, nnz, B, cols, slabs, per_warp, nullptr);
+    else
+        spmm::gather_probe_kernel<2><<<blocks, spmm::WARPS_PER_BLOCK * 32, 0, stream>>>(col_ind, nnz, B, cols, slabs, per_warp, nullptr);
     return check_cuda(cudaGetLastError(), "gather_probe_kernel launch");
 }
 
