@@ -1270,12 +1270,15 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     // pairs with 512 x 256 tiles, whichever a wave count x tile cost estimate makes fastest.  The
     // kernels are persistent with a static round-robin of tiles, so a launch takes
     // ceil(tiles / slots) rounds; per round a wide tile costs twice a 256 x 256 one, less what it
-    // saves by sharing operands (relative rates measured at 8192^3: wide 1408, pair 1160, single
-    // 1144 TFLOP/s).  Examples the estimate gets right where "wide once it fills the machine"
+    // saves by sharing operands.  The relative rates are the 8192^3 row of the tuning run
+    // `python -m kuiper_b200.tune_tc` (TFLOP/s of each tile shape where all of them fill the
+    // machine); re-run it and update the three constants when a kernel changes.
+    // Examples the estimate gets right where "wide once it fills the machine"
     // did not: 3072^3 (72 wide tiles, one round: 1324 against 1120 TFLOP/s for two rounds of pairs),
     // 3584 x 3072 (84 wide tiles would take two rounds; pairs: 1049 against 910), 2048^2 (one
     // round of 128 single tiles: 720 against 488 for 32 wide tiles on 74 pairs).
-    // KLAS_TC_MODE=single|pair|wide overrides the choice.
+    // The KLAS_KNOB_TC_MODE knob overrides the choice.
+    constexpr double RATE_SINGLE = 1144.0, RATE_PAIR = 1160.0, RATE_WIDE = 1408.0, NARROW_COST = 0.55;
     const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
     const uint64_t pair_tiles = ((rows + 2 * BM - 1) / (2 * BM)) * ((cols + BN - 1) / BN) * batch;
     const uint64_t wide_tiles = ((rows + wide::TILE_M - 1) / wide::TILE_M) * ((cols + BN - 1) / BN) * batch;
@@ -1283,15 +1286,15 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     const uint64_t sms = uint64_t(info.sm_count), pairs = uint64_t(info.sm_count / 2);
     const double cost_single = double((single_tiles + sms - 1) / sms);
     const bool pair_ok = can_pair && rows > BM && single_tiles >= sms && !xform;   // the pair tile has no mapped form
-    const double cost_pair = pair_ok ? double((pair_tiles + pairs - 1) / pairs) * (1144.0 / 1160.0) : 1e30;
-    const double cost_wide = can_pair ? double((wide_tiles + pairs - 1) / pairs) * 2.0 * (1144.0 / 1408.0) : 1e30;
+    const double cost_pair = pair_ok ? double((pair_tiles + pairs - 1) / pairs) * (RATE_SINGLE / RATE_PAIR) : 1e30;
+    const double cost_wide = can_pair ? double((wide_tiles + pairs - 1) / pairs) * 2.0 * (RATE_SINGLE / RATE_WIDE) : 1e30;
     bool use_wide = can_pair && cost_wide < cost_single && cost_wide <= cost_pair;
     bool pair = pair_ok && !use_wide && cost_pair <= cost_single;
     // Small outputs: the single-CTA kernel with 128-column tiles puts twice as many CTAs to work
     // (1024^2: 64 tiles instead of 32 on 148 SMs); a narrow tile costs a little more than half a
     // full one (the A operand is read from shared memory once per 128 instead of 256 columns).
     const uint64_t narrow_tiles = ((rows + BM - 1) / BM) * ((cols + 127) / 128) * batch;
-    bool narrow = !use_wide && !pair && double((narrow_tiles + sms - 1) / sms) * 0.55 < cost_single;
+    bool narrow = !use_wide && !pair && double((narrow_tiles + sms - 1) / sms) * NARROW_COST < cost_single;
     switch (debug_knob(KLAS_KNOB_TC_MODE)) {   // a test or tuning run forcing one tile shape
         case 1: pair = use_wide = narrow = false; break;
         case 2: pair = use_wide = false; narrow = true; break;

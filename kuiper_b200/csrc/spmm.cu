@@ -443,9 +443,11 @@ static int persistent_grid(const void *kernel, int *blocks) {
 }
 
 // Elements per gathered piece: 4 (slabs of 128 columns), 2 (slabs of 64) or 1 (slabs of 32; any
-// cols and alignment).  Slabs of 128 move the fewest instructions per byte; once the part of B a
-// slab touches (shared x 512 bytes) no longer fits the half of L2 that data read by every SM can
-// use, slabs of 64 keep it resident at the price of streaming the CSR arrays twice as often.
+// cols and alignment).  Slabs of 128 move the fewest instructions per byte and win whenever B has
+// more than 64 columns -- also when a slab of B (shared x 512 bytes) outgrows L2: at 131072 rows
+// of B the 64-column form, whose slab does fit, measured 0.66 ms against 0.50 (it streams the CSR
+// arrays twice as often and issues twice the loads).  With 64 columns or fewer the narrower
+// piece keeps every lane busy (131072^2 x 64: 0.17 against 0.22 ms).
 static int piece_elems(uint32_t shared, uint32_t cols, const void *B, const void *C) {
     const uintptr_t both = reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C);
     const bool can4 = cols % 4 == 0 && (both & 15u) == 0, can2 = cols % 2 == 0 && (both & 7u) == 0;
@@ -453,11 +455,10 @@ static int piece_elems(uint32_t shared, uint32_t cols, const void *B, const void
     if (knob == 128 && can4) return 4;
     if (knob == 64 && can2) return 2;
     if (knob == 32) return 1;
-    if (!can4) return can2 && cols > 32 ? 2 : 1;
-    DeviceInfo info;
-    if (device_info(&info)) return 4;
-    const uint64_t slab_bytes = uint64_t(shared) * 512u;
-    return cols > 64 && slab_bytes > uint64_t(info.l2_bytes) * 3 / 8 ? 2 : 4;
+    (void)shared;
+    if (cols <= 32) return 1;
+    if (cols <= 64 || !can4) return can2 ? 2 : 1;
+    return 4;
 }
 
 template <typename T>

@@ -1,0 +1,70 @@
+"""Tuning run of the tensor-core GEMM's tile shapes (the counterpart of the reference's
+tuning/tune_tc2d.sh, which sweeps its 72 instances at 4096^3):
+
+    python -m kuiper_b200.tune_tc [--laps 20] [--json]
+
+For a grid of shapes it times every tile shape the library has (single-CTA 128 x 256 and 128 x 128,
+CTA pair 256 x 256, wide pair 512 x 256) and the library's own choice, bf16 -> f32 with column-major
+B, and prints TFLOP/s per shape and mode.  The 8192^3 row is where the relative rates RATE_SINGLE,
+RATE_PAIR and RATE_WIDE in csrc/gemm_umma.cu come from; the other rows show what the
+rounds-times-cost estimate built on them picks and what that costs against the best mode.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import klas, synth
+
+SHAPES = [(1024, 1024, 1024), (2048, 2048, 2048), (2560, 2048, 4096), (3072, 3072, 3072), (3584, 3072, 4096),
+          (4096, 4096, 4096), (8192, 8192, 8192), (8192, 1024, 8192), (1024, 8192, 8192), (8192, 8192, 512),
+          (1024, 1024, 4096), (16384, 4096, 4096)]
+MODES = ["single", "narrow", "pair", "wide", "auto"]
+
+
+def time_ms(fn, laps):
+    for _ in range(3):
+        fn()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(laps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / laps
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--laps", type=int, default=20)
+    ap.add_argument("--json", action="store_true")
+    a = ap.parse_args(argv)
+    rows = []
+    for m, n, k in SHAPES:
+        A, Bt = synth.gemm_bf16(1, m, n, k, b_col_major=True, device="cuda")
+        D = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        rec = {"rows": m, "cols": n, "shared": k}
+        for mode in MODES:
+            klas.debug_set("tc_mode", mode)
+            ms = time_ms(lambda: klas.gemm_tc(A, Bt, b_col_major=True, D=D), a.laps)
+            rec[mode] = 2.0 * m * n * k / ms / 1e9
+        klas.debug_set("tc_mode", "auto")
+        klas.gemm_tc_status()
+        best = max(MODES[:-1], key=lambda md: rec[md])
+        rec["best"], rec["auto_over_best"] = best, rec["auto"] / rec[best]
+        rows.append(rec)
+        del A, Bt, D
+    if a.json:
+        print(json.dumps(rows))
+    else:
+        print("%-22s %8s %8s %8s %8s %8s  %s" % ("rows x cols x shared", *MODES, "best (auto / best)"))
+        for r in rows:
+            print("%-22s %8.0f %8.0f %8.0f %8.0f %8.0f  %s (%.2f)" % ("%d x %d x %d" % (r["rows"], r["cols"], r["shared"]),
+                                                                      *(r[md] for md in MODES), r["best"], r["auto_over_best"]))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -173,19 +173,19 @@ def test_guards_raise():
 
 def test_compensated_f32_keeps_what_cancellation_destroys():
     """Klas_GEMM_Naive3 adds with Kahan's correction (dist/Klas_GEMM_Naive3.cu:17-30).  Rows built to
-    cancel -- huge terms of both signs around small ones -- lose the small terms in a plain f32 sum;
-    the compensated entry point (f64 accumulation of the exact products) must return the correctly
-    rounded f32 result, under the reference's name as well."""
+    cancel -- +3e7, a term of order 1, -3e7, another small term, ... -- lose the small terms in a
+    plain f32 sum (the running sum sits at 3e7, where f32 numbers are 2 apart, every other step);
+    the compensated entry point (f64 accumulation of the exact products) must return the sum of the
+    small terms to the last place, under the reference's name as well."""
     m, n, k = 65, 33, 4096
     g = torch.Generator().manual_seed(11)
-    small = torch.rand((m, k), generator=g) + 0.5
-    big = torch.where(torch.arange(k) % 2 == 0, torch.tensor(3.0e7), torch.tensor(-3.0e7)).repeat(m, 1)
-    A = (small + big).float()                 # alternating +-3e7, each carrying a term of order 1
+    A = torch.rand((m, k), generator=g) + 0.5
+    A[:, 0::4] = 3.0e7
+    A[:, 2::4] = -3.0e7
     B = torch.ones((k, n))
-    want = A.double() @ B.double()            # sums of about 4096: the big terms cancel pair by pair
-    ulp = 2.0 ** -11                          # spacing of f32 just above 4096
+    want = A.double() @ B.double()            # about 2048: the big terms cancel pair by pair
+    ulp = 2.0 ** -12                          # spacing of f32 between 2048 and 4096
     got = klas.gemm_compensated(A.cuda(), B.cuda()).cpu()
-    # an f64 sum in another order than torch's, rounded to f32 once: within one unit in the last place
     assert float((got.double() - want).abs().max()) <= ulp
     named = torch.zeros((m, n), device="cuda")
     klas.call("Klas_GEMM_Naive3_g_matmul_f32_rrr", m, n, k, A.cuda(), B.cuda(), named)
