@@ -527,13 +527,16 @@ int klas_b200_mg_spmm(klas_mg_context *ctx, int dtype, const uint32_t *row_bound
  * never reads the environment.
  *
  *   KLAS_KNOB_TC_MODE    tensor-core tile: 0 library's choice (default), 1 single-CTA 128x256,
- *                        2 single-CTA 128x128, 3 CTA pair 256x256, 4 wide pair 512x256
+ *                        2 single-CTA 128x128, 3 CTA pair 256x256, 4 wide pair 512x256,
+ *                        5 single-CTA 128x64
  *   KLAS_KNOB_TC_RASTER  tile columns swept together: 0 default (8), else 1..1024
  *   KLAS_KNOB_SIMT_SPLIT_K  CTAs per output tile along K in the CUDA-core kernel: 0 library's choice
  *                        (two when one part-filled wave of tiles would leave each SM with one CTA), 1 never, 2 whenever legal
  *   KLAS_KNOB_F64_MODE   0 library's choice, 1 keep fp64 products on the CUDA-core kernel
  *   KLAS_KNOB_SIMT_TILE  CUDA-core tile of 4-byte types: -1 library's choice, 0 64x64, 1 128x64, 2 128x128
  *   KLAS_KNOB_SPMM_SLAB  columns per slab of the SpMM kernel: 0 library's choice, 32, 64 or 128
+ *   KLAS_KNOB_TC_KSPLIT  parts a tile's K range is cut into (single-CTA and pair tiles): 0 library's choice,
+ *                        1 never, 2..8 that many where the shape allows it
  *   KLAS_KNOB_HOST_GRID  blocks per side of the 2-D schedule of klas_b200_gemm_tc_host: -1 default (4),
  *                        0 row blocks only, 1..16
  * Returns KLAS_ERR_INVALID for an unknown knob or a value outside its range.  klas_b200_debug_get
@@ -547,7 +550,8 @@ typedef enum klas_knob_e {
     KLAS_KNOB_SIMT_TILE = 4,
     KLAS_KNOB_HOST_GRID = 5,
     KLAS_KNOB_SPMM_SLAB = 6,
-    KLAS_KNOB_COUNT = 7
+    KLAS_KNOB_TC_KSPLIT = 7,
+    KLAS_KNOB_COUNT = 8
 } klas_knob;
 int klas_b200_debug_set(int knob, int value);
 int klas_b200_debug_get(int knob);

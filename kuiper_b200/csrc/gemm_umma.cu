@@ -57,6 +57,9 @@ constexpr uint32_t XFORM_WARPS = KLAS_XFORM_WARPS;   // extra warps of the kerne
 constexpr uint32_t XFORM_THREADS = XFORM_WARPS * 32;
 constexpr uint32_t XFULL_OFFSET = 192;    // byte offset of the "operands mapped" barriers in the barrier block
 constexpr uint32_t BARRIER_BYTES = 256;
+constexpr uint32_t MAX_STAGES = 8;        // barrier slots per ring (the 128 x 64 tile runs eight 24 KiB stages)
+constexpr uint32_t RING_BYTES = 192 * 1024;            // operand ring of every tile shape
+constexpr uint32_t EPI_BLOCK_BYTES = 32 * 128;         // output staging block of one epilogue warp: 32 rows x 128 bytes
 constexpr uint32_t DEFAULT_RASTER_GROUP = 8;  // tile columns swept together for L2 reuse
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
@@ -78,7 +81,8 @@ struct Shape {
     static constexpr uint32_t RELEASE_GROUP = PAIR ? KLAS_PAIR_RELEASE : 1;
     static constexpr uint32_t B_STAGE_BYTES = B_COLS * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;
+    static_assert(STAGES * STAGE_BYTES == RING_BYTES && STAGES <= MAX_STAGES, "ring layout");
+    static constexpr uint32_t SMEM_BYTES = RING_BYTES + NUM_EPI_WARPS * EPI_BLOCK_BYTES + BARRIER_BYTES + 1024;
 };
 
 // First failing wait of the most recent launches on this device (0 = none).
@@ -95,7 +99,12 @@ struct Params {
     uint32_t M, N, K, batch;
     uint64_t ldd, sd;      // C / D: elements between rows, elements between pages
     uint32_t tiles_m, tiles_n, num_tiles, num_kb;
-    uint32_t tile_n;       // columns per tile of the single-CTA kernel: 256, or 128 for small outputs
+    uint32_t tile_n;       // columns per tile of the single-CTA kernel: 256, or 128 / 64 for small outputs
+    uint32_t stages, stage_bytes;   // single-CTA kernel: ring depth and bytes per stage (4 x 48, 6 x 32 or 8 x 24 KiB)
+    // K split (single-CTA and pair kernels): a tile's K range is cut into `ksplit` parts of `kb_per`
+    // K blocks, one work item each; `num_work` = num_tiles * ksplit.  Part q of page b writes its
+    // f32 partial product as page b * ksplit + q of D (a workspace then; a second kernel adds the parts).
+    uint32_t ksplit, kb_per, num_work;
     float alpha, beta;
     uint32_t idesc;
     uint32_t b_row_major;  // 1: B is K x N (N contiguous) -> MN-major operand
@@ -174,6 +183,19 @@ __device__ __forceinline__ void decode_tile(uint32_t t, const Params &p, uint32_
     tm = in / width;
     tn = first_n + in % width;
 }
+
+// One unit of the persistent loops of the single-CTA and pair kernels: a tile, or with a K split
+// one part of a tile's K blocks.  The parts of a tile are consecutive work items, so they run
+// at the same time on neighbouring CTA groups.
+struct WorkItem {
+    uint32_t tile, part, kb0, kb1;
+    __device__ __forceinline__ WorkItem(uint32_t w, const Params &p) {
+        tile = p.ksplit > 1 ? w / p.ksplit : w;
+        part = w - tile * p.ksplit;
+        kb0 = part * p.kb_per;
+        kb1 = min(kb0 + p.kb_per, p.num_kb);
+    }
+};
 
 template <typename T>
 struct OutTraits;
@@ -377,6 +399,125 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT 
     }
 }
 
+// Output path of a product that meets no old C: converts one chunk (32 rows x 32 columns, lane r
+// holding row r) and transposes it through shared memory so that global stores are coalesced.
+// Lane r writes 16-byte piece j of its row to piece (j ^ (r & 7)) of a 32-row x 128-byte block
+// (conflict-free); once the block's last chunk is staged the warp reads it back four rows per
+// instruction -- 8 lanes per row, 128 contiguous bytes -- and stores those.  A warp storing its
+// own rows directly would touch 32 different lines per instruction: measured on the 128 x 256
+// tile at 2048^3, 9100 cycles per tile of a 43000-cycle kernel.  `c` is the chunk's index in
+// the tile (it decides the position within the block), `col` its first column, `row0` the
+// warp's first row, `buf` the warp's staging block.
+template <typename OutT>
+__device__ __forceinline__ void emit_staged(const uint32_t (&v)[32], uint32_t c, uint32_t col, uint32_t row0,
+                                            uint32_t b, uint32_t buf, uint32_t lane, const Params &p,
+                                            bool relu, float plain_scale) {
+    constexpr uint32_t COLS_PER_BLOCK = 128 / sizeof(OutT);     // columns of one 128-byte staging row
+    constexpr uint32_t CHUNKS_PER_BLOCK = COLS_PER_BLOCK / 32;  // TMEM chunks (32 columns) per block
+    constexpr uint32_t PIECES = 32 * sizeof(OutT) / 16;         // 16-byte pieces per chunk per row
+    OutT *const D = static_cast<OutT *>(p.D);
+    const uint32_t sub = c % CHUNKS_PER_BLOCK;
+#pragma unroll
+    for (uint32_t j = 0; j < PIECES; ++j) {
+        union {
+            uint4 raw;
+            OutT e[16 / sizeof(OutT)];
+        } pk;
+#pragma unroll
+        for (uint32_t e = 0; e < 16 / sizeof(OutT); ++e) {
+            const float a = __uint_as_float(v[j * (16 / sizeof(OutT)) + e]) * plain_scale;
+            pk.e[e] = OutTraits<OutT>::from_f32(relu ? fmaxf(a, 0.0f) : a);
+        }
+        const uint32_t piece = (sub * PIECES + j) ^ (lane & 7u);
+        const uint32_t addr = buf + lane * 128u + piece * 16u;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.raw.x),
+                     "r"(pk.raw.y), "r"(pk.raw.z), "r"(pk.raw.w)
+                     : "memory");
+    }
+    if (sub == CHUNKS_PER_BLOCK - 1) {
+        __syncwarp();
+        const uint32_t col_blk = col - sub * 32u;
+        const uint32_t piece = lane & 7u;
+        const uint32_t gcol = col_blk + piece * (16 / sizeof(OutT));
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t r = i * 4u + (lane >> 3);
+            uint4 val;
+            const uint32_t addr = buf + r * 128u + ((piece ^ (r & 7u)) * 16u);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                         : "r"(addr)
+                         : "memory");
+            if (row0 + r < p.M && gcol < p.N)
+                *reinterpret_cast<uint4 *>(D + size_t(b) * p.sd + size_t(row0 + r) * p.ldd + gcol) = val;
+        }
+        __syncwarp();   // the buffer may be overwritten by the next block
+    }
+}
+
+// Second step of a K-split product: adds the f32 partial products (pages b * parts + q of `ws`,
+// each rows x cols, dense) in the order of q -- so the result is the same from run to run -- and
+// sends the sum through the output rule of the unsplit kernel: alpha / beta / the old C / relu /
+// the output type.  One thread per 4 consecutive columns; everything it reads is in L2.
+struct ReduceArgs {
+    const float *ws;
+    const void *C;
+    void *D;
+    uint32_t rows, cols, parts, batch;
+    uint64_t ldd, sd;
+    float alpha, beta;
+    uint32_t comb;
+};
+
+template <typename OutT, uint32_t COMB>
+__device__ __forceinline__ void reduce_store(const float (&acc)[4], OutT *d, const OutT *c, const ReduceArgs &a) {
+    OutT out[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float v;
+        if (c != nullptr)
+            v = comb_f32<COMB>(OutTraits<OutT>::to_f32(c[j]), acc[j], a.alpha, a.beta);
+        else
+            v = a.comb == KLAS_COMB_RELU ? fmaxf(acc[j], 0.0f) : (a.comb == KLAS_COMB_SCALED ? acc[j] * a.alpha : acc[j]);
+        out[j] = OutTraits<OutT>::from_f32(v);
+    }
+    if constexpr (sizeof(OutT) == 4)
+        *reinterpret_cast<uint4 *>(d) = *reinterpret_cast<const uint4 *>(out);
+    else
+        *reinterpret_cast<uint2 *>(d) = *reinterpret_cast<const uint2 *>(out);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceArgs a) {
+    const uint64_t quads_per_row = a.cols / 4;
+    const uint64_t total = uint64_t(a.batch) * a.rows * quads_per_row;
+    const uint64_t page_elems = uint64_t(a.rows) * a.cols;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
+        const uint64_t b = i / (uint64_t(a.rows) * quads_per_row);
+        const uint64_t in_page = i - b * a.rows * quads_per_row;
+        const uint64_t r = in_page / quads_per_row, c4 = (in_page - r * quads_per_row) * 4;
+        const float *src = a.ws + (b * a.parts) * page_elems + r * a.cols + c4;
+        float acc[4];
+        {
+            const float4 q = __ldcg(reinterpret_cast<const float4 *>(src));
+            acc[0] = q.x, acc[1] = q.y, acc[2] = q.z, acc[3] = q.w;
+        }
+        for (uint32_t part = 1; part < a.parts; ++part) {
+            const float4 q = __ldcg(reinterpret_cast<const float4 *>(src + part * page_elems));
+            acc[0] += q.x, acc[1] += q.y, acc[2] += q.z, acc[3] += q.w;
+        }
+        const uint64_t off = b * a.sd + r * a.ldd + c4;
+        OutT *d = static_cast<OutT *>(a.D) + off;
+        const OutT *c = a.C ? static_cast<const OutT *>(a.C) + off : nullptr;
+        switch (a.comb) {
+            case KLAS_COMB_MAX: reduce_store<OutT, KLAS_COMB_MAX>(acc, d, c, a); break;
+            case KLAS_COMB_MIN: reduce_store<OutT, KLAS_COMB_MIN>(acc, d, c, a); break;
+            case KLAS_COMB_MUL: reduce_store<OutT, KLAS_COMB_MUL>(acc, d, c, a); break;
+            default: reduce_store<OutT, KLAS_COMB_AXPBY>(acc, d, c, a); break;
+        }
+    }
+}
+
 // XFORM adds four warps that map the staged A / B bytes in place between the copy and the MMA
 // (single-CTA tiles only).
 template <typename OutT, bool PAIR, bool XFORM = false>
@@ -385,8 +526,10 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
                      const __grid_constant__ CUtensorMap tm_b, const Params p) {
     static_assert(!(PAIR && XFORM), "operand maps are built for the single-CTA and the wide tiles");
     using S = Shape<PAIR>;
-    constexpr uint32_t STAGES = S::STAGES;
-    constexpr uint32_t STAGE_BYTES = S::STAGE_BYTES;
+    // The single-CTA tile comes in three widths; a narrower tile has smaller stages and a deeper
+    // ring (the same 192 KiB), because what it lacks is bytes in flight, not arithmetic.
+    const uint32_t STAGES = PAIR ? S::STAGES : p.stages;
+    const uint32_t STAGE_BYTES = PAIR ? S::STAGE_BYTES : p.stage_bytes;
 
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzled tiles need 1024-byte aligned bases.  The dynamic shared window
@@ -396,17 +539,18 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
     uint8_t *smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
 
-    uint8_t *bar_region = smem + STAGES * STAGE_BYTES;
-    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
-    // layout: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag
+    const uint32_t epi_base = smem_base + RING_BYTES;
+    uint8_t *bar_region = smem + RING_BYTES + NUM_EPI_WARPS * EPI_BLOCK_BYTES;
+    const uint32_t bar_base = epi_base + NUM_EPI_WARPS * EPI_BLOCK_BYTES;
+    // layout: full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag
     auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
-    auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
-    auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + ACC_STAGES + a); };
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_region + 8u * (2 * STAGES + 2 * ACC_STAGES));
+    auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (MAX_STAGES + s); };
+    auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * MAX_STAGES + a); };
+    auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * MAX_STAGES + ACC_STAGES + a); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_region + 8u * (2 * MAX_STAGES + 2 * ACC_STAGES));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     [[maybe_unused]] auto xfull_bar = [&](uint32_t s) { return bar_base + XFULL_OFFSET + 8u * s; };
-    static_assert(8u * (2 * STAGES + 2 * ACC_STAGES) + 8u <= XFULL_OFFSET && XFULL_OFFSET + 8u * STAGES <= BARRIER_BYTES,
+    static_assert(8u * (2 * MAX_STAGES + 2 * ACC_STAGES) + 8u <= XFULL_OFFSET && XFULL_OFFSET + 8u * MAX_STAGES <= BARRIER_BYTES,
                   "barrier block layout");
 
     const uint32_t warp = threadIdx.x >> 5;
@@ -456,53 +600,57 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         // One thread runs the whole loop: no warp-wide votes or re-convergence per stage.
+        // Like the MMA issuer's, this thread's instruction stream is kept short: destination, barrier
+        // and K coordinate are running values.
         uint32_t stage = 0, phase = 0;
         bool ok = lane == 0;
-        [[maybe_unused]] const uint32_t full_bars_cta0 = PAIR ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);
-        for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
+        const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
+        [[maybe_unused]] const uint32_t full0_cta0 = PAIR ? ptx::map_to_cta(full0, 0) : full0;
+        uint32_t a_dst = smem_base, fullb = full0, emptyb = empty0;
+        [[maybe_unused]] uint32_t fullb_cta0 = full0_cta0;
+        const uint32_t tile_n = PAIR ? BN : p.tile_n;
+        const uint32_t tx_bytes = PAIR ? 2 * STAGE_BYTES : A_STAGE_BYTES + tile_n * BK * 2u;   // the even CTA's barrier counts both CTAs' loads
+        const bool b_row_major = p.b_row_major != 0;
+        for (uint32_t w = group; ok && w < p.num_work; w += num_groups) {
+            const WorkItem wi(w, p);
             uint32_t b, tm, tn;
-            decode_tile(t, p, b, tm, tn);
+            decode_tile(wi.tile, p, b, tm, tn);
             const int32_t a_row = int32_t(tm * S::TILE_M + cta_rank * BM);
-            const uint32_t tile_n = PAIR ? BN : p.tile_n;
             const int32_t b_col = int32_t(tn * tile_n + cta_rank * S::B_COLS);
-            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+            int32_t k0 = int32_t(wi.kb0 * BK);
+            for (uint32_t kb = wi.kb0; kb < wi.kb1; ++kb, k0 += int32_t(BK)) {
                 if (stage % S::RELEASE_GROUP == 0) {
                     // stages are handed back in groups; the group's last stage carries the barrier
-                    ok = bounded_wait(empty_bar(stage + S::RELEASE_GROUP - 1), phase ^ 1u, ctl, SITE_PRODUCER_EMPTY, WAIT_LIMIT_NS, 64);
+                    ok = bounded_wait(emptyb + 8u * (S::RELEASE_GROUP - 1), phase ^ 1u, ctl, SITE_PRODUCER_EMPTY, WAIT_LIMIT_NS, 64);
                     if (!ok) break;
                 }
-                {
-                    const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
-                    const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-                    const int32_t k0 = int32_t(kb * BK);
-                    if constexpr (PAIR) {
-                        // the even CTA's barrier counts the bytes of both CTAs' loads
-                        if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
-                        const uint32_t bar = full_bars_cta0 + 8u * stage;
-                        ptx::tma_load_3d_pair(a_dst, &tm_a, bar, k0, a_row, int32_t(b));
-                        if (p.b_row_major) {
+                const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+                if constexpr (PAIR) {
+                    if (cta_rank == 0) ptx::mbar_arrive_expect_tx(fullb, tx_bytes);
+                    ptx::tma_load_3d_pair(a_dst, &tm_a, fullb_cta0, k0, a_row, int32_t(b));
+                    if (b_row_major) {
 #pragma unroll
-                            for (uint32_t j = 0; j < S::B_COLS / 64; ++j)
-                                ptx::tma_load_3d_pair(b_dst + j * B_CHUNK_BYTES, &tm_b, bar,
-                                                      b_col + int32_t(j * 64), k0, int32_t(b));
-                        } else {
-                            ptx::tma_load_3d_pair(b_dst, &tm_b, bar, k0, b_col, int32_t(b));
-                        }
+                        for (uint32_t j = 0; j < S::B_COLS / 64; ++j)
+                            ptx::tma_load_3d_pair(b_dst + j * B_CHUNK_BYTES, &tm_b, fullb_cta0, b_col + int32_t(j * 64), k0, int32_t(b));
                     } else {
-                        ptx::mbar_arrive_expect_tx(full_bar(stage), A_STAGE_BYTES + tile_n * BK * 2u);
-                        ptx::tma_load_3d(a_dst, &tm_a, full_bar(stage), k0, a_row, int32_t(b));
-                        if (p.b_row_major) {
-                            for (uint32_t j = 0; j < tile_n / 64; ++j)
-                                ptx::tma_load_3d(b_dst + j * B_CHUNK_BYTES, &tm_b, full_bar(stage),
-                                                 b_col + int32_t(j * 64), k0, int32_t(b));
-                        } else {
-                            ptx::tma_load_3d(b_dst, &tm_b, full_bar(stage), k0, b_col, int32_t(b));
-                        }
+                        ptx::tma_load_3d_pair(b_dst, &tm_b, fullb_cta0, k0, b_col, int32_t(b));
+                    }
+                } else {
+                    ptx::mbar_arrive_expect_tx(fullb, tx_bytes);
+                    ptx::tma_load_3d(a_dst, &tm_a, fullb, k0, a_row, int32_t(b));
+                    if (b_row_major) {
+                        for (uint32_t j = 0; j < tile_n / 64; ++j)
+                            ptx::tma_load_3d(b_dst + j * B_CHUNK_BYTES, &tm_b, fullb, b_col + int32_t(j * 64), k0, int32_t(b));
+                    } else {
+                        ptx::tma_load_3d(b_dst, &tm_b, fullb, k0, b_col, int32_t(b));
                     }
                 }
-                if (++stage == STAGES) {
+                ++stage;
+                a_dst += STAGE_BYTES, fullb += 8u, emptyb += 8u, fullb_cta0 += 8u;
+                if (stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
+                    a_dst = smem_base, fullb = full0, emptyb = empty0, fullb_cta0 = full0_cta0;
                 }
             }
         }
@@ -512,49 +660,59 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
         // K-major operand: 8-row groups 1024 bytes apart; a K step of 16 elements = 32 bytes.
         // MN-major B: 64-column slabs 8192 bytes apart (leading), 8-row K groups 1024 bytes
         // apart (stride); a K step of 16 rows = 2048 bytes.
+        // The loop below is one thread's instruction stream, and that stream is what bounds the
+        // narrower tiles, so it is kept short: descriptors as 32-bit halves with the low half a running
+        // value (start address >> 4; stage and K step add constants), barrier addresses as running values.
         const uint64_t a_desc_base = ptx::umma_desc_base_sw128(16, 1024);
         const uint64_t b_desc_base = p.b_row_major ? ptx::umma_desc_base_sw128(B_CHUNK_BYTES, 1024)
                                                    : ptx::umma_desc_base_sw128(16, 1024);
-        const uint32_t b_kstep = p.b_row_major ? UMMA_K * 128u : UMMA_K * 2u;
+        const uint32_t a_hi = uint32_t(a_desc_base >> 32), b_hi = uint32_t(b_desc_base >> 32);
+        const uint32_t a_lo0 = uint32_t(a_desc_base) | ((smem_base & 0x3FFFFu) >> 4);
+        const uint32_t b_lo0 = uint32_t(b_desc_base) | (((smem_base + A_STAGE_BYTES) & 0x3FFFFu) >> 4);
+        const uint32_t stage_step = STAGE_BYTES >> 4;
+        const uint32_t b_step = (p.b_row_major ? UMMA_K * 128u : UMMA_K * 2u) >> 4;   // one K step of 16
+        const uint32_t full0 = XFORM ? xfull_bar(0) : full_bar(0), empty0 = empty_bar(0);
+        const uint32_t idesc = p.idesc;
         uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+        uint32_t a_lo = a_lo0, b_lo = b_lo0, fullb = full0, emptyb = empty0;
         bool ok = lane == 0;   // one thread runs the whole loop
         const bool issuer = cta_rank == 0;
-        for (uint32_t t = group; issuer && ok && p.num_kb > 0 && t < p.num_tiles; t += num_groups) {
-            {
-                ok = bounded_wait(tempty_bar(acc), acc_phase ^ 1u, ctl, SITE_MMA_TMEM_EMPTY);
-            }
+        auto mma = [&](uint32_t d, uint32_t kk, uint32_t accumulate) {
+            if constexpr (PAIR)
+                ptx::umma_f16_ss_pair_halves(d, a_lo + kk * (UMMA_K * 2u >> 4), a_hi, b_lo + kk * b_step, b_hi, idesc, accumulate);
+            else
+                ptx::umma_f16_ss_halves(d, a_lo + kk * (UMMA_K * 2u >> 4), a_hi, b_lo + kk * b_step, b_hi, idesc, accumulate);
+        };
+        static_assert(BK / UMMA_K == 4, "the K block is issued as four MMAs");
+        for (uint32_t w = group; issuer && ok && p.num_kb > 0 && w < p.num_work; w += num_groups) {
+            const WorkItem wi(w, p);
+            ok = bounded_wait(tempty_bar(acc), acc_phase ^ 1u, ctl, SITE_MMA_TMEM_EMPTY);
             if (!ok) break;
             ptx::tc_fence_after_sync();   // orders the epilogue's TMEM reads before these MMAs' writes
             const uint32_t d_tmem = tmem_base + acc * BN;
-            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-                ok = bounded_wait(XFORM ? xfull_bar(stage) : full_bar(stage), phase, ctl, SITE_MMA_FULL);
+            uint32_t later = 0;   // 0 in the tile's first K block: its first MMA overwrites the accumulator
+            for (uint32_t kb = wi.kb0; kb < wi.kb1; ++kb) {
+                ok = bounded_wait(fullb, phase, ctl, SITE_MMA_FULL);
                 if (!ok) break;
-                {
-                    const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
-                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
-#pragma unroll
-                    for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
-                        const uint64_t a_desc =
-                            ptx::umma_desc_at(a_desc_base, a_addr + kk * UMMA_K * 2u);
-                        const uint64_t b_desc = ptx::umma_desc_at(b_desc_base, b_addr + kk * b_kstep);
-                        if constexpr (PAIR)
-                            ptx::umma_f16_ss_pair(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
-                        else
-                            ptx::umma_f16_ss(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
-                    }
-                    // free the shared-memory stage (in both CTAs) once these MMAs retire
-                    if constexpr (PAIR) {
-                        if (stage % S::RELEASE_GROUP == S::RELEASE_GROUP - 1)
-                            ptx::umma_commit_pair_mask(empty_bar(stage), 0x3);
-                        if (kb + 1 == p.num_kb) ptx::umma_commit_pair_mask(tfull_bar(acc), 0x3);
-                    } else {
-                        ptx::umma_commit(empty_bar(stage));
-                        if (kb + 1 == p.num_kb) ptx::umma_commit(tfull_bar(acc));
-                    }
+                mma(d_tmem, 0, later);
+                mma(d_tmem, 1, 1u);
+                mma(d_tmem, 2, 1u);
+                mma(d_tmem, 3, 1u);
+                later = 1u;
+                // free the shared-memory stage (in both CTAs) once these MMAs retire
+                if constexpr (PAIR) {
+                    if (stage % S::RELEASE_GROUP == S::RELEASE_GROUP - 1) ptx::umma_commit_pair_mask(emptyb, 0x3);
+                    if (kb + 1 == wi.kb1) ptx::umma_commit_pair_mask(tfull_bar(acc), 0x3);
+                } else {
+                    ptx::umma_commit(emptyb);
+                    if (kb + 1 == wi.kb1) ptx::umma_commit(tfull_bar(acc));
                 }
-                if (++stage == STAGES) {
+                ++stage;
+                a_lo += stage_step, b_lo += stage_step, fullb += 8u, emptyb += 8u;
+                if (stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
+                    a_lo = a_lo0, b_lo = b_lo0, fullb = full0, emptyb = empty0;
                 }
             }
             if (++acc == ACC_STAGES) {
@@ -568,8 +726,9 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
         const uint32_t xw = warp - (2 + NUM_EPI_WARPS);
         uint32_t stage = 0, phase = 0, turn = 0;
         bool ok = true;
-        for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
-            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+        for (uint32_t w = group; ok && w < p.num_work; w += num_groups) {
+            const WorkItem wi(w, p);
+            for (uint32_t kb = wi.kb0; kb < wi.kb1; ++kb) {
                 if (turn == xw)
                     ok = xform_stage(p, full_bar(stage), phase, ctl, SITE_XFORM_FULL, smem_base + stage * STAGE_BYTES,
                                      A_STAGE_BYTES, PAIR ? S::B_STAGE_BYTES : p.tile_n * BK * 2u, xfull_bar(stage), lane);
@@ -588,33 +747,65 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
         const OutT *const C = static_cast<const OutT *>(p.C);
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
-        for (uint32_t t = group; ok && t < p.num_tiles; t += num_groups) {
+        for (uint32_t w = group; ok && w < p.num_work; w += num_groups) {
+            const WorkItem wi(w, p);
             uint32_t b, tm, tn;
-            decode_tile(t, p, b, tm, tn);
+            decode_tile(wi.tile, p, b, tm, tn);
             if (p.num_kb > 0) {
                 ok = lane != 0 || bounded_wait(tfull_bar(acc), acc_phase, ctl, SITE_EPI_TMEM_FULL, WAIT_LIMIT_NS, 128);
                 ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;   // lane 0 polls, the warp follows
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
             }
-            const uint32_t row = tm * S::TILE_M + cta_rank * BM + quad * 32u + lane;
+            const uint32_t row0 = tm * S::TILE_M + cta_rank * BM + quad * 32u;
+            const uint32_t row = row0 + lane;
             const uint32_t tile_n = PAIR ? BN : p.tile_n;
             const uint32_t col0 = tn * tile_n;
             const size_t row_off = size_t(b) * p.sd + size_t(row) * p.ldd;
-#pragma unroll 1
-            for (uint32_t c = 0; c < tile_n / 32; ++c) {
-                uint32_t v[32];
-                if (p.num_kb > 0) {
-                    ptx::tmem_ld_32x32b_x32(tmem_base + ((quad * 32u) << 16) + acc * BN + c * 32u, v);
-                    ptx::tmem_ld_wait();
+            const uint32_t buf = epi_base + (warp - 2) * EPI_BLOCK_BYTES;
+            const uint32_t taddr0 = tmem_base + ((quad * 32u) << 16) + acc * BN;
+            const bool relu = p.comb == KLAS_COMB_RELU;
+            const float plain_scale = p.comb == KLAS_COMB_SCALED ? p.alpha : 1.0f;   // x * 1.0f is exact
+            const bool have_acc = p.num_kb > 0;
+            const uint32_t nchunk = tile_n / 32;   // 2, 4 or 8
+            const uint32_t page = b * p.ksplit + wi.part;   // = b unless K is split
+            if (C == nullptr) {
+                // Plain product: chunks leave through the staging block, with the next chunk's
+                // tcgen05.ld in flight while the current one is converted and stored.
+                uint32_t va[32], vb[32];
+                if (have_acc) {
+                    ptx::tmem_ld_32x32b_x32(taddr0, va);
                 } else {
 #pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j) v[j] = 0u;
+                    for (uint32_t j = 0; j < 32; ++j) va[j] = vb[j] = 0u;
                 }
-                const uint32_t col = col0 + c * 32u;
-                if (row < p.M && col < p.N) {
-                    store_row_chunk<OutT>(v, D + row_off + col, C ? C + row_off + col : nullptr,
-                                          p.alpha, p.beta, p.N - col, p.comb);
+#pragma unroll 1
+                for (uint32_t c = 0; c < nchunk; c += 2) {
+                    if (have_acc) {
+                        ptx::tmem_ld_wait();
+                        ptx::tmem_ld_32x32b_x32(taddr0 + (c + 1) * 32u, vb);
+                    }
+                    emit_staged<OutT>(va, c, col0 + c * 32u, row0, page, buf, lane, p, relu, plain_scale);
+                    if (have_acc) {
+                        ptx::tmem_ld_wait();
+                        if (c + 2 < nchunk) ptx::tmem_ld_32x32b_x32(taddr0 + (c + 2) * 32u, va);
+                    }
+                    emit_staged<OutT>(vb, c + 1, col0 + (c + 1) * 32u, row0, page, buf, lane, p, relu, plain_scale);
+                }
+            } else {
+#pragma unroll 1
+                for (uint32_t c = 0; c < tile_n / 32; ++c) {
+                    uint32_t v[32];
+                    if (p.num_kb > 0) {
+                        ptx::tmem_ld_32x32b_x32(taddr0 + c * 32u, v);
+                        ptx::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (uint32_t j = 0; j < 32; ++j) v[j] = 0u;
+                    }
+                    const uint32_t col = col0 + c * 32u;
+                    if (row < p.M && col < p.N)
+                        store_row_chunk<OutT>(v, D + row_off + col, C + row_off + col, p.alpha, p.beta, p.N - col, p.comb);
                 }
             }
             if (p.num_kb > 0) {
@@ -872,9 +1063,6 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
         const uint32_t h = (warp - 2) >> 2;
         OutT *const D = static_cast<OutT *>(p.D);
         const OutT *const C = static_cast<const OutT *>(p.C);
-        constexpr uint32_t COLS_PER_BLOCK = 128 / sizeof(OutT);     // columns of one 128-byte staging row
-        constexpr uint32_t CHUNKS_PER_BLOCK = COLS_PER_BLOCK / 32;  // TMEM chunks (32 columns) per block
-        constexpr uint32_t PIECES = 32 * sizeof(OutT) / 16;         // 16-byte pieces per chunk per row
         constexpr uint32_t NCHUNK = BN / 32;
         const uint32_t buf = epi_base + (warp - 2) * EPI_BUF_BYTES;
         const uint32_t tempty_cta0 = ptx::map_to_cta(tempty_bar, 0);
@@ -897,11 +1085,8 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
             const uint32_t row = row0 + lane;
             const size_t row_off = size_t(b) * p.sd + size_t(row) * p.ldd;
 
-            // Converts one chunk and either stores it directly (alpha/beta path, C read with plain
-            // loads) or transposes it through shared memory so that global stores are coalesced:
-            // lane r (= row r) writes 16-byte piece j of its row to piece (j ^ (r & 7)) of a
-            // 32-row x 128-byte buffer (conflict-free), then the warp reads the buffer back four
-            // rows per instruction -- 8 lanes per row, 128 contiguous bytes -- and stores those.
+            // One chunk either goes out directly (alpha/beta path, C read with plain loads) or
+            // through the warp's staging block (emit_staged).
             auto emit = [&](const uint32_t (&v)[32], uint32_t c) {
                 const uint32_t col = tn * BN + c * 32u;
                 if (C != nullptr) {
@@ -910,43 +1095,7 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
                                               p.N - col, p.comb);
                     return;
                 }
-                const uint32_t sub = c % CHUNKS_PER_BLOCK;
-#pragma unroll
-                for (uint32_t j = 0; j < PIECES; ++j) {
-                    union {
-                        uint4 raw;
-                        OutT e[16 / sizeof(OutT)];
-                    } pk;
-#pragma unroll
-                    for (uint32_t e = 0; e < 16 / sizeof(OutT); ++e) {
-                        const float a = __uint_as_float(v[j * (16 / sizeof(OutT)) + e]) * plain_scale;
-                        pk.e[e] = OutTraits<OutT>::from_f32(relu ? fmaxf(a, 0.0f) : a);
-                    }
-                    const uint32_t piece = (sub * PIECES + j) ^ (lane & 7u);
-                    const uint32_t addr = buf + lane * 128u + piece * 16u;
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.raw.x),
-                                 "r"(pk.raw.y), "r"(pk.raw.z), "r"(pk.raw.w)
-                                 : "memory");
-                }
-                if (sub == CHUNKS_PER_BLOCK - 1) {
-                    __syncwarp();
-                    const uint32_t col_blk = col - sub * 32u;
-                    const uint32_t piece = lane & 7u;
-                    const uint32_t gcol = col_blk + piece * (16 / sizeof(OutT));
-#pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) {
-                        const uint32_t r = i * 4u + (lane >> 3);
-                        uint4 val;
-                        const uint32_t addr = buf + r * 128u + ((piece ^ (r & 7u)) * 16u);
-                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                                     : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
-                                     : "r"(addr)
-                                     : "memory");
-                        if (row0 + r < p.M && gcol < p.N)
-                            *reinterpret_cast<uint4 *>(D + size_t(b) * p.sd + size_t(row0 + r) * p.ldd + gcol) = val;
-                    }
-                    __syncwarp();   // the buffer may be overwritten by the next block
-                }
+                emit_staged<OutT>(v, c, col, row0, b, buf, lane, p, relu, plain_scale);
             };
 
             uint32_t va[32], vb[32];
@@ -1141,6 +1290,69 @@ static int launch_wide_mode(int out_dtype, const CUtensorMap &ta, const CUtensor
 
 int umma_ensure_host_flag();
 
+// Workspace of the K-split launches: the partial products.  One buffer per (device, stream) that
+// has run a split launch, because launches on different streams may overlap; launches on one
+// stream follow one another and share theirs.
+namespace {
+constexpr int SPLIT_POOL = 8;                        // streams per device with a buffer of their own
+struct SplitBuffer {
+    cudaStream_t stream = nullptr;
+    void *ptr = nullptr;
+    size_t cap = 0;
+    bool used = false;
+};
+std::mutex g_split_mutex;
+SplitBuffer g_split[64][SPLIT_POOL];
+}  // namespace
+
+// Finds or makes the buffer of `stream` with room for `bytes` of partial sums.  Returns KLAS_OK with
+// *out = nullptr when none can be had without disturbing the caller (the stream is recording a
+// graph and memory would have to be allocated, or the pool is full): the launch then runs unsplit.
+static int split_workspace(cudaStream_t stream, size_t bytes, void **out) {
+    *out = nullptr;
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    if (dev < 0 || dev >= 64) return KLAS_OK;
+    std::lock_guard<std::mutex> lock(g_split_mutex);
+    SplitBuffer *slot = nullptr;
+    for (SplitBuffer &b : g_split[dev])
+        if (b.used && b.stream == stream) slot = &b;
+    if (!slot)
+        for (SplitBuffer &b : g_split[dev])
+            if (!b.used && !slot) slot = &b;
+    if (!slot) return KLAS_OK;
+    const size_t want = bytes;
+    if (slot->cap < want) {
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (int rc = check_cuda(cudaStreamIsCapturing(stream, &capturing), "cudaStreamIsCapturing")) return rc;
+        if (capturing != cudaStreamCaptureStatusNone) return KLAS_OK;
+        if (slot->ptr)
+            if (int rc = check_cuda(cudaFree(slot->ptr), "cudaFree")) return rc;   // waits for the device
+        *slot = SplitBuffer{};
+        void *fresh = nullptr;
+        if (int rc = check_cuda(cudaMalloc(&fresh, want), "cudaMalloc (K-split workspace)")) return rc;
+        slot->ptr = fresh;
+        slot->cap = want;
+        slot->stream = stream;
+        slot->used = true;
+    }
+    *out = slot->ptr;
+    return KLAS_OK;
+}
+
+int umma_release_split_workspace() {
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    if (dev < 0 || dev >= 64) return KLAS_OK;
+    std::lock_guard<std::mutex> lock(g_split_mutex);
+    for (SplitBuffer &b : g_split[dev]) {
+        if (b.ptr)
+            if (int rc = check_cuda(cudaFree(b.ptr), "cudaFree")) return rc;
+        b = SplitBuffer{};
+    }
+    return KLAS_OK;
+}
+
 int umma_wait_probe(uint32_t limit_ms, int *gave_up, cudaStream_t stream) {
     if (int rc = umma_ensure_host_flag()) return rc;
     umma::wait_probe_kernel<<<1, 32, 0, stream>>>(uint64_t(limit_ms) * 1000000ull, nullptr, gave_up);
@@ -1274,11 +1486,12 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     // `python -m kuiper_b200.tune_tc` (TFLOP/s of each tile shape where all of them fill the
     // machine); re-run it and update the three constants when a kernel changes.
     // Examples the estimate gets right where "wide once it fills the machine"
-    // did not: 3072^3 (72 wide tiles, one round: 1324 against 1120 TFLOP/s for two rounds of pairs),
-    // 3584 x 3072 (84 wide tiles would take two rounds; pairs: 1049 against 910), 2048^2 (one
-    // round of 128 single tiles: 720 against 488 for 32 wide tiles on 74 pairs).
+    // did not: 3072^3 (72 wide tiles, one round: 1388 against 1267 TFLOP/s for two rounds of single tiles),
+    // 3584 x 3072 (84 wide tiles would take two rounds; pairs: 1167 against 959), 2048^2 (one
+    // round of 128 single tiles: 896 against 600 for 32 wide tiles on 74 pairs).
     // The KLAS_KNOB_TC_MODE knob overrides the choice.
-    constexpr double RATE_SINGLE = 1144.0, RATE_PAIR = 1160.0, RATE_WIDE = 1408.0, NARROW_COST = 0.55;
+    constexpr double RATE_SINGLE = 1336.0, RATE_PAIR = 1433.0, RATE_WIDE = 1539.0, WIDE_DRAIN_KB = 6.0, NARROW_COST = 0.75, SLIM_COST = 0.65;
+    constexpr uint32_t SPLIT_MIN_SAVED_KB = 22;   // K blocks (of 64) a split must take off a tile to pay for its second kernel
     const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
     const uint64_t pair_tiles = ((rows + 2 * BM - 1) / (2 * BM)) * ((cols + BN - 1) / BN) * batch;
     const uint64_t wide_tiles = ((rows + wide::TILE_M - 1) / wide::TILE_M) * ((cols + BN - 1) / BN) * batch;
@@ -1287,19 +1500,51 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     const double cost_single = double((single_tiles + sms - 1) / sms);
     const bool pair_ok = can_pair && rows > BM && single_tiles >= sms && !xform;   // the pair tile has no mapped form
     const double cost_pair = pair_ok ? double((pair_tiles + pairs - 1) / pairs) * (RATE_SINGLE / RATE_PAIR) : 1e30;
-    const double cost_wide = can_pair ? double((wide_tiles + pairs - 1) / pairs) * 2.0 * (RATE_SINGLE / RATE_WIDE) : 1e30;
+    // The wide tile's epilogue is not hidden behind the next tile's MMAs (both accumulator halves
+    // belong to one tile): about six K blocks' worth per tile, which the rate measured at K = 8192
+    // contains once per 128 K blocks.  8192 x 8192 x 512: single tiles 791, wide 708 TFLOP/s.
+    const double num_kb_d = double((shared + BK - 1) / BK);
+    const double wide_drain = num_kb_d > 0 ? (1.0 + WIDE_DRAIN_KB / num_kb_d) / (1.0 + WIDE_DRAIN_KB / 128.0) : 1.0;
+    const double cost_wide = can_pair ? double((wide_tiles + pairs - 1) / pairs) * 2.0 * (RATE_SINGLE / RATE_WIDE) * wide_drain : 1e30;
     bool use_wide = can_pair && cost_wide < cost_single && cost_wide <= cost_pair;
     bool pair = pair_ok && !use_wide && cost_pair <= cost_single;
     // Small outputs: the single-CTA kernel with 128-column tiles puts twice as many CTAs to work
-    // (1024^2: 64 tiles instead of 32 on 148 SMs); a narrow tile costs a little more than half a
-    // full one (the A operand is read from shared memory once per 128 instead of 256 columns).
+    // (1024^2: 64 tiles instead of 32 on 148 SMs).  A CTA takes the same time per K block whatever
+    // the tile's width (about 660 cycles: the copy-issue and MMA-issue threads, not the arithmetic,
+    // set it), so a narrower tile only pays through its shorter prologue and epilogue when the
+    // round count stays the same (2048^2, K = 2048: one round of 128 x 256 tiles 19.4 us, two
+    // rounds of 128 x 128 29.2 us, four of 128 x 64 50.0 us).
+    // Smaller still (1024^2: 128 tiles of 128 x 64) when even the 128-column tiles leave SMs idle.
     const uint64_t narrow_tiles = ((rows + BM - 1) / BM) * ((cols + 127) / 128) * batch;
-    bool narrow = !use_wide && !pair && double((narrow_tiles + sms - 1) / sms) * NARROW_COST < cost_single;
+    const uint64_t slim_tiles = ((rows + BM - 1) / BM) * ((cols + 63) / 64) * batch;
+    const double cost_narrow = double((narrow_tiles + sms - 1) / sms) * NARROW_COST;
+    const double cost_slim = double((slim_tiles + sms - 1) / sms) * SLIM_COST;
+    uint32_t single_tile_n = BN;
+    if (!use_wide && !pair) {
+        double best = cost_single;
+        if (cost_narrow < best) best = cost_narrow, single_tile_n = 128;
+        if (cost_slim < best) best = cost_slim, single_tile_n = 64;
+    }
+    // Long K over few tiles: cut each 128 x 256 tile's K range into parts that fill the SMs
+    // (1024 x 1024 x 4096: 32 tiles x 4 parts, 17.3 us against 27.4 us for 128 tiles of 128 x 64).
+    // A split costs a second kernel that adds the parts (4-6 us for a 1024^2 output), a K block 0.34 us.
+    const uint64_t num_kb_all = (shared + BK - 1) / BK;
+    uint64_t auto_parts = 1;
+    if (!use_wide && !pair && single_tiles * 2 <= sms && debug_knob(KLAS_KNOB_TC_MODE) == 0) {
+        uint64_t parts = sms / single_tiles;
+        if (parts > 8) parts = 8;
+        const uint64_t kb_per = (num_kb_all + parts - 1) / parts;
+        if (num_kb_all >= kb_per + SPLIT_MIN_SAVED_KB) {
+            auto_parts = parts;
+            single_tile_n = BN;
+        }
+    }
     switch (debug_knob(KLAS_KNOB_TC_MODE)) {   // a test or tuning run forcing one tile shape
-        case 1: pair = use_wide = narrow = false; break;
-        case 2: pair = use_wide = false; narrow = true; break;
-        case 3: pair = can_pair && !xform; use_wide = false; narrow = narrow && !pair; break;
-        case 4: use_wide = can_pair; narrow = narrow && !use_wide; break;
+        case 1: pair = use_wide = false; single_tile_n = BN; break;
+        case 2: pair = use_wide = false; single_tile_n = 128; break;
+        case 3: pair = can_pair && !xform; use_wide = false; break;
+        case 4: use_wide = can_pair; break;
+        case 5: pair = use_wide = false; single_tile_n = 64; break;
         default: break;
     }
     if (use_wide) {
@@ -1350,7 +1595,9 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     p.N = uint32_t(cols);
     p.K = uint32_t(shared);
     p.batch = batch;
-    p.tile_n = (narrow && !pair) ? 128u : BN;
+    p.tile_n = pair ? BN : single_tile_n;
+    p.stage_bytes = A_STAGE_BYTES + p.tile_n * BK * 2u;
+    p.stages = RING_BYTES / p.stage_bytes;   // 4 x 48, 6 x 32 or 8 x 24 KiB
     p.tiles_m = uint32_t((rows + tile_m - 1) / tile_m);
     p.tiles_n = uint32_t((cols + p.tile_n - 1) / p.tile_n);
     const uint64_t num_tiles = uint64_t(p.tiles_m) * p.tiles_n * batch;
@@ -1371,6 +1618,64 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     p.raster_group = DEFAULT_RASTER_GROUP;
     if (const int v = debug_knob(KLAS_KNOB_TC_RASTER); v >= 1) p.raster_group = uint32_t(v);
 
+    // K split (chosen above, or forced by the knob): the parts write f32 partial products into a
+    // workspace and a second kernel adds them in index order and applies the output rule (alpha,
+    // beta, the old C, the output type), so the result is the same from run to run.
+    p.ksplit = 1;
+    float *split_ws = nullptr;
+    {
+        const int knob = debug_knob(KLAS_KNOB_TC_KSPLIT);
+        uint64_t parts = 1;
+        if (knob >= 2) {
+            parts = uint64_t(knob);
+        } else if (knob == 0) {
+            parts = auto_parts;
+        }
+        if (parts > 8) parts = 8;
+        if (parts > p.num_kb) parts = p.num_kb;
+        if (parts >= 2 && num_tiles * parts <= 0xffffffffull) {
+            const uint32_t kb_per = uint32_t((p.num_kb + parts - 1) / parts);
+            parts = (p.num_kb + kb_per - 1) / kb_per;   // no empty part
+            void *ws = nullptr;
+            const size_t bytes = size_t(batch) * parts * rows * cols * sizeof(float);
+            if (parts >= 2)
+                if (int rc = split_workspace(stream, bytes, &ws)) return rc;
+            if (ws != nullptr) {
+                p.ksplit = uint32_t(parts);
+                p.kb_per = kb_per;
+                split_ws = static_cast<float *>(ws);
+            }
+        }
+    }
+    if (p.ksplit == 1) p.kb_per = p.num_kb;
+    const uint64_t num_work = num_tiles * p.ksplit;
+    p.num_work = uint32_t(num_work);
+    int kernel_out_dtype = out_dtype;
+    if (split_ws != nullptr) {
+        // the product kernel writes plain f32 parts; the output rule moves to the second kernel
+        p.C = nullptr;
+        p.D = split_ws;
+        p.ldd = cols;
+        p.sd = rows * cols;
+        p.comb = KLAS_COMB_NEW;
+        p.alpha = 1.0f;
+        p.beta = 0.0f;
+        kernel_out_dtype = KLAS_F32;
+    }
+    auto finish_split = [&](int rc) -> int {
+        if (rc != KLAS_OK || split_ws == nullptr) return rc;
+        ReduceArgs ra{split_ws, C, D, uint32_t(rows), uint32_t(cols), p.ksplit, batch, ldd, sd, alpha, beta, uint32_t(comb)};
+        const uint64_t threads = uint64_t(batch) * rows * (cols / 4);
+        uint64_t blocks = (threads + 255) / 256;
+        if (blocks > uint64_t(info.sm_count) * 8) blocks = uint64_t(info.sm_count) * 8;
+        switch (out_dtype) {
+            case KLAS_F32: splitk_reduce_kernel<float><<<unsigned(blocks), 256, 0, stream>>>(ra); break;
+            case KLAS_F16: splitk_reduce_kernel<__half><<<unsigned(blocks), 256, 0, stream>>>(ra); break;
+            default: splitk_reduce_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, stream>>>(ra); break;
+        }
+        return check_cuda(cudaGetLastError(), "splitk_reduce_kernel launch");
+    };
+
     const uint32_t b_cols = pair ? Shape<true>::B_COLS : p.tile_n;
     CUtensorMap ta{}, tb{};
     if (shared > 0) {
@@ -1382,12 +1687,12 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
         }
     }
     if (pair) {
-        const uint64_t groups = num_tiles < uint64_t(info.sm_count / 2) ? num_tiles : uint64_t(info.sm_count / 2);
-        return launch_mode<true, false>(out_dtype, ta, tb, p, int(groups * 2), stream);
+        const uint64_t groups = num_work < uint64_t(info.sm_count / 2) ? num_work : uint64_t(info.sm_count / 2);
+        return finish_split(launch_mode<true, false>(kernel_out_dtype, ta, tb, p, int(groups * 2), stream));
     }
-    const int grid = int(num_tiles < uint64_t(info.sm_count) ? num_tiles : uint64_t(info.sm_count));
-    return xform ? launch_mode<false, true>(out_dtype, ta, tb, p, grid, stream)
-                 : launch_mode<false, false>(out_dtype, ta, tb, p, grid, stream);
+    const int grid = int(num_work < uint64_t(info.sm_count) ? num_work : uint64_t(info.sm_count));
+    return finish_split(xform ? launch_mode<false, true>(kernel_out_dtype, ta, tb, p, grid, stream)
+                              : launch_mode<false, false>(kernel_out_dtype, ta, tb, p, grid, stream));
 }
 
 }  // namespace klas

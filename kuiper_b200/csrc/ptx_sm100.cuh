@@ -276,6 +276,41 @@ __device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_des
         : "memory");
 }
 
+// The same two instructions with each shared-memory descriptor given as its 32-bit halves.  Only
+// the low half (start address, leading offset) changes from one K step to the next, so the issuing
+// thread keeps it in one register and adds a constant: that thread's instruction count per MMA is
+// what bounds the narrow tiles (a K block of four MMAs cost it 660 cycles with 64-bit descriptor
+// arithmetic per MMA, whatever the tile's width).
+__device__ __forceinline__ void umma_f16_ss_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                   uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_f16_ss_pair_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                        uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Arrives once on the barrier at shared::cluster address `cluster_bar` (own or peer CTA)
 // when every pair-MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {

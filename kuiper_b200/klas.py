@@ -383,16 +383,17 @@ def gemm_tc_strided(A: torch.Tensor, B: torch.Tensor, D: torch.Tensor, *, b_col_
     return D
 
 
-_KNOBS = {"tc_mode": (_lib.KNOB_TC_MODE, {"auto": 0, "single": 1, "narrow": 2, "pair": 3, "wide": 4}),
+_KNOBS = {"tc_mode": (_lib.KNOB_TC_MODE, {"auto": 0, "single": 1, "narrow": 2, "pair": 3, "wide": 4, "slim": 5}),
           "tc_raster": (_lib.KNOB_TC_RASTER, {"auto": 0}), "simt_split_k": (_lib.KNOB_SIMT_SPLIT_K, {"auto": 0}),
           "f64_mode": (_lib.KNOB_F64_MODE, {"auto": 0, "simt": 1}), "simt_tile": (_lib.KNOB_SIMT_TILE, {"auto": -1}),
-          "host_grid": (_lib.KNOB_HOST_GRID, {"auto": -1}), "spmm_slab": (_lib.KNOB_SPMM_SLAB, {"auto": 0})}
+          "host_grid": (_lib.KNOB_HOST_GRID, {"auto": -1}), "spmm_slab": (_lib.KNOB_SPMM_SLAB, {"auto": 0}),
+          "tc_ksplit": (_lib.KNOB_TC_KSPLIT, {"auto": 0, "off": 1})}
 
 
 def debug_set(knob: str, value="auto") -> None:
     """Forces one variant of a kernel choice the library otherwise makes itself (klas_b200_debug_set):
-    knob in {"tc_mode", "tc_raster", "simt_split_k", "f64_mode", "simt_tile", "host_grid", "spmm_slab"}, value a name
-    ("auto" restores the library's choice; tc_mode: "single", "narrow", "pair", "wide"; f64_mode: "simt") or an int."""
+    knob in {"tc_mode", "tc_raster", "simt_split_k", "f64_mode", "simt_tile", "host_grid", "spmm_slab", "tc_ksplit"}, value a name
+    ("auto" restores the library's choice; tc_mode: "single", "narrow", "slim", "pair", "wide"; f64_mode: "simt") or an int."""
     code, names = _KNOBS[knob]
     check(_lib.load().klas_b200_debug_set(code, names[value] if isinstance(value, str) else int(value)))
 

@@ -20,7 +20,7 @@ TOL_F16_OUT = 1e-2
 MAP_CODE = {None: 0, "sqrt": 1, "abs": 2, "square": 3, "relu": 4, "neg": 5}
 
 
-@pytest.fixture(autouse=True, params=["single", "narrow", "wide", "auto"])
+@pytest.fixture(autouse=True, params=["single", "narrow", "slim", "wide", "auto"])
 def tc_mode(request):
     """Single-CTA tiles, wide pair tiles, and the library's own choice (the 256 x 256 pair tiles
     carry no mapping warps and are never chosen for a mapped product)."""

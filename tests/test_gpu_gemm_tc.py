@@ -13,10 +13,10 @@ TOL_BF16_F32 = 2e-3   # bf16 x bf16 -> f32, relative to fp64, component-wise sca
 TOL_F16_F16 = 1e-2    # f16 x f16 -> f16
 
 
-@pytest.fixture(autouse=True, params=["single", "narrow", "pair", "wide", "auto"])
+@pytest.fixture(autouse=True, params=["single", "narrow", "slim", "pair", "wide", "auto"])
 def tc_mode(request):
-    """Every test runs with the single-CTA tiles (256 and 128 columns wide), the CTA-pair tiles, the wide pair
-    tiles and the library's own choice."""
+    """Every test runs with the single-CTA tiles (256, 128 and 64 columns wide), the CTA-pair tiles, the wide
+    pair tiles and the library's own choice."""
     klas.debug_set("tc_mode", request.param)
     yield request.param
     klas.debug_set("tc_mode", "auto")
@@ -179,14 +179,68 @@ def test_tile_choice_does_not_change_results(oracle, rows, cols, expect, tc_mode
     shared = 192
     A, Bt = synth.gemm_bf16(31, rows, cols, shared, b_col_major=True, device="cuda")
     results = {}
-    for mode in ("auto", "single", "narrow", "pair", "wide"):
+    for mode in ("auto", "single", "narrow", "slim", "pair", "wide"):
         klas.debug_set("tc_mode", mode)
         results[mode] = klas.gemm_tc(A, Bt, out_dtype=torch.float32, b_col_major=True)
     torch.cuda.synchronize()
     assert klas.gemm_tc_status() == 0
-    for mode in ("single", "narrow", "pair", "wide"):
+    for mode in ("single", "narrow", "slim", "pair", "wide"):
         assert torch.equal(results["auto"], results[mode]), "%s differs (%s)" % (mode, expect)
     pick = torch.arange(0, rows, 97, device="cuda")
     acc, scale = tc_reference(oracle, A[pick].cpu(), Bt.cpu(), True)
     err = rel_err_componentwise(results["auto"][pick].cpu().numpy(), acc, scale)
     assert err <= 1e-5, "relative error %.3e" % err
+
+
+@pytest.mark.parametrize("parts", [2, 3, 8])
+@pytest.mark.parametrize("rows,cols,shared", [(256, 512, 1024), (328, 200, 1160), (1024, 1024, 4096)])
+def test_k_split_parts_are_added_in_fixed_order(oracle, rows, cols, shared, parts, tc_mode):
+    """A tile's K range cut into parts (the single-CTA and pair kernels; the wide kernel has no
+    split and ignores the knob): the parts' f32 products are added in index order by a second
+    kernel, so the result equals the unsplit product up to fp32 re-association, is the same from
+    run to run, and goes through every output rule: plain, alpha/beta with an old C, 16-bit
+    output, relu."""
+    A, Bt = synth.gemm_bf16(17, rows, cols, shared, b_col_major=True, device="cuda")
+    C0 = torch.randn(rows, cols, device="cuda")
+    klas.debug_set("tc_ksplit", "off")
+    whole = klas.gemm_tc(A, Bt, b_col_major=True)
+    whole_ab = klas.gemm_tc(A, Bt, b_col_major=True, C_=C0, alpha=0.5, beta=-1.25)
+    whole_bf = klas.gemm_tc(A, Bt, b_col_major=True, out_dtype=torch.bfloat16)
+    try:
+        klas.debug_set("tc_ksplit", parts)
+        split = [klas.gemm_tc(A, Bt, b_col_major=True) for _ in range(3)]
+        split_ab = klas.gemm_tc(A, Bt, b_col_major=True, C_=C0, alpha=0.5, beta=-1.25)
+        split_bf = klas.gemm_tc(A, Bt, b_col_major=True, out_dtype=torch.bfloat16)
+        split_relu = klas.gemm_tc(A, Bt, b_col_major=True, comb="relu")
+    finally:
+        klas.debug_set("tc_ksplit", "auto")
+    torch.cuda.synchronize()
+    assert klas.gemm_tc_status() == 0
+    assert torch.equal(split[0], split[1]) and torch.equal(split[0], split[2]), "run-to-run difference"
+    scale = (A.float().abs() @ Bt.float().abs().t()).clamp_min(1e-30)
+    assert float(((split[0] - whole).abs() / scale).max()) <= 1e-6
+    assert float(((split_ab - whole_ab).abs() / (scale + C0.abs())).max()) <= 1e-6
+    assert float(((split_bf.float() - whole_bf.float()).abs() / scale).max()) <= 2 ** -8
+    assert torch.equal(split_relu, split[0].clamp_min(0.0))
+    pick = torch.arange(0, rows, 37, device="cuda")
+    acc, sc = tc_reference(oracle, A[pick].cpu(), Bt.cpu(), True)
+    assert rel_err_componentwise(split[0][pick].cpu().numpy(), acc, sc) <= 1e-5
+
+
+def test_k_split_chosen_for_small_outputs_with_long_k(oracle, tc_mode):
+    """1024 x 1024 x 4096 fills a quarter of the SMs with 128 x 256 tiles: the library cuts K by
+    itself.  The result is checked against the oracle on sampled rows and against the unsplit
+    product."""
+    if tc_mode != "auto":
+        return
+    A, Bt = synth.gemm_bf16(19, 1024, 1024, 4096, b_col_major=True, device="cuda")
+    auto = klas.gemm_tc(A, Bt, b_col_major=True)
+    klas.debug_set("tc_ksplit", "off")
+    whole = klas.gemm_tc(A, Bt, b_col_major=True)
+    klas.debug_set("tc_ksplit", "auto")
+    torch.cuda.synchronize()
+    pick = torch.arange(0, 1024, 61, device="cuda")
+    acc, sc = tc_reference(oracle, A[pick].cpu(), Bt.cpu(), True)
+    assert rel_err_componentwise(auto[pick].cpu().numpy(), acc, sc) <= 1e-5
+    scale = (A.float().abs() @ Bt.float().abs().t())
+    assert float(((auto - whole).abs() / scale).max()) <= 1e-6

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 TOL = {torch.float32: 1e-5, torch.float16: 1e-2, torch.bfloat16: 2e-2}
 
 
-@pytest.fixture(autouse=True, params=["single", "narrow", "wide", "auto"])
+@pytest.fixture(autouse=True, params=["single", "narrow", "slim", "wide", "auto"])
 def tc_mode(request):
     klas.debug_set("tc_mode", request.param)
     yield request.param
