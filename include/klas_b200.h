@@ -163,6 +163,14 @@ int klas_b200_gemm_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, ui
  * Requires shared % 8 == 0, cols % 8 == 0 and 16-byte aligned A, B, C, D.
  * `status_word`: optional device int (may be NULL) that receives a non-zero
  * code when a bounded device-side wait gives up.
+ * A small output with a long shared dimension (128 x 256 tiles filling less than half of the SMs,
+ * e.g. 1024 x 1024 x 4096) is computed as up to 8 partial products over parts of the shared
+ * dimension, which a second kernel on the same stream adds in a fixed order: the result is the
+ * same from run to run and within fp32 re-association of the one-pass product.  The parts live
+ * in a device buffer the library keeps per (device, stream), allocated at the first such call on
+ * the stream (a call that would have to allocate while the stream is recording a CUDA graph
+ * runs in one pass instead) and freed by klas_b200_release_workspace(); at most 8 streams per
+ * device get one, further streams run in one pass.  KLAS_KNOB_TC_KSPLIT = 1 turns the split off.
  *
  * Replaces: Klas_GEMM_TensorCore2D_g_gemm_{bf16_f32,f16_f16}_* (dist/Klas_GEMM_TensorCore2D.h:8-1220),
  * Klas_GEMM_TensorCore2D_To_g_gemm_bf16_f32_bf16_* (dist/Klas_GEMM_TensorCore2D_To.h),
@@ -556,7 +564,8 @@ typedef enum klas_knob_e {
 int klas_b200_debug_set(int knob, int value);
 int klas_b200_debug_get(int knob);
 
-/* Frees the calling device's host-variant workspace. */
+/* Frees the calling device's workspaces: the host-variant staging buffers and the partial-product
+ * buffers of the tensor-core GEMM's K split.  Synchronises the device. */
 int klas_b200_release_workspace(void);
 
 #ifdef __cplusplus
