@@ -13,7 +13,7 @@
 //               128-byte-swizzled A operand into shared memory.  O accumulates in tensor memory across
 //               the tiles; m follows the running maximum only in steps of 2^8 or more, and only then
 //               are O (tcgen05.ld / st) and l rescaled.
-// Where a tile's time goes (cycle counters of one softmax warp, -DKLAS_FA_PROFILE): of ~2950 cycles
+// Where a tile's time goes (cycle counters of one softmax warp, in a scratch build): of ~2950 cycles
 // per 128 x 128 tile at E = 128, 1340 are the exponentials -- the special-function unit's rate for
 // the two warps of a scheduler, 2 x 64 x 8 cycles -- and the rest is the serial chain around them
 // (wait for S and load it 540, maximum 200, exchange 300, wait for the previous P.V 275, store and
@@ -38,6 +38,8 @@
 // src/lib/kernel/Kuiper.Kernel.SDPA.Naive.fst:390-470 (GEMM, row softmax, GEMM through global
 // memory) and src/lib/kernel/Kuiper.Kernel.FlashAttention.fst (one thread block per query tile,
 // running maximum and sum per row).
+#include <atomic>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -61,15 +63,6 @@ constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
 enum : int { SITE_FA = 0x200 };
 
-#ifdef KLAS_FA_PROFILE
-// Developer build only: cycles one softmax warp of CTA 0 spends in each phase of a tile.
-__device__ unsigned long long g_fa_prof[8];
-#define FA_T(n) const long long fa_t##n = clock64()
-#define FA_ACC(slot, a, b) fa_acc[slot] += (unsigned long long)(fa_t##b - fa_t##a)
-#else
-#define FA_T(n)
-#define FA_ACC(slot, a, b)
-#endif
 
 template <uint32_t E>
 struct Cfg {
@@ -313,12 +306,8 @@ __global__ void __launch_bounds__(THREADS, 1)
             if (w) ptx::tc_fence_after_sync();
             return w;
         };
-#ifdef KLAS_FA_PROFILE
-        unsigned long long fa_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
         for (uint32_t j = 0; ok && j < p.num_kv; ++j) {
             const uint32_t sb = j & 1u;
-            FA_T(0);
             ok = lane != 0 || bounded_wait(s_full(sb), (j / 2) & 1u, ctl, 0x31, 32);
             ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
             if (!ok) break;
@@ -331,7 +320,6 @@ __global__ void __launch_bounds__(THREADS, 1)
             ptx::tmem_ld_32x32b_x32(s_addr, sv[0]);
             ptx::tmem_ld_32x32b_x32(s_addr + 32u, sv[1]);
             ptx::tmem_ld_wait();
-            FA_T(1);
             if (valid < 64u) {
 #pragma unroll
                 for (uint32_t c = 0; c < 2; ++c)
@@ -351,11 +339,9 @@ __global__ void __launch_bounds__(THREADS, 1)
                 for (uint32_t i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             float other_mx;
-            FA_T(2);
             ok = trade(xchg + (sb * 2 + half) * BM + r, xchg + (sb * 2 + (half ^ 1u)) * BM + r, mx, j + 1, other_mx);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            FA_T(3);
             const float m_cand = fmaxf(m, fmaxf(mx, other_mx) * p.scale_log2);
             // The reference point m only has to keep exp2(x - m) in range, so it is moved (and the sums
             // so far rescaled) only when the maximum has grown by more than 2^8; until then P.V simply
@@ -401,32 +387,17 @@ __global__ void __launch_bounds__(THREADS, 1)
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             // P of the previous tile must have been consumed before it is overwritten
-            FA_T(4);
             if (!pv_done) {
                 ok = wait_pv(j - 1, 0x35);
                 if (!ok) break;
             }
-            FA_T(5);
 #pragma unroll
             for (uint32_t piece = 0; piece < 8; ++piece)          // eight 16-byte pieces of 8 keys, swizzled A operand
                 ptx::sts128(p_base + half * ATOM_BYTES + r * 128u + ((piece ^ (r & 7u)) * 16u), pw[piece]);
-            FA_T(6);
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(p_full);
-            FA_T(7);
-            FA_ACC(0, 0, 1);   // wait for S + load
-            FA_ACC(1, 1, 2);   // mask, release, max
-            FA_ACC(2, 2, 3);   // trade
-            FA_ACC(3, 3, 4);   // rescale decision, exponentials, packing
-            FA_ACC(4, 4, 5);   // wait for the previous P.V
-            FA_ACC(5, 5, 6);   // stores of P
-            FA_ACC(6, 6, 7);   // fence + arrive
         }
-#ifdef KLAS_FA_PROFILE
-        if (blockIdx.x == 0 && warp == FIRST_SOFTMAX_WARP && lane == 0)
-            for (int i = 0; i < 8; ++i) g_fa_prof[i] = fa_acc[i];
-#endif
         if (ok && p.num_kv > 0) ok = wait_pv(p.num_kv - 1, 0x33);
         if (ok) {
             // the row sum is the sum of the two partial sums (both relative to the same m)
@@ -472,11 +443,6 @@ __global__ void __launch_bounds__(THREADS, 1)
 
 }  // namespace fa
 
-#ifdef KLAS_FA_PROFILE
-extern "C" int klas_dev_read_fa_profile(unsigned long long *out) {
-    return cudaMemcpyFromSymbol(out, fa::g_fa_prof, sizeof(unsigned long long) * 8) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 int umma_status_address(int **out);
 int make_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t inner, uint64_t outer, uint64_t batch,
@@ -485,7 +451,7 @@ int make_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t i
 template <uint32_t E>
 static int launch_sdpa_e(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const fa::Params &p,
                          unsigned grid, cudaStream_t stream) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {

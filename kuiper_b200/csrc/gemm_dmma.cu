@@ -18,6 +18,8 @@
 // dist/Klas_GEMM_BlockTiling1D.cu and dist/Klas_GEMM_Naive{1,2,3}.cu.
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "klas_internal.h"
 
 namespace klas {
@@ -185,7 +187,7 @@ int launch_gemm_dmma(uint32_t batch, uint64_t m, uint64_t n, uint64_t k, const d
     a.beta = beta ? *beta : 0.0;
     const uint64_t blocks = a.tiles_m * a.tiles_n * batch;
     if (blocks > 0x7fffffffull) return fail(KLAS_ERR_TOO_LARGE, "gemm: too many tiles for one grid");
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {

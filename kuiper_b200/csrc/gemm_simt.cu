@@ -26,6 +26,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <type_traits>
@@ -430,7 +431,7 @@ static int launch_kernel(const Args<T> &a, unsigned blocks, cudaStream_t stream)
     constexpr int PAD = 16 / sizeof(T);
     constexpr size_t SMEM = sizeof(T) * 2 * BK * (BM + PAD + BN + PAD);
     if constexpr (SMEM > 48 * 1024) {
-        static bool configured[64] = {};
+        static std::atomic<bool> configured[64] = {};
         int dev = 0;
         KLAS_TRY_CUDA(cudaGetDevice(&dev));
         if (dev < 0 || dev >= 64 || !configured[dev]) {
