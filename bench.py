@@ -77,10 +77,12 @@ class ClockSampler:
     REASONS = {
         0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
         0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown",
+        0x2: "applications_clocks_setting", 0x10: "sync_boost", 0x100: "display_clock_setting",
     }
 
     def __init__(self, index: int):
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.mask, self.watts = 0, []   # every reason bit seen (0x1 = idle included), board power
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -105,9 +107,11 @@ class ClockSampler:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
                 mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(
                     nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.mask |= mask
                 for bit, name in self.REASONS.items():
                     if mask & bit:
                         self.reasons.add(name)
+                self.watts.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
             except Exception:
                 pass
             time.sleep(0.002)
@@ -126,8 +130,15 @@ class ClockSampler:
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        out = {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+               "reasons": sorted(self.reasons), "samples": len(self.samples), "reasons_mask": hex(self.mask)}
+        if self.watts:
+            out["power_w"] = round(statistics.median(self.watts), 1)
+            try:
+                out["power_limit_w"] = self.nv.nvmlDeviceGetEnforcedPowerLimit(self.h) / 1000.0
+            except Exception:
+                pass
+        return out
 
 
 # --------------------------------------------------------------------------- workloads
