@@ -244,3 +244,22 @@ def test_k_split_chosen_for_small_outputs_with_long_k(oracle, tc_mode):
     assert rel_err_componentwise(auto[pick].cpu().numpy(), acc, sc) <= 1e-5
     scale = (A.float().abs() @ Bt.float().abs().t())
     assert float(((auto - whole).abs() / scale).max()) <= 1e-6
+
+
+def test_k_split_with_pages_and_row_major_b(tc_mode):
+    """The split's workspace holds parts x pages partial products; checked against the unsplit
+    product of the same pages (f16, row-major B, 16-bit output)."""
+    A, B = synth.gemm_f16_batched(23, 3, 200, 264, 1096, device="cuda")
+    klas.debug_set("tc_ksplit", "off")
+    whole = klas.gemm_tc(A, B, out_dtype=torch.float16)
+    try:
+        klas.debug_set("tc_ksplit", 5)
+        split = klas.gemm_tc(A, B, out_dtype=torch.float16)
+        again = klas.gemm_tc(A, B, out_dtype=torch.float16)
+    finally:
+        klas.debug_set("tc_ksplit", "auto")
+    torch.cuda.synchronize()
+    assert klas.gemm_tc_status() == 0
+    assert torch.equal(split, again)
+    scale = torch.bmm(A.float().abs(), B.float().abs())
+    assert float(((split.float() - whole.float()).abs() / scale).max()) <= 2 ** -9
