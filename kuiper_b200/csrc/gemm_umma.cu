@@ -33,6 +33,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "klas_internal.h"
 #include "ptx_sm100.cuh"
@@ -350,95 +351,109 @@ __device__ __forceinline__ float comb_f32(float old, float acc, float alpha, flo
     else return fmaf(alpha, acc, beta * old);
 }
 
-// Writes 32 consecutive columns of one output row (`acc` = this lane's slice of
-// the accumulator) with 16-byte accesses.  `ncols_left` = columns of the matrix
-// remaining from the first of the 32 (a multiple of 8 by the entry point's contract).
-// COMB says how the old values at `crow` enter; without `crow` the accumulator is written
-// as it is (`relu`: its positive part).
-template <typename OutT, uint32_t COMB>
-__device__ __forceinline__ void store_row_chunk_t(const uint32_t (&acc)[32], OutT *drow,
-                                                  const OutT *crow, float alpha, float beta,
-                                                  uint32_t ncols_left, bool relu, float plain_scale) {
-    constexpr uint32_t VEC = 16 / sizeof(OutT);  // elements per 16-byte access
-#pragma unroll
-    for (uint32_t v0 = 0; v0 < 32; v0 += VEC) {
-        if (v0 < ncols_left) {
-            union {
-                uint4 raw;
-                OutT e[VEC];
-            } out, cin;
-            if (crow != nullptr) {
-                cin.raw = *reinterpret_cast<const uint4 *>(crow + v0);
-#pragma unroll
-                for (uint32_t j = 0; j < VEC; ++j)
-                    out.e[j] = OutTraits<OutT>::from_f32(comb_f32<COMB>(
-                        OutTraits<OutT>::to_f32(cin.e[j]), __uint_as_float(acc[v0 + j]), alpha, beta));
-            } else {
-#pragma unroll
-                for (uint32_t j = 0; j < VEC; ++j) {
-                    const float a = __uint_as_float(acc[v0 + j]) * plain_scale;
-                    out.e[j] = OutTraits<OutT>::from_f32(relu ? fmaxf(a, 0.0f) : a);
-                }
-            }
-            *reinterpret_cast<uint4 *>(drow + v0) = out.raw;
-        }
-    }
-}
+// One 32-row x 128-byte block of the old C as a warp fetches it: four rows per instruction, 8 lanes
+// per row, 128 contiguous bytes (`q[i]` is this lane's 16 bytes of row 4 i + lane / 8).
+struct OldBlock {
+    uint4 q[8];
+};
 
 template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(const uint32_t (&acc)[32], OutT *drow, const OutT *crow,
-                                                float alpha, float beta, uint32_t ncols_left, uint32_t comb) {
-    switch (comb) {
-        case KLAS_COMB_MAX: store_row_chunk_t<OutT, KLAS_COMB_MAX>(acc, drow, crow, alpha, beta, ncols_left, false, 1.0f); break;
-        case KLAS_COMB_MIN: store_row_chunk_t<OutT, KLAS_COMB_MIN>(acc, drow, crow, alpha, beta, ncols_left, false, 1.0f); break;
-        case KLAS_COMB_MUL: store_row_chunk_t<OutT, KLAS_COMB_MUL>(acc, drow, crow, alpha, beta, ncols_left, false, 1.0f); break;
-        default:
-            store_row_chunk_t<OutT, KLAS_COMB_AXPBY>(acc, drow, crow, alpha, beta, ncols_left, comb == KLAS_COMB_RELU,
-                                                     comb == KLAS_COMB_SCALED ? alpha : 1.0f);
-            break;
+__device__ __forceinline__ void load_old_block(OldBlock &ob, const OutT *C, uint32_t col_blk, uint32_t row0,
+                                               uint32_t b, uint32_t lane, const Params &p) {
+    const uint32_t gcol = col_blk + (lane & 7u) * (16 / sizeof(OutT));
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        const uint32_t r = i * 4u + (lane >> 3);
+        ob.q[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (row0 + r < p.M && gcol < p.N)   // plain loads: C may be D (in-place accumulate)
+            ob.q[i] = *reinterpret_cast<const uint4 *>(C + size_t(b) * p.sd + size_t(row0 + r) * p.ldd + gcol);
     }
 }
 
-// Output path of a product that meets no old C: converts one chunk (32 rows x 32 columns, lane r
-// holding row r) and transposes it through shared memory so that global stores are coalesced.
+// Output path of the accumulators: converts one chunk (32 rows x 32 columns, lane r holding row r)
+// and transposes it through shared memory so that global accesses are coalesced.
 // Lane r writes 16-byte piece j of its row to piece (j ^ (r & 7)) of a 32-row x 128-byte block
 // (conflict-free); once the block's last chunk is staged the warp reads it back four rows per
 // instruction -- 8 lanes per row, 128 contiguous bytes -- and stores those.  A warp storing its
-// own rows directly would touch 32 different lines per instruction: measured on the 128 x 256
+// own rows directly touches 32 different lines per instruction: measured on the 128 x 256
 // tile at 2048^3, 9100 cycles per tile of a 43000-cycle kernel.  `c` is the chunk's index in
 // the tile (it decides the position within the block), `col` its first column, `row0` the
 // warp's first row, `buf` the warp's staging block.
+// With an old C (alpha / beta, max / min / mul, in-place accumulate) the block of C travels the
+// other way first: `ob` holds it (fetched coalesced while the previous block was on its way out),
+// it is laid into the staging block in the same swizzle, each lane picks up its own row's pieces
+// from there, combines and overwrites them.  `next_col_blk` < `tile_end`: the block to fetch next.
+// (Each lane reading and writing its own row of C and D in global memory made the alpha/beta
+// product at 8192^3 take 1.00-1.14 ms against 0.74 ms for the plain one, 0.38 against 0.12 ms at K = 1024.)
 template <typename OutT>
 __device__ __forceinline__ void emit_staged(const uint32_t (&v)[32], uint32_t c, uint32_t col, uint32_t row0,
                                             uint32_t b, uint32_t buf, uint32_t lane, const Params &p,
-                                            bool relu, float plain_scale) {
+                                            bool relu, float plain_scale, const OutT *C = nullptr,
+                                            OldBlock *ob = nullptr, uint32_t next_col_blk = 0, uint32_t tile_end = 0) {
     constexpr uint32_t COLS_PER_BLOCK = 128 / sizeof(OutT);     // columns of one 128-byte staging row
     constexpr uint32_t CHUNKS_PER_BLOCK = COLS_PER_BLOCK / 32;  // TMEM chunks (32 columns) per block
     constexpr uint32_t PIECES = 32 * sizeof(OutT) / 16;         // 16-byte pieces per chunk per row
+    constexpr uint32_t VEC = 16 / sizeof(OutT);
     OutT *const D = static_cast<OutT *>(p.D);
     const uint32_t sub = c % CHUNKS_PER_BLOCK;
+    if (C != nullptr && sub == 0) {
 #pragma unroll
-    for (uint32_t j = 0; j < PIECES; ++j) {
-        union {
-            uint4 raw;
-            OutT e[16 / sizeof(OutT)];
-        } pk;
-#pragma unroll
-        for (uint32_t e = 0; e < 16 / sizeof(OutT); ++e) {
-            const float a = __uint_as_float(v[j * (16 / sizeof(OutT)) + e]) * plain_scale;
-            pk.e[e] = OutTraits<OutT>::from_f32(relu ? fmaxf(a, 0.0f) : a);
+        for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t r = i * 4u + (lane >> 3);
+            const uint32_t addr = buf + r * 128u + (((lane & 7u) ^ (r & 7u)) * 16u);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(ob->q[i].x), "r"(ob->q[i].y),
+                         "r"(ob->q[i].z), "r"(ob->q[i].w)
+                         : "memory");
         }
-        const uint32_t piece = (sub * PIECES + j) ^ (lane & 7u);
-        const uint32_t addr = buf + lane * 128u + piece * 16u;
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.raw.x),
-                     "r"(pk.raw.y), "r"(pk.raw.z), "r"(pk.raw.w)
-                     : "memory");
+        __syncwarp();
+        if (next_col_blk < tile_end) load_old_block<OutT>(*ob, C, next_col_blk, row0, b, lane, p);
+    }
+    auto stage_pieces = [&](auto comb_tag) {
+        constexpr uint32_t COMB = decltype(comb_tag)::value;
+#pragma unroll
+        for (uint32_t j = 0; j < PIECES; ++j) {
+            union {
+                uint4 raw;
+                OutT e[VEC];
+            } pk, old;
+            const uint32_t piece = (sub * PIECES + j) ^ (lane & 7u);
+            const uint32_t addr = buf + lane * 128u + piece * 16u;
+            if (C != nullptr) {
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(old.raw.x), "=r"(old.raw.y), "=r"(old.raw.z), "=r"(old.raw.w)
+                             : "r"(addr)
+                             : "memory");
+#pragma unroll
+                for (uint32_t e = 0; e < VEC; ++e)
+                    pk.e[e] = OutTraits<OutT>::from_f32(comb_f32<COMB>(OutTraits<OutT>::to_f32(old.e[e]),
+                                                                        __uint_as_float(v[j * VEC + e]), p.alpha, p.beta));
+            } else {
+#pragma unroll
+                for (uint32_t e = 0; e < VEC; ++e) {
+                    const float a = __uint_as_float(v[j * VEC + e]) * plain_scale;
+                    pk.e[e] = OutTraits<OutT>::from_f32(relu ? fmaxf(a, 0.0f) : a);
+                }
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk.raw.x),
+                         "r"(pk.raw.y), "r"(pk.raw.z), "r"(pk.raw.w)
+                         : "memory");
+        }
+    };
+    if (C == nullptr) {
+        stage_pieces(std::integral_constant<uint32_t, KLAS_COMB_AXPBY>{});
+    } else {
+        switch (p.comb) {
+            case KLAS_COMB_MAX: stage_pieces(std::integral_constant<uint32_t, KLAS_COMB_MAX>{}); break;
+            case KLAS_COMB_MIN: stage_pieces(std::integral_constant<uint32_t, KLAS_COMB_MIN>{}); break;
+            case KLAS_COMB_MUL: stage_pieces(std::integral_constant<uint32_t, KLAS_COMB_MUL>{}); break;
+            default: stage_pieces(std::integral_constant<uint32_t, KLAS_COMB_AXPBY>{}); break;
+        }
     }
     if (sub == CHUNKS_PER_BLOCK - 1) {
         __syncwarp();
         const uint32_t col_blk = col - sub * 32u;
         const uint32_t piece = lane & 7u;
-        const uint32_t gcol = col_blk + piece * (16 / sizeof(OutT));
+        const uint32_t gcol = col_blk + piece * VEC;
 #pragma unroll
         for (uint32_t i = 0; i < 8; ++i) {
             const uint32_t r = i * 4u + (lane >> 3);
@@ -520,7 +535,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceArgs a) 
 
 // XFORM adds four warps that map the staged A / B bytes in place between the copy and the MMA
 // (single-CTA tiles only).
-template <typename OutT, bool PAIR, bool XFORM = false>
+// OLD_C: the instantiation whose epilogue meets an old C (alpha / beta, max / min / mul, in-place
+// accumulate).  Products without one run instantiations that carry none of that path's registers.
+template <typename OutT, bool PAIR, bool XFORM = false, bool OLD_C = false>
 __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
     gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b, const Params p) {
@@ -743,35 +760,36 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
-        OutT *const D = static_cast<OutT *>(p.D);
-        const OutT *const C = static_cast<const OutT *>(p.C);
+        const OutT *const C = OLD_C ? static_cast<const OutT *>(p.C) : nullptr;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (uint32_t w = group; ok && w < p.num_work; w += num_groups) {
             const WorkItem wi(w, p);
             uint32_t b, tm, tn;
             decode_tile(wi.tile, p, b, tm, tn);
+            const uint32_t row0 = tm * S::TILE_M + cta_rank * BM + quad * 32u;
+            const uint32_t tile_n = PAIR ? BN : p.tile_n;
+            const uint32_t col0 = tn * tile_n;
+            const uint32_t page = b * p.ksplit + wi.part;   // = b unless K is split (a split launch has no old C)
+            constexpr uint32_t COLS_PER_BLOCK = 128 / sizeof(OutT);
+            // the first block of the old C is on its way while the accumulator is still being computed
+            OldBlock old_c;
+            if (C != nullptr) load_old_block<OutT>(old_c, C, col0, row0, page, lane, p);
             if (p.num_kb > 0) {
                 ok = lane != 0 || bounded_wait(tfull_bar(acc), acc_phase, ctl, SITE_EPI_TMEM_FULL, WAIT_LIMIT_NS, 128);
                 ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;   // lane 0 polls, the warp follows
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
             }
-            const uint32_t row0 = tm * S::TILE_M + cta_rank * BM + quad * 32u;
-            const uint32_t row = row0 + lane;
-            const uint32_t tile_n = PAIR ? BN : p.tile_n;
-            const uint32_t col0 = tn * tile_n;
-            const size_t row_off = size_t(b) * p.sd + size_t(row) * p.ldd;
             const uint32_t buf = epi_base + (warp - 2) * EPI_BLOCK_BYTES;
             const uint32_t taddr0 = tmem_base + ((quad * 32u) << 16) + acc * BN;
             const bool relu = p.comb == KLAS_COMB_RELU;
             const float plain_scale = p.comb == KLAS_COMB_SCALED ? p.alpha : 1.0f;   // x * 1.0f is exact
             const bool have_acc = p.num_kb > 0;
             const uint32_t nchunk = tile_n / 32;   // 2, 4 or 8
-            const uint32_t page = b * p.ksplit + wi.part;   // = b unless K is split
-            if (C == nullptr) {
-                // Plain product: chunks leave through the staging block, with the next chunk's
-                // tcgen05.ld in flight while the current one is converted and stored.
+            {
+                // Chunks leave through the staging block (with an old C: after meeting it there), the
+                // next chunk's tcgen05.ld in flight while the current one is converted and stored.
                 uint32_t va[32], vb[32];
                 if (have_acc) {
                     ptx::tmem_ld_32x32b_x32(taddr0, va);
@@ -779,33 +797,23 @@ __global__ void __launch_bounds__(NUM_THREADS + (XFORM ? XFORM_THREADS : 0), 1)
 #pragma unroll
                     for (uint32_t j = 0; j < 32; ++j) va[j] = vb[j] = 0u;
                 }
+                auto emit = [&](const uint32_t (&v)[32], uint32_t c) {
+                    const uint32_t col = col0 + c * 32u;
+                    const uint32_t next_blk = col - (c % (COLS_PER_BLOCK / 32)) * 32u + COLS_PER_BLOCK;
+                    emit_staged<OutT>(v, c, col, row0, page, buf, lane, p, relu, plain_scale, C, &old_c, next_blk, col0 + tile_n);
+                };
 #pragma unroll 1
                 for (uint32_t c = 0; c < nchunk; c += 2) {
                     if (have_acc) {
                         ptx::tmem_ld_wait();
                         ptx::tmem_ld_32x32b_x32(taddr0 + (c + 1) * 32u, vb);
                     }
-                    emit_staged<OutT>(va, c, col0 + c * 32u, row0, page, buf, lane, p, relu, plain_scale);
+                    emit(va, c);
                     if (have_acc) {
                         ptx::tmem_ld_wait();
                         if (c + 2 < nchunk) ptx::tmem_ld_32x32b_x32(taddr0 + (c + 2) * 32u, va);
                     }
-                    emit_staged<OutT>(vb, c + 1, col0 + (c + 1) * 32u, row0, page, buf, lane, p, relu, plain_scale);
-                }
-            } else {
-#pragma unroll 1
-                for (uint32_t c = 0; c < tile_n / 32; ++c) {
-                    uint32_t v[32];
-                    if (p.num_kb > 0) {
-                        ptx::tmem_ld_32x32b_x32(taddr0 + c * 32u, v);
-                        ptx::tmem_ld_wait();
-                    } else {
-#pragma unroll
-                        for (uint32_t j = 0; j < 32; ++j) v[j] = 0u;
-                    }
-                    const uint32_t col = col0 + c * 32u;
-                    if (row < p.M && col < p.N)
-                        store_row_chunk<OutT>(v, D + row_off + col, C + row_off + col, p.alpha, p.beta, p.N - col, p.comb);
+                    emit(vb, c + 1);
                 }
             }
             if (p.num_kb > 0) {
@@ -880,7 +888,7 @@ enum : int { SITE_WIDE = 0x100 };
 // stages in turn.  Each CTA then counts its own copies on its own barrier, the stage's mapping
 // warp waits there, and the two warps of the pair (one per CTA) report to a barrier of the even
 // CTA that the MMA thread waits on.
-template <typename OutT, bool XFORM = false>
+template <typename OutT, bool XFORM = false, bool OLD_C = false>
 __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1)
     gemm_umma_wide_kernel(const __grid_constant__ CUtensorMap tm_a,
                           const __grid_constant__ CUtensorMap tm_b, const Params p) {
@@ -1061,8 +1069,7 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
         // the accumulator back as soon as its last chunk is in registers.
         const uint32_t quad = warp & 3u;
         const uint32_t h = (warp - 2) >> 2;
-        OutT *const D = static_cast<OutT *>(p.D);
-        const OutT *const C = static_cast<const OutT *>(p.C);
+        const OutT *const C = OLD_C ? static_cast<const OutT *>(p.C) : nullptr;
         constexpr uint32_t NCHUNK = BN / 32;
         const uint32_t buf = epi_base + (warp - 2) * EPI_BUF_BYTES;
         const uint32_t tempty_cta0 = ptx::map_to_cta(tempty_bar, 0);
@@ -1075,27 +1082,23 @@ __global__ void __launch_bounds__(wide::THREADS + (XFORM ? XFORM_THREADS : 0), 1
             uint32_t b, tm, tn;
             decode_tile(t, p, b, tm, tn);
             const bool have_acc = p.num_kb > 0;
+            const uint32_t row0 = tm * TILE_M + cta_rank * A_ROWS + h * BM + quad * 32u;
+            constexpr uint32_t COLS_PER_BLOCK = 128 / sizeof(OutT);
+            // the first block of the old C is on its way while the accumulator is still being computed
+            OldBlock old_c;
+            if (C != nullptr) load_old_block<OutT>(old_c, C, tn * BN, row0, b, lane, p);
             if (have_acc) {
                 ok = lane != 0 || bounded_wait(tfull_bar, tile_phase, ctl, SITE_WIDE | SITE_EPI_TMEM_FULL, WAIT_LIMIT_NS, 128);
                 ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;   // lane 0 polls, the warp follows
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
             }
-            const uint32_t row0 = tm * TILE_M + cta_rank * A_ROWS + h * BM + quad * 32u;
-            const uint32_t row = row0 + lane;
-            const size_t row_off = size_t(b) * p.sd + size_t(row) * p.ldd;
 
-            // One chunk either goes out directly (alpha/beta path, C read with plain loads) or
-            // through the warp's staging block (emit_staged).
+            // Every chunk goes through the warp's staging block (emit_staged), where it meets the old C if there is one.
             auto emit = [&](const uint32_t (&v)[32], uint32_t c) {
                 const uint32_t col = tn * BN + c * 32u;
-                if (C != nullptr) {
-                    if (row < p.M && col < p.N)
-                        store_row_chunk<OutT>(v, D + row_off + col, C + row_off + col, p.alpha, p.beta,
-                                              p.N - col, p.comb);
-                    return;
-                }
-                emit_staged<OutT>(v, c, col, row0, b, buf, lane, p, relu, plain_scale);
+                const uint32_t next_blk = col - (c % (COLS_PER_BLOCK / 32)) * 32u + COLS_PER_BLOCK;
+                emit_staged<OutT>(v, c, col, row0, b, buf, lane, p, relu, plain_scale, C, &old_c, next_blk, (tn + 1) * BN);
             };
 
             uint32_t va[32], vb[32];
@@ -1210,14 +1213,14 @@ static int make_map(CUtensorMap *map, int dtype, const void *base, uint64_t inne
     return KLAS_OK;
 }
 
-template <typename OutT, bool XFORM>
-static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
-                             cudaStream_t stream) {
+template <typename OutT, bool XFORM, bool OLD_C>
+static int launch_wide_typed_c(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
+                               cudaStream_t stream) {
     static std::atomic<bool> configured[64] = {};
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_wide_kernel<OutT, XFORM>,
+        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_wide_kernel<OutT, XFORM, OLD_C>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
@@ -1233,19 +1236,26 @@ static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_wide_kernel<OutT, XFORM>, ta, tb, p),
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_wide_kernel<OutT, XFORM, OLD_C>, ta, tb, p),
                       "gemm_umma_wide_kernel launch");
 }
 
-template <typename OutT, bool PAIR, bool XFORM>
-static int launch_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
-                        cudaStream_t stream) {
+template <typename OutT, bool XFORM>
+static int launch_wide_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
+                             cudaStream_t stream) {
+    return p.C != nullptr ? launch_wide_typed_c<OutT, XFORM, true>(ta, tb, p, grid, stream)
+                          : launch_wide_typed_c<OutT, XFORM, false>(ta, tb, p, grid, stream);
+}
+
+template <typename OutT, bool PAIR, bool XFORM, bool OLD_C>
+static int launch_typed_c(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
+                          cudaStream_t stream) {
     constexpr uint32_t SMEM = Shape<PAIR>::SMEM_BYTES;
     static std::atomic<bool> configured[64] = {};
     int dev = 0;
     KLAS_TRY_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<OutT, PAIR, XFORM>,
+        KLAS_TRY_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<OutT, PAIR, XFORM, OLD_C>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
@@ -1261,8 +1271,15 @@ static int launch_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Para
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_kernel<OutT, PAIR, XFORM>, ta, tb, p),
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_umma_kernel<OutT, PAIR, XFORM, OLD_C>, ta, tb, p),
                       "gemm_umma_kernel launch");
+}
+
+template <typename OutT, bool PAIR, bool XFORM>
+static int launch_typed(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p, int grid,
+                        cudaStream_t stream) {
+    return p.C != nullptr ? launch_typed_c<OutT, PAIR, XFORM, true>(ta, tb, p, grid, stream)
+                          : launch_typed_c<OutT, PAIR, XFORM, false>(ta, tb, p, grid, stream);
 }
 
 template <bool PAIR, bool XFORM>
