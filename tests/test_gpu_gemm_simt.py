@@ -221,3 +221,44 @@ def test_two_ctas_per_tile_along_k(oracle, m, n, k):
         assert rel_err_componentwise(got.cpu().numpy(), acc, scale) <= TOL_F32
     assert torch.equal(split1, split2)
     assert torch.equal(uw, us)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.int32, torch.int64, torch.float64])
+@pytest.mark.parametrize("m,n,k,batch", [(1000, 1000, 1000, 1), (130, 260, 36, 3), (1, 8, 8, 1), (515, 132, 2052, 1)])
+def test_shapes_of_whole_vectors_but_not_whole_tiles(dt, m, n, k, batch):
+    """Rows that are whole 16-byte vectors without being whole tiles take the vector kernel with
+    guarded edges: checked against fp64 / wrapping integer arithmetic, with alpha and beta, and
+    with sentinels on both sides of C."""
+    klas.debug_set("f64_mode", "simt")
+    try:
+        if dt in (torch.int32, torch.int64):
+            A = torch.randint(-2 ** 20, 2 ** 20, (batch, m, k), device="cuda", dtype=dt)
+            B = torch.randint(-2 ** 20, 2 ** 20, (batch, k, n), device="cuda", dtype=dt)
+            C0 = torch.randint(-2 ** 20, 2 ** 20, (batch, m, n), device="cuda", dtype=dt)
+            want = torch.bmm(A.cpu().to(torch.int64), B.cpu().to(torch.int64))
+            want_ab = (3 * want + 5 * C0.cpu().to(torch.int64)).to(dt)
+            want = want.to(dt)       # wraps
+        else:
+            A = torch.randn(batch, m, k, device="cuda").to(dt)
+            B = torch.randn(batch, k, n, device="cuda").to(dt)
+            C0 = torch.randn(batch, m, n, device="cuda").to(dt)
+            want = torch.bmm(A.double().cpu(), B.double().cpu())
+            want_ab = 3 * want + 5 * C0.double().cpu()
+        guard = 4096
+        flat = torch.full((guard + batch * m * n + guard,), 7, device="cuda", dtype=dt)
+        Cv = flat[guard:guard + batch * m * n].view(batch, m, n)
+        klas.gemm(A, B, Cv)
+        torch.cuda.synchronize()
+        assert bool((flat[:guard] == 7).all()) and bool((flat[-guard:] == 7).all()), "wrote outside C"
+        Cab = C0.clone()
+        klas.gemm(A, B, Cab, alpha=3, beta=5)
+        torch.cuda.synchronize()
+        if dt in (torch.int32, torch.int64):
+            assert torch.equal(Cv.cpu(), want) and torch.equal(Cab.cpu(), want_ab)
+        else:
+            scale = torch.bmm(A.double().abs().cpu(), B.double().abs().cpu())
+            tol = 1e-5 if dt == torch.float32 else 1e-13
+            assert float(((Cv.double().cpu() - want).abs() / scale).max()) <= tol
+            assert float(((Cab.double().cpu() - want_ab).abs() / (3 * scale + 5 * C0.double().abs().cpu())).max()) <= tol
+    finally:
+        klas.debug_set("f64_mode", "auto")
