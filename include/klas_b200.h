@@ -170,7 +170,9 @@ int klas_b200_gemm_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, ui
  * in a device buffer the library keeps per (device, stream), allocated at the first such call on
  * the stream (a call that would have to allocate while the stream is recording a CUDA graph
  * runs in one pass instead) and freed by klas_b200_release_workspace(); at most 8 streams per
- * device get one, further streams run in one pass.  KLAS_KNOB_TC_KSPLIT = 1 turns the split off.
+ * device get one, further streams run in one pass.  A CUDA graph that recorded such a call holds
+ * the buffer's address: do not release the workspace while the graph may still be launched.
+ * KLAS_KNOB_TC_KSPLIT = 1 turns the split off.
  *
  * Replaces: Klas_GEMM_TensorCore2D_g_gemm_{bf16_f32,f16_f16}_* (dist/Klas_GEMM_TensorCore2D.h:8-1220),
  * Klas_GEMM_TensorCore2D_To_g_gemm_bf16_f32_bf16_* (dist/Klas_GEMM_TensorCore2D_To.h),
