@@ -703,12 +703,12 @@ def cpu_baseline_leg(workload_name, seconds=12.0):
 # to the SHA-256 of the kernel source it was captured from: when the source has changed since,
 # the figure is withheld (traffic null, with a note) instead of going stale silently.
 NCU_TRAFFIC = {
-    "gemm_bf16": (1.149e+09, "kuiper_b200/csrc/gemm_umma.cu", "ef992e1805ad03b5"),
-    "gemm_f16b": (1.611e+09, "kuiper_b200/csrc/gemm_umma.cu", "ef992e1805ad03b5"),
-    "spmm": (1.134e+09, "kuiper_b200/csrc/spmm.cu", "00fe2789a6167b7d"),
-    "gemm_u64": (2.17e+09, "kuiper_b200/csrc/gemm_simt.cu", "77eea601899b31b5"),
-    "gemm_f32": (1.263e+07, "kuiper_b200/csrc/gemm_simt.cu", "77eea601899b31b5"),
-    "softmax_f32": (3.162e+09, "kuiper_b200/csrc/rowops.cu", "06bc7eefe6fa1b1b"),
+    "gemm_bf16": (1.195e+09, "kuiper_b200/csrc/gemm_umma.cu", "63919d4cd53fdb67"),
+    "gemm_f16b": (1.858e+09, "kuiper_b200/csrc/gemm_umma.cu", "63919d4cd53fdb67"),
+    "spmm": (1.131e+09, "kuiper_b200/csrc/spmm.cu", "00fe2789a6167b7d"),
+    "gemm_u64": (2.167e+09, "kuiper_b200/csrc/gemm_simt.cu", "1347f823e1dfa70e"),
+    "gemm_f32": (1.261e+07, "kuiper_b200/csrc/gemm_simt.cu", "1347f823e1dfa70e"),
+    "softmax_f32": (3.163e+09, "kuiper_b200/csrc/rowops.cu", "06bc7eefe6fa1b1b"),
 }
 NOMINAL_BF16_TFLOPS = 2250.0     # dense bf16, vendor figure
 NOMINAL_HBM_GBS = 8000.0
