@@ -263,3 +263,25 @@ def test_k_split_with_pages_and_row_major_b(tc_mode):
     assert torch.equal(split, again)
     scale = torch.bmm(A.float().abs(), B.float().abs())
     assert float(((split.float() - whole.float()).abs() / scale).max()) <= 2 ** -9
+
+
+def test_k_split_does_not_allocate_while_a_graph_records(tc_mode):
+    """A split launch needs a buffer for its parts.  On a stream that has none yet and is recording a
+    CUDA graph the library must not allocate (that would invalidate the capture): the launch runs
+    in one pass, the graph records and replays, and the result matches the eager one."""
+    if tc_mode != "auto":
+        return
+    A, Bt = synth.gemm_bf16(29, 1024, 1024, 4096, b_col_major=True, device="cuda")
+    eager = klas.gemm_tc(A, Bt, b_col_major=True)          # split, on the current stream
+    D = torch.empty_like(eager)
+    fresh = torch.cuda.Stream()
+    fresh.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(fresh):
+        with torch.cuda.graph(g, stream=fresh):
+            klas.gemm_tc(A, Bt, b_col_major=True, D=D)      # first call on this stream: no buffer yet
+    g.replay()
+    torch.cuda.synchronize()
+    assert klas.gemm_tc_status() == 0
+    scale = A.float().abs() @ Bt.float().abs().t()
+    assert float(((D - eager).abs() / scale).max()) <= 1e-6
