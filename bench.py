@@ -11,6 +11,8 @@ benchmark configurations; see kuiper_b200/synth.py):
   gemm_bf16   bf16 x bf16 -> f32 tensor-core GEMM, 8192 rows per GPU, N = K = 8192,
               A row-major, B column-major (default; at 8 GPUs this is the row-sharded
               65536 x 8192 x 8192 case).  Metric: TFLOP/s.
+  gemm_bf16_65536  the same product with the TOTAL size fixed at 65536 x 8192 x 8192: 65536 / N rows
+              per GPU (strong scaling).
   gemm_f16b   batched f16 x f16 -> f16, 2048^3 pages, 64 / N pages per GPU.
   gemm_u64    wrapping u64 GEMM 4096^3, rows sharded.
   gemm_f32    f32 GEMM 1024^3 (single GPU only).
@@ -230,6 +232,23 @@ class GemmBf16(Workload):
 
     def cpu_units(self, rows):
         return 2.0 * rows * self.N * self.K
+
+
+class GemmBf16Sharded(GemmBf16):
+    """The row-sharded 65536 x 8192 x 8192 case with its TOTAL size fixed: 65536 / N rows per GPU
+    (strong scaling; at N = 8 it is the default workload's 8192 rows per GPU)."""
+    name = "gemm_bf16_65536"
+    TOTAL_ROWS = 65536
+
+    def __init__(self, rank, world, device):
+        if self.TOTAL_ROWS % (world * 512) != 0:
+            raise SystemExit("gemm_bf16_65536 wants the 65536 rows to split into whole 512-row tiles per GPU")
+        type(self).ROWS_PER_GPU = self.TOTAL_ROWS // world     # read by the base class
+        super().__init__(rank, world, device)
+        self.config = {"workload": "bf16 x bf16 -> f32 GEMM (tensor-core path), M=65536 in total (%d rows per GPU) N=K=8192, "
+                                   "A row-major, B column-major, N(0,1) values, seed 1" % self.rows,
+                       "rows_per_gpu": self.rows, "sharding": "M row blocks, B replicated, no collective",
+                       "cache": "inputs+output %d MiB per GPU > 126 MB L2" % ((self.h2d + self.d2h) >> 20)}
 
 
 class CublasBf16(GemmBf16):
@@ -521,6 +540,8 @@ def make_workload(name, rank, world, device, args=None):
         return Softmax(rank, world, device, args.softmax_log2n if args else 28)
     if name == "gemm_bf16":
         return GemmBf16(rank, world, device)
+    if name == "gemm_bf16_65536":
+        return GemmBf16Sharded(rank, world, device)
     if name == "cublas_bf16":
         return CublasBf16(rank, world, device)
     if name == "gemm_f16b":
@@ -1069,7 +1090,7 @@ def main():
                     help="gemm_bf16 through the multi-GPU C entry points: one process drives --gpus devices (no torchrun)")
     ap.add_argument("--no-numa-bind", action="store_true",
                     help="do not bind this rank's host thread and pinned buffers to the NUMA node of its GPU")
-    ap.add_argument("--tc-mode", default="auto", choices=["auto", "single", "narrow", "pair", "wide"],
+    ap.add_argument("--tc-mode", default="auto", choices=["auto", "single", "narrow", "slim", "pair", "wide"],
                     help="force one tile shape of the tensor-core kernel (profiler captures of the variants)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--attention-heads", type=int, default=256,
@@ -1148,7 +1169,7 @@ def main():
     # ... and, with several ranks, one pass with C assembled on every rank (NCCL all-gather over
     # NVLink): each rank compares its own block of the gathered matrix bit for bit, and the other
     # ranks' blocks through a checksum every rank computed of its local block.
-    if world > 1 and wl.name == "gemm_bf16" and check is not None:
+    if world > 1 and wl.name in ("gemm_bf16", "gemm_bf16_65536") and check is not None:
         ranks = sharding.Ranks(rank, world, local, device)
         ranges = [(r * wl.rows, (r + 1) * wl.rows) for r in range(world)]
         t0 = time.perf_counter()
