@@ -285,3 +285,29 @@ def test_k_split_does_not_allocate_while_a_graph_records(tc_mode):
     assert klas.gemm_tc_status() == 0
     scale = A.float().abs() @ Bt.float().abs().t()
     assert float(((D - eager).abs() / scale).max()) <= 1e-6
+
+
+def test_k_split_on_two_streams_at_once(tc_mode):
+    """Split launches on different streams may overlap, so each stream has its own buffer for the
+    parts: two streams running different products at the same time must both get their own result."""
+    if tc_mode != "auto":
+        return
+    A1, B1 = synth.gemm_bf16(41, 1024, 1024, 4096, b_col_major=True, device="cuda")
+    A2, B2 = synth.gemm_bf16(43, 1024, 1024, 4096, b_col_major=True, device="cuda")
+    klas.debug_set("tc_ksplit", "off")
+    want1, want2 = klas.gemm_tc(A1, B1, b_col_major=True), klas.gemm_tc(A2, B2, b_col_major=True)
+    klas.debug_set("tc_ksplit", "auto")
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    got1, got2 = torch.empty_like(want1), torch.empty_like(want2)
+    for _ in range(20):
+        with torch.cuda.stream(s1):
+            klas.gemm_tc(A1, B1, b_col_major=True, D=got1)
+        with torch.cuda.stream(s2):
+            klas.gemm_tc(A2, B2, b_col_major=True, D=got2)
+    torch.cuda.synchronize()
+    assert klas.gemm_tc_status() == 0
+    scale1 = A1.float().abs() @ B1.float().abs().t()
+    scale2 = A2.float().abs() @ B2.float().abs().t()
+    assert float(((got1 - want1).abs() / scale1).max()) <= 1e-6
+    assert float(((got2 - want2).abs() / scale2).max()) <= 1e-6
