@@ -90,12 +90,14 @@ struct Ctl {
 };
 
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const Ctl &ctl, int site, uint32_t backoff_ns = 0) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
+    // `backoff_ns` > 0: a role whose wait may be long polls with a suspend-time hint (the hardware parks
+    // the thread and wakes it when the phase completes) instead of spinning
+    auto poll = [&] { return backoff_ns ? ptx::mbar_try_wait_hint(bar, parity, backoff_ns * 32u) : ptx::mbar_try_wait(bar, parity); };
+    if (poll()) return true;
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
     for (;;) {
-        if (ptx::mbar_try_wait(bar, parity)) return true;
-        if (backoff_ns) __nanosleep(backoff_ns);
+        if (poll()) return true;
         if ((++spins & 0x3F) == 0) {
             if (*ctl.abort_flag != 0) return false;
             if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
