@@ -556,7 +556,7 @@ def make_workload(name, rank, world, device, args=None):
 
 
 # --------------------------------------------------------------------------- CPU legs
-CPU_METRICS = {"gemm_bf16": (1.148e+09, "kuiper_b200/csrc/gemm_umma.cu", "ac2024f10ab4eea1"), "gemm_f16b": (1.61e+09, "kuiper_b200/csrc/gemm_umma.cu", "ac2024f10ab4eea1"),
+CPU_METRICS = {"gemm_bf16": ("bf16_gemm_tflops", "TFLOP/s", "bf16"), "gemm_f16b": ("f16_batched_gemm_tflops", "TFLOP/s", "f16"),
                "gemm_u64": ("u64_gemm_tops", "Tops/s", "u64"), "gemm_f32": ("f32_gemm_tflops", "TFLOP/s", "f32"),
                "spmm": ("spmm_compulsory_gbs", "GB/s", "f32")}
 
