@@ -166,7 +166,9 @@ int klas_b200_gemm_strided(int dtype, uint32_t batch, uint64_t m, uint64_t n, ui
  * A small output with a long shared dimension (128 x 256 tiles filling less than half of the SMs,
  * e.g. 1024 x 1024 x 4096) is computed as up to 8 partial products over parts of the shared
  * dimension, which a second kernel on the same stream adds in a fixed order: the result is the
- * same from run to run and within fp32 re-association of the one-pass product.  The parts live
+ * same from run to run and within fp32 re-association of the one-pass product.  The same is done
+ * for the tiles of a part-filled last round when the shared dimension is long (2560 x 2048 x 8192:
+ * one launch for the 74 tile pairs of the full round, one for the last 6 cut into 8 parts; KLAS_KNOB_TC_TAIL).  The parts live
  * in a device buffer the library keeps per (device, stream), allocated at the first such call on
  * the stream (a call that would have to allocate while the stream is recording a CUDA graph
  * runs in one pass instead) and freed by klas_b200_release_workspace(); at most 8 streams per
@@ -547,6 +549,8 @@ int klas_b200_mg_spmm(klas_mg_context *ctx, int dtype, const uint32_t *row_bound
  *   KLAS_KNOB_SPMM_SLAB  columns per slab of the SpMM kernel: 0 library's choice, 32, 64 or 128
  *   KLAS_KNOB_TC_KSPLIT  parts a tile's K range is cut into (single-CTA and pair tiles): 0 library's choice,
  *                        1 never, 2..8 that many where the shape allows it
+ *   KLAS_KNOB_TC_TAIL    a part-filled last round of single-CTA or pair tiles cut along K in a second launch:
+ *                        0 library's choice, 1 never, 2 whenever there is one
  *   KLAS_KNOB_HOST_GRID  blocks per side of the 2-D schedule of klas_b200_gemm_tc_host: -1 default (4),
  *                        0 row blocks only, 1..16
  * Returns KLAS_ERR_INVALID for an unknown knob or a value outside its range.  klas_b200_debug_get
@@ -561,7 +565,8 @@ typedef enum klas_knob_e {
     KLAS_KNOB_HOST_GRID = 5,
     KLAS_KNOB_SPMM_SLAB = 6,
     KLAS_KNOB_TC_KSPLIT = 7,
-    KLAS_KNOB_COUNT = 8
+    KLAS_KNOB_TC_TAIL = 8,
+    KLAS_KNOB_COUNT = 9
 } klas_knob;
 int klas_b200_debug_set(int knob, int value);
 int klas_b200_debug_get(int knob);

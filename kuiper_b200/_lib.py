@@ -16,7 +16,7 @@ MAP_ID, MAP_SQRT, MAP_ABS, MAP_SQUARE, MAP_RELU, MAP_NEG = range(6)
 COMB_NEW, COMB_AXPBY, COMB_MAX, COMB_MIN, COMB_MUL, COMB_RELU, COMB_SCALED = range(7)
 
 MG_NO_GATHER, MG_GATHER_ALL, MG_GATHER_FIRST = range(3)
-KNOB_TC_MODE, KNOB_TC_RASTER, KNOB_SIMT_SPLIT_K, KNOB_F64_MODE, KNOB_SIMT_TILE, KNOB_HOST_GRID, KNOB_SPMM_SLAB, KNOB_TC_KSPLIT = range(8)
+KNOB_TC_MODE, KNOB_TC_RASTER, KNOB_SIMT_SPLIT_K, KNOB_F64_MODE, KNOB_SIMT_TILE, KNOB_HOST_GRID, KNOB_SPMM_SLAB, KNOB_TC_KSPLIT, KNOB_TC_TAIL = range(9)
 
 _u32, _u64, _vp, _int, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int, C.c_float
 

@@ -29,9 +29,9 @@ int fail(int code, const char *fmt, ...) {
 void clear_error() { tls_error[0] = '\0'; }
 
 // tuning knobs (klas_knob): defaults = the library's own choice
-static std::atomic<int> g_knobs[KLAS_KNOB_COUNT] = {{0}, {0}, {0}, {0}, {-1}, {-1}, {0}, {0}};
+static std::atomic<int> g_knobs[KLAS_KNOB_COUNT] = {{0}, {0}, {0}, {0}, {-1}, {-1}, {0}, {0}, {0}};
 struct KnobRange { int lo, hi; };
-static const KnobRange g_knob_range[KLAS_KNOB_COUNT] = {{0, 5}, {0, 1024}, {0, 2}, {0, 1}, {-1, 2}, {-1, 16}, {0, 128}, {0, 8}};
+static const KnobRange g_knob_range[KLAS_KNOB_COUNT] = {{0, 5}, {0, 1024}, {0, 2}, {0, 1}, {-1, 2}, {-1, 16}, {0, 128}, {0, 8}, {0, 2}};
 
 int debug_knob(int knob) {
     return knob >= 0 && knob < KLAS_KNOB_COUNT ? g_knobs[knob].load(std::memory_order_relaxed) : INT_MIN;

@@ -106,6 +106,7 @@ struct Params {
     // K blocks, one work item each; `num_work` = num_tiles * ksplit.  Part q of page b writes its
     // f32 partial product as page b * ksplit + q of D (a workspace then; a second kernel adds the parts).
     uint32_t ksplit, kb_per, num_work;
+    uint32_t tile0;        // first tile of this launch (single-CTA and pair kernels): a launch may cover the tail of the tile list only
     float alpha, beta;
     uint32_t idesc;
     uint32_t b_row_major;  // 1: B is K x N (N contiguous) -> MN-major operand
@@ -192,8 +193,9 @@ __device__ __forceinline__ void decode_tile(uint32_t t, const Params &p, uint32_
 struct WorkItem {
     uint32_t tile, part, kb0, kb1;
     __device__ __forceinline__ WorkItem(uint32_t w, const Params &p) {
-        tile = p.ksplit > 1 ? w / p.ksplit : w;
-        part = w - tile * p.ksplit;
+        const uint32_t local = p.ksplit > 1 ? w / p.ksplit : w;
+        tile = p.tile0 + local;
+        part = w - local * p.ksplit;
         kb0 = part * p.kb_per;
         kb1 = min(kb0 + p.kb_per, p.num_kb);
     }
@@ -483,6 +485,9 @@ struct ReduceArgs {
     uint64_t ldd, sd;
     float alpha, beta;
     uint32_t comb;
+    // tile0 > 0: only the tiles from tile0 on (in the product kernel's tile order) were split; the
+    // columns before `col_begin` hold none of them
+    uint32_t tile0, tile_m, tile_n, tiles_m, tiles_n, raster_group, col_begin;
 };
 
 template <typename OutT, uint32_t COMB>
@@ -505,13 +510,21 @@ __device__ __forceinline__ void reduce_store(const float (&acc)[4], OutT *d, con
 
 template <typename OutT>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceArgs a) {
-    const uint64_t quads_per_row = a.cols / 4;
+    const uint64_t quads_per_row = (a.cols - a.col_begin) / 4;
     const uint64_t total = uint64_t(a.batch) * a.rows * quads_per_row;
     const uint64_t page_elems = uint64_t(a.rows) * a.cols;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
         const uint64_t b = i / (uint64_t(a.rows) * quads_per_row);
         const uint64_t in_page = i - b * a.rows * quads_per_row;
-        const uint64_t r = in_page / quads_per_row, c4 = (in_page - r * quads_per_row) * 4;
+        const uint64_t r = in_page / quads_per_row, c4 = a.col_begin + (in_page - r * quads_per_row) * 4;
+        if (a.tile0 > 0) {
+            // the inverse of decode_tile: which tile owns (r, c4), and was it among the split ones
+            const uint32_t tm = uint32_t(r / a.tile_m), tn = uint32_t(c4 / a.tile_n);
+            const uint32_t g = tn / a.raster_group, first_n = g * a.raster_group;
+            const uint32_t width = min(a.raster_group, a.tiles_n - first_n);
+            const uint32_t t = g * a.raster_group * a.tiles_m + tm * width + (tn - first_n);
+            if (t < a.tile0) continue;
+        }
         const float *src = a.ws + (b * a.parts) * page_elems + r * a.cols + c4;
         float acc[4];
         {
@@ -1510,6 +1523,7 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     // The KLAS_KNOB_TC_MODE knob overrides the choice.
     constexpr double RATE_SINGLE = 1336.0, RATE_PAIR = 1433.0, RATE_WIDE = 1539.0, WIDE_DRAIN_KB = 6.0, NARROW_COST = 0.75, SLIM_COST = 0.65;
     constexpr uint32_t SPLIT_MIN_SAVED_KB = 22;   // K blocks (of 64) a split must take off a tile to pay for its second kernel
+    constexpr double TAIL_OVERHEAD_KB = 60.0;     // what the extra launch and the adding kernel of a cut last round cost, in K blocks
     const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
     const uint64_t pair_tiles = ((rows + 2 * BM - 1) / (2 * BM)) * ((cols + BN - 1) / BN) * batch;
     const uint64_t wide_tiles = ((rows + wide::TILE_M - 1) / wide::TILE_M) * ((cols + BN - 1) / BN) * batch;
@@ -1524,8 +1538,26 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     const double num_kb_d = double((shared + BK - 1) / BK);
     const double wide_drain = num_kb_d > 0 ? (1.0 + WIDE_DRAIN_KB / num_kb_d) / (1.0 + WIDE_DRAIN_KB / 128.0) : 1.0;
     const double cost_wide = can_pair ? double((wide_tiles + pairs - 1) / pairs) * 2.0 * (RATE_SINGLE / RATE_WIDE) * wide_drain : 1e30;
-    bool use_wide = can_pair && cost_wide < cost_single && cost_wide <= cost_pair;
-    bool pair = pair_ok && !use_wide && cost_pair <= cost_single;
+    // A part-filled last round of single or pair tiles can be cut along K so that it fills the machine
+    // too (second launch + the kernel that adds the parts: about TAIL_OVERHEAD_KB K blocks' worth).
+    const uint64_t num_kb_all = (shared + BK - 1) / BK;
+    auto with_tail_cut = [&](uint64_t tiles, uint64_t slots) -> double {   // rounds, or 1e30 where it does not apply
+        const uint64_t rem = tiles % slots, full = tiles / slots;
+        if (batch != 1 || rem == 0 || full == 0 || num_kb_all == 0) return 1e30;
+        uint64_t parts = slots / rem;
+        if (parts > 8) parts = 8;
+        if (parts < 2) return 1e30;
+        const uint64_t kb_per = (num_kb_all + parts - 1) / parts;
+        if (num_kb_all < kb_per + SPLIT_MIN_SAVED_KB) return 1e30;
+        return double(full) + double(kb_per) / double(num_kb_all) + TAIL_OVERHEAD_KB / double(num_kb_all);
+    };
+    const double cost_single_tail = with_tail_cut(single_tiles, sms);
+    const double cost_pair_tail = pair_ok ? with_tail_cut(pair_tiles, pairs) * (RATE_SINGLE / RATE_PAIR) : 1e30;
+    const double best_single = cost_single_tail < cost_single ? cost_single_tail : cost_single;
+    const double best_pair = cost_pair_tail < cost_pair ? cost_pair_tail : cost_pair;
+    bool use_wide = can_pair && cost_wide < best_single && cost_wide <= best_pair;
+    bool pair = pair_ok && !use_wide && best_pair <= best_single;
+    bool tail_split = !use_wide && (pair ? cost_pair_tail < cost_pair : cost_single_tail < cost_single);
     // Small outputs: the single-CTA kernel with 128-column tiles puts twice as many CTAs to work
     // (1024^2: 64 tiles instead of 32 on 148 SMs).  A CTA takes the same time per K block whatever
     // the tile's width (about 660 cycles: the copy-issue and MMA-issue threads, not the arithmetic,
@@ -1539,14 +1571,13 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     const double cost_slim = double((slim_tiles + sms - 1) / sms) * SLIM_COST;
     uint32_t single_tile_n = BN;
     if (!use_wide && !pair) {
-        double best = cost_single;
-        if (cost_narrow < best) best = cost_narrow, single_tile_n = 128;
-        if (cost_slim < best) best = cost_slim, single_tile_n = 64;
+        double best = best_single;
+        if (cost_narrow < best) best = cost_narrow, single_tile_n = 128, tail_split = false;
+        if (cost_slim < best) best = cost_slim, single_tile_n = 64, tail_split = false;
     }
     // Long K over few tiles: cut each 128 x 256 tile's K range into parts that fill the SMs
     // (1024 x 1024 x 4096: 32 tiles x 4 parts, 17.3 us against 27.4 us for 128 tiles of 128 x 64).
     // A split costs a second kernel that adds the parts (4-6 us for a 1024^2 output), a K block 0.34 us.
-    const uint64_t num_kb_all = (shared + BK - 1) / BK;
     uint64_t auto_parts = 1;
     if (!use_wide && !pair && single_tiles * 2 <= sms && debug_knob(KLAS_KNOB_TC_MODE) == 0) {
         uint64_t parts = sms / single_tiles;
@@ -1557,6 +1588,7 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
             single_tile_n = BN;
         }
     }
+    if (debug_knob(KLAS_KNOB_TC_MODE) != 0) tail_split = false;   // forced shapes run one launch unless KLAS_KNOB_TC_TAIL asks
     switch (debug_knob(KLAS_KNOB_TC_MODE)) {   // a test or tuning run forcing one tile shape
         case 1: pair = use_wide = false; single_tile_n = BN; break;
         case 2: pair = use_wide = false; single_tile_n = 128; break;
@@ -1636,63 +1668,61 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     p.raster_group = DEFAULT_RASTER_GROUP;
     if (const int v = debug_knob(KLAS_KNOB_TC_RASTER); v >= 1) p.raster_group = uint32_t(v);
 
-    // K split (chosen above, or forced by the knob): the parts write f32 partial products into a
-    // workspace and a second kernel adds them in index order and applies the output rule (alpha,
-    // beta, the old C, the output type), so the result is the same from run to run.
-    p.ksplit = 1;
+    // One launch covers a range of the tile list, whole or with each tile's K range cut into parts.
+    // Cut tiles write f32 partial products into a workspace and a second kernel adds them in index
+    // order and applies the output rule (alpha, beta, the old C, the output type), so the result is
+    // the same from run to run.  Two plans use that:
+    //  * every tile cut (few tiles, long K: chosen above, or forced by KLAS_KNOB_TC_KSPLIT);
+    //  * only the tiles of a part-filled last round cut, so that they fill the machine too, after a
+    //    first launch for the full rounds (2560 x 2048 x 4096 in pair tiles: 74 tiles whole, then
+    //    6 tiles x 8 parts, instead of two rounds).
+    struct Pass {
+        uint32_t tile0, tiles, parts, kb_per;
+    };
+    const uint64_t slots = pair ? pairs : sms;
+    Pass first{0, uint32_t(num_tiles), 1, p.num_kb}, tail{0, 0, 1, p.num_kb};
     float *split_ws = nullptr;
+    auto parts_for = [&](uint64_t want, Pass &pass) {   // settles parts and K blocks per part; false: stay whole
+        if (want > 8) want = 8;
+        if (want > p.num_kb) want = p.num_kb;
+        if (want < 2) return false;
+        const uint32_t kb_per = uint32_t((p.num_kb + want - 1) / want);
+        want = (p.num_kb + kb_per - 1) / kb_per;   // no empty part
+        if (want < 2) return false;
+        pass.parts = uint32_t(want);
+        pass.kb_per = kb_per;
+        return true;
+    };
     {
         const int knob = debug_knob(KLAS_KNOB_TC_KSPLIT);
-        uint64_t parts = 1;
-        if (knob >= 2) {
-            parts = uint64_t(knob);
-        } else if (knob == 0) {
-            parts = auto_parts;
-        }
-        if (parts > 8) parts = 8;
-        if (parts > p.num_kb) parts = p.num_kb;
-        if (parts >= 2 && num_tiles * parts <= 0xffffffffull) {
-            const uint32_t kb_per = uint32_t((p.num_kb + parts - 1) / parts);
-            parts = (p.num_kb + kb_per - 1) / kb_per;   // no empty part
+        const uint64_t want = knob >= 2 ? uint64_t(knob) : (knob == 0 ? auto_parts : 1);
+        Pass cut = first;
+        if (want >= 2 && parts_for(want, cut)) {
             void *ws = nullptr;
-            const size_t bytes = size_t(batch) * parts * rows * cols * sizeof(float);
-            if (parts >= 2)
-                if (int rc = split_workspace(stream, bytes, &ws)) return rc;
+            if (int rc = split_workspace(stream, size_t(batch) * cut.parts * rows * cols * sizeof(float), &ws)) return rc;
             if (ws != nullptr) {
-                p.ksplit = uint32_t(parts);
-                p.kb_per = kb_per;
+                first = cut;
                 split_ws = static_cast<float *>(ws);
             }
         }
     }
-    if (p.ksplit == 1) p.kb_per = p.num_kb;
-    const uint64_t num_work = num_tiles * p.ksplit;
-    p.num_work = uint32_t(num_work);
-    int kernel_out_dtype = out_dtype;
-    if (split_ws != nullptr) {
-        // the product kernel writes plain f32 parts; the output rule moves to the second kernel
-        p.C = nullptr;
-        p.D = split_ws;
-        p.ldd = cols;
-        p.sd = rows * cols;
-        p.comb = KLAS_COMB_NEW;
-        p.alpha = 1.0f;
-        p.beta = 0.0f;
-        kernel_out_dtype = KLAS_F32;
-    }
-    auto finish_split = [&](int rc) -> int {
-        if (rc != KLAS_OK || split_ws == nullptr) return rc;
-        ReduceArgs ra{split_ws, C, D, uint32_t(rows), uint32_t(cols), p.ksplit, batch, ldd, sd, alpha, beta, uint32_t(comb)};
-        const uint64_t threads = uint64_t(batch) * rows * (cols / 4);
-        uint64_t blocks = (threads + 255) / 256;
-        if (blocks > uint64_t(info.sm_count) * 8) blocks = uint64_t(info.sm_count) * 8;
-        switch (out_dtype) {
-            case KLAS_F32: splitk_reduce_kernel<float><<<unsigned(blocks), 256, 0, stream>>>(ra); break;
-            case KLAS_F16: splitk_reduce_kernel<__half><<<unsigned(blocks), 256, 0, stream>>>(ra); break;
-            default: splitk_reduce_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, stream>>>(ra); break;
+    if (first.parts == 1 && batch == 1 && num_tiles > 0) {
+        const int knob = debug_knob(KLAS_KNOB_TC_TAIL);
+        const uint64_t rem = num_tiles % slots, full = num_tiles - rem;
+        const bool wanted = knob == 2 || (knob == 0 && tail_split);
+        Pass cut{uint32_t(full), uint32_t(rem), 1, p.num_kb};
+        if (wanted && rem > 0 && full > 0 && parts_for(slots / rem, cut)) {
+            const size_t bytes = size_t(cut.parts) * rows * cols * sizeof(float);
+            void *ws = nullptr;
+            if (bytes <= (size_t(1) << 30))
+                if (int rc = split_workspace(stream, bytes, &ws)) return rc;
+            if (ws != nullptr) {
+                first.tiles = uint32_t(full);
+                tail = cut;
+                split_ws = static_cast<float *>(ws);
+            }
         }
-        return check_cuda(cudaGetLastError(), "splitk_reduce_kernel launch");
-    };
+    }
 
     const uint32_t b_cols = pair ? Shape<true>::B_COLS : p.tile_n;
     CUtensorMap ta{}, tb{};
@@ -1704,13 +1734,57 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
             if (int rc = make_map(&tb, in_dtype, B, shared, cols, batch, BK, b_cols, ldb, sb)) return rc;
         }
     }
-    if (pair) {
-        const uint64_t groups = num_work < uint64_t(info.sm_count / 2) ? num_work : uint64_t(info.sm_count / 2);
-        return finish_split(launch_mode<true, false>(kernel_out_dtype, ta, tb, p, int(groups * 2), stream));
-    }
-    const int grid = int(num_work < uint64_t(info.sm_count) ? num_work : uint64_t(info.sm_count));
-    return finish_split(xform ? launch_mode<false, true>(kernel_out_dtype, ta, tb, p, grid, stream)
-                              : launch_mode<false, false>(kernel_out_dtype, ta, tb, p, grid, stream));
+    auto run = [&](const Pass &pass) -> int {
+        Params q = p;
+        q.tile0 = pass.tile0;
+        q.num_tiles = pass.tiles;
+        q.ksplit = pass.parts;
+        q.kb_per = pass.parts > 1 ? pass.kb_per : p.num_kb;
+        const uint64_t num_work = uint64_t(pass.tiles) * pass.parts;
+        q.num_work = uint32_t(num_work);
+        int kernel_out_dtype = out_dtype;
+        if (pass.parts > 1) {
+            // the product kernel writes plain f32 parts; the output rule moves to the second kernel
+            q.C = nullptr;
+            q.D = split_ws;
+            q.ldd = cols;
+            q.sd = rows * cols;
+            q.comb = KLAS_COMB_NEW;
+            q.alpha = 1.0f;
+            q.beta = 0.0f;
+            kernel_out_dtype = KLAS_F32;
+        }
+        int rc;
+        if (pair) {
+            const uint64_t groups = num_work < pairs ? num_work : pairs;
+            rc = launch_mode<true, false>(kernel_out_dtype, ta, tb, q, int(groups * 2), stream);
+        } else {
+            const int grid = int(num_work < sms ? num_work : sms);
+            rc = xform ? launch_mode<false, true>(kernel_out_dtype, ta, tb, q, grid, stream)
+                       : launch_mode<false, false>(kernel_out_dtype, ta, tb, q, grid, stream);
+        }
+        if (rc != KLAS_OK || pass.parts == 1) return rc;
+        ReduceArgs ra{split_ws, C, D, uint32_t(rows), uint32_t(cols), pass.parts, batch, ldd, sd, alpha, beta, uint32_t(comb),
+                      pass.tile0, tile_m, p.tile_n, p.tiles_m, p.tiles_n, p.raster_group, 0u};
+        if (pass.tile0 > 0) {
+            // tiles from tile0 on lie in the column groups from tile0's group on
+            const uint32_t g = pass.tile0 / (p.raster_group * p.tiles_m);
+            ra.col_begin = g * p.raster_group * p.tile_n;
+        }
+        const uint64_t threads = uint64_t(batch) * rows * ((cols - ra.col_begin) / 4);
+        uint64_t blocks = (threads + 255) / 256;
+        if (blocks > sms * 8) blocks = sms * 8;
+        if (blocks == 0) blocks = 1;
+        switch (out_dtype) {
+            case KLAS_F32: splitk_reduce_kernel<float><<<unsigned(blocks), 256, 0, stream>>>(ra); break;
+            case KLAS_F16: splitk_reduce_kernel<__half><<<unsigned(blocks), 256, 0, stream>>>(ra); break;
+            default: splitk_reduce_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, stream>>>(ra); break;
+        }
+        return check_cuda(cudaGetLastError(), "splitk_reduce_kernel launch");
+    };
+    if (int rc = run(first)) return rc;
+    if (tail.tiles > 0) return run(tail);
+    return KLAS_OK;
 }
 
 }  // namespace klas

@@ -387,12 +387,13 @@ _KNOBS = {"tc_mode": (_lib.KNOB_TC_MODE, {"auto": 0, "single": 1, "narrow": 2, "
           "tc_raster": (_lib.KNOB_TC_RASTER, {"auto": 0}), "simt_split_k": (_lib.KNOB_SIMT_SPLIT_K, {"auto": 0}),
           "f64_mode": (_lib.KNOB_F64_MODE, {"auto": 0, "simt": 1}), "simt_tile": (_lib.KNOB_SIMT_TILE, {"auto": -1}),
           "host_grid": (_lib.KNOB_HOST_GRID, {"auto": -1}), "spmm_slab": (_lib.KNOB_SPMM_SLAB, {"auto": 0}),
-          "tc_ksplit": (_lib.KNOB_TC_KSPLIT, {"auto": 0, "off": 1})}
+          "tc_ksplit": (_lib.KNOB_TC_KSPLIT, {"auto": 0, "off": 1}),
+          "tc_tail": (_lib.KNOB_TC_TAIL, {"auto": 0, "off": 1, "always": 2})}
 
 
 def debug_set(knob: str, value="auto") -> None:
     """Forces one variant of a kernel choice the library otherwise makes itself (klas_b200_debug_set):
-    knob in {"tc_mode", "tc_raster", "simt_split_k", "f64_mode", "simt_tile", "host_grid", "spmm_slab", "tc_ksplit"}, value a name
+    knob in {"tc_mode", "tc_raster", "simt_split_k", "f64_mode", "simt_tile", "host_grid", "spmm_slab", "tc_ksplit", "tc_tail"}, value a name
     ("auto" restores the library's choice; tc_mode: "single", "narrow", "slim", "pair", "wide"; f64_mode: "simt") or an int."""
     code, names = _KNOBS[knob]
     check(_lib.load().klas_b200_debug_set(code, names[value] if isinstance(value, str) else int(value)))

@@ -311,3 +311,41 @@ def test_k_split_on_two_streams_at_once(tc_mode):
     scale2 = A2.float().abs() @ B2.float().abs().t()
     assert float(((got1 - want1).abs() / scale1).max()) <= 1e-6
     assert float(((got2 - want2).abs() / scale2).max()) <= 1e-6
+
+
+@pytest.mark.parametrize("rows,cols,shared", [(2560, 2048, 1024), (2500, 2040, 1032), (4096, 4096, 512)])
+def test_last_round_cut_along_k(oracle, rows, cols, shared, tc_mode):
+    """More tiles than CTA groups with a part-filled last round: the full rounds run as one launch,
+    the last round's tiles with their K range cut into parts as a second one, and a third kernel
+    adds the parts (restricted to those tiles).  Forced here for every tile shape that has the
+    path; the result must match the one-launch product (the tiles of the full rounds bit for
+    bit, the others to fp32 re-association), through every output rule."""
+    A, Bt = synth.gemm_bf16(37, rows, cols, shared, b_col_major=True, device="cuda")
+    C0 = torch.randn(rows, cols, device="cuda")
+    klas.debug_set("tc_tail", "off")
+    whole = klas.gemm_tc(A, Bt, b_col_major=True)
+    whole_ab = klas.gemm_tc(A, Bt, b_col_major=True, C_=C0, alpha=0.5, beta=-1.25)
+    whole_bf = klas.gemm_tc(A, Bt, b_col_major=True, out_dtype=torch.bfloat16)
+    try:
+        klas.debug_set("tc_tail", "always")
+        cut = [klas.gemm_tc(A, Bt, b_col_major=True) for _ in range(2)]
+        cut_ab = klas.gemm_tc(A, Bt, b_col_major=True, C_=C0, alpha=0.5, beta=-1.25)
+        cut_bf = klas.gemm_tc(A, Bt, b_col_major=True, out_dtype=torch.bfloat16)
+        inplace = C0.clone()
+        klas.gemm_tc(A, Bt, b_col_major=True, C_=inplace, D=inplace, alpha=0.5, beta=-1.25)
+    finally:
+        klas.debug_set("tc_tail", "auto")
+    torch.cuda.synchronize()
+    assert klas.gemm_tc_status() == 0
+    assert torch.equal(cut[0], cut[1]), "run-to-run difference"
+    scale = (A.float().abs() @ Bt.float().abs().t()).clamp_min(1e-30)
+    assert float(((cut[0] - whole).abs() / scale).max()) <= 1e-6
+    assert float(((cut_ab - whole_ab).abs() / (scale + C0.abs())).max()) <= 1e-6
+    assert torch.equal(inplace, cut_ab)
+    assert float(((cut_bf.float() - whole_bf.float()).abs() / scale).max()) <= 2 ** -8
+    if tc_mode not in ("wide", "auto"):
+        # most of the matrix belongs to the full rounds and is untouched by the cut
+        assert float((cut[0] == whole).float().mean()) >= 0.5
+    pick = torch.arange(0, rows, 111, device="cuda")
+    acc, sc = tc_reference(oracle, A[pick].cpu(), Bt.cpu(), True)
+    assert rel_err_componentwise(cut[0][pick].cpu().numpy(), acc, sc) <= 1e-5
