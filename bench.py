@@ -1241,6 +1241,13 @@ def main():
         extras = world == 1 and wl.name == "gemm_bf16" and not args.no_extras
         if extras:
             line["sustained"] = sustained_leg(torch, wl, local, peaks)
+            # A short timed region can run below the maximum clock before the driver flags why (its
+            # throttle reasons lag the clock by more than the region lasts); the seconds-long leg of
+            # the same process shows the reason.
+            ck, sk = line["clocks"], line["sustained"]["clocks"]
+            if ck.get("sm_mhz") and ck.get("sm_max_mhz") and ck["sm_mhz"] < 0.9 * ck["sm_max_mhz"] and not ck["reasons"] and sk.get("reasons"):
+                ck["note"] = ("no reason flagged within the %.0f ms timed region; the sustained leg of this process ran at %s MHz with %s"
+                              % (line["ms_per_step"] * line["steps"], sk.get("sm_mhz"), "+".join(sk["reasons"])))
         if not args.no_cpu_baseline and world == 1:
             cb = cpu_baseline_leg(wl.name)
             if cb:
