@@ -6,17 +6,26 @@
 //   warp 1      owns tensor memory and issues tcgen05.mma (K=16 per instruction) from
 //               one thread; the fp32 accumulator lives in TMEM, double-buffered
 //               (2 x 256 columns) so tile i+1's main loop overlaps tile i's epilogue;
-//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, apply
-//               alpha/beta, convert, and store to global memory.
-// Two instantiations:
-//   single   one CTA per 128 x 256 tile, 4 stages of 48 KiB (small problems);
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, the output rule (alpha /
+//               beta / the old C / relu / the output type) and coalesced stores through a
+//               swizzled 32-row x 128-byte staging block per warp; with an old C the block of C
+//               comes in the same way, one block ahead (instantiations of their own, OLD_C).
+// Three kernels:
+//   single   one CTA per 128 x 256 (or 128 x 128, 128 x 64) tile over a 192 KiB ring cut into
+//            4 x 48 (6 x 32, 8 x 24) KiB stages: small problems;
 //   pair     two CTAs of a cluster share a 256 x 256 tile (cta_group::2): each stages
 //            its own 128 rows of A and its own 128 columns of B (32 KiB per stage,
 //            6 stages), the even CTA issues M=256 MMAs that read both CTAs' shared
 //            memory, and each CTA drains its own 128 accumulator rows.  Per SM this
 //            halves the B bytes staged and read per flop.  Every load is an ordinary
 //            per-CTA TMA load; completion of the odd CTA's loads is counted on the even
-//            CTA's barrier.
+//            CTA's barrier;
+//   wide     two CTAs share a 512 x 256 tile (see gemm_umma_wide_kernel): problems that fill the
+//            machine.
+// The single and pair kernels can cut a tile's K range into parts (few tiles with a long K, or the
+// tiles of a part-filled last round): the parts go to a workspace as f32 and splitk_reduce_kernel
+// adds them in a fixed order.  The host picks kernel, tile width and split from the shape
+// (launch_gemm_umma_strided).
 // All hand-offs are mbarriers; every wait is bounded in time and a wait that
 // gives up raises a status word and makes all roles drain and return.
 //
