@@ -494,9 +494,8 @@ struct ReduceArgs {
     uint64_t ldd, sd;
     float alpha, beta;
     uint32_t comb;
-    // tile0 > 0: only the tiles from tile0 on (in the product kernel's tile order) were split; the
-    // columns before `col_begin` hold none of them
-    uint32_t tile0, tile_m, tile_n, tiles_m, tiles_n, raster_group, col_begin;
+    // tile0 > 0: only the tiles from tile0 on (in the product kernel's tile order) were split
+    uint32_t tile0, tile_m, tile_n, tiles_m, tiles_n, raster_group;
 };
 
 template <typename OutT, uint32_t COMB>
@@ -519,31 +518,43 @@ __device__ __forceinline__ void reduce_store(const float (&acc)[4], OutT *d, con
 
 template <typename OutT>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceArgs a) {
-    const uint64_t quads_per_row = (a.cols - a.col_begin) / 4;
-    const uint64_t total = uint64_t(a.batch) * a.rows * quads_per_row;
     const uint64_t page_elems = uint64_t(a.rows) * a.cols;
+    // whole matrix: one item per 4 columns of every row and page; tail only (tile0 > 0, one page):
+    // one item per 4 columns of every row of the tiles from tile0 on, found through the tile order
+    const uint64_t quads_per_row = a.cols / 4;
+    const uint64_t tile_quads = uint64_t(a.tile_m) * (a.tile_n / 4);
+    const uint64_t total = a.tile0 > 0 ? uint64_t(a.tiles_m * a.tiles_n - a.tile0) * tile_quads
+                                       : uint64_t(a.batch) * a.rows * quads_per_row;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x) {
-        const uint64_t b = i / (uint64_t(a.rows) * quads_per_row);
-        const uint64_t in_page = i - b * a.rows * quads_per_row;
-        const uint64_t r = in_page / quads_per_row, c4 = a.col_begin + (in_page - r * quads_per_row) * 4;
+        uint64_t b = 0, r, c4;
         if (a.tile0 > 0) {
-            // the inverse of decode_tile: which tile owns (r, c4), and was it among the split ones
-            const uint32_t tm = uint32_t(r / a.tile_m), tn = uint32_t(c4 / a.tile_n);
-            const uint32_t g = tn / a.raster_group, first_n = g * a.raster_group;
+            const uint32_t t = a.tile0 + uint32_t(i / tile_quads);
+            const uint32_t in_tile = uint32_t(i % tile_quads);
+            // decode_tile's order: groups of `raster_group` tile columns, rows fastest within a group
+            const uint32_t group_tiles = a.raster_group * a.tiles_m;
+            const uint32_t g = t / group_tiles, first_n = g * a.raster_group;
             const uint32_t width = min(a.raster_group, a.tiles_n - first_n);
-            const uint32_t t = g * a.raster_group * a.tiles_m + tm * width + (tn - first_n);
-            if (t < a.tile0) continue;
+            const uint32_t in = t - g * group_tiles;
+            const uint32_t tm = in / width, tn = first_n + in % width;
+            r = uint64_t(tm) * a.tile_m + in_tile / (a.tile_n / 4);
+            c4 = uint64_t(tn) * a.tile_n + (in_tile % (a.tile_n / 4)) * 4;
+            if (r >= a.rows || c4 >= a.cols) continue;
+        } else {
+            b = i / (uint64_t(a.rows) * quads_per_row);
+            const uint64_t in_page = i - b * a.rows * quads_per_row;
+            r = in_page / quads_per_row;
+            c4 = (in_page - r * quads_per_row) * 4;
         }
         const float *src = a.ws + (b * a.parts) * page_elems + r * a.cols + c4;
-        float acc[4];
-        {
-            const float4 q = __ldcg(reinterpret_cast<const float4 *>(src));
-            acc[0] = q.x, acc[1] = q.y, acc[2] = q.z, acc[3] = q.w;
-        }
-        for (uint32_t part = 1; part < a.parts; ++part) {
-            const float4 q = __ldcg(reinterpret_cast<const float4 *>(src + part * page_elems));
-            acc[0] += q.x, acc[1] += q.y, acc[2] += q.z, acc[3] += q.w;
-        }
+        // all parts' loads go out together (at most 8); the sum is taken in index order
+        float4 q[8];
+#pragma unroll
+        for (uint32_t part = 0; part < 8; ++part)
+            if (part < a.parts) q[part] = __ldcg(reinterpret_cast<const float4 *>(src + part * page_elems));
+        float acc[4] = {q[0].x, q[0].y, q[0].z, q[0].w};
+#pragma unroll
+        for (uint32_t part = 1; part < 8; ++part)
+            if (part < a.parts) acc[0] += q[part].x, acc[1] += q[part].y, acc[2] += q[part].z, acc[3] += q[part].w;
         const uint64_t off = b * a.sd + r * a.ldd + c4;
         OutT *d = static_cast<OutT *>(a.D) + off;
         const OutT *c = a.C ? static_cast<const OutT *>(a.C) + off : nullptr;
@@ -1532,7 +1543,7 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     // The KLAS_KNOB_TC_MODE knob overrides the choice.
     constexpr double RATE_SINGLE = 1336.0, RATE_PAIR = 1433.0, RATE_WIDE = 1539.0, WIDE_DRAIN_KB = 6.0, NARROW_COST = 0.75, SLIM_COST = 0.65;
     constexpr uint32_t SPLIT_MIN_SAVED_KB = 22;   // K blocks (of 64) a split must take off a tile to pay for its second kernel
-    constexpr double TAIL_OVERHEAD_KB = 60.0;     // what the extra launch and the adding kernel of a cut last round cost, in K blocks
+    constexpr double TAIL_OVERHEAD_KB = 45.0;     // what the extra launch and the adding kernel of a cut last round cost, in K blocks
     const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
     const uint64_t pair_tiles = ((rows + 2 * BM - 1) / (2 * BM)) * ((cols + BN - 1) / BN) * batch;
     const uint64_t wide_tiles = ((rows + wide::TILE_M - 1) / wide::TILE_M) * ((cols + BN - 1) / BN) * batch;
@@ -1775,13 +1786,8 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
         }
         if (rc != KLAS_OK || pass.parts == 1) return rc;
         ReduceArgs ra{split_ws, C, D, uint32_t(rows), uint32_t(cols), pass.parts, batch, ldd, sd, alpha, beta, uint32_t(comb),
-                      pass.tile0, tile_m, p.tile_n, p.tiles_m, p.tiles_n, p.raster_group, 0u};
-        if (pass.tile0 > 0) {
-            // tiles from tile0 on lie in the column groups from tile0's group on
-            const uint32_t g = pass.tile0 / (p.raster_group * p.tiles_m);
-            ra.col_begin = g * p.raster_group * p.tile_n;
-        }
-        const uint64_t threads = uint64_t(batch) * rows * ((cols - ra.col_begin) / 4);
+                      pass.tile0, tile_m, p.tile_n, p.tiles_m, p.tiles_n, p.raster_group};
+        const uint64_t threads = pass.tile0 > 0 ? uint64_t(pass.tiles) * tile_m * (p.tile_n / 4) : uint64_t(batch) * rows * (cols / 4);
         uint64_t blocks = (threads + 255) / 256;
         if (blocks > sms * 8) blocks = sms * 8;
         if (blocks == 0) blocks = 1;

@@ -1,7 +1,7 @@
 """Tuning run of the tensor-core GEMM's tile shapes (the counterpart of the reference's
 tuning/tune_tc2d.sh, which sweeps its 72 instances at 4096^3):
 
-    python -m kuiper_b200.tune_tc [--laps 20] [--json]
+    python -m kuiper_b200.tune_tc [--laps 20] [--json] [--shapes 2048x2048x2048,1024x1024x4096] [--modes auto,wide] [--eager]
 
 For a grid of shapes it times every tile shape the library has (single-CTA 128 x 256, 128 x 128 and
 128 x 64, CTA pair 256 x 256, wide pair 512 x 256) and the library's own choice, bf16 -> f32 with
@@ -51,10 +51,29 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--laps", type=int, default=20)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--shapes", default="", help="comma-separated ROWSxCOLSxSHARED instead of the built-in grid")
+    ap.add_argument("--modes", default="", help="with --eager: comma-separated subset of %s" % ",".join(MODES))
+    ap.add_argument("--eager", action="store_true",
+                    help="plain launches, `laps` per shape and mode, no timing table: what a profiler run wants")
     a = ap.parse_args(argv)
+    shapes = [tuple(int(x) for x in sh.split("x")) for sh in a.shapes.split(",") if sh] or SHAPES
+    modes = [md for md in a.modes.split(",") if md] or MODES
+    if a.eager:
+        for m, n, k in shapes:
+            A, Bt = synth.gemm_bf16(1, m, n, k, b_col_major=True, device="cuda")
+            D = torch.empty((m, n), dtype=torch.float32, device="cuda")
+            for mode in modes:
+                klas.debug_set("tc_mode", mode)
+                klas.debug_set("tc_ksplit", "auto" if mode == "auto" else "off")
+                for _ in range(a.laps):
+                    klas.gemm_tc(A, Bt, b_col_major=True, D=D)
+            torch.cuda.synchronize()
+        klas.debug_set("tc_mode", "auto")
+        klas.debug_set("tc_ksplit", "auto")
+        return 0 if klas.gemm_tc_status() == 0 else 1
     rows = []
     side = torch.cuda.Stream()
-    for m, n, k in SHAPES:
+    for m, n, k in shapes:
         A, Bt = synth.gemm_bf16(1, m, n, k, b_col_major=True, device="cuda")
         D = torch.empty((m, n), dtype=torch.float32, device="cuda")
         rec = {"rows": m, "cols": n, "shared": k}
