@@ -1541,7 +1541,7 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     // 3584 x 3072 (84 wide tiles would take two rounds; pairs: 1167 against 959), 2048^2 (one
     // round of 128 single tiles: 896 against 600 for 32 wide tiles on 74 pairs).
     // The KLAS_KNOB_TC_MODE knob overrides the choice.
-    constexpr double RATE_SINGLE = 1336.0, RATE_PAIR = 1433.0, RATE_WIDE = 1539.0, WIDE_DRAIN_KB = 6.0, NARROW_COST = 0.75, SLIM_COST = 0.65;
+    constexpr double RATE_SINGLE = 1336.0, RATE_PAIR = 1433.0, RATE_WIDE = 1539.0, WIDE_DRAIN_KB = 6.0, PAIR_TILE_KB = 1.3, NARROW_COST = 0.75, SLIM_COST = 0.65;
     constexpr uint32_t SPLIT_MIN_SAVED_KB = 22;   // K blocks (of 64) a split must take off a tile to pay for its second kernel
     constexpr double TAIL_OVERHEAD_KB = 45.0;     // what the extra launch and the adding kernel of a cut last round cost, in K blocks
     const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
@@ -1551,11 +1551,15 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     const uint64_t sms = uint64_t(info.sm_count), pairs = uint64_t(info.sm_count / 2);
     const double cost_single = double((single_tiles + sms - 1) / sms);
     const bool pair_ok = can_pair && rows > BM && single_tiles >= sms && !xform;   // the pair tile has no mapped form
-    const double cost_pair = pair_ok ? double((pair_tiles + pairs - 1) / pairs) * (RATE_SINGLE / RATE_PAIR) : 1e30;
+    const double num_kb_d = double((shared + BK - 1) / BK);
+    // A pair tile's fixed cost (cluster hand-shakes per tile) weighs more the shorter K is: at
+    // 8192 x 8192 x 512 single tiles measured 801 against 749 TFLOP/s, at K = 8192 1336 against 1433.
+    const double pair_short_k = num_kb_d > 0 ? (1.0 + PAIR_TILE_KB / num_kb_d) / (1.0 + PAIR_TILE_KB / 128.0) : 1.0;
+    const double pair_rate = (RATE_SINGLE / RATE_PAIR) * pair_short_k;
+    const double cost_pair = pair_ok ? double((pair_tiles + pairs - 1) / pairs) * pair_rate : 1e30;
     // The wide tile's epilogue is not hidden behind the next tile's MMAs (both accumulator halves
     // belong to one tile): about six K blocks' worth per tile, which the rate measured at K = 8192
     // contains once per 128 K blocks.  8192 x 8192 x 512: single tiles 791, wide 708 TFLOP/s.
-    const double num_kb_d = double((shared + BK - 1) / BK);
     const double wide_drain = num_kb_d > 0 ? (1.0 + WIDE_DRAIN_KB / num_kb_d) / (1.0 + WIDE_DRAIN_KB / 128.0) : 1.0;
     const double cost_wide = can_pair ? double((wide_tiles + pairs - 1) / pairs) * 2.0 * (RATE_SINGLE / RATE_WIDE) * wide_drain : 1e30;
     // A part-filled last round of single or pair tiles can be cut along K so that it fills the machine
@@ -1572,11 +1576,10 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
         return double(full) + double(kb_per) / double(num_kb_all) + TAIL_OVERHEAD_KB / double(num_kb_all);
     };
     const double cost_single_tail = with_tail_cut(single_tiles, sms);
-    const double cost_pair_tail = pair_ok ? with_tail_cut(pair_tiles, pairs) * (RATE_SINGLE / RATE_PAIR) : 1e30;
+    const double cost_pair_tail = pair_ok ? with_tail_cut(pair_tiles, pairs) * pair_rate : 1e30;
     const double best_single = cost_single_tail < cost_single ? cost_single_tail : cost_single;
     const double best_pair = cost_pair_tail < cost_pair ? cost_pair_tail : cost_pair;
-    // (pair tiles must win by 3 %: at 3072^3 the estimate has two rounds of pairs level with one of wide tiles, measured 1316 against 1385)
-    bool use_wide = can_pair && cost_wide < best_single && cost_wide <= best_pair * 1.03;
+    bool use_wide = can_pair && cost_wide < best_single && cost_wide <= best_pair;
     bool pair = pair_ok && !use_wide && best_pair <= best_single;
     bool tail_split = !use_wide && (pair ? cost_pair_tail < cost_pair : cost_single_tail < cost_single);
     // Small outputs: the single-CTA kernel with 128-column tiles puts twice as many CTAs to work
