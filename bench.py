@@ -104,19 +104,23 @@ class ClockSampler:
 
     def _poll(self):
         nv = self.nv
+        reasons_of = nv.nvmlDeviceGetCurrentClocksEventReasons if hasattr(
+            nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        turn = 0
         while not self._stop.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
-                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(
-                    nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                mask = reasons_of(self.h)
                 self.mask |= mask
                 for bit, name in self.REASONS.items():
                     if mask & bit:
                         self.reasons.add(name)
-                self.watts.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+                if turn % 16 == 2:   # the power query is the slow one: a short timed region must still get its clock samples
+                    self.watts.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
             except Exception:
                 pass
-            time.sleep(0.002)
+            turn += 1
+            time.sleep(0.001)
 
     def __enter__(self):
         if self.nv:
