@@ -728,8 +728,8 @@ def cpu_baseline_leg(workload_name, seconds=12.0):
 # to the SHA-256 of the kernel source it was captured from: when the source has changed since,
 # the figure is withheld (traffic null, with a note) instead of going stale silently.
 NCU_TRAFFIC = {
-    "gemm_bf16": (1.148e+09, "kuiper_b200/csrc/gemm_umma.cu", "6aab08404fb62cb4"),
-    "gemm_f16b": (1.585e+09, "kuiper_b200/csrc/gemm_umma.cu", "6aab08404fb62cb4"),
+    "gemm_bf16": (1.148e+09, "kuiper_b200/csrc/gemm_umma.cu", "d152cda6d0ff23f4"),
+    "gemm_f16b": (1.645e+09, "kuiper_b200/csrc/gemm_umma.cu", "d152cda6d0ff23f4"),
     "spmm": (1.131e+09, "kuiper_b200/csrc/spmm.cu", "00fe2789a6167b7d"),
     "gemm_u64": (2.167e+09, "kuiper_b200/csrc/gemm_simt.cu", "1347f823e1dfa70e"),
     "gemm_f32": (1.261e+07, "kuiper_b200/csrc/gemm_simt.cu", "1347f823e1dfa70e"),

@@ -571,6 +571,19 @@ typedef enum klas_knob_e {
 int klas_b200_debug_set(int knob, int value);
 int klas_b200_debug_get(int knob);
 
+/*
+ * What klas_b200_gemm_tc would run for a shape on a device with `sm_count` SMs: no device is touched.
+ *   *kind       0 single-CTA tiles (128 rows), 1 CTA-pair tiles (256 x 256), 2 wide pair tiles (512 x 256)
+ *   *tile_cols  columns of a tile (256, or 128 / 64 for narrow single-CTA tiles)
+ *   *k_parts    parts every tile's shared dimension is cut into (1: one pass)
+ *   *tail_cut   1: only the tiles of a part-filled last round are cut, in a second launch
+ * The plan follows the tuning knobs.  It is what the tile-choice tests and the tuning run look at;
+ * a launch that finds no buffer for the parts (see klas_b200_gemm_tc) still runs in one pass.
+ * Any output pointer may be NULL.
+ */
+int klas_b200_gemm_tc_plan(uint64_t rows, uint64_t shared, uint64_t cols, uint32_t batch, int sm_count,
+                           int *kind, int *tile_cols, int *k_parts, int *tail_cut);
+
 /* Frees the calling device's workspaces: the host-variant staging buffers and the partial-product
  * buffers of the tensor-core GEMM's K split.  Synchronises the device. */
 int klas_b200_release_workspace(void);

@@ -75,6 +75,7 @@ SIGNATURES = {
     "klas_b200_mg_spmm": (_int, [_vp, _int, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "klas_b200_debug_set": (_int, [_int, _int]),
     "klas_b200_debug_get": (_int, [_int]),
+    "klas_b200_gemm_tc_plan": (_int, [_u64, _u64, _u64, _u32, _int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "klas_b200_release_workspace": (_int, []),
 }
 

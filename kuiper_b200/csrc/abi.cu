@@ -102,6 +102,8 @@ int workspace_release() {
 
 int umma_read_status(int *value);
 int umma_peek_status();
+int umma_plan(uint64_t rows, uint64_t shared, uint64_t cols, uint32_t batch, int sm_count, int *kind, int *tile_cols,
+              int *k_parts, int *tail_cut);
 int umma_release_split_workspace();
 int umma_clear_status();
 int umma_wait_probe(uint32_t limit_ms, int *gave_up, cudaStream_t stream);
@@ -635,6 +637,12 @@ int klas_b200_debug_set(int knob, int value) {
 }
 
 int klas_b200_debug_get(int knob) { return debug_knob(knob); }
+
+int klas_b200_gemm_tc_plan(uint64_t rows, uint64_t shared, uint64_t cols, uint32_t batch, int sm_count, int *kind,
+                           int *tile_cols, int *k_parts, int *tail_cut) {
+    clear_error();
+    return umma_plan(rows, shared, cols, batch, sm_count, kind, tile_cols, k_parts, tail_cut);
+}
 
 int klas_b200_release_workspace(void) {
     clear_error();

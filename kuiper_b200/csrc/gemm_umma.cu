@@ -1482,53 +1482,17 @@ int launch_gemm_umma_fused(int in_dtype, int out_dtype, int b_major, uint32_t ba
                                     map_a, map_b, comb, status_word, stream);
 }
 
-int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
-                             uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
-                             void *D, const TcStrides &st, float alpha, float beta, int map_a, int map_b, int comb,
-                             int *status_word, cudaStream_t stream) {
+// What a launch of the given shape will run: kernel, tile width, K parts, whether the last round is cut.
+// Pure host arithmetic on the shape, the SM count and the tuning knobs (klas_b200_gemm_tc_plan
+// exposes it, so the choice can be tested without a GPU).
+struct TilePlan {
+    bool use_wide, pair, tail_split;
+    uint32_t single_tile_n;
+    uint64_t auto_parts;
+};
+
+static TilePlan plan_tiles(uint64_t rows, uint64_t cols, uint64_t shared, uint32_t batch, bool xform, int sm_count) {
     using namespace umma;
-    // rows of A are `shared` long; rows of B `cols` (row-major) or `shared` (column-major) long
-    const uint64_t b_inner = b_major == KLAS_B_ROW_MAJOR ? cols : shared, b_outer = b_major == KLAS_B_ROW_MAJOR ? shared : cols;
-    const uint64_t lda = st.lda ? st.lda : shared, ldb = st.ldb ? st.ldb : b_inner, ldd = st.ldd ? st.ldd : cols;
-    const uint64_t sa = st.stride_a ? st.stride_a : lda * rows, sb = st.stride_b ? st.stride_b : ldb * b_outer,
-                   sd = st.stride_d ? st.stride_d : ldd * rows;
-    if (lda < shared || ldb < b_inner || ldd < cols) return fail(KLAS_ERR_INVALID, "gemm_tc: a row stride is shorter than the row");
-    if ((lda | ldb | ldd | sa | sb | sd) % 8 != 0)
-        return fail(KLAS_ERR_UNSUPPORTED, "gemm_tc: row and page strides must be multiples of 8 elements");
-    if (batch > 1 && sd < (rows - 1) * ldd + cols) return fail(KLAS_ERR_INVALID, "gemm_tc: pages of D overlap");
-    if (map_a < KLAS_MAP_ID || map_a > KLAS_MAP_NEG || map_b < KLAS_MAP_ID || map_b > KLAS_MAP_NEG)
-        return fail(KLAS_ERR_INVALID, "gemm_tc: unknown operand map (%d, %d)", map_a, map_b);
-    if (comb < KLAS_COMB_NEW || comb > KLAS_COMB_SCALED) return fail(KLAS_ERR_INVALID, "gemm_tc: unknown combine rule %d", comb);
-    const bool reads_c = comb != KLAS_COMB_NEW && comb != KLAS_COMB_RELU && comb != KLAS_COMB_SCALED;
-    if (reads_c && !C && rows && cols && batch) return fail(KLAS_ERR_INVALID, "gemm_tc: this combine rule needs C");
-    if (!reads_c) C = nullptr;
-    const bool xform = (map_a != KLAS_MAP_ID || map_b != KLAS_MAP_ID) && shared > 0;
-    if (in_dtype != KLAS_BF16 && in_dtype != KLAS_F16)
-        return fail(KLAS_ERR_INVALID, "gemm_tc: in_dtype must be KLAS_BF16 or KLAS_F16");
-    if (out_dtype != KLAS_F32 && out_dtype != KLAS_F16 && out_dtype != KLAS_BF16)
-        return fail(KLAS_ERR_INVALID, "gemm_tc: out_dtype must be KLAS_F32, KLAS_F16 or KLAS_BF16");
-    if (b_major != KLAS_B_ROW_MAJOR && b_major != KLAS_B_COL_MAJOR)
-        return fail(KLAS_ERR_INVALID, "gemm_tc: bad b_major");
-    if (rows == 0 || cols == 0 || batch == 0) return KLAS_OK;
-    if (!D || (shared > 0 && (!A || !B)))
-        return fail(KLAS_ERR_INVALID, "gemm_tc: null matrix pointer");
-    if (int rc = umma_ensure_host_flag()) return rc;
-    if (shared % 8 != 0 || cols % 8 != 0)
-        return fail(KLAS_ERR_UNSUPPORTED,
-                    "gemm_tc: shared (%llu) and cols (%llu) must be multiples of 8",
-                    (unsigned long long)shared, (unsigned long long)cols);
-    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
-         reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(D)) & 15u)
-        return fail(KLAS_ERR_INVALID, "gemm_tc: A, B, C, D must be 16-byte aligned");
-    if (rows > 0x7fffffffull || cols > 0x7fffffffull || shared > 0x7fffffffull)
-        return fail(KLAS_ERR_TOO_LARGE, "gemm_tc: dimension beyond 2^31-1");
-
-    DeviceInfo info;
-    if (int rc = device_info(&info)) return rc;
-    if (info.cc_major != 10)
-        return fail(KLAS_ERR_UNSUPPORTED, "gemm_tc needs an sm_100 device (found sm_%d%d)",
-                    info.cc_major, info.cc_minor);
-
     // Tile shape: single CTAs with 128 x 256 tiles, CTA pairs with 256 x 256 tiles, or "wide" CTA
     // pairs with 512 x 256 tiles, whichever a wave count x tile cost estimate makes fastest.  The
     // kernels are persistent with a static round-robin of tiles, so a launch takes
@@ -1547,8 +1511,8 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
     const uint64_t single_tiles = ((rows + BM - 1) / BM) * ((cols + BN - 1) / BN) * batch;
     const uint64_t pair_tiles = ((rows + 2 * BM - 1) / (2 * BM)) * ((cols + BN - 1) / BN) * batch;
     const uint64_t wide_tiles = ((rows + wide::TILE_M - 1) / wide::TILE_M) * ((cols + BN - 1) / BN) * batch;
-    const bool can_pair = info.sm_count >= 2;
-    const uint64_t sms = uint64_t(info.sm_count), pairs = uint64_t(info.sm_count / 2);
+    const bool can_pair = sm_count >= 2;
+    const uint64_t sms = uint64_t(sm_count), pairs = uint64_t(sm_count / 2);
     const double cost_single = double((single_tiles + sms - 1) / sms);
     const bool pair_ok = can_pair && rows > BM && single_tiles >= sms && !xform;   // the pair tile has no mapped form
     const double num_kb_d = double((shared + BK - 1) / BK);
@@ -1621,6 +1585,95 @@ int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t 
         case 5: pair = use_wide = false; single_tile_n = 64; break;
         default: break;
     }
+    return TilePlan{use_wide, pair, tail_split, single_tile_n, auto_parts};
+}
+
+int umma_plan(uint64_t rows, uint64_t shared, uint64_t cols, uint32_t batch, int sm_count, int *kind, int *tile_cols,
+              int *k_parts, int *tail_cut) {
+    if (sm_count < 1 || batch == 0) return fail(KLAS_ERR_INVALID, "gemm_tc_plan: sm_count and batch must be positive");
+    const TilePlan pl = plan_tiles(rows, cols, shared, batch, false, sm_count);
+    const uint64_t sms = uint64_t(sm_count), pairs = uint64_t(sm_count / 2);
+    if (kind) *kind = pl.use_wide ? 2 : (pl.pair ? 1 : 0);
+    if (tile_cols) *tile_cols = (pl.use_wide || pl.pair) ? int(umma::BN) : int(pl.single_tile_n);
+    int parts = 1, tail = 0;
+    if (!pl.use_wide) {
+        const int knob = debug_knob(KLAS_KNOB_TC_KSPLIT);
+        uint64_t want = knob >= 2 ? uint64_t(knob) : (knob == 0 ? pl.auto_parts : 1);
+        const uint64_t num_kb = (shared + umma::BK - 1) / umma::BK;
+        if (want > 8) want = 8;
+        if (want > num_kb) want = num_kb;
+        if (want >= 2) {
+            const uint64_t kb_per = (num_kb + want - 1) / want;
+            want = (num_kb + kb_per - 1) / kb_per;
+        }
+        parts = want >= 2 ? int(want) : 1;
+        const uint64_t tile_m = pl.pair ? 2 * umma::BM : umma::BM, tile_n = pl.pair ? umma::BN : pl.single_tile_n;
+        const uint64_t tiles = ((rows + tile_m - 1) / tile_m) * ((cols + tile_n - 1) / tile_n) * batch;
+        const uint64_t slots = pl.pair ? pairs : sms;
+        const int tknob = debug_knob(KLAS_KNOB_TC_TAIL);
+        const uint64_t rem = slots ? tiles % slots : 0;
+        if (parts == 1 && batch == 1 && rem > 0 && tiles > rem && slots / rem >= 2 && num_kb >= 2 &&
+            (tknob == 2 || (tknob == 0 && pl.tail_split)))
+            tail = 1;
+    }
+    if (k_parts) *k_parts = parts;
+    if (tail_cut) *tail_cut = tail;
+    return KLAS_OK;
+}
+
+int launch_gemm_umma_strided(int in_dtype, int out_dtype, int b_major, uint32_t batch, uint64_t rows,
+                             uint64_t shared, uint64_t cols, const void *A, const void *B, const void *C,
+                             void *D, const TcStrides &st, float alpha, float beta, int map_a, int map_b, int comb,
+                             int *status_word, cudaStream_t stream) {
+    using namespace umma;
+    // rows of A are `shared` long; rows of B `cols` (row-major) or `shared` (column-major) long
+    const uint64_t b_inner = b_major == KLAS_B_ROW_MAJOR ? cols : shared, b_outer = b_major == KLAS_B_ROW_MAJOR ? shared : cols;
+    const uint64_t lda = st.lda ? st.lda : shared, ldb = st.ldb ? st.ldb : b_inner, ldd = st.ldd ? st.ldd : cols;
+    const uint64_t sa = st.stride_a ? st.stride_a : lda * rows, sb = st.stride_b ? st.stride_b : ldb * b_outer,
+                   sd = st.stride_d ? st.stride_d : ldd * rows;
+    if (lda < shared || ldb < b_inner || ldd < cols) return fail(KLAS_ERR_INVALID, "gemm_tc: a row stride is shorter than the row");
+    if ((lda | ldb | ldd | sa | sb | sd) % 8 != 0)
+        return fail(KLAS_ERR_UNSUPPORTED, "gemm_tc: row and page strides must be multiples of 8 elements");
+    if (batch > 1 && sd < (rows - 1) * ldd + cols) return fail(KLAS_ERR_INVALID, "gemm_tc: pages of D overlap");
+    if (map_a < KLAS_MAP_ID || map_a > KLAS_MAP_NEG || map_b < KLAS_MAP_ID || map_b > KLAS_MAP_NEG)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: unknown operand map (%d, %d)", map_a, map_b);
+    if (comb < KLAS_COMB_NEW || comb > KLAS_COMB_SCALED) return fail(KLAS_ERR_INVALID, "gemm_tc: unknown combine rule %d", comb);
+    const bool reads_c = comb != KLAS_COMB_NEW && comb != KLAS_COMB_RELU && comb != KLAS_COMB_SCALED;
+    if (reads_c && !C && rows && cols && batch) return fail(KLAS_ERR_INVALID, "gemm_tc: this combine rule needs C");
+    if (!reads_c) C = nullptr;
+    const bool xform = (map_a != KLAS_MAP_ID || map_b != KLAS_MAP_ID) && shared > 0;
+    if (in_dtype != KLAS_BF16 && in_dtype != KLAS_F16)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: in_dtype must be KLAS_BF16 or KLAS_F16");
+    if (out_dtype != KLAS_F32 && out_dtype != KLAS_F16 && out_dtype != KLAS_BF16)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: out_dtype must be KLAS_F32, KLAS_F16 or KLAS_BF16");
+    if (b_major != KLAS_B_ROW_MAJOR && b_major != KLAS_B_COL_MAJOR)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: bad b_major");
+    if (rows == 0 || cols == 0 || batch == 0) return KLAS_OK;
+    if (!D || (shared > 0 && (!A || !B)))
+        return fail(KLAS_ERR_INVALID, "gemm_tc: null matrix pointer");
+    if (int rc = umma_ensure_host_flag()) return rc;
+    if (shared % 8 != 0 || cols % 8 != 0)
+        return fail(KLAS_ERR_UNSUPPORTED,
+                    "gemm_tc: shared (%llu) and cols (%llu) must be multiples of 8",
+                    (unsigned long long)shared, (unsigned long long)cols);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+         reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(D)) & 15u)
+        return fail(KLAS_ERR_INVALID, "gemm_tc: A, B, C, D must be 16-byte aligned");
+    if (rows > 0x7fffffffull || cols > 0x7fffffffull || shared > 0x7fffffffull)
+        return fail(KLAS_ERR_TOO_LARGE, "gemm_tc: dimension beyond 2^31-1");
+
+    DeviceInfo info;
+    if (int rc = device_info(&info)) return rc;
+    if (info.cc_major != 10)
+        return fail(KLAS_ERR_UNSUPPORTED, "gemm_tc needs an sm_100 device (found sm_%d%d)",
+                    info.cc_major, info.cc_minor);
+
+    const TilePlan plan = plan_tiles(rows, cols, shared, batch, xform, info.sm_count);
+    const bool use_wide = plan.use_wide, pair = plan.pair, tail_split = plan.tail_split;
+    const uint32_t single_tile_n = plan.single_tile_n;
+    const uint64_t auto_parts = plan.auto_parts;
+    const uint64_t sms = uint64_t(info.sm_count), pairs = uint64_t(info.sm_count / 2);
+    const uint64_t wide_tiles = ((rows + wide::TILE_M - 1) / wide::TILE_M) * ((cols + BN - 1) / BN) * batch;
     if (use_wide) {
         Params p{};
         p.C = C;

@@ -683,3 +683,13 @@ def call(name: str, *args):
         gemm_tc(_view(A, t, m, k), _view(B, t, k, n), out_dtype=t, D=_view(Cc, t, m, n), map_a="sqrt")
         return None
     raise KeyError("unknown Klas entry point: %s" % name)
+
+
+def gemm_tc_plan(rows: int, shared: int, cols: int, batch: int = 1, sm_count: int = 148) -> dict:
+    """What gemm_tc would run for this shape on a device with `sm_count` SMs (klas_b200_gemm_tc_plan;
+    needs no GPU): {"kind": "single" | "pair" | "wide", "tile_cols", "k_parts", "tail_cut"}."""
+    kind, tile_cols, parts, tail = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+    check(_lib.load().klas_b200_gemm_tc_plan(rows, shared, cols, batch, sm_count, C.byref(kind), C.byref(tile_cols),
+                                             C.byref(parts), C.byref(tail)))
+    return {"kind": ("single", "pair", "wide")[kind.value], "tile_cols": tile_cols.value, "k_parts": parts.value,
+            "tail_cut": bool(tail.value)}
