@@ -85,6 +85,7 @@ class ClockSampler:
     def __init__(self, index: int):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self.mask, self.watts = 0, []   # every reason bit seen (0x1 = idle included), board power
+        self.recording = True           # False: the thread polls (and stays warm) but keeps nothing
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -109,17 +110,19 @@ class ClockSampler:
         turn = 0
         while not self._stop.is_set():
             try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
                 mask = reasons_of(self.h)
-                self.mask |= mask
-                for bit, name in self.REASONS.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-                if turn % 16 == 2:   # the power query is the slow one: a short timed region must still get its clock samples
-                    self.watts.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+                if self.recording:
+                    self.samples.append(mhz)
+                    self.mask |= mask
+                    for bit, name in self.REASONS.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                    if turn % 16 == 2:   # the power query is the slow one: a short timed region must still get its clock samples
+                        self.watts.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
             except Exception:
                 pass
-            turn += 1
+            turn = turn + 1 if self.recording else 0
             time.sleep(0.001)
 
     def __enter__(self):
@@ -1142,13 +1145,16 @@ def main():
 
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
-    barrier()
-    with sampler:
+    sampler.recording = False
+    with sampler:                     # the polling thread is up and warm before the region starts ...
+        barrier()
+        sampler.recording = True      # ... and keeps what it reads only while the timed launches run
         start.record()
         for _ in range(args.steps):
             wl.launch()
         stop.record()
         torch.cuda.synchronize()
+        sampler.recording = False
     barrier()
     ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
     if world > 1:
