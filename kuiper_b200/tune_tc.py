@@ -100,15 +100,19 @@ def main(argv=None) -> int:
         klas.gemm_tc_status()
         best = max(MODES[:-1], key=lambda md: rec[md])
         rec["best"], rec["auto_over_best"] = best, rec["auto"] / rec[best]
+        plan = klas.gemm_tc_plan(m, k, n, sm_count=torch.cuda.get_device_properties(0).multi_processor_count)
+        rec["plan"] = "%s %d" % (plan["kind"], plan["tile_cols"]) + (", K in %d parts" % plan["k_parts"] if plan["k_parts"] > 1 else "") + (
+            ", last round cut" if plan["tail_cut"] else "")
         rows.append(rec)
         del graphs, A, Bt, D
     if a.json:
         print(json.dumps(rows))
     else:
-        print("%-22s %8s %8s %8s %8s %8s %8s  %s" % ("rows x cols x shared", *MODES, "best (auto / best)"))
+        print("%-22s %8s %8s %8s %8s %8s %8s  %-22s %s" % ("rows x cols x shared", *MODES, "best (auto / best)", "auto is"))
         for r in rows:
-            print("%-22s %8.0f %8.0f %8.0f %8.0f %8.0f %8.0f  %s (%.2f)" % ("%d x %d x %d" % (r["rows"], r["cols"], r["shared"]),
-                                                                      *(r[md] for md in MODES), r["best"], r["auto_over_best"]))
+            print("%-22s %8.0f %8.0f %8.0f %8.0f %8.0f %8.0f  %-22s %s" % ("%d x %d x %d" % (r["rows"], r["cols"], r["shared"]),
+                                                                           *(r[md] for md in MODES),
+                                                                           "%s (%.2f)" % (r["best"], r["auto_over_best"]), r["plan"]))
     return 0
 
 
